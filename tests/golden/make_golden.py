@@ -80,7 +80,11 @@ def _ew_float(dtype, lanes):
     p = a.input((RAG,), dtype)          # positive operand
     outs = [a.binop(op, x, y) for op in _BIN_F]
     outs.append(a.binop(L.OP_POW_F32, p, y))
-    outs += [a.unop(op, x) for op in _UN_F]
+    # round_nearest_afz is left out for 2-byte floats: the validator evaluates
+    # floor(|x| + 0.5) in the storage precision (ops/elementwise.py:171-175),
+    # which double-rounds just below .5; the device calls round() on the f32.
+    outs += [a.unop(op, x) for op in _UN_F
+             if dtype == F32 or op != L.OP_ROUND_NEAREST_AFZ_F32]
     outs += [a.unop(op, p) for op in _UN_F_POS]
     outs.append(a.gelu_fused(x))
     outs.append(a.copy(x))
@@ -119,10 +123,11 @@ def _ew_int(dtype, lanes):
     outs.append(a.copy(x))
     blob, prog = a.finish(outs, nlanes=lanes)
     d = DN[dtype]
-    # y in a range that contains 0 (integer divide by zero yields 0 on device;
-    # numpy yields 0 for integer division by zero as well)
+    # The divisor never is 0: the validators divide in float64 and cast inf to an
+    # undefined integer, while the device defines x / 0 = 0 (ew.cl:410); that
+    # device rule is covered by a known-answer test, not by a fixture.
     lo, hi = (-1000, 1000) if dtype != U32 else (0, 2000)
-    return blob, prog, (2, [I((RAG,), lo * 1000, hi * 1000, d), I((RAG,), lo // 100, hi // 100, d),
+    return blob, prog, (2, [I((RAG,), lo * 1000, hi * 1000, d), I((RAG,), 1, 21, d),
                             I((RAG,), 0, 32, d)])
 
 
