@@ -1,0 +1,180 @@
+// VMProgram v3 wire format and the device-side tables the loader derives from it.
+// Shared by the host runtime (.cc) and the megakernel (.cu).
+//
+// Wire layout (little-endian, every section 8-byte aligned), as written by the
+// reference's VMProgram.serialize (python/pjrt_ocl/lowering.py:286-331) and
+// Schedule.serialize_sections (python/pjrt_ocl/scheduler.py:226-248):
+//   header 48 B | buffer table n x 24 B | input ids | output ids | io shapes |
+//   aux pool u32[n_aux] | const pool | instrs n x 32 B |
+//   sched header 16 B | tasks n x 48 B | lane table n_lanes x 16 B | entries n x 32 B
+#ifndef B2VM_FORMAT_H_
+#define B2VM_FORMAT_H_
+
+#include <stdint.h>
+
+namespace b2 {
+
+constexpr uint32_t kMagic = 0x314D5056u;  // "VPM1"
+constexpr uint32_t kVersion = 3;
+
+// dtype enum (lowering.py:59-68)
+enum Dtype : uint32_t { kF32 = 0, kI32, kU32, kBool, kI64, kF64, kF16, kBF16, kDtMax = kBF16 };
+
+// tile ops (scheduler.py:47-71)
+enum TileOp : uint32_t {
+  kTopEw = 0, kTopMma, kTopGather, kTopRedPart, kTopRedComb, kTopIotaDim, kTopScatter,
+  kTopDynGather, kTopDynScatter, kTopRedWindow, kTopRedSeg, kTopSoftmaxSeg, kTopLayernormSeg,
+  kTopMapRegion, kTopFlashAttn, kTopRedStrided, kTopGatherIndex, kTopConv, kTopScatterIndex,
+  kTopMax = kTopScatterIndex
+};
+
+// elementwise subops (pjrt_plugin/kernels/vm_common.cl:118-146)
+enum Sub : uint32_t {
+  kAdd = 0, kMul, kSubt, kDiv, kMax, kMin, kPow, kCopy, kNeg, kExp, kLog, kSqrt, kRsqrt, kTanh,
+  kAbs, kFloor, kCeil, kSign, kFill, kIotaFlat, kCmp, kSelect, kLts, kConvert, kBitcast, kAtan2,
+  kRemainder, kLog1p, kExpm1, kCbrt, kSin, kCos, kTan, kRint, kRound, kAnd, kOr, kXor, kNot,
+  kIsFinite, kAffine, kGelu, kShl, kShrL, kShrA, kSubMax = kShrA
+};
+
+// reduction kinds (python/pjrt_ocl/ops/reduce.py:56)
+enum RedKind : uint32_t { kSum = 0, kRMax, kRMin, kProd, kRAnd, kROr, kRXor };
+
+// entry sentinels (scheduler.py:80-85)
+constexpr uint32_t kEntNop = 0xFFFFFFFFu;
+constexpr uint32_t kEntBarrier = 0xFFFFFFFEu;
+constexpr uint32_t kEntWhile = 0xFFFFFFFDu;
+constexpr uint32_t kEntIf = 0xFFFFFFFCu;
+constexpr uint32_t kEntFor = 0xFFFFFFFBu;
+
+struct VmTask { uint32_t tile_op, dst, a, b, p0, p1, p2, p3, p4, p5, p6, p7; };
+struct VmEntry { uint32_t task, tile_lo, tile_hi, wait_flag, wait_count, signal_flag, slots, pad; };
+struct VmLane { uint32_t off, count, root_len, pad; };
+static_assert(sizeof(VmTask) == 48 && sizeof(VmEntry) == 32 && sizeof(VmLane) == 16, "wire structs");
+
+// Tile geometry this backend executes with and advertises to the scheduler
+// (PJRT_OCL_EW_TS / PJRT_OCL_MMA_T; scheduler.py:36-45).
+constexpr uint32_t kEwTs = 4096;
+constexpr uint32_t kMmaT = 128;
+constexpr int kMaxDepth = 8;          // control frame stack (vm_main.cl:103)
+constexpr uint32_t kMaxIoPorts = 64;  // zero-copy I/O buffers passed by kernel parameter
+
+// ---------------------------------------------------------------------------
+// Device tables
+// ---------------------------------------------------------------------------
+
+// A buffer reference in a device task: either an absolute device address
+// (arena-resident buffers, resolved once at load) or, with bit 63 set, the index
+// of an I/O port whose address arrives with each launch.
+typedef uint64_t BufRef;
+constexpr uint64_t kPortBit = 1ull << 63;
+
+// A strided view, collapsed at load time to at most kViewDims dims (outermost first).
+// index(i) = off + sum_k coord_k(i) * stride[k], coord by row-major unravel of i
+// over dim[]. rank 0 = every element reads `off`.
+struct DView {
+  int32_t rank;
+  int32_t vec_ok;       // 1: dim[rank-1] % 4 == 0, innermost stride is 0 or 1, and a
+                        // group of 4 consecutive consumer elements never straddles it
+  int32_t inner_stride; // stride[rank-1] (0 or 1 when vec_ok)
+  int32_t aligned4;     // 1: off and every outer stride are multiples of 4 elements
+  int64_t off;
+  uint32_t dim[6];
+  int32_t stride[6];
+};
+constexpr int kViewDims = 6;
+
+enum TaskFlags : uint32_t {
+  kFwdA = 1u << 0,      // EW chain: operand a is the previous chain op's result (in registers)
+  kFwdB = 1u << 1,
+  kDeadStore = 1u << 2, // EW chain: nothing but the next chain op reads dst; skip the store
+  kViewA = 1u << 3,
+  kViewB = 1u << 4,
+  kVecPath = 1u << 5,   // every pointer 16-byte aligned and dtypes on the 4-wide path
+  kFwdC = 1u << 6,      // select predicate forwarded
+};
+
+struct DTask {
+  uint32_t op, dt, adt, flags;
+  BufRef ptr[4];        // dst, a, b, c (select predicate / flash V / epilogue residual)
+  uint32_t p[8];        // p0..p7 as in the wire task (buffer ids already resolved elsewhere)
+  uint32_t desc;        // word offset into the descriptor pool (op specific), 0 = none
+  uint32_t cdt;         // dtype of ptr[3] where it matters (epilogue residual)
+  uint32_t pad[2];
+};
+static_assert(sizeof(DTask) == 96, "DTask layout");
+
+// A device entry: the wire entry with control cond buffers resolved and chain
+// annotations added by the loader.
+struct DEntry {
+  uint32_t task, tile_lo, tile_hi, a, b;  // a/b: wait_flag / wait_count of the wire entry
+  uint32_t chain;        // number of consecutive EW entries (this one included) to run as one fused chain; 0/1 = alone
+  BufRef cond;           // WHILE / IF: address of the 4-byte condition word
+};
+static_assert(sizeof(DEntry) == 32, "DEntry layout");
+
+enum StatusCode : uint32_t { kStOk = 0, kStBarrierTimeout = 1, kStStackOverflow = 2, kStBadOp = 3, kStTensorTimeout = 4 };
+
+// Barrier + status block in device memory (one per loaded program).
+struct DSync {
+  uint32_t arrive;       // arrival counter
+  uint32_t gen;          // barrier generation
+  uint32_t abort;        // set by the first lane whose wait ran out; polled by all
+  uint32_t status[4];    // code, lane, where, detail (first writer wins)
+  uint32_t pad;
+  unsigned long long barriers;   // lane 0
+  unsigned long long device_ns;  // lane 0
+};
+
+// ---- per-op descriptors the loader writes into the descriptor pool -------------
+// Descriptor the loader writes for GATHER / SCATTER / DYN_* tasks.
+struct DMove {
+  DView view;          // linear side index -> strided side index (in elements)
+  uint32_t esz;        // element size in bytes
+  uint32_t chunk;      // elements per 16-byte chunk when vector-movable, else 0
+  uint32_t n_idx;      // DYN_*: number of runtime start indices (rank), else 0
+  uint32_t is64;       // DYN_*: start scalars are i64
+  int32_t clamp_max[8];
+  int32_t idx_stride[8];
+  BufRef idx_ptr[8];   // DYN_*: where each start scalar lives
+};
+
+struct DRegion {            // loader-built: the 8 input references (a, b, p2..p7)
+  BufRef in[8];
+};
+
+struct DMma {          // loader-built
+  DView va, vb;
+  uint32_t tc_mode;    // 0: CUDA-core path only; else operand layout class for the tensor-core path
+  uint32_t pad;
+  int64_t a_ld, b_ld;  // tensor-core path: leading dimensions (elements)
+  int64_t a_gs, b_gs;  // tensor-core path: batch strides (elements)
+};
+
+struct DFlash {        // loader-built
+  DView vq, vk, vv;
+  uint32_t has_q, has_k, has_v;   // operand is read through its view
+  uint32_t tc_mode;               // 0: CUDA-core path only
+  // tensor-core path: element strides of Q[h,t,d], K[h,c,d] (d contiguous), V[h,c,d]
+  int64_t q_h1, q_h0, q_t, k_h1, k_h0, k_c, v_h1, v_h0, v_c;
+  uint32_t h0_size;               // h = h1 * h0_size + h0
+  uint32_t pad;
+};
+
+struct IoTable { void *p[kMaxIoPorts]; };
+
+struct KParams {
+  const DTask *tasks;
+  const DEntry *entries;
+  const VmLane *lanes;
+  const int32_t *aux;       // the program's aux pool, unmodified
+  const uint64_t *desc;     // loader-built descriptor pool (views, pointers, ...)
+  DSync *sync;
+  uint8_t *scratch;         // per-program scratch (split reductions, tensor-core staging)
+  uint32_t n_lanes;
+  uint32_t pad;
+  unsigned long long wait_budget_ns;
+  IoTable io;
+};
+
+}  // namespace b2
+#endif

@@ -1,0 +1,102 @@
+// Data-movement tile ops: strided GATHER, strided SCATTER, IOTA_DIM, and the
+// dynamic-offset gather/scatter behind dynamic_slice / dynamic_update_slice.
+//
+// Replaces vmo_gather_tile (pjrt_plugin/kernels/ops/gather.cl:9-82),
+// vmo_scatter_tile (ops/scatter.cl:9-50), vmo_iota_tile (ops/iota.cl:4-29) and
+// vmo_dyn_gather_tile / vmo_dyn_scatter_tile (ops/dynslice.cl:28-166).
+// Semantics: python/pjrt_ocl/ops/shape.py:196-217, ops/concat.py:214-236,
+// ops/making.py:85-117, ops/dynslice.py:134-190.
+//
+// The loader collapses each access map to <= 4 dims and marks the ones whose
+// innermost run is contiguous on both sides and a whole number of 16-byte
+// chunks; those move as 16-byte vectors (one index computation per chunk),
+// coalesced on the contiguous side. Everything else moves element by element,
+// coalesced on the side that is walked linearly.
+#ifndef B2VM_OPS_MOVE_CUH_
+#define B2VM_OPS_MOVE_CUH_
+
+#include "dev_common.cuh"
+
+namespace b2 {
+
+
+__device__ __forceinline__ void copy_elem(uint8_t *d, int64_t di, const uint8_t *s, int64_t si, uint32_t esz) {
+  switch (esz) {
+    case 1: d[di] = s[si]; break;
+    case 2: reinterpret_cast<uint16_t *>(d)[di] = reinterpret_cast<const uint16_t *>(s)[si]; break;
+    case 4: reinterpret_cast<uint32_t *>(d)[di] = reinterpret_cast<const uint32_t *>(s)[si]; break;
+    default: reinterpret_cast<unsigned long long *>(d)[di] = reinterpret_cast<const unsigned long long *>(s)[si]; break;
+  }
+}
+
+// Runtime base offset of a dynamic slice: sum_d clamp(start_d, 0, max_d) * stride_d.
+__device__ __forceinline__ int64_t dyn_base(const KParams &P, const DMove &m) {
+  int64_t base = 0;
+  for (uint32_t d = 0; d < m.n_idx; ++d) {
+    const uint8_t *ip = resolve(P, m.idx_ptr[d]);
+    long long s = m.is64 ? *reinterpret_cast<const long long *>(ip) : *reinterpret_cast<const int32_t *>(ip);
+    s = s < 0 ? 0 : (s > m.clamp_max[d] ? m.clamp_max[d] : s);
+    base += s * m.idx_stride[d];
+  }
+  return base;
+}
+
+// gather: dst[i] = a[base + view(i)];  scatter: dst[base + view(i)] = a[i]
+__device__ __noinline__ void move_tiles(const Lane &L, const DTask &t, uint32_t tile_lo, uint32_t tile_hi, bool scatter) {
+  const KParams &P = *L.P;
+  const DMove &m = *reinterpret_cast<const DMove *>(P.desc + t.desc);
+  uint8_t *dst = resolve(P, t.ptr[0]);
+  const uint8_t *src = resolve(P, t.ptr[1]);
+  const uint32_t n = t.p[1];
+  const uint64_t lo64 = static_cast<uint64_t>(tile_lo) * kEwTs;
+  uint64_t hi64 = static_cast<uint64_t>(tile_hi) * kEwTs;
+  if (hi64 > n) hi64 = n;
+  if (lo64 >= hi64) return;
+  const uint32_t lo = static_cast<uint32_t>(lo64), hi = static_cast<uint32_t>(hi64);
+  const int64_t base = m.n_idx ? dyn_base(P, m) : 0;
+  const uint32_t esz = m.esz;
+  const bool vec = m.chunk && (base % m.chunk == 0);
+  if (vec) {
+    // lo is a multiple of 4096 and chunk divides 16, so chunks never straddle lo.
+    const uint32_t c = m.chunk, c_lo = lo / c, c_hi = hi / c;
+    for (uint32_t k = c_lo + L.tid; k < c_hi; k += L.nthr) {
+      const int64_t s = base + view_index(m.view, k * c);
+      if (scatter)
+        *reinterpret_cast<uint4 *>(dst + s * esz) = *reinterpret_cast<const uint4 *>(src + static_cast<int64_t>(k) * 16);
+      else
+        *reinterpret_cast<uint4 *>(dst + static_cast<int64_t>(k) * 16) = *reinterpret_cast<const uint4 *>(src + s * esz);
+    }
+    for (uint32_t i = c_hi * c + L.tid; i < hi; i += L.nthr) {  // ragged tail of the range
+      const int64_t s = base + view_index(m.view, i);
+      if (scatter) copy_elem(dst, s, src, i, esz); else copy_elem(dst, i, src, s, esz);
+    }
+    return;
+  }
+  for (uint32_t i = lo + L.tid; i < hi; i += L.nthr) {
+    const int64_t s = base + view_index(m.view, i);
+    if (scatter) copy_elem(dst, s, src, i, esz); else copy_elem(dst, i, src, s, esz);
+  }
+}
+
+// iota: dst[i] = coordinate of i along `dim` (aux {rank, dims[rank], dim}); the
+// loader stores {dim_size, inner} = sizes such that coord = (i / inner) % dim_size.
+__device__ __noinline__ void iota_tiles(const Lane &L, const DTask &t, uint32_t tile_lo, uint32_t tile_hi) {
+  const KParams &P = *L.P;
+  const uint32_t *d = reinterpret_cast<const uint32_t *>(P.desc + t.desc);
+  const uint32_t dim_size = d[0], inner = d[1];
+  uint8_t *dst = resolve(P, t.ptr[0]);
+  const uint32_t n = t.p[1], dt = t.dt;
+  const uint64_t lo64 = static_cast<uint64_t>(tile_lo) * kEwTs;
+  uint64_t hi64 = static_cast<uint64_t>(tile_hi) * kEwTs;
+  if (hi64 > n) hi64 = n;
+  for (uint64_t i = lo64 + L.tid; i < hi64; i += L.nthr) {
+    const uint32_t c = dim_size ? (static_cast<uint32_t>(i) / inner) % dim_size : 0u;
+    if (is_float_dt(dt)) storef(dst, dt, i, static_cast<float>(c));
+    else if (dt == kF64) reinterpret_cast<double *>(dst)[i] = static_cast<double>(c);
+    else if (dt == kI64) reinterpret_cast<long long *>(dst)[i] = c;
+    else store1(dst, dt, i, c);
+  }
+}
+
+}  // namespace b2
+#endif

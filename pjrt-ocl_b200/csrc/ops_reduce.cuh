@@ -1,0 +1,276 @@
+// Reduction tile ops: RED_PART / RED_COMB (two-phase full reduce), RED_SEG
+// (innermost-segment reduce, incl. the GEMV "dot mode") and RED_STRIDED
+// (interior / prefix axis block).
+//
+// Replaces vmo_reduce_part_tile / vmo_reduce_comb_tile / vmo_redseg_tile /
+// vmo_redstrided_tile (pjrt_plugin/kernels/ops/reduce.cl:45-281,488-549).
+// Semantics: python/pjrt_ocl/ops/reduce.py:252-266,307-326,372-382,432-444.
+// Kinds 0 sum 1 max 2 min 3 prod 4 and 5 or 6 xor; floats accumulate in f32 with
+// warp-shuffle trees (any association is within the f32 tolerance), integers are
+// exact in any order, float max/min propagate NaN like numpy.
+//
+// B200 design: instead of one local-memory tree per segment, the cooperating
+// group scales with the segment: one thread per segment for tiny segments (the
+// 16.7 M segments of 3 of the n-body step stay coalesced), one warp per segment
+// with 16-byte lane loads up to 16 K elements, the whole lane beyond.
+#ifndef B2VM_OPS_REDUCE_CUH_
+#define B2VM_OPS_REDUCE_CUH_
+
+#include "dev_common.cuh"
+#include "ops_ew.cuh"
+
+namespace b2 {
+
+__device__ __forceinline__ float red_f(uint32_t kind, float a, float b) {
+  switch (kind) {
+    case kSum: return a + b;
+    case kRMax: return np_max(a, b);
+    case kRMin: return np_min(a, b);
+    default: return a * b;
+  }
+}
+__device__ __forceinline__ float red_f_identity(uint32_t kind) {
+  return kind == kSum ? 0.0f : kind == kProd ? 1.0f : kind == kRMax ? -INFINITY : INFINITY;
+}
+// 32-bit integer / bool accumulators (dt decides signedness of max/min)
+__device__ __forceinline__ uint32_t red_i(uint32_t kind, uint32_t dt, uint32_t a, uint32_t b) {
+  switch (kind) {
+    case kSum: return a + b;
+    case kProd: return a * b;
+    case kRMax: return dt == kI32 ? static_cast<uint32_t>(max(static_cast<int32_t>(a), static_cast<int32_t>(b))) : max(a, b);
+    case kRMin: return dt == kI32 ? static_cast<uint32_t>(min(static_cast<int32_t>(a), static_cast<int32_t>(b))) : min(a, b);
+    case kRAnd: return a & b;
+    case kROr: return a | b;
+    default: return a ^ b;
+  }
+}
+__device__ __forceinline__ uint32_t red_i_identity(uint32_t kind, uint32_t dt) {
+  switch (kind) {
+    case kSum: case kROr: case kRXor: return 0u;
+    case kProd: return 1u;
+    case kRMax: return dt == kI32 ? 0x80000000u : 0u;
+    case kRMin: return dt == kI32 ? 0x7fffffffu : (dt == kBool ? 1u : 0xffffffffu);
+    default: return dt == kBool ? 1u : 0xffffffffu;  // and
+  }
+}
+__device__ __forceinline__ long long red_l(uint32_t kind, long long a, long long b) {
+  switch (kind) {
+    case kSum: return static_cast<long long>(static_cast<unsigned long long>(a) + static_cast<unsigned long long>(b));
+    case kProd: return static_cast<long long>(static_cast<unsigned long long>(a) * static_cast<unsigned long long>(b));
+    case kRMax: return a > b ? a : b;
+    case kRMin: return a < b ? a : b;
+    case kRAnd: return a & b;
+    case kROr: return a | b;
+    default: return a ^ b;
+  }
+}
+__device__ __forceinline__ long long red_l_identity(uint32_t kind) {
+  switch (kind) {
+    case kSum: case kROr: case kRXor: return 0;
+    case kProd: return 1;
+    case kRMax: return LLONG_MIN;
+    case kRMin: return LLONG_MAX;
+    default: return -1;
+  }
+}
+__device__ __forceinline__ double red_d(uint32_t kind, double a, double b) {
+  switch (kind) {
+    case kSum: return a + b;
+    case kRMax: return (a != a || b != b) ? nan("") : fmax(a, b);
+    case kRMin: return (a != a || b != b) ? nan("") : fmin(a, b);
+    default: return a * b;
+  }
+}
+
+// A 64-bit accumulator that holds whichever representation `dt` needs, so the
+// drivers below are written once. f32-class and 32-bit integers use the low word.
+struct Acc {
+  unsigned long long bits;
+};
+__device__ __forceinline__ Acc acc_identity(uint32_t kind, uint32_t dt) {
+  Acc a;
+  if (is_float_dt(dt)) a.bits = __float_as_uint(red_f_identity(kind));
+  else if (dt == kF64) a.bits = __double_as_longlong(static_cast<double>(red_f_identity(kind)));
+  else if (dt == kI64) a.bits = static_cast<unsigned long long>(red_l_identity(kind));
+  else a.bits = red_i_identity(kind, dt);
+  return a;
+}
+__device__ __forceinline__ Acc acc_load(const uint8_t *p, uint32_t dt, int64_t i) {
+  Acc a;
+  if (dt == kF64 || dt == kI64) a.bits = reinterpret_cast<const unsigned long long *>(p)[i];
+  else a.bits = load1(p, dt, i);
+  return a;
+}
+__device__ __forceinline__ Acc acc_combine(uint32_t kind, uint32_t dt, Acc a, Acc b) {
+  Acc r;
+  if (is_float_dt(dt))
+    r.bits = __float_as_uint(red_f(kind, __uint_as_float(static_cast<uint32_t>(a.bits)), __uint_as_float(static_cast<uint32_t>(b.bits))));
+  else if (dt == kF64)
+    r.bits = __double_as_longlong(red_d(kind, __longlong_as_double(a.bits), __longlong_as_double(b.bits)));
+  else if (dt == kI64)
+    r.bits = static_cast<unsigned long long>(red_l(kind, static_cast<long long>(a.bits), static_cast<long long>(b.bits)));
+  else
+    r.bits = red_i(kind, dt, static_cast<uint32_t>(a.bits), static_cast<uint32_t>(b.bits));
+  return r;
+}
+__device__ __forceinline__ void acc_store(uint8_t *p, uint32_t dt, int64_t i, Acc a) {
+  if (dt == kF64 || dt == kI64) reinterpret_cast<unsigned long long *>(p)[i] = a.bits;
+  else store1(p, dt, i, static_cast<uint32_t>(a.bits));
+}
+__device__ __forceinline__ Acc acc_shfl_xor(Acc a, int o) {
+  Acc r;
+  r.bits = __shfl_xor_sync(0xffffffffu, a.bits, o);
+  return r;
+}
+__device__ __forceinline__ Acc acc_warp_reduce(uint32_t kind, uint32_t dt, Acc a) {
+#pragma unroll
+  for (int o = kWarp / 2; o > 0; o >>= 1) a = acc_combine(kind, dt, a, acc_shfl_xor(a, o));
+  return a;
+}
+// All threads of the lane call; every thread gets the result.
+__device__ __forceinline__ Acc acc_block_reduce(const Lane &L, uint32_t kind, uint32_t dt, Acc a) {
+  unsigned long long *red = reinterpret_cast<unsigned long long *>(L.smem + kSmemRed);
+  a = acc_warp_reduce(kind, dt, a);
+  const uint32_t w = L.tid / kWarp, l = L.tid % kWarp, nw = (L.nthr + kWarp - 1) / kWarp;
+  __syncthreads();
+  if (l == 0) red[w] = a.bits;
+  __syncthreads();
+  Acc r = acc_identity(kind, dt);
+  if (l < nw) r.bits = red[l];
+  return acc_warp_reduce(kind, dt, r);
+}
+
+// Reduce elements [lo, hi) of `p`, strided over `nthreads` cooperating threads
+// (this thread is `rank`); 16-byte loads when the run is 4-aligned f32-class.
+__device__ __forceinline__ Acc reduce_run(const uint8_t *p, uint32_t dt, uint32_t kind, int64_t lo, int64_t hi,
+                                          uint32_t rank, uint32_t nthreads, const uint8_t *dotvec, int64_t dot_off) {
+  Acc acc = acc_identity(kind, dt);
+  const uint32_t esz = dt_size(dt);
+  const bool vec = esz <= 4 && (lo % 4 == 0) && (reinterpret_cast<uintptr_t>(p) % 16 == 0) &&
+                   (!dotvec || ((dot_off % 4 == 0) && reinterpret_cast<uintptr_t>(dotvec) % 16 == 0));
+  if (vec) {
+    const int64_t g_lo = lo >> 2, g_hi = hi >> 2;
+    for (int64_t g = g_lo + rank; g < g_hi; g += nthreads) {
+      uint32_t v[4];
+      load4(p, dt, g << 2, v);
+      if (dotvec) {
+        uint32_t w[4];
+        load4(dotvec, dt, (g << 2) - lo + dot_off, w);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) v[e] = __float_as_uint(__uint_as_float(v[e]) * __uint_as_float(w[e]));
+      }
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        Acc x;
+        x.bits = v[e];
+        acc = acc_combine(kind, dt, acc, x);
+      }
+    }
+    for (int64_t i = (g_hi << 2) + rank; i < hi; i += nthreads) {
+      Acc x = acc_load(p, dt, i);
+      if (dotvec) x.bits = __float_as_uint(__uint_as_float(static_cast<uint32_t>(x.bits)) * loadf(dotvec, dt, i - lo + dot_off));
+      acc = acc_combine(kind, dt, acc, x);
+    }
+    return acc;
+  }
+  for (int64_t i = lo + rank; i < hi; i += nthreads) {
+    Acc x = acc_load(p, dt, i);
+    if (dotvec) x.bits = __float_as_uint(__uint_as_float(static_cast<uint32_t>(x.bits)) * loadf(dotvec, dt, i - lo + dot_off));
+    acc = acc_combine(kind, dt, acc, x);
+  }
+  return acc;
+}
+
+// RED_PART: tile t reduces in[t*chunk, min((t+1)*chunk, n)) into partials[t].
+__device__ __noinline__ void red_part_tiles(const Lane &L, const DTask &t, uint32_t tile_lo, uint32_t tile_hi) {
+  const KParams &P = *L.P;
+  uint8_t *dst = resolve(P, t.ptr[0]);
+  const uint8_t *a = resolve(P, t.ptr[1]);
+  const int64_t n = t.p[0], chunk = t.p[1];
+  const uint32_t kind = t.p[2], dt = t.dt;
+  for (uint32_t tile = tile_lo; tile < tile_hi; ++tile) {
+    const int64_t lo = tile * chunk, hi = min(lo + chunk, n);
+    if (lo >= hi) continue;
+    Acc acc = reduce_run(a, dt, kind, lo, hi, L.tid, L.nthr, nullptr, 0);
+    acc = acc_block_reduce(L, kind, dt, acc);
+    if (L.tid == 0) acc_store(dst, dt, tile, acc);
+  }
+}
+
+// RED_COMB: fold n_parts partials into dst[0] (single tile).
+__device__ __noinline__ void red_comb_tiles(const Lane &L, const DTask &t, uint32_t tile_lo, uint32_t tile_hi) {
+  if (!(tile_lo == 0 && tile_hi > 0)) return;
+  const KParams &P = *L.P;
+  uint8_t *dst = resolve(P, t.ptr[0]);
+  const uint8_t *a = resolve(P, t.ptr[1]);
+  const uint32_t kind = t.p[1], dt = t.dt;
+  Acc acc = reduce_run(a, dt, kind, 0, t.p[0], L.tid, L.nthr, nullptr, 0);
+  acc = acc_block_reduce(L, kind, dt, acc);
+  if (L.tid == 0) acc_store(dst, dt, 0, acc);
+}
+
+// RED_SEG: out[o] = reduce(in[o*seg, (o+1)*seg)), one segment per tile index;
+// p3 = 1: dot mode, out[o] = sum_j in[o*seg+j] * b[j].
+__device__ __noinline__ void red_seg_tiles(const Lane &L, const DTask &t, uint32_t tile_lo, uint32_t tile_hi) {
+  const KParams &P = *L.P;
+  uint8_t *dst = resolve(P, t.ptr[0]);
+  const uint8_t *a = resolve(P, t.ptr[1]);
+  const uint32_t n_out = t.p[0], kind = t.p[3] ? static_cast<uint32_t>(kSum) : t.p[2];
+  const int64_t seg = t.p[1];
+  const uint32_t dt = t.p[3] ? t.adt : t.dt;  // reduce keeps the input dtype; dot mode reads adt
+  const uint8_t *vecb = t.p[3] ? resolve(P, t.ptr[2]) : nullptr;
+  const uint32_t hi = min(tile_hi, n_out);
+  if (seg <= 16) {  // thread per segment
+    for (uint32_t o = tile_lo + L.tid; o < hi; o += L.nthr) {
+      Acc acc = reduce_run(a, dt, kind, o * seg, (o + 1) * seg, 0, 1, vecb, 0);
+      acc_store(dst, t.dt, o, acc);
+    }
+  } else if (seg <= 16384) {  // warp per segment
+    const uint32_t w = L.tid / kWarp, l = L.tid % kWarp, nw = L.nthr / kWarp;
+    for (uint32_t o = tile_lo + w; o < hi; o += nw) {
+      Acc acc = reduce_run(a, dt, kind, o * seg, (o + 1) * seg, l, kWarp, vecb, 0);
+      acc = acc_warp_reduce(kind, dt, acc);
+      if (l == 0) acc_store(dst, t.dt, o, acc);
+    }
+  } else {  // the whole lane per segment
+    for (uint32_t o = tile_lo; o < hi; ++o) {
+      Acc acc = reduce_run(a, dt, kind, o * seg, (o + 1) * seg, L.tid, L.nthr, vecb, 0);
+      acc = acc_block_reduce(L, kind, dt, acc);
+      if (L.tid == 0) acc_store(dst, t.dt, o, acc);
+    }
+  }
+}
+
+// RED_STRIDED: out[o*inner + i] = reduce_r in[(o*red + r)*inner + i]; EW-style
+// tiling of the outputs. Consecutive threads own consecutive outputs (coalesced
+// along `inner`), each keeps kQ independent outputs in flight.
+__device__ __noinline__ void red_strided_tiles(const Lane &L, const DTask &t, uint32_t tile_lo, uint32_t tile_hi) {
+  const KParams &P = *L.P;
+  uint8_t *dst = resolve(P, t.ptr[0]);
+  const uint8_t *a = resolve(P, t.ptr[1]);
+  const int64_t n_out = t.p[0], red = t.p[1], inner = t.p[2];
+  const uint32_t kind = t.p[3], dt = t.dt;
+  const int64_t lo = static_cast<int64_t>(tile_lo) * kEwTs, hi = min(static_cast<int64_t>(tile_hi) * kEwTs, n_out);
+  constexpr int kQ = 8;
+  for (int64_t g0 = lo + L.tid; g0 < hi; g0 += static_cast<int64_t>(L.nthr) * kQ) {
+    Acc acc[kQ];
+    int64_t base[kQ];
+#pragma unroll
+    for (int q = 0; q < kQ; ++q) {
+      const int64_t g = g0 + static_cast<int64_t>(q) * L.nthr;
+      acc[q] = acc_identity(kind, dt);
+      base[q] = g < hi ? (g / inner) * red * inner + (g % inner) : -1;
+    }
+    for (int64_t r = 0; r < red; ++r) {
+#pragma unroll
+      for (int q = 0; q < kQ; ++q)
+        if (base[q] >= 0) acc[q] = acc_combine(kind, dt, acc[q], acc_load(a, dt, base[q] + r * inner));
+    }
+#pragma unroll
+    for (int q = 0; q < kQ; ++q)
+      if (base[q] >= 0) acc_store(dst, dt, g0 + static_cast<int64_t>(q) * L.nthr, acc[q]);
+  }
+}
+
+}  // namespace b2
+#endif

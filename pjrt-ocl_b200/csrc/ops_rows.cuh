@@ -1,0 +1,212 @@
+// Fused row ops: SOFTMAX_SEG and LAYERNORM_SEG over the innermost `seg` elements.
+//
+// Replaces vmo_softmax_seg / vmo_layernorm_seg (pjrt_plugin/kernels/ops/
+// reduce.cl:304-479), which stage one row of at most 1024 floats in local memory.
+// Semantics: python/pjrt_ocl/ops/reduce.py:464-475 - softmax = exp(x - max) / sum;
+// layernorm core = (x - mean) / sqrt(E[x^2] - mean^2 + eps), one-pass variance.
+//
+// B200 design: any segment length. Rows whose byte length is a multiple of 16
+// (and that fit the staging buffers) are streamed HBM -> shared memory by the
+// bulk asynchronous copy engine (TMA, untiled form) with an mbarrier per buffer:
+// the lane is split into groups of 4 warps, each group double-buffers its rows,
+// so the next row is in flight while the current one is reduced and normalised
+// out of shared memory; every element is read from HBM exactly once and written
+// once. Other rows (ragged / tiny / huge) take a warp-per-row path that re-reads
+// the row through L1/L2.
+#ifndef B2VM_OPS_ROWS_CUH_
+#define B2VM_OPS_ROWS_CUH_
+
+#include "dev_common.cuh"
+#include "ops_ew.cuh"
+
+namespace b2 {
+
+constexpr int kRowGroupWarps = 4;
+constexpr int kRowGroupThreads = kRowGroupWarps * kWarp;
+
+// Reduce across the 4 warps of a row group. `slot` = 4 floats of scratch per group.
+template <typename F>
+__device__ __forceinline__ float group_reduce(float v, F f, float *slot, int barrier_id, uint32_t gl) {
+  v = warp_reduce(v, f);
+  bar_sync(barrier_id, kRowGroupThreads);          // previous users of `slot` are done
+  if ((gl & (kWarp - 1)) == 0) slot[gl / kWarp] = v;
+  bar_sync(barrier_id, kRowGroupThreads);
+  float r = slot[0];
+#pragma unroll
+  for (int w = 1; w < kRowGroupWarps; ++w) r = f(r, slot[w]);
+  return r;
+}
+
+// rows [tile_lo, tile_hi) through the staged pipeline. Preconditions (checked by
+// the caller): seg*esz % 16 == 0, both buffers 16-byte aligned, 2 buffers per group fit.
+__device__ __forceinline__ void rows_staged(const Lane &L, const DTask &t, uint32_t lo, uint32_t hi, bool softmax) {
+  const KParams &P = *L.P;
+  uint8_t *dst = resolve(P, t.ptr[0]);
+  const uint8_t *src = resolve(P, t.ptr[1]);
+  const uint32_t seg = t.p[1], adt = t.adt, dt = t.dt;
+  const uint32_t in_bytes = seg * dt_size(adt);
+  const float eps = __uint_as_float(t.p[2]);
+  const uint32_t ngroups = L.nthr / kRowGroupThreads;
+  const uint32_t gi = L.tid / kRowGroupThreads, gl = L.tid % kRowGroupThreads;
+  uint64_t *bars = reinterpret_cast<uint64_t *>(L.smem + kSmemSys);               // [ngroups][2]
+  float *slots = reinterpret_cast<float *>(L.smem + kSmemSys + 256);              // [ngroups][4]
+  const uint32_t buf_stride = (in_bytes + 127u) & ~127u;
+  uint8_t *bufs = L.smem + kSmemSys + 512 + static_cast<size_t>(gi) * 2 * buf_stride;
+
+  __syncthreads();
+  if (L.tid == 0) {
+    for (uint32_t i = 0; i < ngroups * 2; ++i) mbar_init(&bars[i], 1);
+    fence_mbar_init();
+  }
+  __syncthreads();
+
+  uint64_t *bar = bars + gi * 2;
+  float *slot = slots + gi * 4;
+  const int bid = 1 + static_cast<int>(gi);
+  const uint32_t first = lo + gi;
+  if (gl == 0 && first < hi) {
+    mbar_arrive_expect_tx(&bar[0], in_bytes);
+    bulk_g2s(bufs, src + static_cast<size_t>(first) * in_bytes, in_bytes, &bar[0]);
+  }
+  // Every group runs the same trip count so the lane-wide vote below stays uniform;
+  // a group that has run out of rows just votes.
+  const uint32_t max_it = (hi - lo + ngroups - 1) / ngroups;
+  for (uint32_t it = 0; it < max_it; ++it) {
+    const uint32_t row = first + it * ngroups;
+    const bool active = row < hi;
+    const uint32_t b = it & 1u, parity = (it >> 1) & 1u;
+    bool ok = true;
+    if (active && !mbar_wait_bounded(&bar[b], parity, P.wait_budget_ns)) {
+      set_status(P, kStTensorTimeout, L.lane, row, t.op);
+      ok = false;
+    }
+    // Lane-wide vote: (1) a copy that never landed abandons the op for everybody,
+    // (2) every thread has left the previous iteration, so the other buffer is free.
+    if (!__syncthreads_and(ok)) break;
+    const uint32_t next = row + ngroups;
+    if (gl == 0 && next < hi) {
+      // the other buffer was last read through the generic proxy: order those
+      // reads before the asynchronous-proxy write that refills it.
+      fence_proxy_async_smem();
+      mbar_arrive_expect_tx(&bar[b ^ 1u], in_bytes);
+      bulk_g2s(bufs + (b ^ 1u) * buf_stride, src + static_cast<size_t>(next) * in_bytes, in_bytes, &bar[b ^ 1u]);
+    }
+    if (!active) continue;
+    const uint8_t *rowp = bufs + b * buf_stride;
+    uint8_t *outp = dst + static_cast<size_t>(row) * seg * dt_size(dt);
+    const uint32_t ng = seg >> 2;   // the caller checked seg % 4 == 0
+    if (softmax) {
+      float m = -INFINITY;
+      for (uint32_t g = gl; g < ng; g += kRowGroupThreads) {
+        uint32_t v[4];
+        load4(rowp, adt, g << 2, v);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) m = np_max(m, __uint_as_float(v[e]));
+      }
+      m = group_reduce(m, [](float a, float c) { return np_max(a, c); }, slot, bid, gl);
+      float s = 0.0f;
+      for (uint32_t g = gl; g < ng; g += kRowGroupThreads) {
+        uint32_t v[4];
+        load4(rowp, adt, g << 2, v);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) s += expf(__uint_as_float(v[e]) - m);
+      }
+      s = group_reduce(s, [](float a, float c) { return a + c; }, slot, bid, gl);
+      for (uint32_t g = gl; g < ng; g += kRowGroupThreads) {
+        uint32_t v[4];
+        load4(rowp, adt, g << 2, v);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) v[e] = __float_as_uint(__fdiv_rn(expf(__uint_as_float(v[e]) - m), s));
+        store4(outp, dt, g << 2, v);
+      }
+    } else {
+      float s = 0.0f, s2 = 0.0f;
+      for (uint32_t g = gl; g < ng; g += kRowGroupThreads) {
+        uint32_t v[4];
+        load4(rowp, adt, g << 2, v);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float x = __uint_as_float(v[e]);
+          s += x;
+          s2 = fmaf(x, x, s2);
+        }
+      }
+      s = group_reduce(s, [](float a, float c) { return a + c; }, slot, bid, gl);
+      s2 = group_reduce(s2, [](float a, float c) { return a + c; }, slot, bid, gl);
+      const float inv_n = 1.0f / static_cast<float>(seg);
+      const float mu = s * inv_n;
+      const float var = __fsub_rn(s2 * inv_n, __fmul_rn(mu, mu));
+      const float den = __fsqrt_rn(__fadd_rn(var, eps));
+      for (uint32_t g = gl; g < ng; g += kRowGroupThreads) {
+        uint32_t v[4];
+        load4(rowp, adt, g << 2, v);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) v[e] = __float_as_uint(__fdiv_rn(__fsub_rn(__uint_as_float(v[e]), mu), den));
+        store4(outp, dt, g << 2, v);
+      }
+    }
+  }
+  __syncthreads();
+  if (L.tid == 0)
+    for (uint32_t i = 0; i < ngroups * 2; ++i) mbar_inval(&bars[i]);
+  __syncthreads();
+}
+
+// warp per row; re-reads the row (L1/L2) instead of staging it.
+__device__ __forceinline__ void rows_generic(const Lane &L, const DTask &t, uint32_t lo, uint32_t hi, bool softmax) {
+  const KParams &P = *L.P;
+  uint8_t *dst = resolve(P, t.ptr[0]);
+  const uint8_t *src = resolve(P, t.ptr[1]);
+  const uint32_t seg = t.p[1], adt = t.adt, dt = t.dt;
+  const float eps = __uint_as_float(t.p[2]);
+  const uint32_t w = L.tid / kWarp, l = L.tid % kWarp, nw = L.nthr / kWarp;
+  for (uint32_t row = lo + w; row < hi; row += nw) {
+    const int64_t base = static_cast<int64_t>(row) * seg;
+    if (softmax) {
+      float m = -INFINITY;
+      for (uint32_t j = l; j < seg; j += kWarp) m = np_max(m, loadf(src, adt, base + j));
+      m = warp_reduce(m, [](float a, float c) { return np_max(a, c); });
+      float s = 0.0f;
+      for (uint32_t j = l; j < seg; j += kWarp) s += expf(loadf(src, adt, base + j) - m);
+      s = warp_reduce(s, [](float a, float c) { return a + c; });
+      for (uint32_t j = l; j < seg; j += kWarp)
+        storef(dst, dt, base + j, __fdiv_rn(expf(loadf(src, adt, base + j) - m), s));
+    } else {
+      float s = 0.0f, s2 = 0.0f;
+      for (uint32_t j = l; j < seg; j += kWarp) {
+        const float x = loadf(src, adt, base + j);
+        s += x;
+        s2 = fmaf(x, x, s2);
+      }
+      s = warp_reduce(s, [](float a, float c) { return a + c; });
+      s2 = warp_reduce(s2, [](float a, float c) { return a + c; });
+      const float inv_n = 1.0f / static_cast<float>(seg);
+      const float mu = s * inv_n;
+      const float var = __fsub_rn(s2 * inv_n, __fmul_rn(mu, mu));
+      const float den = __fsqrt_rn(__fadd_rn(var, eps));
+      for (uint32_t j = l; j < seg; j += kWarp)
+        storef(dst, dt, base + j, __fdiv_rn(__fsub_rn(loadf(src, adt, base + j), mu), den));
+    }
+  }
+}
+
+__device__ __noinline__ void rows_tiles(const Lane &L, const DTask &t, uint32_t tile_lo, uint32_t tile_hi, bool softmax) {
+  const KParams &P = *L.P;
+  const uint32_t n_out = t.p[0], seg = t.p[1];
+  const uint32_t hi = min(tile_hi, n_out);
+  if (tile_lo >= hi) return;
+  const uint32_t in_bytes = seg * dt_size(t.adt);
+  const uint32_t ngroups = L.nthr / kRowGroupThreads;
+  const uint32_t buf_stride = (in_bytes + 127u) & ~127u;
+  const uint8_t *src = resolve(P, t.ptr[1]);
+  uint8_t *dst = resolve(P, t.ptr[0]);
+  const bool staged = ngroups >= 1 && L.nthr % kRowGroupThreads == 0 && ngroups <= 15 &&
+                      seg >= 1024 && seg % 4 == 0 && in_bytes % 16 == 0 && dt_size(t.adt) <= 4 && dt_size(t.dt) <= 4 &&
+                      reinterpret_cast<uintptr_t>(src) % 16 == 0 && reinterpret_cast<uintptr_t>(dst) % 16 == 0 &&
+                      static_cast<size_t>(kSmemSys) + 512 + static_cast<size_t>(ngroups) * 2 * buf_stride <= L.smem_bytes;
+  if (staged) rows_staged(L, t, tile_lo, hi, softmax);
+  else rows_generic(L, t, tile_lo, hi, softmax);
+}
+
+}  // namespace b2
+#endif

@@ -1,0 +1,552 @@
+// CUDA runtime side of the backend and its C ABI (include/b2vm.h).
+//
+// Mirrors, for the execution path only, the reference's OclRuntime and
+// LoadedProgram (pjrt_plugin/src/runtime.h:120-435; runtime.cc:255-662 Create,
+// :735-1074 Load, :1103-1218 Execute/LaunchKernel, :2107-2277 ExecuteDevice and
+// the buffer pool): one device, one stream, one mutex per runtime; an arena per
+// loaded program with constants uploaded once; <= 64 zero-copy I/O ports;
+// synchronous execute; size-keyed pool for result buffers.
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstddef>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <memory>
+#include <mutex>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "../../include/b2vm.h"
+#include "format.h"
+#include "loader.h"
+#include "vmprog.h"
+
+namespace b2 {
+cudaError_t LaunchVm(const KParams &params, uint32_t n_lanes, int threads, uint32_t smem_bytes, cudaStream_t stream);
+cudaError_t VmResidency(int device, int threads, uint32_t smem_bytes, int *max_lanes);
+}  // namespace b2
+
+namespace {
+
+void SetErr(char *err, size_t cap, const std::string &m) {
+  if (err && cap) {
+    std::snprintf(err, cap, "%s", m.c_str());
+  }
+}
+std::string CudaMsg(const char *what, cudaError_t e) {
+  return std::string(what) + ": " + cudaGetErrorName(e) + " (" + cudaGetErrorString(e) + ")";
+}
+
+constexpr size_t kPoolPerSize = 4;  // runtime.h:304
+
+}  // namespace
+
+struct b2_program {
+  b2::VmProgram prog;
+};
+
+struct b2_runtime {
+  int device = 0;
+  cudaStream_t stream = nullptr;
+  cudaDeviceProp prop{};
+  int threads = 512;
+  uint32_t smem_bytes = 0;
+  int max_lanes = 0;
+  std::mutex mu;        // serialises execute and host<->device copies (runtime.h:301)
+  std::mutex pool_mu;   // runtime.h:302
+  std::unordered_map<size_t, std::vector<void *>> pool;
+
+  cudaError_t Bind() const { return cudaSetDevice(device); }
+
+  void *PoolAlloc(size_t bytes, std::string *err) {
+    const size_t key = bytes ? bytes : 8;
+    {
+      std::lock_guard<std::mutex> g(pool_mu);
+      auto it = pool.find(key);
+      if (it != pool.end() && !it->second.empty()) {
+        void *p = it->second.back();
+        it->second.pop_back();
+        return p;
+      }
+    }
+    void *p = nullptr;
+    const cudaError_t e = cudaMalloc(&p, key);
+    if (e != cudaSuccess) {
+      *err = CudaMsg("device allocation", e) + " for " + std::to_string(key) + " bytes";
+      cudaGetLastError();
+      return nullptr;
+    }
+    return p;
+  }
+  void PoolFree(void *p, size_t bytes) {
+    if (!p) return;
+    const size_t key = bytes ? bytes : 8;
+    {
+      std::lock_guard<std::mutex> g(pool_mu);
+      auto &v = pool[key];
+      if (v.size() < kPoolPerSize) {
+        v.push_back(p);
+        return;
+      }
+    }
+    cudaFree(p);
+  }
+};
+
+struct b2_loaded {
+  b2_runtime *rt = nullptr;
+  b2::VmProgram prog;
+  b2::DeviceTables tab;
+  uint8_t *arena = nullptr;
+  b2::DTask *d_tasks = nullptr;
+  b2::DEntry *d_entries = nullptr;
+  b2::VmLane *d_lanes = nullptr;
+  int32_t *d_aux = nullptr;
+  uint64_t *d_desc = nullptr;
+  b2::DSync *d_sync = nullptr;
+  b2::DSync *h_sync = nullptr;  // pinned mirror
+  uint64_t launches = 0;
+  uint64_t wait_budget_ns = 2000000000ull;
+  cudaStream_t last_stream = nullptr;
+
+  ~b2_loaded() {
+    if (rt) rt->Bind();
+    cudaFree(arena); cudaFree(d_tasks); cudaFree(d_entries); cudaFree(d_lanes);
+    cudaFree(d_aux); cudaFree(d_desc); cudaFree(d_sync);
+    if (h_sync) cudaFreeHost(h_sync);
+  }
+};
+
+namespace {
+
+template <typename T>
+cudaError_t Upload(T **dptr, const std::vector<T> &v) {
+  const size_t bytes = std::max<size_t>(v.size() * sizeof(T), 16);
+  cudaError_t e = cudaMalloc(reinterpret_cast<void **>(dptr), bytes);
+  if (e != cudaSuccess) return e;
+  if (!v.empty()) e = cudaMemcpy(*dptr, v.data(), v.size() * sizeof(T), cudaMemcpyHostToDevice);
+  return e;
+}
+
+// Enqueue one execution on `stream`: reset the sync block, launch the megakernel,
+// copy the sync block back to its pinned mirror. `io` holds the port addresses.
+b2_status Enqueue(b2_loaded *lp, const b2::IoTable &io, cudaStream_t stream, std::string *err) {
+  cudaError_t e = cudaMemsetAsync(lp->d_sync, 0, sizeof(b2::DSync), stream);
+  if (e != cudaSuccess) { *err = CudaMsg("sync reset", e); return B2_INTERNAL; }
+  b2::KParams kp;
+  std::memset(&kp, 0, sizeof(kp));
+  kp.tasks = lp->d_tasks;
+  kp.entries = lp->d_entries;
+  kp.lanes = lp->d_lanes;
+  kp.aux = lp->d_aux;
+  kp.desc = lp->d_desc;
+  kp.sync = lp->d_sync;
+  kp.scratch = nullptr;
+  kp.n_lanes = lp->prog.n_lanes;
+  kp.wait_budget_ns = lp->wait_budget_ns;
+  kp.io = io;
+  e = b2::LaunchVm(kp, lp->prog.n_lanes, lp->rt->threads, lp->rt->smem_bytes, stream);
+  if (e != cudaSuccess) { *err = CudaMsg("megakernel launch", e); cudaGetLastError(); return B2_INTERNAL; }
+  lp->launches++;
+  e = cudaMemcpyAsync(lp->h_sync, lp->d_sync, sizeof(b2::DSync), cudaMemcpyDeviceToHost, stream);
+  if (e != cudaSuccess) { *err = CudaMsg("status readback", e); return B2_INTERNAL; }
+  lp->last_stream = stream;
+  return B2_OK;
+}
+
+b2_status CheckDeviceStatus(const b2_loaded *lp, std::string *err) {
+  const b2::DSync &s = *lp->h_sync;
+  switch (s.status[0]) {
+    case b2::kStOk: return B2_OK;
+    case b2::kStBarrierTimeout:
+      *err = "device wait ran out: lane " + std::to_string(s.status[1]) + " at grid barrier " +
+             std::to_string(s.status[2]) + " (are all " + std::to_string(lp->prog.n_lanes) + " lanes co-resident?)";
+      return B2_DEADLINE_EXCEEDED;
+    case b2::kStTensorTimeout:
+      *err = "device wait ran out: lane " + std::to_string(s.status[1]) + " asynchronous copy / tensor-core wait in tile op " +
+             std::to_string(s.status[3]);
+      return B2_DEADLINE_EXCEEDED;
+    case b2::kStStackOverflow:
+      *err = "control nesting exceeds " + std::to_string(b2::kMaxDepth) + " on lane " + std::to_string(s.status[1]);
+      return B2_INVALID_ARGUMENT;
+    case b2::kStBadOp:
+      *err = "tile op " + std::to_string(s.status[3]) + " reached on device but not implemented";
+      return B2_UNIMPLEMENTED;
+    default:
+      *err = "unknown device status " + std::to_string(s.status[0]);
+      return B2_INTERNAL;
+  }
+}
+
+}  // namespace
+
+extern "C" {
+
+b2_status b2_runtime_create(int device_ordinal, b2_runtime **out, char *err, size_t err_cap) {
+  *out = nullptr;
+  int n = 0;
+  cudaError_t e = cudaGetDeviceCount(&n);
+  if (e != cudaSuccess || n == 0) {
+    SetErr(err, err_cap, e != cudaSuccess ? CudaMsg("no CUDA device", e) : "no CUDA device");
+    cudaGetLastError();
+    return B2_FAILED_PRECONDITION;
+  }
+  if (device_ordinal < 0 || device_ordinal >= n) {
+    SetErr(err, err_cap, "device ordinal " + std::to_string(device_ordinal) + " out of range (" + std::to_string(n) + " devices)");
+    return B2_INVALID_ARGUMENT;
+  }
+  auto rt = std::make_unique<b2_runtime>();
+  rt->device = device_ordinal;
+  if ((e = rt->Bind()) != cudaSuccess || (e = cudaGetDeviceProperties(&rt->prop, device_ordinal)) != cudaSuccess) {
+    SetErr(err, err_cap, CudaMsg("device query", e));
+    return B2_INTERNAL;
+  }
+  if (rt->prop.major < 10) {
+    SetErr(err, err_cap, std::string("device ") + rt->prop.name + " is sm_" + std::to_string(rt->prop.major) +
+                             std::to_string(rt->prop.minor) + "; this backend is built for sm_100a only");
+    return B2_FAILED_PRECONDITION;
+  }
+  if (const char *t = std::getenv("B2VM_THREADS")) {
+    const int v = std::atoi(t);
+    if (v == 128 || v == 512) rt->threads = v;
+  }
+  // All of the opt-in shared memory of one CTA per SM, minus a margin for the
+  // runtime's own reservation.
+  size_t optin = rt->prop.sharedMemPerBlockOptin;
+  rt->smem_bytes = static_cast<uint32_t>(std::min<size_t>(optin, 227 * 1024) - 1024);
+  if ((e = b2::VmResidency(device_ordinal, rt->threads, rt->smem_bytes, &rt->max_lanes)) != cudaSuccess) {
+    SetErr(err, err_cap, CudaMsg("megakernel occupancy query", e));
+    cudaGetLastError();
+    return B2_INTERNAL;
+  }
+  if ((e = cudaStreamCreateWithFlags(&rt->stream, cudaStreamNonBlocking)) != cudaSuccess) {
+    SetErr(err, err_cap, CudaMsg("stream create", e));
+    return B2_INTERNAL;
+  }
+  *out = rt.release();
+  return B2_OK;
+}
+
+void b2_runtime_destroy(b2_runtime *rt) {
+  if (!rt) return;
+  rt->Bind();
+  for (auto &kv : rt->pool)
+    for (void *p : kv.second) cudaFree(p);
+  if (rt->stream) cudaStreamDestroy(rt->stream);
+  delete rt;
+}
+
+b2_status b2_runtime_info(const b2_runtime *rt, b2_device_info *out) {
+  if (!rt || !out) return B2_INVALID_ARGUMENT;
+  std::memset(out, 0, sizeof(*out));
+  std::snprintf(out->device_name, sizeof(out->device_name), "%s", rt->prop.name);
+  out->device_ordinal = rt->device;
+  out->sm_count = rt->prop.multiProcessorCount;
+  out->cc_major = rt->prop.major;
+  out->cc_minor = rt->prop.minor;
+  out->total_mem_bytes = rt->prop.totalGlobalMem;
+  out->lanes = static_cast<uint32_t>(rt->max_lanes);
+  out->ew_ts = b2::kEwTs;
+  out->mma_t = b2::kMmaT;
+  out->threads_per_lane = static_cast<uint32_t>(rt->threads);
+  return B2_OK;
+}
+
+b2_status b2_alloc(b2_runtime *rt, size_t bytes, void **dev_ptr, char *err, size_t err_cap) {
+  if (!rt || !dev_ptr) return B2_INVALID_ARGUMENT;
+  rt->Bind();
+  std::string m;
+  *dev_ptr = rt->PoolAlloc(bytes, &m);
+  if (!*dev_ptr) { SetErr(err, err_cap, m); return B2_RESOURCE_EXHAUSTED; }
+  return B2_OK;
+}
+
+b2_status b2_free(b2_runtime *rt, void *dev_ptr, size_t bytes) {
+  if (!rt) return B2_INVALID_ARGUMENT;
+  rt->Bind();
+  rt->PoolFree(dev_ptr, bytes);
+  return B2_OK;
+}
+
+b2_status b2_h2d(b2_runtime *rt, void *dev_dst, const void *host_src, size_t bytes, char *err, size_t err_cap) {
+  if (!rt) return B2_INVALID_ARGUMENT;
+  std::lock_guard<std::mutex> g(rt->mu);
+  rt->Bind();
+  cudaError_t e = cudaMemcpyAsync(dev_dst, host_src, bytes, cudaMemcpyHostToDevice, rt->stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(rt->stream);
+  if (e != cudaSuccess) { SetErr(err, err_cap, CudaMsg("host to device copy", e)); return B2_INTERNAL; }
+  return B2_OK;
+}
+
+b2_status b2_d2h(b2_runtime *rt, void *host_dst, const void *dev_src, size_t bytes, char *err, size_t err_cap) {
+  if (!rt) return B2_INVALID_ARGUMENT;
+  std::lock_guard<std::mutex> g(rt->mu);
+  rt->Bind();
+  cudaError_t e = cudaMemcpyAsync(host_dst, dev_src, bytes, cudaMemcpyDeviceToHost, rt->stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(rt->stream);
+  if (e != cudaSuccess) { SetErr(err, err_cap, CudaMsg("device to host copy", e)); return B2_INTERNAL; }
+  return B2_OK;
+}
+
+// ---- program ------------------------------------------------------------------------
+b2_status b2_program_parse(const uint8_t *blob, size_t len, b2_program **out, char *err, size_t err_cap) {
+  if (!out) return B2_INVALID_ARGUMENT;
+  *out = nullptr;
+  auto p = std::make_unique<b2_program>();
+  std::string m;
+  if (!blob || !b2::VmProgram::Parse(blob, len, &p->prog, &m)) {
+    SetErr(err, err_cap, blob ? m : "null blob");
+    return B2_INVALID_ARGUMENT;
+  }
+  *out = p.release();
+  return B2_OK;
+}
+void b2_program_destroy(b2_program *prog) { delete prog; }
+uint32_t b2_program_num_inputs(const b2_program *p) { return static_cast<uint32_t>(p->prog.inputs.size()); }
+uint32_t b2_program_num_outputs(const b2_program *p) { return static_cast<uint32_t>(p->prog.outputs.size()); }
+uint32_t b2_program_num_lanes(const b2_program *p) { return p->prog.n_lanes; }
+uint32_t b2_program_num_tasks(const b2_program *p) { return static_cast<uint32_t>(p->prog.tasks.size()); }
+uint64_t b2_program_arena_bytes(const b2_program *p) { return p->prog.arena_bytes; }
+static const b2::VmBuffer *IoBuf(const b2_program *p, int is_output, uint32_t i) {
+  const auto &ids = is_output ? p->prog.outputs : p->prog.inputs;
+  return i < ids.size() ? &p->prog.buffers[ids[i]] : nullptr;
+}
+uint64_t b2_program_io_bytes(const b2_program *p, int is_output, uint32_t i) {
+  const b2::VmBuffer *b = IoBuf(p, is_output, i);
+  return b ? b->size_bytes : 0;
+}
+uint32_t b2_program_io_dtype(const b2_program *p, int is_output, uint32_t i) {
+  const b2::VmBuffer *b = IoBuf(p, is_output, i);
+  return b ? b->dtype : 0;
+}
+uint32_t b2_program_io_rank(const b2_program *p, int is_output, uint32_t i) {
+  const auto &d = is_output ? p->prog.output_dims : p->prog.input_dims;
+  return i < d.size() ? static_cast<uint32_t>(d[i].size()) : 0;
+}
+int64_t b2_program_io_dim(const b2_program *p, int is_output, uint32_t i, uint32_t k) {
+  const auto &d = is_output ? p->prog.output_dims : p->prog.input_dims;
+  return (i < d.size() && k < d[i].size()) ? d[i][k] : 0;
+}
+
+// ---- load ---------------------------------------------------------------------------------
+b2_status b2_program_load(b2_runtime *rt, b2_program *prog, b2_loaded **out, char *err, size_t err_cap) {
+  if (!rt || !prog || !out) return B2_INVALID_ARGUMENT;
+  *out = nullptr;
+  const b2::VmProgram &p = prog->prog;
+  rt->Bind();
+  // The grid barrier needs every lane resident at once: refuse rather than launch.
+  if (static_cast<int>(p.n_lanes) > rt->max_lanes) {
+    SetErr(err, err_cap, "program is scheduled for " + std::to_string(p.n_lanes) + " lanes but only " +
+                             std::to_string(rt->max_lanes) + " megakernel CTAs are co-resident on " + rt->prop.name);
+    return B2_FAILED_PRECONDITION;
+  }
+  auto lp = std::make_unique<b2_loaded>();
+  lp->rt = rt;
+  cudaError_t e = cudaMalloc(reinterpret_cast<void **>(&lp->arena), std::max<uint64_t>(p.arena_bytes, 256));
+  if (e != cudaSuccess) {
+    SetErr(err, err_cap, CudaMsg("arena allocation", e) + " for " + std::to_string(p.arena_bytes) + " bytes");
+    cudaGetLastError();
+    return B2_RESOURCE_EXHAUSTED;
+  }
+  std::string m;
+  bool unimpl = false;
+  if (!b2::BuildDeviceTables(p, reinterpret_cast<uint64_t>(lp->arena), &lp->tab, &m, &unimpl)) {
+    SetErr(err, err_cap, "load: " + m);
+    return unimpl ? B2_UNIMPLEMENTED : B2_INVALID_ARGUMENT;
+  }
+  std::vector<int32_t> aux = p.aux;
+  if ((e = Upload(&lp->d_tasks, lp->tab.tasks)) != cudaSuccess || (e = Upload(&lp->d_entries, lp->tab.entries)) != cudaSuccess ||
+      (e = Upload(&lp->d_lanes, p.lane_tab)) != cudaSuccess || (e = Upload(&lp->d_aux, aux)) != cudaSuccess ||
+      (e = Upload(&lp->d_desc, lp->tab.desc)) != cudaSuccess ||
+      (e = cudaMalloc(reinterpret_cast<void **>(&lp->d_sync), sizeof(b2::DSync))) != cudaSuccess ||
+      (e = cudaMallocHost(reinterpret_cast<void **>(&lp->h_sync), sizeof(b2::DSync))) != cudaSuccess) {
+    SetErr(err, err_cap, CudaMsg("device table upload", e));
+    cudaGetLastError();
+    return B2_RESOURCE_EXHAUSTED;
+  }
+  std::memset(lp->h_sync, 0, sizeof(b2::DSync));
+  for (const auto &k : p.consts) {  // constants are uploaded once (runtime.cc:1064-1072)
+    if (k.second.empty()) continue;
+    e = cudaMemcpy(lp->arena + p.buffers[k.first].arena_byte_offset, k.second.data(), k.second.size(), cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) { SetErr(err, err_cap, CudaMsg("constant upload", e)); return B2_INTERNAL; }
+  }
+  lp->prog = std::move(prog->prog);
+  delete prog;
+  *out = lp.release();
+  return B2_OK;
+}
+
+void b2_loaded_destroy(b2_loaded *lp) { delete lp; }
+
+const b2_program *b2_loaded_program(const b2_loaded *lp) {
+  // b2_program is a thin wrapper around VmProgram: same address.
+  static_assert(offsetof(b2_program, prog) == 0, "wrapper layout");
+  return reinterpret_cast<const b2_program *>(&lp->prog);
+}
+
+uint64_t b2_loaded_launch_count(const b2_loaded *lp) { return lp->launches; }
+void b2_loaded_set_wait_budget_ns(b2_loaded *lp, uint64_t ns) { lp->wait_budget_ns = ns; }
+
+b2_status b2_loaded_status(b2_loaded *lp, b2_exec_status *out, char *err, size_t err_cap) {
+  if (!lp || !out) return B2_INVALID_ARGUMENT;
+  const b2::DSync &s = *lp->h_sync;
+  out->code = s.status[0]; out->lane = s.status[1]; out->where = s.status[2]; out->detail = s.status[3];
+  out->barriers = s.barriers; out->device_ns = s.device_ns;
+  std::string m;
+  const b2_status st = CheckDeviceStatus(lp, &m);
+  if (st != B2_OK) SetErr(err, err_cap, m);
+  return st;
+}
+
+// ---- execute ---------------------------------------------------------------------------------
+static b2_status BindAndRun(b2_loaded *lp, void *const *dev_in, void *const *dev_out, cudaStream_t stream,
+                            bool synchronous, std::string *err) {
+  const b2::VmProgram &p = lp->prog;
+  b2::IoTable io;
+  std::memset(&io, 0, sizeof(io));
+  cudaError_t e;
+  for (size_t i = 0; i < p.inputs.size(); ++i) {
+    const auto &b = p.buffers[p.inputs[i]];
+    if (!b.size_bytes) continue;
+    if (lp->tab.input_port[i] >= 0) {
+      if (reinterpret_cast<uintptr_t>(dev_in[i]) % 16) { *err = "argument " + std::to_string(i) + " is not 16-byte aligned"; return B2_INVALID_ARGUMENT; }
+      io.p[lp->tab.input_port[i]] = dev_in[i];
+    } else if ((e = cudaMemcpyAsync(lp->arena + b.arena_byte_offset, dev_in[i], b.size_bytes, cudaMemcpyDeviceToDevice, stream)) != cudaSuccess) {
+      *err = CudaMsg("argument copy into the arena", e);
+      return B2_INTERNAL;
+    }
+  }
+  for (size_t o = 0; o < p.outputs.size(); ++o) {
+    if (lp->tab.output_port[o] < 0 || !p.buffers[p.outputs[o]].size_bytes) continue;
+    if (reinterpret_cast<uintptr_t>(dev_out[o]) % 16) { *err = "result " + std::to_string(o) + " is not 16-byte aligned"; return B2_INVALID_ARGUMENT; }
+    io.p[lp->tab.output_port[o]] = dev_out[o];
+  }
+  const b2_status st = Enqueue(lp, io, stream, err);
+  if (st != B2_OK) return st;
+  for (size_t o = 0; o < p.outputs.size(); ++o) {
+    const auto &b = p.buffers[p.outputs[o]];
+    if (lp->tab.output_port[o] >= 0 || !b.size_bytes) continue;
+    if ((e = cudaMemcpyAsync(dev_out[o], lp->arena + b.arena_byte_offset, b.size_bytes, cudaMemcpyDeviceToDevice, stream)) != cudaSuccess) {
+      *err = CudaMsg("result copy out of the arena", e);
+      return B2_INTERNAL;
+    }
+  }
+  if (!synchronous) return B2_OK;
+  if ((e = cudaStreamSynchronize(stream)) != cudaSuccess) {
+    *err = CudaMsg("execute", e);
+    cudaGetLastError();
+    return B2_INTERNAL;
+  }
+  return CheckDeviceStatus(lp, err);
+}
+
+b2_status b2_execute_device_async(b2_loaded *lp, void *const *dev_inputs, size_t n_inputs, void *const *dev_outputs,
+                                  size_t n_outputs, void *cuda_stream, char *err, size_t err_cap) {
+  if (!lp) return B2_INVALID_ARGUMENT;
+  const b2::VmProgram &p = lp->prog;
+  if (n_inputs != p.inputs.size() || n_outputs != p.outputs.size()) {
+    SetErr(err, err_cap, "execute: got " + std::to_string(n_inputs) + " args / " + std::to_string(n_outputs) +
+                             " results, want " + std::to_string(p.inputs.size()) + " / " + std::to_string(p.outputs.size()));
+    return B2_INVALID_ARGUMENT;
+  }
+  std::lock_guard<std::mutex> g(lp->rt->mu);
+  lp->rt->Bind();
+  std::string m;
+  const b2_status st = BindAndRun(lp, dev_inputs, dev_outputs,
+                                  cuda_stream ? static_cast<cudaStream_t>(cuda_stream) : lp->rt->stream, false, &m);
+  if (st != B2_OK) SetErr(err, err_cap, m);
+  return st;
+}
+
+b2_status b2_execute_device(b2_loaded *lp, void *const *dev_inputs, size_t n_inputs, void **dev_outputs,
+                            size_t n_outputs, char *err, size_t err_cap) {
+  if (!lp) return B2_INVALID_ARGUMENT;
+  const b2::VmProgram &p = lp->prog;
+  if (n_inputs != p.inputs.size() || n_outputs != p.outputs.size()) {
+    SetErr(err, err_cap, "execute: got " + std::to_string(n_inputs) + " args / " + std::to_string(n_outputs) +
+                             " results, want " + std::to_string(p.inputs.size()) + " / " + std::to_string(p.outputs.size()));
+    return B2_INVALID_ARGUMENT;
+  }
+  std::lock_guard<std::mutex> g(lp->rt->mu);
+  lp->rt->Bind();
+  std::string m;
+  for (size_t o = 0; o < n_outputs; ++o) dev_outputs[o] = nullptr;
+  for (size_t o = 0; o < n_outputs; ++o) {
+    dev_outputs[o] = lp->rt->PoolAlloc(p.buffers[p.outputs[o]].size_bytes, &m);
+    if (!dev_outputs[o]) {
+      for (size_t k = 0; k < o; ++k) lp->rt->PoolFree(dev_outputs[k], p.buffers[p.outputs[k]].size_bytes);
+      SetErr(err, err_cap, m);
+      return B2_RESOURCE_EXHAUSTED;
+    }
+  }
+  const b2_status st = BindAndRun(lp, dev_inputs, dev_outputs, lp->rt->stream, true, &m);
+  if (st != B2_OK) {
+    for (size_t o = 0; o < n_outputs; ++o) {
+      lp->rt->PoolFree(dev_outputs[o], p.buffers[p.outputs[o]].size_bytes);
+      dev_outputs[o] = nullptr;
+    }
+    SetErr(err, err_cap, m);
+  }
+  return st;
+}
+
+b2_status b2_execute_host(b2_loaded *lp, const void *const *inputs, size_t n_inputs, void *const *outputs,
+                          size_t n_outputs, char *err, size_t err_cap) {
+  if (!lp) return B2_INVALID_ARGUMENT;
+  const b2::VmProgram &p = lp->prog;
+  if (n_inputs != p.inputs.size() || n_outputs != p.outputs.size()) {
+    SetErr(err, err_cap, "Execute: got " + std::to_string(n_inputs) + " args, want " + std::to_string(p.inputs.size()));
+    return B2_INVALID_ARGUMENT;
+  }
+  std::lock_guard<std::mutex> g(lp->rt->mu);
+  b2_runtime *rt = lp->rt;
+  rt->Bind();
+  std::string m;
+  std::vector<void *> din(n_inputs, nullptr), dout(n_outputs, nullptr);
+  auto cleanup = [&] {
+    for (size_t i = 0; i < n_inputs; ++i) rt->PoolFree(din[i], p.buffers[p.inputs[i]].size_bytes);
+    for (size_t o = 0; o < n_outputs; ++o) rt->PoolFree(dout[o], p.buffers[p.outputs[o]].size_bytes);
+  };
+  b2_status st = B2_OK;
+  cudaError_t e = cudaSuccess;
+  for (size_t i = 0; i < n_inputs && st == B2_OK; ++i) {
+    const size_t bytes = p.buffers[p.inputs[i]].size_bytes;
+    din[i] = rt->PoolAlloc(bytes, &m);
+    if (!din[i]) { st = B2_RESOURCE_EXHAUSTED; break; }
+    if (bytes && (e = cudaMemcpyAsync(din[i], inputs[i], bytes, cudaMemcpyHostToDevice, rt->stream)) != cudaSuccess) {
+      m = CudaMsg("Execute: input write", e);
+      st = B2_INTERNAL;
+    }
+  }
+  for (size_t o = 0; o < n_outputs && st == B2_OK; ++o) {
+    dout[o] = rt->PoolAlloc(p.buffers[p.outputs[o]].size_bytes, &m);
+    if (!dout[o]) st = B2_RESOURCE_EXHAUSTED;
+  }
+  if (st == B2_OK) st = BindAndRun(lp, din.data(), dout.data(), rt->stream, false, &m);
+  for (size_t o = 0; o < n_outputs && st == B2_OK; ++o) {
+    const size_t bytes = p.buffers[p.outputs[o]].size_bytes;
+    if (bytes && (e = cudaMemcpyAsync(outputs[o], dout[o], bytes, cudaMemcpyDeviceToHost, rt->stream)) != cudaSuccess) {
+      m = CudaMsg("Execute: output read", e);
+      st = B2_INTERNAL;
+    }
+  }
+  if (st == B2_OK) {
+    if ((e = cudaStreamSynchronize(rt->stream)) != cudaSuccess) {
+      m = CudaMsg("Execute", e);
+      cudaGetLastError();
+      st = B2_INTERNAL;
+    } else {
+      st = CheckDeviceStatus(lp, &m);
+    }
+  } else {
+    cudaStreamSynchronize(rt->stream);
+  }
+  cleanup();
+  if (st != B2_OK) SetErr(err, err_cap, m);
+  return st;
+}
+
+}  // extern "C"

@@ -1,0 +1,215 @@
+// The persistent megakernel: one CTA per scheduler lane interprets its lane's
+// entry stream - tile entries, scheduler-placed global barriers, and the
+// WHILE / IF / FOR frame stack - exactly as the reference's `vm2` does
+// (pjrt_plugin/kernels/vm_main.cl:107-258; control semantics mirrored by
+// python/pjrt_ocl/vmreader.py:655-773).
+//
+// Differences from the reference that the bytecode cannot see:
+//  - the grid barrier is one release-add plus an acquire-polled generation word
+//    (vm_common.cl:284-300 uses the same two words), every wait is bounded: when
+//    the budget runs out the lane records {code, lane, barrier index}, raises an
+//    abort flag all other waits poll, and every lane leaves the kernel normally;
+//  - consecutive lane-local elementwise entries run as one fused pass (ops_ew.cuh);
+//  - frame-stack overflow and unknown tile ops set a status instead of corrupting state.
+#include <cuda_runtime.h>
+
+#include "dev_common.cuh"
+#include "ops_ew.cuh"
+#include "ops_flash.cuh"
+#include "ops_mma.cuh"
+#include "ops_move.cuh"
+#include "ops_reduce.cuh"
+#include "ops_region.cuh"
+#include "ops_rows.cuh"
+
+namespace b2 {
+
+struct Frame { uint32_t pc, end, widx, phase; };  // phase: 0 while-cond, 1 while-body, 2 if, FOR: trips left
+constexpr uint32_t kRoot = 0xFFFFFFFFu;
+
+// Grid-wide barrier over the n_lanes co-resident CTAs. Returns false when the
+// wait was abandoned (budget exhausted here or abort raised by another lane).
+__device__ __forceinline__ bool grid_barrier(const Lane &L, uint32_t barrier_index) {
+  const KParams &P = *L.P;
+  volatile uint32_t &ok_flag = *reinterpret_cast<volatile uint32_t *>(L.smem + kSmemFlag);
+  __syncthreads();
+  if (L.tid == 0) {
+    bool ok = true;
+    DSync *s = P.sync;
+    const uint32_t gen = ld_relaxed_gpu(&s->gen);
+    __threadfence();  // release this lane's stores (made visible to thread 0 by the CTA barrier above)
+    const uint32_t prev = atom_add_acq_rel_gpu(&s->arrive, 1u);
+    if (prev == P.n_lanes - 1u) {
+      st_relaxed_gpu(&s->arrive, 0u);
+      __threadfence();
+      red_release_gpu_add(&s->gen, 1u);
+    } else {
+      const unsigned long long t0 = globaltimer_ns();
+      uint32_t spins = 0;
+      while (ld_acquire_gpu(&s->gen) == gen) {
+        if (++spins > 32u) {
+          nanosleep_ns(64);
+          if ((spins & 255u) == 0u) {
+            if (ld_relaxed_gpu(&s->abort)) { ok = false; break; }
+            if (globaltimer_ns() - t0 > P.wait_budget_ns) {
+              set_status(P, kStBarrierTimeout, L.lane, barrier_index, 0u);
+              ok = false;
+              break;
+            }
+          }
+        }
+      }
+    }
+    __threadfence();  // acquire: later plain loads of this CTA see every lane's stores
+    if (ok && ld_relaxed_gpu(&s->abort)) ok = false;
+    ok_flag = ok ? 1u : 0u;
+  }
+  __syncthreads();
+  return ok_flag != 0u;
+}
+
+template <int NT>
+__device__ __forceinline__ void exec_entry(const Lane &L, const DEntry &en) {
+  const KParams &P = *L.P;
+  const DTask &t = P.tasks[en.task];
+  switch (t.op) {
+    case kTopMma: mma_simt_tiles<NT>(L, t, en.tile_lo, en.tile_hi); break;
+    case kTopGather: case kTopDynGather: move_tiles(L, t, en.tile_lo, en.tile_hi, false); break;
+    case kTopScatter: case kTopDynScatter: move_tiles(L, t, en.tile_lo, en.tile_hi, true); break;
+    case kTopRedPart: red_part_tiles(L, t, en.tile_lo, en.tile_hi); break;
+    case kTopRedComb: red_comb_tiles(L, t, en.tile_lo, en.tile_hi); break;
+    case kTopIotaDim: iota_tiles(L, t, en.tile_lo, en.tile_hi); break;
+    case kTopRedSeg: red_seg_tiles(L, t, en.tile_lo, en.tile_hi); break;
+    case kTopSoftmaxSeg: rows_tiles(L, t, en.tile_lo, en.tile_hi, true); break;
+    case kTopLayernormSeg: rows_tiles(L, t, en.tile_lo, en.tile_hi, false); break;
+    case kTopMapRegion: region_tiles(L, t, en.tile_lo, en.tile_hi); break;
+    case kTopFlashAttn: flash_simt_tiles(L, t, en.tile_lo, en.tile_hi); break;
+    case kTopRedStrided: red_strided_tiles(L, t, en.tile_lo, en.tile_hi); break;
+    default:
+      if (L.tid == 0) set_status(P, kStBadOp, L.lane, en.task, t.op);
+      break;
+  }
+}
+
+template <int NT>
+__global__ void __launch_bounds__(NT, 1) b2_vm(const __grid_constant__ KParams P, const uint32_t smem_bytes) {
+  B2_DYN_SMEM(smem);
+  Lane L;
+  L.P = &P;
+  L.smem = smem;
+  L.smem_bytes = smem_bytes;
+  L.lane = blockIdx.x;
+  L.tid = threadIdx.x;
+  L.nthr = NT;
+  const VmLane span = P.lanes[L.lane];
+  const DEntry *stream = P.entries + span.off;
+  const unsigned long long t_start = globaltimer_ns();
+
+  Frame st[kMaxDepth + 1];
+  int sp = 0;
+  st[0].pc = 0; st[0].end = span.root_len; st[0].widx = kRoot; st[0].phase = 0;
+  uint32_t barrier_i = 0;
+  bool pub = false;   // a tile entry ran since the last barrier (vm_main.cl:82-100)
+  bool alive = true;
+
+  while (alive) {
+    Frame &f = st[sp];
+    if (f.pc >= f.end) {
+      if (f.widx == kRoot) break;
+      const DEntry w = stream[f.widx];
+      if (w.task == kEntIf) {                    // branch done: no closing barrier
+        sp--;
+        st[sp].pc++;
+        continue;
+      }
+      alive = grid_barrier(L, barrier_i++);
+      pub = false;
+      if (!alive) break;
+      if (w.task == kEntFor) {                   // one iteration done
+        if (--f.phase != 0u) { f.pc = w.tile_lo; f.end = w.tile_lo + w.tile_hi; }
+        else { sp--; st[sp].pc++; }
+      } else if (f.phase == 0u) {                // while-cond range done: read the flag
+        const uint32_t cbits = ld_relaxed_gpu(reinterpret_cast<const uint32_t *>(resolve(P, w.cond)));
+        if (cbits != 0u) { f.pc = w.a; f.end = w.a + w.b; f.phase = 1u; }
+        else { sp--; st[sp].pc++; }
+      } else {                                   // while-body done: re-run the cond range
+        f.pc = w.tile_lo; f.end = w.tile_lo + w.tile_hi; f.phase = 0u;
+      }
+      continue;
+    }
+    const uint32_t epc = f.pc;
+    const DEntry en = stream[epc];
+    if (en.task == kEntBarrier) {
+      alive = grid_barrier(L, barrier_i++);
+      pub = false;
+      f.pc++;
+      continue;
+    }
+    if (en.task == kEntWhile || en.task == kEntFor || en.task == kEntIf) {
+      uint32_t start, len, phase;
+      if (en.task == kEntWhile) {
+        start = en.tile_lo; len = en.tile_hi; phase = 0u;
+      } else if (en.task == kEntFor) {
+        if (en.a == 0u) { f.pc++; continue; }    // trip 0: skip the loop
+        start = en.tile_lo; len = en.tile_hi; phase = en.a;
+      } else {
+        const uint32_t cbits = ld_relaxed_gpu(reinterpret_cast<const uint32_t *>(resolve(P, en.cond)));
+        start = cbits ? en.tile_lo : en.a;
+        len = cbits ? en.tile_hi : en.b;
+        phase = 2u;
+        if (len == 0u) { f.pc++; continue; }
+      }
+      if (sp + 1 > kMaxDepth) {
+        if (L.tid == 0) set_status(P, kStStackOverflow, L.lane, epc, 0u);
+        break;
+      }
+      sp++;
+      st[sp].pc = start; st[sp].end = start + len; st[sp].widx = epc; st[sp].phase = phase;
+      continue;
+    }
+    if (en.task != kEntNop) {
+      // Publish the previous tile entry's stores to the whole lane: consecutive
+      // entries map elements to threads differently.
+      if (pub) { __threadfence_block(); __syncthreads(); }
+      pub = true;
+      const uint32_t chain = en.chain > 1u ? en.chain : 1u;
+      if (P.tasks[en.task].op == kTopEw) {
+        ew_entries(L, stream + epc, chain);
+        f.pc += chain;
+        continue;
+      }
+      exec_entry<NT>(L, en);
+    }
+    f.pc++;
+  }
+  if (L.lane == 0 && L.tid == 0) {
+    P.sync->barriers = barrier_i;
+    P.sync->device_ns = globaltimer_ns() - t_start;
+  }
+}
+
+// ---- host-side launch glue (called from runtime.cc) ----------------------------------
+cudaError_t LaunchVm(const KParams &params, uint32_t n_lanes, int threads, uint32_t smem_bytes,
+                     cudaStream_t stream) {
+  void *args[2] = {const_cast<KParams *>(&params), &smem_bytes};
+  const void *fn = threads == 512 ? reinterpret_cast<const void *>(&b2_vm<512>)
+                                  : reinterpret_cast<const void *>(&b2_vm<128>);
+  return cudaLaunchCooperativeKernel(fn, dim3(n_lanes), dim3(threads), args, smem_bytes, stream);
+}
+
+// Co-resident CTAs of the megakernel at `threads` per lane and `smem_bytes` of dynamic shared memory.
+cudaError_t VmResidency(int device, int threads, uint32_t smem_bytes, int *max_lanes) {
+  const void *fn = threads == 512 ? reinterpret_cast<const void *>(&b2_vm<512>)
+                                  : reinterpret_cast<const void *>(&b2_vm<128>);
+  cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_bytes));
+  if (e != cudaSuccess) return e;
+  int per_sm = 0, sms = 0;
+  e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fn, threads, smem_bytes);
+  if (e != cudaSuccess) return e;
+  e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+  if (e != cudaSuccess) return e;
+  *max_lanes = per_sm * sms;
+  return cudaSuccess;
+}
+
+}  // namespace b2
