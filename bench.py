@@ -1,0 +1,289 @@
+#!/usr/bin/env python
+"""Benchmark of the device path on the BASELINE configurations.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
+
+A step = one Execute of one loaded VMProgram (one megakernel launch) on synthetic
+inputs of the configuration's shapes and distributions (seeded; see
+pjrt-ocl_b200/programs/cases.py). `value` is measured with the arguments already
+resident in HBM (CUDA events on the launching stream); `e2e` goes through the
+host-buffer Execute call (pinned host -> device, launch, device -> host every
+step). Multi-GPU runs are weak-scaling replicas (one process per GPU, nothing on
+the data path crosses GPUs for this configuration; the scalar results are
+all-reduced once per step over NCCL).
+
+`--impl reference` times the CPU arm: the reference's device kernels are OpenCL
+C and cannot be built or run on this box, so the arm is the C restatement of the
+reference's per-phase host walk and CPU tile bodies (oracle/), on all host cores,
+on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import gzip
+import importlib
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+PROG_DIR = os.path.join(ROOT, "pjrt-ocl_b200", "programs")
+for p in (ROOT, PROG_DIR):
+    if p not in sys.path:
+        sys.path.insert(0, p)
+
+import numpy as np  # noqa: E402
+
+import inputs as gen_inputs  # noqa: E402
+
+N_C2 = 8192 * 4096
+
+# name -> program blob, CPU-arm sample blob (+ fraction of the full workload it is),
+# algorithmic bytes per step, metric
+WORKLOADS = {
+    "c2_f32": dict(
+        program="c2_chain_f32", sample="c2_chain_f32_cpu_sample", sample_frac=512 / 8192,
+        # LayerNorm r+w, GELU r+w, softmax r+w, full sum r  (f32) + gamma/beta
+        alg_bytes=7 * N_C2 * 4 + 2 * 4096 * 4, dtype="f32", metric="eltwise HBM GB/s", unit="GB/s",
+        desc="config 2: LayerNorm -> tanh-GELU -> softmax -> full sum on f32 (8192,4096)"),
+    "c2_bf16": dict(
+        program="c2_chain_bf16", sample="c2_chain_bf16_cpu_sample", sample_frac=512 / 8192,
+        alg_bytes=7 * N_C2 * 2 + 2 * 4096 * 2, dtype="bf16", metric="eltwise HBM GB/s", unit="GB/s",
+        desc="config 2 on bf16-storage copies of the same values"),
+    "c2_i32": dict(
+        program="c2_int_chain", sample="c2_int_chain_cpu_sample", sample_frac=512 / 8192,
+        alg_bytes=5 * N_C2 * 4, dtype="i32", metric="eltwise HBM GB/s", unit="GB/s",
+        desc="config 2: max((a+b)^c, d) on i32 (8192,4096), bit-exact"),
+}
+
+
+def load_blob(name: str) -> bytes:
+    with gzip.open(os.path.join(PROG_DIR, name + ".vmprog.gz"), "rb") as f:
+        return f.read()
+
+
+def manifest():
+    return json.load(open(os.path.join(PROG_DIR, "manifest.json")))
+
+
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons during the timed region."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.lines = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for nme, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(nme)
+        return {"sm_mhz": float(np.median(sm)) if sm else None,
+                "sm_max_mhz": float(max(mx)) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def cpu_arm(w: dict, steps: int, warmup: int, threads: int):
+    """Time the oracle on the bounded sample; returns (metric value, seconds/step)."""
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import vmoracle
+    man = manifest()[w["sample"]]
+    blob = load_blob(w["sample"])
+    args = gen_inputs.gen_all(man["seed"], man["items"])
+    prog = vmoracle.Program(blob)
+    for _ in range(warmup):
+        prog.execute(args, threads=threads)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        prog.execute(args, threads=threads)
+    dt = (time.perf_counter() - t0) / steps
+    return w["alg_bytes"] * w["sample_frac"] / dt / 1e9, dt
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--workload", default="c2_f32", choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-extra", action="store_true", help="skip the secondary workloads")
+    a = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    w = WORKLOADS[a.workload]
+    cores = os.cpu_count() or 1
+    base = {"metric": w["metric"], "unit": w["unit"], "n_gpus": a.gpus, "steps": a.steps,
+            "warmup": a.warmup, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": w["dtype"], "data": "synthetic",
+            "config": {"workload": a.workload, "what": w["desc"], "program": w["program"],
+                       "lanes": 148, "ew_tile": 4096, "l2": "inputs larger than L2 (>= 128 MiB per operand)"}}
+
+    if a.impl == "reference":
+        if rank != 0:
+            return
+        steps = max(1, min(a.steps, 5))
+        val, dt = cpu_arm(w, steps, min(a.warmup, 1), cores)
+        sample = f"{w['sample']}: {w['sample_frac']:.4f} of the rows, {steps} steps"
+        line = dict(base, impl="reference", value=val, steps=steps, ms_per_step=dt * 1e3 / w["sample_frac"],
+                    cpu_baseline={"value": val, "unit": w["unit"], "cores": cores, "kind": "port", "sample": sample},
+                    e2e={"value": val, "unit": w["unit"], "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                    gpu_launches=0,
+                    note="reference device kernels are OpenCL C (no OpenCL runtime on this box): "
+                         "CPU arm = C restatement of its CPU tile bodies, OpenMP over all host cores")
+        print(json.dumps(line))
+        return
+
+    import torch
+    import torch.distributed as dist
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    vm = importlib.import_module("pjrt-ocl_b200")
+    rt = vm.Runtime.Create(local_rank)
+    stream = torch.cuda.current_stream()
+
+    def run_workload(wl: dict, steps: int, warmup: int, want_e2e: bool):
+        man = manifest()[wl["program"]]
+        lp = vm.LoadedProgram.Load(rt, vm.VmProgram.Parse(load_blob(wl["program"])))
+        host_in = [np.ascontiguousarray(x) for x in gen_inputs.gen_all(man["seed"], man["items"])]
+        pin_in = []
+        for x in host_in:
+            t = torch.empty(max(x.nbytes, 1), dtype=torch.uint8, pin_memory=True)
+            t[:x.nbytes] = torch.from_numpy(x.reshape(-1).view(np.uint8))
+            pin_in.append(t)
+        dev_in = [t.cuda(non_blocking=True) for t in pin_in]
+        dev_out = [torch.empty(max(s["bytes"], 16), dtype=torch.uint8, device="cuda") for s in lp.prog.outputs]
+        pin_out = [torch.empty(max(s["bytes"], 1), dtype=torch.uint8, pin_memory=True) for s in lp.prog.outputs]
+        torch.cuda.synchronize()
+        ins = [t.data_ptr() for t in dev_in]
+        outs = [t.data_ptr() for t in dev_out]
+        scalar = dev_out[-1][:4].view(torch.float32) if wl["dtype"] != "i32" else None
+
+        def step():
+            lp.ExecuteDeviceAsync(ins, outs, stream.cuda_stream)
+            if world > 1 and scalar is not None:
+                dist.all_reduce(scalar)           # the only cross-GPU step of this configuration
+
+        for _ in range(warmup):
+            step()
+        torch.cuda.synchronize()
+        st = lp.Status()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        sampler = ClockSampler(local_rank)
+        sampler.start()
+        launches0 = lp.launch_count
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(steps):
+            step()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        clocks = sampler.stop()
+        lp.Status()
+        launches = lp.launch_count - launches0
+        e2e = None
+        if want_e2e:
+            np_in = [t.numpy()[:x.nbytes].view(x.dtype).reshape(x.shape) for t, x in zip(pin_in, host_in)]
+            np_out = [t.numpy()[:s["bytes"]] for t, s in zip(pin_out, lp.prog.outputs)]
+            for _ in range(2):
+                lp.Execute(np_in, out=np_out)
+            n_e2e = max(3, min(steps, 10))
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            for _ in range(n_e2e):
+                lp.Execute(np_in, out=np_out)
+            dt = (time.perf_counter() - t0) / n_e2e
+            e2e = {"seconds": dt, "h2d": int(sum(x.nbytes for x in host_in)),
+                   "d2h": int(sum(s["bytes"] for s in lp.prog.outputs)), "steps": n_e2e}
+        lp.close()
+        return ms / steps, launches, clocks, e2e, st
+
+    ms_step, launches, clocks, e2e, st = run_workload(w, a.steps, a.warmup, True)
+    t_max = torch.tensor([ms_step], device="cuda")
+    e2e_t = torch.tensor([e2e["seconds"]], device="cuda")
+    if world > 1:
+        dist.all_reduce(t_max, op=dist.ReduceOp.MAX)
+        dist.all_reduce(e2e_t, op=dist.ReduceOp.MAX)
+    ms_step = float(t_max.item())
+    value = w["alg_bytes"] * world / (ms_step * 1e-3) / 1e9
+    achieved = w["alg_bytes"] / (ms_step * 1e-3) / 1e9
+
+    extra = {}
+    if rank == 0 and world == 1 and not a.no_extra:
+        for name, wl in WORKLOADS.items():
+            if name == a.workload:
+                continue
+            m, _, _, _, _ = run_workload(wl, max(5, a.steps // 2), 3, False)
+            extra[name] = {"GB/s": wl["alg_bytes"] / (m * 1e-3) / 1e9, "ms_per_step": m}
+
+    if rank == 0:
+        peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+        if os.path.exists(peaks_path):
+            peak, peak_src = json.load(open(peaks_path))["hbm_gbs"], "measured (MEASURED_PEAKS.json hbm_gbs)"
+        else:
+            peak, peak_src = 6650.0, "fallback"
+        cpu = None
+        if world == 1:
+            cv, cdt = cpu_arm(w, 3, 1, cores)
+            cpu = {"value": cv, "unit": w["unit"], "cores": cores, "kind": "port",
+                   "sample": f"{w['sample']}: {w['sample_frac']:.4f} of the rows, 3 steps, {cdt:.2f} s each"}
+        line = dict(base, value=value, ms_per_step=ms_step, clocks=clocks, gpu_launches=launches,
+                    e2e={"value": w["alg_bytes"] * world / float(e2e_t.item()) / 1e9, "unit": w["unit"],
+                         "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"]},
+                    roofline={"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                              "frac": achieved / peak, "traffic": None, "peak_source": peak_src,
+                              "kernel": "b2_vm<512> (one launch per step)"},
+                    cpu_baseline=cpu, device_ns_per_step=st["device_ns"], grid_barriers=st["barriers"],
+                    other_workloads=extra)
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

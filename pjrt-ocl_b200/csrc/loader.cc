@@ -347,10 +347,26 @@ bool BuildDeviceTables(const VmProgram &p, uint64_t arena_base, DeviceTables *ou
   for (const VmLane &l : p.lane_tab) {
     uint32_t i = l.off;
     const uint32_t end = l.off + l.count;
+    // A chain must stay inside one control range: the root walk and every
+    // cond / body / branch range are contiguous in the stream, so consecutive
+    // entries can belong to different frames.
+    std::set<uint32_t> cuts;
+    cuts.insert(l.off + l.root_len);
+    for (uint32_t e = l.off; e < end; ++e) {
+      const VmEntry &en = p.entries[e];
+      if (en.task == kEntWhile || en.task == kEntIf || en.task == kEntFor) {
+        cuts.insert(l.off + en.tile_lo);
+        cuts.insert(l.off + en.tile_lo + en.tile_hi);
+        if (en.task != kEntFor) {
+          cuts.insert(l.off + en.wait_flag);
+          cuts.insert(l.off + en.wait_flag + en.wait_count);
+        }
+      }
+    }
     while (i < end) {
       if (!is_ew(p.entries[i])) { ++i; continue; }
       uint32_t j = i + 1;
-      while (j < end && j - i < static_cast<uint32_t>(8) && is_ew(p.entries[j]) &&
+      while (j < end && !cuts.count(j) && j - i < static_cast<uint32_t>(8) && is_ew(p.entries[j]) &&
              p.entries[j].tile_lo == p.entries[i].tile_lo && p.entries[j].tile_hi == p.entries[i].tile_hi &&
              p.tasks[p.entries[j].task].p1 == p.tasks[p.entries[i].task].p1)
         ++j;

@@ -276,10 +276,13 @@ class LoadedProgram:
         view._h = None  # borrowed: owned by the loaded program
         return LoadedProgram(rt, h, view)
 
-    def Execute(self, inputs) -> list:
+    def Execute(self, inputs, out=None) -> list:
         """Host arrays in, host arrays out (LoadedProgram::Execute,
-        runtime.cc:1103-1177); synchronous."""
+        runtime.cc:1103-1177); synchronous. `out` may supply the result arrays
+        (e.g. views of pinned memory) instead of fresh pageable ones."""
         p = self.prog
+        if out is not None:
+            return self._execute_into(inputs, out)
         if len(inputs) != p.n_inputs:
             raise InvalidArgument(f"Execute: got {len(inputs)} args, want {p.n_inputs}")
         keep = []
@@ -294,6 +297,20 @@ class LoadedProgram:
         err = _errbuf()
         _check(lib().b2_execute_host(self._h, ins, p.n_inputs, outs, p.n_outputs, err, _ERRCAP), err)
         return [o[:s["bytes"]].view(s["dtype"]).reshape(s["shape"]) for o, s in zip(outs_np, p.outputs)]
+
+    def _execute_into(self, inputs, out) -> list:
+        p = self.prog
+        if len(inputs) != p.n_inputs or len(out) != p.n_outputs:
+            raise InvalidArgument(f"Execute: got {len(inputs)} args / {len(out)} results, "
+                                  f"want {p.n_inputs} / {p.n_outputs}")
+        for a, spec in zip(list(inputs) + list(out), p.inputs + p.outputs):
+            if not a.flags["C_CONTIGUOUS"] or a.nbytes != spec["bytes"]:
+                raise InvalidArgument("Execute: host buffers must be contiguous and of the buffer's size")
+        ins = (ctypes.c_void_p * max(1, p.n_inputs))(*[a.ctypes.data for a in inputs])
+        outs = (ctypes.c_void_p * max(1, p.n_outputs))(*[o.ctypes.data for o in out])
+        err = _errbuf()
+        _check(lib().b2_execute_host(self._h, ins, p.n_inputs, outs, p.n_outputs, err, _ERRCAP), err)
+        return list(out)
 
     def ExecuteDevice(self, dev_inputs) -> list:
         """Device pointers in, freshly pooled device pointers out (caller owns;

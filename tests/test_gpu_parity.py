@@ -1,0 +1,125 @@
+"""Parity of the CUDA backend, through the C ABI, against (a) the golden
+fixtures produced by the reference's two validators and (b) the C oracle on the
+same seeded inputs. Integer / bool / index outputs bit-exact; f32 within rel 1e-5
+class tolerances, bf16 / f16 within rel 2e-2 (exact numbers per fixture)."""
+import numpy as np
+import pytest
+
+from conftest import Golden, check_outputs, golden_names, package
+
+import kat_programs as K
+import vmoracle
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def rt():
+    vm = package()
+    r = vm.Runtime.Create(0)
+    yield r
+    r.close()
+
+
+def _raw(arrs):
+    return [np.ascontiguousarray(a).view(np.uint8).reshape(-1) for a in arrs]
+
+
+@pytest.mark.parametrize("name", golden_names())
+def test_execute_matches_reference_validators(rt, name):
+    vm = package()
+    g = Golden(name)
+    lp = vm.LoadedProgram.Load(rt, vm.VmProgram.Parse(g.blob))
+    out = lp.Execute(g.args)
+    check_outputs(g, _raw(out), "cuda")
+    st = lp.Status()
+    assert st["code"] == 0 and lp.launch_count == 1
+    # twice in a row: the arena keeps the previous run's contents
+    out2 = lp.Execute(g.args)
+    for a, b in zip(_raw(out), _raw(out2)):
+        np.testing.assert_array_equal(a, b)
+
+
+@pytest.mark.parametrize("name", ["c2_int_chain_small", "c2_chain_f32_small", "c3_mlp_bf16_small",
+                                  "c4_nbody_small", "c5_block_bf16_small", "dynslice",
+                                  "while_loop_data_dependent"])
+def test_execute_device_matches_oracle(rt, name):
+    """ExecuteDevice (device pointers in, pooled device buffers out) against the
+    C oracle run on the same inputs."""
+    vm = package()
+    g = Golden(name)
+    lp = vm.LoadedProgram.Load(rt, vm.VmProgram.Parse(g.blob))
+    dins = []
+    for a in g.args:
+        a = np.ascontiguousarray(a)
+        p = rt.AllocDevice(max(a.nbytes, 16))
+        rt.WriteToDevice(p, a)
+        dins.append((p, max(a.nbytes, 16)))
+    douts = lp.ExecuteDevice([p for p, _ in dins])
+    got = [rt.ReadFromDevice(p, s["bytes"]) for p, s in zip(douts, lp.prog.outputs)]
+    for p, s in zip(douts, lp.prog.outputs):
+        rt.PoolFree(p, s["bytes"])
+    for p, n in dins:
+        rt.PoolFree(p, n)
+    check_outputs(g, got, "cuda-device")
+    want = vmoracle.Program(g.blob).execute(g.args)
+    for i, (a, b, e) in enumerate(zip(got, want, g.expected)):
+        if g.meta.get("exact") or e.dtype.kind in "iub":
+            np.testing.assert_array_equal(a, b, err_msg=f"{name} out {i} vs oracle")
+
+
+@pytest.mark.parametrize("name", sorted(K.ALL))
+def test_known_answer_programs(rt, name):
+    vm = package()
+    blob, args, expected = K.ALL[name]()
+    out = vm.LoadedProgram.Load(rt, vm.VmProgram.Parse(blob)).Execute(args)
+    for o, e in zip(out, expected):
+        e = np.asarray(e)
+        if name == "C_region_gelu":
+            np.testing.assert_allclose(o.reshape(e.shape), e, rtol=1e-5, atol=1e-5)
+        else:
+            np.testing.assert_array_equal(o.reshape(e.shape), e)
+
+
+@pytest.mark.parametrize("flag", [1.0, 0.0])
+def test_for_zero_trip_and_if(rt, flag):
+    vm = package()
+    blob, x, expected = K.kat_for_zero_trip_and_if()
+    out = vm.LoadedProgram.Load(rt, vm.VmProgram.Parse(blob)).Execute([x, np.float32(flag)])
+    for o, e in zip(out, expected[flag]):
+        np.testing.assert_array_equal(o.reshape(e.shape), e)
+
+
+def test_lanes_beyond_residency_are_refused_at_load(rt):
+    vm = package()
+    from blobs import Builder
+    b = Builder(min(4096, rt.lanes + 1))
+    x = b.buf(8)
+    b.outputs, b.out_dims = [x], [[8]]
+    t = b.task(0, x, x, x, 18, 8)
+    b.ent(0, t, 0, 1)
+    with pytest.raises(vm.FailedPrecondition, match="co-resident"):
+        vm.LoadedProgram.Load(rt, vm.VmProgram.Parse(b.serialize()))
+
+
+def test_bounded_barrier_wait_reports_deadline_and_context_survives(rt):
+    """A wait that nothing will ever satisfy runs out after its budget: the
+    kernel returns normally with a status, the host reports DEADLINE_EXCEEDED,
+    and the same runtime keeps working. (Lane 0's FOR body holds one more grid
+    barrier than lane 1's, so lane 0 waits for an arrival that never comes.)"""
+    vm = package()
+    from blobs import BARRIER, FOR, NOP, Builder
+    b = Builder(2)
+    x = b.buf(8)
+    b.outputs, b.out_dims = [x], [[8]]
+    t = b.task(0, x, x, x, 18, 8, 0x3F800000)
+    b.ent(0, FOR, 1, 2, 1); b.ent(0, t, 0, 1); b.ent(0, BARRIER)
+    b.ent(1, FOR, 1, 1, 1); b.ent(1, NOP); b.ent(1, NOP)
+    b.root_lens = [1, 1]
+    lp = vm.LoadedProgram.Load(rt, vm.VmProgram.Parse(b.serialize()))
+    lp.set_wait_budget_ns(50_000_000)
+    with pytest.raises(vm.DeadlineExceeded, match="grid barrier"):
+        lp.Execute([])
+    blob, args, expected = K.kat_a_two_level()
+    out = vm.LoadedProgram.Load(rt, vm.VmProgram.Parse(blob)).Execute(args)
+    np.testing.assert_array_equal(out[0], expected[0])
