@@ -140,8 +140,8 @@ def cpu_arm(w: dict, steps: int, warmup: int, threads: int):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=300)
+    ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--workload", default="c2_f32", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-extra", action="store_true", help="skip the secondary workloads")
@@ -179,7 +179,10 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     vm = importlib.import_module("pjrt-ocl_b200")
     rt = vm.Runtime.Create(local_rank)
-    stream = torch.cuda.current_stream()
+    # a non-default stream: its handle is what the C ABI launches on, and what the
+    # timing events are recorded on
+    stream = torch.cuda.Stream()
+    torch.cuda.set_stream(stream)
 
     def run_workload(wl: dict, steps: int, warmup: int, want_e2e: bool):
         man = manifest()[wl["program"]]
@@ -203,15 +206,16 @@ def main():
             if world > 1 and scalar is not None:
                 dist.all_reduce(scalar)           # the only cross-GPU step of this configuration
 
+        sampler = ClockSampler(local_rank)
+        sampler.start()                       # nvidia-smi needs a moment to start sampling
         for _ in range(warmup):
             step()
         torch.cuda.synchronize()
         st = lp.Status()
+        phases = lp.PhaseTimes()
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
-        sampler = ClockSampler(local_rank)
-        sampler.start()
         launches0 = lp.launch_count
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record(stream)
@@ -241,6 +245,7 @@ def main():
             e2e = {"seconds": dt, "h2d": int(sum(x.nbytes for x in host_in)),
                    "d2h": int(sum(s["bytes"] for s in lp.prog.outputs)), "steps": n_e2e}
         lp.close()
+        st["phase_ns"] = phases
         return ms / steps, launches, clocks, e2e, st
 
     ms_step, launches, clocks, e2e, st = run_workload(w, a.steps, a.warmup, True)
@@ -279,6 +284,7 @@ def main():
                               "frac": achieved / peak, "traffic": None, "peak_source": peak_src,
                               "kernel": "b2_vm<512> (one launch per step)"},
                     cpu_baseline=cpu, device_ns_per_step=st["device_ns"], grid_barriers=st["barriers"],
+                    phase_end_ns=st["phase_ns"],
                     other_workloads=extra)
         print(json.dumps(line))
     if world > 1:

@@ -126,6 +126,11 @@ b2_status b2_loaded_status(b2_loaded *lp, b2_exec_status *out, char *err, size_t
 uint64_t b2_loaded_launch_count(const b2_loaded *lp);
 /* Per-wait budget of device-side bounded waits, in nanoseconds (default 2e9). */
 void b2_loaded_set_wait_budget_ns(b2_loaded *lp, uint64_t ns);
+/* Lane 0's arrival time, in ns since kernel entry, at each of the first grid
+ * barriers of the last execute (what the reference prints under
+ * PJRT_OCL_PHASE_TS, runtime.cc:2196-2240). Writes at most `cap` values and
+ * returns how many were written. */
+size_t b2_loaded_phase_ns(const b2_loaded *lp, uint64_t *out, size_t cap);
 
 #ifdef __cplusplus
 }

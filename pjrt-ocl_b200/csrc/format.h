@@ -123,7 +123,12 @@ struct DSync {
   uint32_t pad;
   unsigned long long barriers;   // lane 0
   unsigned long long device_ns;  // lane 0
+  // lane 0's arrival time (ns since kernel entry) at each of its first
+  // kPhaseSlots grid barriers: per-phase wall time, as the reference's
+  // per-barrier timestamps (vm_common.cl:258-282) give it.
+  unsigned long long phase_ns[64];
 };
+constexpr uint32_t kPhaseSlots = 64;
 
 // ---- per-op descriptors the loader writes into the descriptor pool -------------
 // Descriptor the loader writes for GATHER / SCATTER / DYN_* tasks.

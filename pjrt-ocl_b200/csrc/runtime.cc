@@ -389,6 +389,12 @@ const b2_program *b2_loaded_program(const b2_loaded *lp) {
 
 uint64_t b2_loaded_launch_count(const b2_loaded *lp) { return lp->launches; }
 void b2_loaded_set_wait_budget_ns(b2_loaded *lp, uint64_t ns) { lp->wait_budget_ns = ns; }
+size_t b2_loaded_phase_ns(const b2_loaded *lp, uint64_t *out, size_t cap) {
+  if (!lp || !out) return 0;
+  size_t n = std::min<size_t>(std::min<size_t>(lp->h_sync->barriers, b2::kPhaseSlots), cap);
+  for (size_t i = 0; i < n; ++i) out[i] = lp->h_sync->phase_ns[i];
+  return n;
+}
 
 b2_status b2_loaded_status(b2_loaded *lp, b2_exec_status *out, char *err, size_t err_cap) {
   if (!lp || !out) return B2_INVALID_ARGUMENT;

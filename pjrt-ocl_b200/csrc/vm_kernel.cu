@@ -29,13 +29,14 @@ constexpr uint32_t kRoot = 0xFFFFFFFFu;
 
 // Grid-wide barrier over the n_lanes co-resident CTAs. Returns false when the
 // wait was abandoned (budget exhausted here or abort raised by another lane).
-__device__ __forceinline__ bool grid_barrier(const Lane &L, uint32_t barrier_index) {
+__device__ __forceinline__ bool grid_barrier(const Lane &L, uint32_t barrier_index, unsigned long long t_start) {
   const KParams &P = *L.P;
   volatile uint32_t &ok_flag = *reinterpret_cast<volatile uint32_t *>(L.smem + kSmemFlag);
   __syncthreads();
   if (L.tid == 0) {
     bool ok = true;
     DSync *s = P.sync;
+    if (L.lane == 0 && barrier_index < kPhaseSlots) s->phase_ns[barrier_index] = globaltimer_ns() - t_start;
     const uint32_t gen = ld_relaxed_gpu(&s->gen);
     __threadfence();  // release this lane's stores (made visible to thread 0 by the CTA barrier above)
     const uint32_t prev = atom_add_acq_rel_gpu(&s->arrive, 1u);
@@ -122,7 +123,7 @@ __global__ void __launch_bounds__(NT, 1) b2_vm(const __grid_constant__ KParams P
         st[sp].pc++;
         continue;
       }
-      alive = grid_barrier(L, barrier_i++);
+      alive = grid_barrier(L, barrier_i++, t_start);
       pub = false;
       if (!alive) break;
       if (w.task == kEntFor) {                   // one iteration done
@@ -140,7 +141,7 @@ __global__ void __launch_bounds__(NT, 1) b2_vm(const __grid_constant__ KParams P
     const uint32_t epc = f.pc;
     const DEntry en = stream[epc];
     if (en.task == kEntBarrier) {
-      alive = grid_barrier(L, barrier_i++);
+      alive = grid_barrier(L, barrier_i++, t_start);
       pub = false;
       f.pc++;
       continue;

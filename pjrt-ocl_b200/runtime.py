@@ -96,6 +96,7 @@ EXPORTS = [
     "b2_program_io_rank", "b2_program_io_dim", "b2_program_load", "b2_loaded_destroy",
     "b2_loaded_program", "b2_execute_host", "b2_execute_device", "b2_execute_device_async",
     "b2_loaded_status", "b2_loaded_launch_count", "b2_loaded_set_wait_budget_ns",
+    "b2_loaded_phase_ns",
 ]
 
 
@@ -139,6 +140,7 @@ def lib():
         "b2_loaded_status": (ctypes.c_int, [vp, ctypes.POINTER(_ExecStatus), cp, sz]),
         "b2_loaded_launch_count": (ctypes.c_uint64, [vp]),
         "b2_loaded_set_wait_budget_ns": (None, [vp, ctypes.c_uint64]),
+        "b2_loaded_phase_ns": (sz, [vp, ctypes.POINTER(ctypes.c_uint64), sz]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(L, name)
@@ -338,6 +340,13 @@ class LoadedProgram:
         _check(lib().b2_loaded_status(self._h, ctypes.byref(st), err, _ERRCAP), err)
         return {"code": st.code, "lane": st.lane, "where": st.where, "detail": st.detail,
                 "barriers": st.barriers, "device_ns": st.device_ns}
+
+    def PhaseTimes(self) -> list:
+        """ns since kernel entry at which lane 0 reached each grid barrier of the
+        last execute (first 64 barriers)."""
+        buf = (ctypes.c_uint64 * 64)()
+        n = lib().b2_loaded_phase_ns(self._h, buf, 64)
+        return [int(buf[i]) for i in range(n)]
 
     @property
     def launch_count(self) -> int:

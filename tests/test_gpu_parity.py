@@ -113,8 +113,10 @@ def test_bounded_barrier_wait_reports_deadline_and_context_survives(rt):
     x = b.buf(8)
     b.outputs, b.out_dims = [x], [[8]]
     t = b.task(0, x, x, x, 18, 8, 0x3F800000)
+    # both streams hold one BARRIER entry (the parser wants equal counts), but
+    # lane 1's lies outside its FOR body and outside the root walk: never reached.
     b.ent(0, FOR, 1, 2, 1); b.ent(0, t, 0, 1); b.ent(0, BARRIER)
-    b.ent(1, FOR, 1, 1, 1); b.ent(1, NOP); b.ent(1, NOP)
+    b.ent(1, FOR, 1, 1, 1); b.ent(1, NOP); b.ent(1, BARRIER)
     b.root_lens = [1, 1]
     lp = vm.LoadedProgram.Load(rt, vm.VmProgram.Parse(b.serialize()))
     lp.set_wait_budget_ns(50_000_000)
