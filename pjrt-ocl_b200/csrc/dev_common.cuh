@@ -138,14 +138,17 @@ __device__ __forceinline__ int64_t view_index(const DView &v, uint32_t i) {
   int64_t idx = v.off;
   uint32_t rem = i;
 #pragma unroll
-  for (int k = kViewDims - 1; k >= 0; --k) {
+  for (int k = kViewDims - 1; k >= 1; --k) {
     if (k < v.rank) {
       const uint32_t d = v.dim[k];
-      const uint32_t q = rem / d;
+      const uint32_t mh = __umulhi(rem, v.magic[k]);
+      const uint32_t q = (((rem - mh) >> 1) + mh) >> v.shift[k];
       idx += static_cast<int64_t>(rem - q * d) * v.stride[k];
       rem = q;
     }
   }
+  // i < prod(dim): what is left is the outermost coordinate itself
+  if (v.rank > 0) idx += static_cast<int64_t>(rem) * v.stride[0];
   return idx;
 }
 // Uncollapsed aux-pool descriptor {rank, dims[rank], strides[rank], src_off}

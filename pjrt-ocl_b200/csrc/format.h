@@ -80,6 +80,10 @@ struct DView {
   int64_t off;
   uint32_t dim[6];
   int32_t stride[6];
+  // n / dim[k] without a divide instruction, for every 32-bit n (dim >= 2):
+  // q = umulhi(n, magic); ((n - q) >> 1) + q >> shift.
+  uint32_t magic[6];
+  uint32_t shift[6];
 };
 constexpr int kViewDims = 6;
 

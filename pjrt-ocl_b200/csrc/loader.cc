@@ -123,6 +123,22 @@ bool CollapseView(const int32_t *dims, const int32_t *strides, int rank, int64_t
     if (d[k] > 0xFFFFFFFFll) return false;
     out->dim[k] = static_cast<uint32_t>(d[k]);
     out->stride[k] = static_cast<int32_t>(s[k]);
+    // branch-free magic-number division by dim[k] (>= 2 here: size-1 axes were dropped)
+    const uint32_t dv = out->dim[k];
+    uint32_t sh = 31;
+    while (!(dv >> sh)) --sh;                       // floor(log2(dv))
+    if ((dv & (dv - 1)) == 0) {
+      out->magic[k] = 0;
+      out->shift[k] = sh - 1;
+    } else {
+      const unsigned __int128 two = static_cast<unsigned __int128>(1) << (32 + sh);
+      uint64_t m = static_cast<uint64_t>(two / dv);
+      const uint64_t rem = static_cast<uint64_t>(two - static_cast<unsigned __int128>(m) * dv);
+      m *= 2;
+      if (rem * 2 >= dv) m += 1;
+      out->magic[k] = static_cast<uint32_t>(m + 1);
+      out->shift[k] = sh;
+    }
   }
   if (out->rank == 0) {
     out->vec_ok = 1;

@@ -41,9 +41,15 @@ __device__ __forceinline__ bool ew_is_un(uint32_t s) {
 // numpy maximum/minimum: NaN if either operand is NaN
 __device__ __forceinline__ float np_max(float x, float y) { return (x != x || y != y) ? __int_as_float(0x7fc00000) : fmaxf(x, y); }
 __device__ __forceinline__ float np_min(float x, float y) { return (x != x || y != y) ? __int_as_float(0x7fc00000) : fminf(x, y); }
+// tanh-approximation GELU, 0.5 x (1 + tanh(u)) with u = 0.7978845608 (x + 0.044715 x^3),
+// evaluated in the algebraically identical form x / (1 + exp(-2u)): one exp and one
+// reciprocal instead of a full-accuracy tanh; absolute error is ~1e-7 |x|, far
+// inside the f32 tolerance of the path.
 __device__ __forceinline__ float gelu_tanh(float x) {
-  const float inner = __fmul_rn(0.7978845608f, __fadd_rn(x, __fmul_rn(__fmul_rn(__fmul_rn(0.044715f, x), x), x)));
-  return __fmul_rn(__fmul_rn(0.5f, x), __fadd_rn(1.0f, tanhf(inner)));
+  const float x2 = x * x;
+  const float t = fmaf(0.044715f * x2, x, x);
+  const float e = expf(-1.5957691216f * t);
+  return __fdividef(x, 1.0f + e);
 }
 // a*s + t with two roundings, as the validator computes it (no contraction)
 __device__ __forceinline__ float affine2(float a, float s, float t) { return __fadd_rn(__fmul_rn(a, s), t); }
@@ -199,6 +205,20 @@ __device__ __forceinline__ void ew_load_operand(const uint8_t *p, uint32_t dt, b
   for (uint32_t e = 0; e < 4; ++e) out[e] = e < vc ? load1(p, dt, view_index(v, i + e)) : 0u;
 }
 
+// A complete group of a 4-byte operand through a vector-friendly view.
+__device__ __forceinline__ void load_view_w4(const uint8_t *p, const DView &v, uint32_t i, uint32_t out[4]) {
+  const int64_t idx = view_index(v, i);
+  const uint32_t *q = reinterpret_cast<const uint32_t *>(p) + idx;
+  if (v.inner_stride == 0) {
+    out[0] = out[1] = out[2] = out[3] = q[0];
+  } else if (v.aligned4) {
+    const uint4 w = *reinterpret_cast<const uint4 *>(q);
+    out[0] = w.x; out[1] = w.y; out[2] = w.z; out[3] = w.w;
+  } else {
+    out[0] = q[0]; out[1] = q[1]; out[2] = q[2]; out[3] = q[3];
+  }
+}
+
 constexpr int kEwU = 4;  // groups in flight per thread
 
 // One pass of a chain of k ops over elements [lo, hi); lo % 4 == 0, all pointers
@@ -216,6 +236,32 @@ __device__ __noinline__ void ew_chain_run(const Lane &L, const EwOp *ops, uint32
 #pragma unroll
       for (int e = 0; e < 4; ++e) X[u][e] = 0u;
     }
+    const bool full = vc[kEwU - 1] == 4u;   // groups ascend: the last one complete => all complete
+    // The ops of a chain run one after the other, so their loads cannot overlap
+    // each other; instead every contiguous operand of the NEXT trip is pulled
+    // into L2 now, which takes no registers and orders nothing.
+    {
+      const uint32_t gn = g0 + L.nthr * kEwU;
+      if (gn < ngroups) {
+        for (uint32_t j = 0; j < k; ++j) {
+          const EwOp &o = ops[j];
+          const uint32_t esz = dt_size(o.adt);
+          const bool na = !(o.sub == kFill || o.sub == kIotaFlat) && !(o.flags & (kFwdA | kViewA));
+          const bool nb = !(o.flags & (kFwdB | kViewB)) &&
+                          (ew_is_bin(o.sub) || o.sub == kCmp || o.sub == kSelect ||
+                           (o.sub >= kAnd && o.sub <= kXor) || (o.sub >= kShl && o.sub <= kShrA));
+#pragma unroll
+          for (int u = 0; u < kEwU; ++u) {
+            const uint32_t g = gn + u * L.nthr;
+            if (g < ngroups) {
+              const size_t off = static_cast<size_t>(lo + (g << 2)) * esz;
+              if (na) prefetch_l2(o.a + off);
+              if (nb) prefetch_l2(o.b + off);
+            }
+          }
+        }
+      }
+    }
     for (uint32_t j = 0; j < k; ++j) {
       const EwOp &o = ops[j];
       const uint32_t sub = o.sub, dt = o.dt, adt = o.adt, fl = o.flags;
@@ -229,15 +275,53 @@ __device__ __noinline__ void ew_chain_run(const Lane &L, const EwOp *ops, uint32
 #pragma unroll
           for (int e = 0; e < 4; ++e) Y[u][e] = X[u][e];
       }
+      // Operand loads. The dtype / view / ragged-edge decisions are hoisted out of
+      // the unrolled groups: the common cases are four unconditional 16-byte (or
+      // 8-byte) loads back to back.
+      const bool w4 = adt == kF32 || adt == kI32 || adt == kU32;
       if (needs_a && !(fl & kFwdA)) {
+        if (full && !(fl & kViewA) && w4) {
 #pragma unroll
-        for (int u = 0; u < kEwU; ++u)
-          if (vc[u]) ew_load_operand(o.a, adt, fl & kViewA, o.va, base[u], vc[u], X[u]);
+          for (int u = 0; u < kEwU; ++u) {
+            const uint4 w = *reinterpret_cast<const uint4 *>(o.a + static_cast<size_t>(base[u]) * 4);
+            X[u][0] = w.x; X[u][1] = w.y; X[u][2] = w.z; X[u][3] = w.w;
+          }
+        } else if (full && !(fl & kViewA) && adt == kBF16) {
+#pragma unroll
+          for (int u = 0; u < kEwU; ++u) {
+            const uint2 w = *reinterpret_cast<const uint2 *>(o.a + static_cast<size_t>(base[u]) * 2);
+            X[u][0] = w.x << 16; X[u][1] = w.x & 0xffff0000u; X[u][2] = w.y << 16; X[u][3] = w.y & 0xffff0000u;
+          }
+        } else if (full && (fl & kViewA) && w4 && o.va.vec_ok) {
+#pragma unroll
+          for (int u = 0; u < kEwU; ++u) load_view_w4(o.a, o.va, base[u], X[u]);
+        } else {
+#pragma unroll
+          for (int u = 0; u < kEwU; ++u)
+            if (vc[u]) ew_load_operand(o.a, adt, fl & kViewA, o.va, base[u], vc[u], X[u]);
+        }
       }
       if (needs_b && !(fl & kFwdB)) {
+        if (full && !(fl & kViewB) && w4) {
 #pragma unroll
-        for (int u = 0; u < kEwU; ++u)
-          if (vc[u]) ew_load_operand(o.b, adt, fl & kViewB, o.vb, base[u], vc[u], Y[u]);
+          for (int u = 0; u < kEwU; ++u) {
+            const uint4 w = *reinterpret_cast<const uint4 *>(o.b + static_cast<size_t>(base[u]) * 4);
+            Y[u][0] = w.x; Y[u][1] = w.y; Y[u][2] = w.z; Y[u][3] = w.w;
+          }
+        } else if (full && !(fl & kViewB) && adt == kBF16) {
+#pragma unroll
+          for (int u = 0; u < kEwU; ++u) {
+            const uint2 w = *reinterpret_cast<const uint2 *>(o.b + static_cast<size_t>(base[u]) * 2);
+            Y[u][0] = w.x << 16; Y[u][1] = w.x & 0xffff0000u; Y[u][2] = w.y << 16; Y[u][3] = w.y & 0xffff0000u;
+          }
+        } else if (full && (fl & kViewB) && w4 && o.vb.vec_ok) {
+#pragma unroll
+          for (int u = 0; u < kEwU; ++u) load_view_w4(o.b, o.vb, base[u], Y[u]);
+        } else {
+#pragma unroll
+          for (int u = 0; u < kEwU; ++u)
+            if (vc[u]) ew_load_operand(o.b, adt, fl & kViewB, o.vb, base[u], vc[u], Y[u]);
+        }
       }
       // ---- compute (result into X) ----
       if (sub == kSelect) {
@@ -374,10 +458,37 @@ __device__ __noinline__ void ew_chain_run(const Lane &L, const EwOp *ops, uint32
 #pragma unroll
             for (int e = 0; e < 4; ++e) X[u][e] = base[u] + e;
         } else {
+          // one switch, the 16 evaluations inside each case (as for floats)
+#define B2_EW_I(S, EXPR)                                                        \
+  case S:                                                                       \
+    _Pragma("unroll") for (int u = 0; u < kEwU; ++u)                            \
+    _Pragma("unroll") for (int e = 0; e < 4; ++e) {                             \
+      const uint32_t x = X[u][e], y = Y[u][e];                                  \
+      (void)y;                                                                  \
+      X[u][e] = (EXPR);                                                         \
+    }                                                                           \
+    break;
+          switch (sub) {
+            B2_EW_I(kAdd, x + y)
+            B2_EW_I(kMul, x * y)
+            B2_EW_I(kSubt, x - y)
+            B2_EW_I(kAnd, x & y)
+            B2_EW_I(kOr, x | y)
+            B2_EW_I(kXor, x ^ y)
+            B2_EW_I(kNot, ~x)
+            B2_EW_I(kNeg, 0u - x)
+            B2_EW_I(kShl, x << (y & 31u))
+            B2_EW_I(kShrL, x >> (y & 31u))
+            B2_EW_I(kMax, uns ? max(x, y) : static_cast<uint32_t>(max(static_cast<int32_t>(x), static_cast<int32_t>(y))))
+            B2_EW_I(kMin, uns ? min(x, y) : static_cast<uint32_t>(min(static_cast<int32_t>(x), static_cast<int32_t>(y))))
+            default:
 #pragma unroll
-          for (int u = 0; u < kEwU; ++u)
+              for (int u = 0; u < kEwU; ++u)
 #pragma unroll
-            for (int e = 0; e < 4; ++e) X[u][e] = alu_i32(sub, X[u][e], Y[u][e], uns);
+                for (int e = 0; e < 4; ++e) X[u][e] = alu_i32(sub, X[u][e], Y[u][e], uns);
+              break;
+          }
+#undef B2_EW_I
         }
       }
       if (dt == kBF16 || dt == kF16) {  // what the next chain op sees is the value as stored
@@ -390,13 +501,28 @@ __device__ __noinline__ void ew_chain_run(const Lane &L, const EwOp *ops, uint32
       if (!(fl & kDeadStore)) {
         if (sub == kLts) {
           if (lo == 0u && g0 == 0u) store1(o.dst, dt, 0, X[0][0]);
+        } else if (full && (dt == kF32 || dt == kI32 || dt == kU32)) {
+#pragma unroll
+          for (int u = 0; u < kEwU; ++u)
+            *reinterpret_cast<uint4 *>(o.dst + static_cast<size_t>(base[u]) * 4) =
+                make_uint4(X[u][0], X[u][1], X[u][2], X[u][3]);
+        } else if (full && dt == kBF16) {
+#pragma unroll
+          for (int u = 0; u < kEwU; ++u) {   // X already holds bf16-representable values
+            uint2 w;
+            w.x = (X[u][0] >> 16) | (X[u][1] & 0xffff0000u);
+            w.y = (X[u][2] >> 16) | (X[u][3] & 0xffff0000u);
+            *reinterpret_cast<uint2 *>(o.dst + static_cast<size_t>(base[u]) * 2) = w;
+          }
         } else {
 #pragma unroll
           for (int u = 0; u < kEwU; ++u) {
             if (vc[u] == 4u) {
               store4(o.dst, dt, base[u], X[u]);
             } else {
-              for (uint32_t e = 0; e < vc[u]; ++e) store1(o.dst, dt, static_cast<int64_t>(base[u]) + e, X[u][e]);
+#pragma unroll
+              for (uint32_t e = 0; e < 4; ++e)   // static indices: X stays in registers
+                if (e < vc[u]) store1(o.dst, dt, static_cast<int64_t>(base[u]) + e, X[u][e]);
             }
           }
         }

@@ -140,6 +140,62 @@ __device__ __forceinline__ Acc acc_block_reduce(const Lane &L, uint32_t kind, ui
   return acc_warp_reduce(kind, dt, r);
 }
 
+// Combine functors over the 32-bit register representation.
+struct RFSum { static __device__ __forceinline__ uint32_t f(uint32_t a, uint32_t b) { return __float_as_uint(__uint_as_float(a) + __uint_as_float(b)); } };
+struct RFProd { static __device__ __forceinline__ uint32_t f(uint32_t a, uint32_t b) { return __float_as_uint(__uint_as_float(a) * __uint_as_float(b)); } };
+struct RFMax { static __device__ __forceinline__ uint32_t f(uint32_t a, uint32_t b) { return __float_as_uint(np_max(__uint_as_float(a), __uint_as_float(b))); } };
+struct RFMin { static __device__ __forceinline__ uint32_t f(uint32_t a, uint32_t b) { return __float_as_uint(np_min(__uint_as_float(a), __uint_as_float(b))); } };
+struct RISum { static __device__ __forceinline__ uint32_t f(uint32_t a, uint32_t b) { return a + b; } };
+struct RIProd { static __device__ __forceinline__ uint32_t f(uint32_t a, uint32_t b) { return a * b; } };
+struct RIAnd { static __device__ __forceinline__ uint32_t f(uint32_t a, uint32_t b) { return a & b; } };
+struct RIOr { static __device__ __forceinline__ uint32_t f(uint32_t a, uint32_t b) { return a | b; } };
+struct RIXor { static __device__ __forceinline__ uint32_t f(uint32_t a, uint32_t b) { return a ^ b; } };
+struct RIMaxS { static __device__ __forceinline__ uint32_t f(uint32_t a, uint32_t b) { return static_cast<uint32_t>(max(static_cast<int32_t>(a), static_cast<int32_t>(b))); } };
+struct RIMinS { static __device__ __forceinline__ uint32_t f(uint32_t a, uint32_t b) { return static_cast<uint32_t>(min(static_cast<int32_t>(a), static_cast<int32_t>(b))); } };
+struct RIMaxU { static __device__ __forceinline__ uint32_t f(uint32_t a, uint32_t b) { return max(a, b); } };
+struct RIMinU { static __device__ __forceinline__ uint32_t f(uint32_t a, uint32_t b) { return min(a, b); } };
+
+// Groups of 4 elements [g_lo, g_hi), strided over `nthreads`; DOT multiplies by
+// the shared vector at element (4g - dbase) first (GEMV mode).
+template <typename C, bool DOT>
+__device__ __forceinline__ uint32_t reduce_vec32(const uint8_t *p, uint32_t dt, int64_t g_lo, int64_t g_hi,
+                                                 uint32_t rank, uint32_t nthreads, uint32_t ident,
+                                                 const uint8_t *dotvec, int64_t dbase) {
+  constexpr int U = 4;
+  uint32_t acc[U];
+#pragma unroll
+  for (int u = 0; u < U; ++u) acc[u] = ident;
+  int64_t g = g_lo + rank;
+  const int64_t step = nthreads;
+  for (; g + (U - 1) * step < g_hi; g += U * step) {
+    uint32_t v[U][4], w[U][4];
+#pragma unroll
+    for (int u = 0; u < U; ++u) load4(p, dt, (g + u * step) << 2, v[u]);
+    if (DOT) {
+#pragma unroll
+      for (int u = 0; u < U; ++u) load4(dotvec, dt, ((g + u * step) << 2) - dbase, w[u]);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const uint32_t x = DOT ? __float_as_uint(__uint_as_float(v[u][e]) * __uint_as_float(w[u][e])) : v[u][e];
+        acc[u] = C::f(acc[u], x);
+      }
+  }
+  for (; g < g_hi; g += step) {
+    uint32_t v[4], w[4];
+    load4(p, dt, g << 2, v);
+    if (DOT) load4(dotvec, dt, (g << 2) - dbase, w);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const uint32_t x = DOT ? __float_as_uint(__uint_as_float(v[e]) * __uint_as_float(w[e])) : v[e];
+      acc[0] = C::f(acc[0], x);
+    }
+  }
+  return C::f(C::f(acc[0], acc[1]), C::f(acc[2], acc[3]));
+}
+
 // Reduce elements [lo, hi) of `p`, strided over `nthreads` cooperating threads
 // (this thread is `rank`); 16-byte loads when the run is 4-aligned f32-class.
 __device__ __forceinline__ Acc reduce_run(const uint8_t *p, uint32_t dt, uint32_t kind, int64_t lo, int64_t hi,
@@ -150,22 +206,27 @@ __device__ __forceinline__ Acc reduce_run(const uint8_t *p, uint32_t dt, uint32_
                    (!dotvec || ((dot_off % 4 == 0) && reinterpret_cast<uintptr_t>(dotvec) % 16 == 0));
   if (vec) {
     const int64_t g_lo = lo >> 2, g_hi = hi >> 2;
-    for (int64_t g = g_lo + rank; g < g_hi; g += nthreads) {
-      uint32_t v[4];
-      load4(p, dt, g << 2, v);
-      if (dotvec) {
-        uint32_t w[4];
-        load4(dotvec, dt, (g << 2) - lo + dot_off, w);
-#pragma unroll
-        for (int e = 0; e < 4; ++e) v[e] = __float_as_uint(__uint_as_float(v[e]) * __uint_as_float(w[e]));
-      }
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        Acc x;
-        x.bits = v[e];
-        acc = acc_combine(kind, dt, acc, x);
-      }
-    }
+    // The streaming part runs in a loop specialised on the combine (no per-element
+    // dispatch) with four 16-byte loads in flight per thread.
+    const int64_t dbase = lo - dot_off;
+    uint32_t r;
+    const bool fl = is_float_dt(dt);
+    const uint32_t ident = static_cast<uint32_t>(acc.bits);
+    if (fl && dotvec) r = reduce_vec32<RFSum, true>(p, dt, g_lo, g_hi, rank, nthreads, ident, dotvec, dbase);
+    else if (fl && kind == kSum) r = reduce_vec32<RFSum, false>(p, dt, g_lo, g_hi, rank, nthreads, ident, nullptr, 0);
+    else if (fl && kind == kRMax) r = reduce_vec32<RFMax, false>(p, dt, g_lo, g_hi, rank, nthreads, ident, nullptr, 0);
+    else if (fl && kind == kRMin) r = reduce_vec32<RFMin, false>(p, dt, g_lo, g_hi, rank, nthreads, ident, nullptr, 0);
+    else if (fl) r = reduce_vec32<RFProd, false>(p, dt, g_lo, g_hi, rank, nthreads, ident, nullptr, 0);
+    else if (kind == kSum) r = reduce_vec32<RISum, false>(p, dt, g_lo, g_hi, rank, nthreads, ident, nullptr, 0);
+    else if (kind == kProd) r = reduce_vec32<RIProd, false>(p, dt, g_lo, g_hi, rank, nthreads, ident, nullptr, 0);
+    else if (kind == kRAnd) r = reduce_vec32<RIAnd, false>(p, dt, g_lo, g_hi, rank, nthreads, ident, nullptr, 0);
+    else if (kind == kROr) r = reduce_vec32<RIOr, false>(p, dt, g_lo, g_hi, rank, nthreads, ident, nullptr, 0);
+    else if (kind == kRXor) r = reduce_vec32<RIXor, false>(p, dt, g_lo, g_hi, rank, nthreads, ident, nullptr, 0);
+    else if (kind == kRMax && dt == kI32) r = reduce_vec32<RIMaxS, false>(p, dt, g_lo, g_hi, rank, nthreads, ident, nullptr, 0);
+    else if (kind == kRMax) r = reduce_vec32<RIMaxU, false>(p, dt, g_lo, g_hi, rank, nthreads, ident, nullptr, 0);
+    else if (dt == kI32) r = reduce_vec32<RIMinS, false>(p, dt, g_lo, g_hi, rank, nthreads, ident, nullptr, 0);
+    else r = reduce_vec32<RIMinU, false>(p, dt, g_lo, g_hi, rank, nthreads, ident, nullptr, 0);
+    acc.bits = r;
     for (int64_t i = (g_hi << 2) + rank; i < hi; i += nthreads) {
       Acc x = acc_load(p, dt, i);
       if (dotvec) x.bits = __float_as_uint(__uint_as_float(static_cast<uint32_t>(x.bits)) * loadf(dotvec, dt, i - lo + dot_off));

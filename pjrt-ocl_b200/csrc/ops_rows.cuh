@@ -104,19 +104,32 @@ __device__ __forceinline__ void rows_staged(const Lane &L, const DTask &t, uint3
         for (int e = 0; e < 4; ++e) m = np_max(m, __uint_as_float(v[e]));
       }
       m = group_reduce(m, [](float a, float c) { return np_max(a, c); }, slot, bid, gl);
+      // f32 rows keep exp(x - max) in the staged row (each thread revisits exactly
+      // the groups it wrote), so the exponential is evaluated once per element.
+      const bool keep = adt == kF32;
+      float *roww = reinterpret_cast<float *>(const_cast<uint8_t *>(rowp));
       float s = 0.0f;
       for (uint32_t g = gl; g < ng; g += kRowGroupThreads) {
         uint32_t v[4];
         load4(rowp, adt, g << 2, v);
+        float ex[4];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) s += expf(__uint_as_float(v[e]) - m);
+        for (int e = 0; e < 4; ++e) {
+          ex[e] = expf(__uint_as_float(v[e]) - m);
+          s += ex[e];
+        }
+        if (keep) *reinterpret_cast<float4 *>(roww + (g << 2)) = make_float4(ex[0], ex[1], ex[2], ex[3]);
       }
       s = group_reduce(s, [](float a, float c) { return a + c; }, slot, bid, gl);
+      const float rs = __fdiv_rn(1.0f, s);
       for (uint32_t g = gl; g < ng; g += kRowGroupThreads) {
         uint32_t v[4];
         load4(rowp, adt, g << 2, v);
 #pragma unroll
-        for (int e = 0; e < 4; ++e) v[e] = __float_as_uint(__fdiv_rn(expf(__uint_as_float(v[e]) - m), s));
+        for (int e = 0; e < 4; ++e) {
+          const float ev = keep ? __uint_as_float(v[e]) : expf(__uint_as_float(v[e]) - m);
+          v[e] = __float_as_uint(ev * rs);
+        }
         store4(outp, dt, g << 2, v);
       }
     } else {
@@ -136,12 +149,12 @@ __device__ __forceinline__ void rows_staged(const Lane &L, const DTask &t, uint3
       const float inv_n = 1.0f / static_cast<float>(seg);
       const float mu = s * inv_n;
       const float var = __fsub_rn(s2 * inv_n, __fmul_rn(mu, mu));
-      const float den = __fsqrt_rn(__fadd_rn(var, eps));
+      const float rden = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(var, eps)));
       for (uint32_t g = gl; g < ng; g += kRowGroupThreads) {
         uint32_t v[4];
         load4(rowp, adt, g << 2, v);
 #pragma unroll
-        for (int e = 0; e < 4; ++e) v[e] = __float_as_uint(__fdiv_rn(__fsub_rn(__uint_as_float(v[e]), mu), den));
+        for (int e = 0; e < 4; ++e) v[e] = __float_as_uint((__uint_as_float(v[e]) - mu) * rden);
         store4(outp, dt, g << 2, v);
       }
     }

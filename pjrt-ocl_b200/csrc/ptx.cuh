@@ -43,6 +43,8 @@ __device__ __forceinline__ void red_release_gpu_add(uint32_t *p, uint32_t v) {
 }
 __device__ __forceinline__ void fence_acq_rel_gpu() { asm volatile("fence.acq_rel.gpu;" ::: "memory"); }
 __device__ __forceinline__ void nanosleep_ns(uint32_t ns) { asm volatile("nanosleep.u32 %0;" ::"r"(ns)); }
+// Pull the line holding `p` into L2 ahead of use (no register, no dependency).
+__device__ __forceinline__ void prefetch_l2(const void *p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
 
 // Named barrier over `count` threads (count a multiple of 32); id 1..15 (0 is __syncthreads).
 __device__ __forceinline__ void bar_sync(int id, int count) {
