@@ -60,6 +60,17 @@ WORKLOADS = {
 }
 
 
+# the stages of config 2 on their own: one tile-op family per program
+for _stage, _bytes, _what in (
+        ("layernorm", 2 * N_C2 * 4, "LAYERNORM_SEG rows of 4096 (TMA-staged)"),
+        ("affine_gelu", 2 * N_C2 * 4 + 2 * 4096 * 4, "fused chain mul(gamma view), add(beta view), GELU"),
+        ("softmax", 2 * N_C2 * 4, "SOFTMAX_SEG rows of 4096 (TMA-staged)"),
+        ("sum", N_C2 * 4, "full sum: RED_PART + RED_COMB")):
+    WORKLOADS[f"c2_stage_{_stage}"] = dict(
+        program=f"c2_stage_{_stage}_f32", sample=None, sample_frac=0.0, alg_bytes=_bytes, dtype="f32",
+        metric="eltwise HBM GB/s", unit="GB/s", desc=f"config 2 stage: {_what}", secondary=True)
+
+
 def load_blob(name: str) -> bytes:
     with gzip.open(os.path.join(PROG_DIR, name + ".vmprog.gz"), "rb") as f:
         return f.read()
@@ -273,7 +284,7 @@ def main():
         else:
             peak, peak_src = 6650.0, "fallback"
         cpu = None
-        if world == 1:
+        if world == 1 and w["sample"]:
             cv, cdt = cpu_arm(w, 3, 1, cores)
             cpu = {"value": cv, "unit": w["unit"], "cores": cores, "kind": "port",
                    "sample": f"{w['sample']}: {w['sample_frac']:.4f} of the rows, 3 steps, {cdt:.2f} s each"}

@@ -116,8 +116,8 @@ b2_status b2_execute_device(b2_loaded *lp, void *const *dev_inputs, size_t n_inp
 /* Same, but the results are written into caller-provided device buffers and the
  * launch is enqueued on `cuda_stream` (a cudaStream_t; NULL = the runtime's own
  * stream) WITHOUT waiting for it: the asynchronous form a CUDA-stream-aware
- * caller uses to overlap copies, collectives and execution. The device status
- * of this launch is read by b2_loaded_status after the stream is synchronised. */
+ * caller uses to overlap copies, collectives and execution. b2_loaded_status
+ * waits for that stream and reports the device status of the last launch. */
 b2_status b2_execute_device_async(b2_loaded *lp, void *const *dev_inputs, size_t n_inputs,
                                   void *const *dev_outputs, size_t n_outputs,
                                   void *cuda_stream, char *err, size_t err_cap);

@@ -137,15 +137,15 @@ __device__ __forceinline__ void store4(uint8_t *p, uint32_t dt, int64_t i, const
 __device__ __forceinline__ int64_t view_index(const DView &v, uint32_t i) {
   int64_t idx = v.off;
   uint32_t rem = i;
-#pragma unroll
-  for (int k = kViewDims - 1; k >= 1; --k) {
-    if (k < v.rank) {
-      const uint32_t d = v.dim[k];
-      const uint32_t mh = __umulhi(rem, v.magic[k]);
-      const uint32_t q = (((rem - mh) >> 1) + mh) >> v.shift[k];
-      idx += static_cast<int64_t>(rem - q * d) * v.stride[k];
-      rem = q;
-    }
+  // trip count = rank - 1 (1 for the common row / column broadcasts): a real loop,
+  // not a predicated unroll over all kViewDims
+#pragma unroll 1
+  for (int k = v.rank - 1; k >= 1; --k) {
+    const uint32_t d = v.dim[k];
+    const uint32_t mh = __umulhi(rem, v.magic[k]);
+    const uint32_t q = (((rem - mh) >> 1) + mh) >> v.shift[k];
+    idx += static_cast<int64_t>(static_cast<int32_t>(rem - q * d)) * v.stride[k];
+    rem = q;
   }
   // i < prod(dim): what is left is the outermost coordinate itself
   if (v.rank > 0) idx += static_cast<int64_t>(rem) * v.stride[0];

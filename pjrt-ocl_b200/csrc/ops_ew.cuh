@@ -29,6 +29,12 @@ struct EwOp {                  // decoded chain member, lives in shared memory
   uint8_t *dst;
   const uint8_t *a, *b, *c;
   uint32_t p2, p3;
+  // decided once per entry (ew_decode), read every trip:
+  uint32_t la, lb;          // operand load mode: 0 none (unused / forwarded), 1 plain 4-byte,
+                            // 2 plain bf16, 3 4-byte through a vector-friendly view, 4 generic
+  uint32_t st;              // store mode: 0 dead, 1 4-byte, 2 bf16, 3 generic, 4 LTS (element 0 only)
+  uint32_t esz;             // operand element size
+  const uint8_t *pfa, *pfb; // contiguous operands worth prefetching (else null)
   DView va, vb;
 };
 static_assert(sizeof(EwOp) * kChainMax <= kSmemSys - kSmemChain, "chain cache fits");
@@ -48,7 +54,7 @@ __device__ __forceinline__ float np_min(float x, float y) { return (x != x || y 
 __device__ __forceinline__ float gelu_tanh(float x) {
   const float x2 = x * x;
   const float t = fmaf(0.044715f * x2, x, x);
-  const float e = expf(-1.5957691216f * t);
+  const float e = __expf(-1.5957691216f * t);   // ex2(x*log2 e): ~1e-6 relative over the range that matters
   return __fdividef(x, 1.0f + e);
 }
 // a*s + t with two roundings, as the validator computes it (no contraction)
@@ -242,22 +248,16 @@ __device__ __noinline__ void ew_chain_run(const Lane &L, const EwOp *ops, uint32
     // into L2 now, which takes no registers and orders nothing.
     {
       const uint32_t gn = g0 + L.nthr * kEwU;
-      if (gn < ngroups) {
+      if (gn + (kEwU - 1) * L.nthr < ngroups) {
         for (uint32_t j = 0; j < k; ++j) {
-          const EwOp &o = ops[j];
-          const uint32_t esz = dt_size(o.adt);
-          const bool na = !(o.sub == kFill || o.sub == kIotaFlat) && !(o.flags & (kFwdA | kViewA));
-          const bool nb = !(o.flags & (kFwdB | kViewB)) &&
-                          (ew_is_bin(o.sub) || o.sub == kCmp || o.sub == kSelect ||
-                           (o.sub >= kAnd && o.sub <= kXor) || (o.sub >= kShl && o.sub <= kShrA));
+          const uint8_t *pa = ops[j].pfa, *pb = ops[j].pfb;
+          if (!pa && !pb) continue;
+          const uint32_t esz = ops[j].esz;
 #pragma unroll
           for (int u = 0; u < kEwU; ++u) {
-            const uint32_t g = gn + u * L.nthr;
-            if (g < ngroups) {
-              const size_t off = static_cast<size_t>(lo + (g << 2)) * esz;
-              if (na) prefetch_l2(o.a + off);
-              if (nb) prefetch_l2(o.b + off);
-            }
+            const size_t off = static_cast<size_t>(lo + ((gn + u * L.nthr) << 2)) * esz;
+            if (pa) prefetch_l2(pa + off);
+            if (pb) prefetch_l2(pb + off);
           }
         }
       }
@@ -265,9 +265,7 @@ __device__ __noinline__ void ew_chain_run(const Lane &L, const EwOp *ops, uint32
     for (uint32_t j = 0; j < k; ++j) {
       const EwOp &o = ops[j];
       const uint32_t sub = o.sub, dt = o.dt, adt = o.adt, fl = o.flags;
-      const bool needs_a = !(sub == kFill || sub == kIotaFlat);
-      const bool needs_b = ew_is_bin(sub) || sub == kCmp || sub == kSelect || sub == kLts ||
-                           (sub >= kAnd && sub <= kXor) || (sub >= kShl && sub <= kShrA);
+      const uint32_t la = full ? o.la : (o.la ? 4u : 0u), lb = full ? o.lb : (o.lb ? 4u : 0u);
       // X holds the previous op's result on entry; operand a takes it when forwarded.
       if (fl & kFwdB) {
 #pragma unroll
@@ -278,21 +276,20 @@ __device__ __noinline__ void ew_chain_run(const Lane &L, const EwOp *ops, uint32
       // Operand loads. The dtype / view / ragged-edge decisions are hoisted out of
       // the unrolled groups: the common cases are four unconditional 16-byte (or
       // 8-byte) loads back to back.
-      const bool w4 = adt == kF32 || adt == kI32 || adt == kU32;
-      if (needs_a && !(fl & kFwdA)) {
-        if (full && !(fl & kViewA) && w4) {
+      if (la) {
+        if (la == 1u) {
 #pragma unroll
           for (int u = 0; u < kEwU; ++u) {
             const uint4 w = *reinterpret_cast<const uint4 *>(o.a + static_cast<size_t>(base[u]) * 4);
             X[u][0] = w.x; X[u][1] = w.y; X[u][2] = w.z; X[u][3] = w.w;
           }
-        } else if (full && !(fl & kViewA) && adt == kBF16) {
+        } else if (la == 2u) {
 #pragma unroll
           for (int u = 0; u < kEwU; ++u) {
             const uint2 w = *reinterpret_cast<const uint2 *>(o.a + static_cast<size_t>(base[u]) * 2);
             X[u][0] = w.x << 16; X[u][1] = w.x & 0xffff0000u; X[u][2] = w.y << 16; X[u][3] = w.y & 0xffff0000u;
           }
-        } else if (full && (fl & kViewA) && w4 && o.va.vec_ok) {
+        } else if (la == 3u) {
 #pragma unroll
           for (int u = 0; u < kEwU; ++u) load_view_w4(o.a, o.va, base[u], X[u]);
         } else {
@@ -301,20 +298,20 @@ __device__ __noinline__ void ew_chain_run(const Lane &L, const EwOp *ops, uint32
             if (vc[u]) ew_load_operand(o.a, adt, fl & kViewA, o.va, base[u], vc[u], X[u]);
         }
       }
-      if (needs_b && !(fl & kFwdB)) {
-        if (full && !(fl & kViewB) && w4) {
+      if (lb) {
+        if (lb == 1u) {
 #pragma unroll
           for (int u = 0; u < kEwU; ++u) {
             const uint4 w = *reinterpret_cast<const uint4 *>(o.b + static_cast<size_t>(base[u]) * 4);
             Y[u][0] = w.x; Y[u][1] = w.y; Y[u][2] = w.z; Y[u][3] = w.w;
           }
-        } else if (full && !(fl & kViewB) && adt == kBF16) {
+        } else if (lb == 2u) {
 #pragma unroll
           for (int u = 0; u < kEwU; ++u) {
             const uint2 w = *reinterpret_cast<const uint2 *>(o.b + static_cast<size_t>(base[u]) * 2);
             Y[u][0] = w.x << 16; Y[u][1] = w.x & 0xffff0000u; Y[u][2] = w.y << 16; Y[u][3] = w.y & 0xffff0000u;
           }
-        } else if (full && (fl & kViewB) && w4 && o.vb.vec_ok) {
+        } else if (lb == 3u) {
 #pragma unroll
           for (int u = 0; u < kEwU; ++u) load_view_w4(o.b, o.vb, base[u], Y[u]);
         } else {
@@ -498,15 +495,16 @@ __device__ __noinline__ void ew_chain_run(const Lane &L, const EwOp *ops, uint32
           for (int e = 0; e < 4; ++e) X[u][e] = __float_as_uint(quantize(__uint_as_float(X[u][e]), dt));
       }
       // ---- store ----
-      if (!(fl & kDeadStore)) {
-        if (sub == kLts) {
+      const uint32_t st = (full || o.st == 0u || o.st == 4u) ? o.st : 3u;
+      if (st) {
+        if (st == 4u) {
           if (lo == 0u && g0 == 0u) store1(o.dst, dt, 0, X[0][0]);
-        } else if (full && (dt == kF32 || dt == kI32 || dt == kU32)) {
+        } else if (st == 1u) {
 #pragma unroll
           for (int u = 0; u < kEwU; ++u)
             *reinterpret_cast<uint4 *>(o.dst + static_cast<size_t>(base[u]) * 4) =
                 make_uint4(X[u][0], X[u][1], X[u][2], X[u][3]);
-        } else if (full && dt == kBF16) {
+        } else if (st == 2u) {
 #pragma unroll
           for (int u = 0; u < kEwU; ++u) {   // X already holds bf16-representable values
             uint2 w;
@@ -680,6 +678,23 @@ __device__ __forceinline__ void ew_decode(const KParams &P, const DTask &t, EwOp
     if (t.flags & kViewA) o->va = dv[0];
     if (t.flags & kViewB) o->vb = dv[1];
   }
+  const uint32_t sub = o->sub, adt = o->adt, dt = o->dt, fl = o->flags;
+  const bool needs_a = !(sub == kFill || sub == kIotaFlat);
+  const bool needs_b = ew_is_bin(sub) || sub == kCmp || sub == kSelect || sub == kLts ||
+                       (sub >= kAnd && sub <= kXor) || (sub >= kShl && sub <= kShrA);
+  const bool w4 = adt == kF32 || adt == kI32 || adt == kU32;
+  auto mode = [&](bool needed, bool fwd, bool viewed, const DView &v) -> uint32_t {
+    if (!needed || fwd) return 0u;
+    if (!viewed) return w4 ? 1u : (adt == kBF16 ? 2u : 4u);
+    return (w4 && v.vec_ok) ? 3u : 4u;
+  };
+  o->la = mode(needs_a, fl & kFwdA, fl & kViewA, o->va);
+  o->lb = mode(needs_b, fl & kFwdB, fl & kViewB, o->vb);
+  o->st = (fl & kDeadStore) ? 0u : sub == kLts ? 4u
+          : (dt == kF32 || dt == kI32 || dt == kU32) ? 1u : dt == kBF16 ? 2u : 3u;
+  o->esz = dt_size(adt);
+  o->pfa = (o->la == 1u || o->la == 2u) ? o->a : nullptr;
+  o->pfb = (o->lb == 1u || o->lb == 2u) ? o->b : nullptr;
 }
 
 // Run `chain` consecutive EW entries starting at `e0` (all over the same tile range).

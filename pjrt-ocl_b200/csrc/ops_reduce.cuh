@@ -161,7 +161,7 @@ template <typename C, bool DOT>
 __device__ __forceinline__ uint32_t reduce_vec32(const uint8_t *p, uint32_t dt, int64_t g_lo, int64_t g_hi,
                                                  uint32_t rank, uint32_t nthreads, uint32_t ident,
                                                  const uint8_t *dotvec, int64_t dbase) {
-  constexpr int U = 4;
+  constexpr int U = 8;   // 16-byte loads in flight per thread
   uint32_t acc[U];
 #pragma unroll
   for (int u = 0; u < U; ++u) acc[u] = ident;
@@ -193,7 +193,7 @@ __device__ __forceinline__ uint32_t reduce_vec32(const uint8_t *p, uint32_t dt, 
       acc[0] = C::f(acc[0], x);
     }
   }
-  return C::f(C::f(acc[0], acc[1]), C::f(acc[2], acc[3]));
+  return C::f(C::f(C::f(acc[0], acc[1]), C::f(acc[2], acc[3])), C::f(C::f(acc[4], acc[5]), C::f(acc[6], acc[7])));
 }
 
 // Reduce elements [lo, hi) of `p`, strided over `nthreads` cooperating threads

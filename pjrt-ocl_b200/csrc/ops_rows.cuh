@@ -23,6 +23,8 @@ namespace b2 {
 
 constexpr int kRowGroupWarps = 4;
 constexpr int kRowGroupThreads = kRowGroupWarps * kWarp;
+constexpr int kRowMaxBufs = 4;     // staged rows per group (at least 2)
+constexpr int kRowHdr = 1024;      // mbarriers + reduction slots ahead of the row buffers
 
 // Reduce across the 4 warps of a row group. `slot` = 4 floats of scratch per group.
 template <typename F>
@@ -48,25 +50,32 @@ __device__ __forceinline__ void rows_staged(const Lane &L, const DTask &t, uint3
   const float eps = __uint_as_float(t.p[2]);
   const uint32_t ngroups = L.nthr / kRowGroupThreads;
   const uint32_t gi = L.tid / kRowGroupThreads, gl = L.tid % kRowGroupThreads;
-  uint64_t *bars = reinterpret_cast<uint64_t *>(L.smem + kSmemSys);               // [ngroups][2]
-  float *slots = reinterpret_cast<float *>(L.smem + kSmemSys + 256);              // [ngroups][4]
+  uint64_t *bars = reinterpret_cast<uint64_t *>(L.smem + kSmemSys);               // [ngroups][kRowMaxBufs]
+  float *slots = reinterpret_cast<float *>(L.smem + kSmemSys + 512);              // [ngroups][4]
   const uint32_t buf_stride = (in_bytes + 127u) & ~127u;
-  uint8_t *bufs = L.smem + kSmemSys + 512 + static_cast<size_t>(gi) * 2 * buf_stride;
+  // as many row buffers per group as fit (2..kRowMaxBufs): rows in flight hide the HBM latency
+  const uint32_t nbuf = min(static_cast<uint32_t>(kRowMaxBufs),
+                            (L.smem_bytes - kSmemSys - kRowHdr) / (ngroups * buf_stride));
+  uint8_t *bufs = L.smem + kSmemSys + kRowHdr + static_cast<size_t>(gi) * nbuf * buf_stride;
 
   __syncthreads();
   if (L.tid == 0) {
-    for (uint32_t i = 0; i < ngroups * 2; ++i) mbar_init(&bars[i], 1);
+    for (uint32_t i = 0; i < ngroups * kRowMaxBufs; ++i) mbar_init(&bars[i], 1);
     fence_mbar_init();
   }
   __syncthreads();
 
-  uint64_t *bar = bars + gi * 2;
+  uint64_t *bar = bars + gi * kRowMaxBufs;
   float *slot = slots + gi * 4;
   const int bid = 1 + static_cast<int>(gi);
   const uint32_t first = lo + gi;
-  if (gl == 0 && first < hi) {
-    mbar_arrive_expect_tx(&bar[0], in_bytes);
-    bulk_g2s(bufs, src + static_cast<size_t>(first) * in_bytes, in_bytes, &bar[0]);
+  if (gl == 0) {
+    for (uint32_t k = 0; k + 1 < nbuf; ++k) {
+      const uint32_t r = first + k * ngroups;
+      if (r >= hi) break;
+      mbar_arrive_expect_tx(&bar[k], in_bytes);
+      bulk_g2s(bufs + k * buf_stride, src + static_cast<size_t>(r) * in_bytes, in_bytes, &bar[k]);
+    }
   }
   // Every group runs the same trip count so the lane-wide vote below stays uniform;
   // a group that has run out of rows just votes.
@@ -74,7 +83,7 @@ __device__ __forceinline__ void rows_staged(const Lane &L, const DTask &t, uint3
   for (uint32_t it = 0; it < max_it; ++it) {
     const uint32_t row = first + it * ngroups;
     const bool active = row < hi;
-    const uint32_t b = it & 1u, parity = (it >> 1) & 1u;
+    const uint32_t b = it % nbuf, parity = (it / nbuf) & 1u;
     bool ok = true;
     if (active && !mbar_wait_bounded(&bar[b], parity, P.wait_budget_ns)) {
       set_status(P, kStTensorTimeout, L.lane, row, t.op);
@@ -83,28 +92,84 @@ __device__ __forceinline__ void rows_staged(const Lane &L, const DTask &t, uint3
     // Lane-wide vote: (1) a copy that never landed abandons the op for everybody,
     // (2) every thread has left the previous iteration, so the other buffer is free.
     if (!__syncthreads_and(ok)) break;
-    const uint32_t next = row + ngroups;
+    // refill the buffer that was consumed in the previous iteration
+    const uint32_t next = row + (nbuf - 1u) * ngroups;
+    const uint32_t nb = (it + nbuf - 1u) % nbuf;
     if (gl == 0 && next < hi) {
-      // the other buffer was last read through the generic proxy: order those
-      // reads before the asynchronous-proxy write that refills it.
+      // that buffer was last read through the generic proxy: order those reads
+      // before the asynchronous-proxy write that refills it.
       fence_proxy_async_smem();
-      mbar_arrive_expect_tx(&bar[b ^ 1u], in_bytes);
-      bulk_g2s(bufs + (b ^ 1u) * buf_stride, src + static_cast<size_t>(next) * in_bytes, in_bytes, &bar[b ^ 1u]);
+      mbar_arrive_expect_tx(&bar[nb], in_bytes);
+      bulk_g2s(bufs + nb * buf_stride, src + static_cast<size_t>(next) * in_bytes, in_bytes, &bar[nb]);
     }
     if (!active) continue;
     const uint8_t *rowp = bufs + b * buf_stride;
     uint8_t *outp = dst + static_cast<size_t>(row) * seg * dt_size(dt);
     const uint32_t ng = seg >> 2;   // the caller checked seg % 4 == 0
-    if (softmax) {
+    if (adt == kF32 && dt == kF32) {
+      // f32 in, f32 out: the common case, written without any per-element dispatch.
+      const float4 *r4 = reinterpret_cast<const float4 *>(rowp);
+      float4 *w4 = reinterpret_cast<float4 *>(const_cast<uint8_t *>(rowp));
+      float4 *o4 = reinterpret_cast<float4 *>(outp);
+      if (softmax) {
+        float m = -INFINITY;
+        for (uint32_t g = gl; g < ng; g += kRowGroupThreads) {
+          const float4 v = r4[g];
+          m = fmaxf(m, fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w)));
+        }
+        m = group_reduce(m, [](float a, float c) { return fmaxf(a, c); }, slot, bid, gl);
+        // exp(x - m) = 2^(x*log2(e) - m*log2(e)): one FMA and one ex2 per element; the
+        // result stays in the staged row so the third pass only scales it.
+        constexpr float kLog2e = 1.4426950408889634f;
+        const float mb = m * kLog2e;
+        float s = 0.0f;
+        for (uint32_t g = gl; g < ng; g += kRowGroupThreads) {
+          const float4 v = r4[g];
+          float4 e;
+          e.x = fast_ex2(fmaf(v.x, kLog2e, -mb));
+          e.y = fast_ex2(fmaf(v.y, kLog2e, -mb));
+          e.z = fast_ex2(fmaf(v.z, kLog2e, -mb));
+          e.w = fast_ex2(fmaf(v.w, kLog2e, -mb));
+          s += (e.x + e.y) + (e.z + e.w);
+          w4[g] = e;
+        }
+        s = group_reduce(s, [](float a, float c) { return a + c; }, slot, bid, gl);
+        const float rs = __fdiv_rn(1.0f, s);
+        for (uint32_t g = gl; g < ng; g += kRowGroupThreads) {
+          float4 v = r4[g];
+          v.x *= rs; v.y *= rs; v.z *= rs; v.w *= rs;
+          o4[g] = v;
+        }
+      } else {
+        float s = 0.0f, s2 = 0.0f;
+        for (uint32_t g = gl; g < ng; g += kRowGroupThreads) {
+          const float4 v = r4[g];
+          s += (v.x + v.y) + (v.z + v.w);
+          s2 = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, s2))));
+        }
+        s = group_reduce(s, [](float a, float c) { return a + c; }, slot, bid, gl);
+        s2 = group_reduce(s2, [](float a, float c) { return a + c; }, slot, bid, gl);
+        const float inv_n = 1.0f / static_cast<float>(seg);
+        const float mu = s * inv_n;
+        const float var = __fsub_rn(s2 * inv_n, __fmul_rn(mu, mu));
+        const float rden = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(var, eps)));
+        for (uint32_t g = gl; g < ng; g += kRowGroupThreads) {
+          float4 v = r4[g];
+          v.x = (v.x - mu) * rden; v.y = (v.y - mu) * rden; v.z = (v.z - mu) * rden; v.w = (v.w - mu) * rden;
+          o4[g] = v;
+        }
+      }
+    } else if (softmax) {
       float m = -INFINITY;
       for (uint32_t g = gl; g < ng; g += kRowGroupThreads) {
         uint32_t v[4];
         load4(rowp, adt, g << 2, v);
 #pragma unroll
-        for (int e = 0; e < 4; ++e) m = np_max(m, __uint_as_float(v[e]));
+        for (int e = 0; e < 4; ++e) m = fmaxf(m, __uint_as_float(v[e]));   // a NaN still poisons the row through the sum
       }
       m = group_reduce(m, [](float a, float c) { return np_max(a, c); }, slot, bid, gl);
-      // f32 rows keep exp(x - max) in the staged row (each thread revisits exactly
+      // exp(x - max) has a non-positive argument of modest size: the hardware ex2 of
+      // x*log2(e) is within ~1e-6 relative there. f32 rows keep it in the staged row (each thread revisits exactly
       // the groups it wrote), so the exponential is evaluated once per element.
       const bool keep = adt == kF32;
       float *roww = reinterpret_cast<float *>(const_cast<uint8_t *>(rowp));
@@ -115,7 +180,7 @@ __device__ __forceinline__ void rows_staged(const Lane &L, const DTask &t, uint3
         float ex[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          ex[e] = expf(__uint_as_float(v[e]) - m);
+          ex[e] = __expf(__uint_as_float(v[e]) - m);
           s += ex[e];
         }
         if (keep) *reinterpret_cast<float4 *>(roww + (g << 2)) = make_float4(ex[0], ex[1], ex[2], ex[3]);
@@ -127,7 +192,7 @@ __device__ __forceinline__ void rows_staged(const Lane &L, const DTask &t, uint3
         load4(rowp, adt, g << 2, v);
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          const float ev = keep ? __uint_as_float(v[e]) : expf(__uint_as_float(v[e]) - m);
+          const float ev = keep ? __uint_as_float(v[e]) : __expf(__uint_as_float(v[e]) - m);
           v[e] = __float_as_uint(ev * rs);
         }
         store4(outp, dt, g << 2, v);
@@ -161,7 +226,7 @@ __device__ __forceinline__ void rows_staged(const Lane &L, const DTask &t, uint3
   }
   __syncthreads();
   if (L.tid == 0)
-    for (uint32_t i = 0; i < ngroups * 2; ++i) mbar_inval(&bars[i]);
+    for (uint32_t i = 0; i < ngroups * kRowMaxBufs; ++i) mbar_inval(&bars[i]);
   __syncthreads();
 }
 
@@ -216,7 +281,7 @@ __device__ __noinline__ void rows_tiles(const Lane &L, const DTask &t, uint32_t 
   const bool staged = ngroups >= 1 && L.nthr % kRowGroupThreads == 0 && ngroups <= 15 &&
                       seg >= 1024 && seg % 4 == 0 && in_bytes % 16 == 0 && dt_size(t.adt) <= 4 && dt_size(t.dt) <= 4 &&
                       reinterpret_cast<uintptr_t>(src) % 16 == 0 && reinterpret_cast<uintptr_t>(dst) % 16 == 0 &&
-                      static_cast<size_t>(kSmemSys) + 512 + static_cast<size_t>(ngroups) * 2 * buf_stride <= L.smem_bytes;
+                      static_cast<size_t>(kSmemSys) + kRowHdr + static_cast<size_t>(ngroups) * 2 * buf_stride <= L.smem_bytes;
   if (staged) rows_staged(L, t, tile_lo, hi, softmax);
   else rows_generic(L, t, tile_lo, hi, softmax);
 }

@@ -109,6 +109,7 @@ struct b2_loaded {
   b2::DSync *d_sync = nullptr;
   b2::DSync *h_sync = nullptr;  // pinned mirror
   uint64_t launches = 0;
+  bool sync_dirty = true;       // the device sync block must be cleared before the next launch
   uint64_t wait_budget_ns = 2000000000ull;
   cudaStream_t last_stream = nullptr;
 
@@ -134,8 +135,15 @@ cudaError_t Upload(T **dptr, const std::vector<T> &v) {
 // Enqueue one execution on `stream`: reset the sync block, launch the megakernel,
 // copy the sync block back to its pinned mirror. `io` holds the port addresses.
 b2_status Enqueue(b2_loaded *lp, const b2::IoTable &io, cudaStream_t stream, std::string *err) {
-  cudaError_t e = cudaMemsetAsync(lp->d_sync, 0, sizeof(b2::DSync), stream);
-  if (e != cudaSuccess) { *err = CudaMsg("sync reset", e); return B2_INTERNAL; }
+  // The barrier words return to their rest state after every complete run and
+  // the status words are only written on failure, so the block is cleared only
+  // at first use and after a failed run.
+  cudaError_t e = cudaSuccess;
+  if (lp->sync_dirty) {
+    e = cudaMemsetAsync(lp->d_sync, 0, sizeof(b2::DSync), stream);
+    if (e != cudaSuccess) { *err = CudaMsg("sync reset", e); return B2_INTERNAL; }
+    lp->sync_dirty = false;
+  }
   b2::KParams kp;
   std::memset(&kp, 0, sizeof(kp));
   kp.tasks = lp->d_tasks;
@@ -151,14 +159,20 @@ b2_status Enqueue(b2_loaded *lp, const b2::IoTable &io, cudaStream_t stream, std
   e = b2::LaunchVm(kp, lp->prog.n_lanes, lp->rt->threads, lp->rt->smem_bytes, stream);
   if (e != cudaSuccess) { *err = CudaMsg("megakernel launch", e); cudaGetLastError(); return B2_INTERNAL; }
   lp->launches++;
-  e = cudaMemcpyAsync(lp->h_sync, lp->d_sync, sizeof(b2::DSync), cudaMemcpyDeviceToHost, stream);
-  if (e != cudaSuccess) { *err = CudaMsg("status readback", e); return B2_INTERNAL; }
   lp->last_stream = stream;
   return B2_OK;
 }
 
-b2_status CheckDeviceStatus(const b2_loaded *lp, std::string *err) {
+// Enqueue the copy of the device sync block to its pinned mirror.
+b2_status FetchStatus(b2_loaded *lp, cudaStream_t stream, std::string *err) {
+  const cudaError_t e = cudaMemcpyAsync(lp->h_sync, lp->d_sync, sizeof(b2::DSync), cudaMemcpyDeviceToHost, stream);
+  if (e != cudaSuccess) { *err = CudaMsg("status readback", e); return B2_INTERNAL; }
+  return B2_OK;
+}
+
+b2_status CheckDeviceStatus(b2_loaded *lp, std::string *err) {
   const b2::DSync &s = *lp->h_sync;
+  if (s.status[0] != b2::kStOk) lp->sync_dirty = true;
   switch (s.status[0]) {
     case b2::kStOk: return B2_OK;
     case b2::kStBarrierTimeout:
@@ -398,10 +412,22 @@ size_t b2_loaded_phase_ns(const b2_loaded *lp, uint64_t *out, size_t cap) {
 
 b2_status b2_loaded_status(b2_loaded *lp, b2_exec_status *out, char *err, size_t err_cap) {
   if (!lp || !out) return B2_INVALID_ARGUMENT;
+  std::string m;
+  {
+    std::lock_guard<std::mutex> g(lp->rt->mu);
+    lp->rt->Bind();
+    cudaStream_t stream = lp->last_stream ? lp->last_stream : lp->rt->stream;
+    b2_status fs = FetchStatus(lp, stream, &m);
+    if (fs == B2_OK && cudaStreamSynchronize(stream) != cudaSuccess) {
+      m = "status readback: stream synchronize failed";
+      cudaGetLastError();
+      fs = B2_INTERNAL;
+    }
+    if (fs != B2_OK) { SetErr(err, err_cap, m); return fs; }
+  }
   const b2::DSync &s = *lp->h_sync;
   out->code = s.status[0]; out->lane = s.status[1]; out->where = s.status[2]; out->detail = s.status[3];
   out->barriers = s.barriers; out->device_ns = s.device_ns;
-  std::string m;
   const b2_status st = CheckDeviceStatus(lp, &m);
   if (st != B2_OK) SetErr(err, err_cap, m);
   return st;
@@ -441,6 +467,7 @@ static b2_status BindAndRun(b2_loaded *lp, void *const *dev_in, void *const *dev
     }
   }
   if (!synchronous) return B2_OK;
+  if (FetchStatus(lp, stream, err) != B2_OK) return B2_INTERNAL;
   if ((e = cudaStreamSynchronize(stream)) != cudaSuccess) {
     *err = CudaMsg("execute", e);
     cudaGetLastError();
@@ -532,6 +559,7 @@ b2_status b2_execute_host(b2_loaded *lp, const void *const *inputs, size_t n_inp
     if (!dout[o]) st = B2_RESOURCE_EXHAUSTED;
   }
   if (st == B2_OK) st = BindAndRun(lp, din.data(), dout.data(), rt->stream, false, &m);
+  if (st == B2_OK) st = FetchStatus(lp, rt->stream, &m);
   for (size_t o = 0; o < n_outputs && st == B2_OK; ++o) {
     const size_t bytes = p.buffers[p.outputs[o]].size_bytes;
     if (bytes && (e = cudaMemcpyAsync(outputs[o], dout[o], bytes, cudaMemcpyDeviceToHost, rt->stream)) != cudaSuccess) {

@@ -88,6 +88,30 @@ def c2_chain(rows=8192, cols=4096, nlanes=NLANES, dtype=F32, fused=True,
                             ("normal", (cols,), DN[dtype], 0.1, 0.0)])
 
 
+def c2_stage(stage, rows=8192, cols=4096, nlanes=NLANES, dtype=F32, eps=1e-5):
+    """One stage of the config-2 chain as a program of its own."""
+    a_ = Asm()
+    x = a_.input((rows, cols), dtype)
+    items = [("normal", (rows, cols), DN[dtype])]
+    if stage == "layernorm":
+        out = a_.layernorm_fused(x, eps)
+    elif stage == "affine_gelu":
+        gamma = a_.input((cols,), dtype)
+        beta = a_.input((cols,), dtype)
+        items += [("normal", (cols,), DN[dtype], 0.1, 1.0), ("normal", (cols,), DN[dtype], 0.1, 0.0)]
+        y = a_.add(a_.mul(x, a_.broadcast_in_dim(gamma, (rows, cols), [1])),
+                   a_.broadcast_in_dim(beta, (rows, cols), [1]))
+        out = a_.gelu_tanh(y)
+    elif stage == "softmax":
+        out = a_.softmax_fused(x)
+    elif stage == "sum":
+        out = a_.reduce(x, [0, 1], SUM)
+    else:
+        raise ValueError(stage)
+    blob, prog = a_.finish([out], nlanes=nlanes)
+    return blob, prog, (0, items)
+
+
 def c2_int_chain(rows=8192, cols=4096, nlanes=NLANES):
     """max((a + b) ^ c, d) on i32, bit-exact."""
     a_ = Asm()

@@ -38,6 +38,10 @@ for g in (2, 4, 8):
         lambda g=g: cases.c3_mlp_step(batch=8192 // g, global_batch=8192, apply_sgd=False))
     PROGRAMS[f"c5_block_bf16_dp{g}"] = lambda g=g: cases.c5_block(batch=8 // g)
     PROGRAMS[f"c5_decode_bf16_dp{g}"] = lambda g=g: cases.c5_decode(batch=32 // g)
+# the four stages of config 2 as programs of their own (one tile-op family each),
+# for per-family roofline numbers and ncu captures
+for stage in ("layernorm", "affine_gelu", "softmax", "sum"):
+    PROGRAMS[f"c2_stage_{stage}_f32"] = lambda stage=stage: cases.c2_stage(stage)
 # bounded samples of config 2 (512 of the 8192 rows) for the timed CPU arm
 PROGRAMS["c2_chain_f32_cpu_sample"] = lambda: cases.c2_chain(rows=512, dtype=F32)
 PROGRAMS["c2_chain_bf16_cpu_sample"] = lambda: cases.c2_chain(rows=512, dtype=BF16)
