@@ -19,7 +19,7 @@ constexpr int kSmemRed = 0;          // 64 x 16 B reduction scratch
 constexpr int kSmemPtrs = 512;       // 8 resolved pointers (MAP_REGION inputs)
 constexpr int kSmemFlag = 576;       // grid-barrier outcome, broadcast from thread 0
 constexpr int kSmemChain = 1024;     // decoded elementwise chain (EwOp[kChainMax])
-constexpr int kSmemSys = 4096;
+constexpr int kSmemSys = 8192;
 constexpr int kChainMax = 8;
 
 struct Lane {

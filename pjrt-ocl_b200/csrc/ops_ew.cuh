@@ -24,6 +24,15 @@
 
 namespace b2 {
 
+// One micro-step of the register-machine form of a chain (see ops_ew_steps.cuh).
+struct EwStep {
+  uint32_t code, p2, p3;
+  uint32_t voff;            // byte offset of the operand's DView in the lane's shared memory
+  const uint8_t *ptr;
+};
+constexpr int kEwMaxSteps = 6;   // forward-copy, two loads, compute, quantize, store
+constexpr uint32_t kEwNoSteps = 0xffffffffu;
+
 struct EwOp {                  // decoded chain member, lives in shared memory
   uint32_t sub, dt, adt, flags;
   uint8_t *dst;
@@ -36,6 +45,8 @@ struct EwOp {                  // decoded chain member, lives in shared memory
   uint32_t esz;             // operand element size
   const uint8_t *pfa, *pfb; // contiguous operands worth prefetching (else null)
   DView va, vb;
+  uint32_t nsteps, pad;     // kEwNoSteps: this op has no micro-step form (generic executor only)
+  EwStep steps[kEwMaxSteps];
 };
 static_assert(sizeof(EwOp) * kChainMax <= kSmemSys - kSmemChain, "chain cache fits");
 
@@ -54,8 +65,9 @@ __device__ __forceinline__ float np_min(float x, float y) { return (x != x || y 
 __device__ __forceinline__ float gelu_tanh(float x) {
   const float x2 = x * x;
   const float t = fmaf(0.044715f * x2, x, x);
-  const float e = __expf(-1.5957691216f * t);   // ex2(x*log2 e): ~1e-6 relative over the range that matters
-  return __fdividef(x, 1.0f + e);
+  // exp(-2u) = 2^(t * (-2 * 0.7978845608 * log2 e)) on the special-function unit
+  const float e = fast_ex2(t * -2.3022082f);
+  return x * fast_rcp(1.0f + e);
 }
 // a*s + t with two roundings, as the validator computes it (no contraction)
 __device__ __forceinline__ float affine2(float a, float s, float t) { return __fadd_rn(__fmul_rn(a, s), t); }
@@ -695,33 +707,6 @@ __device__ __forceinline__ void ew_decode(const KParams &P, const DTask &t, EwOp
   o->esz = dt_size(adt);
   o->pfa = (o->la == 1u || o->la == 2u) ? o->a : nullptr;
   o->pfb = (o->lb == 1u || o->lb == 2u) ? o->b : nullptr;
-}
-
-// Run `chain` consecutive EW entries starting at `e0` (all over the same tile range).
-__device__ __forceinline__ void ew_entries(const Lane &L, const DEntry *e0, uint32_t chain) {
-  const KParams &P = *L.P;
-  EwOp *ops = reinterpret_cast<EwOp *>(L.smem + kSmemChain);
-  __syncthreads();  // previous users of the chain cache are done
-  if (L.tid < chain) ew_decode(P, P.tasks[e0[L.tid].task], &ops[L.tid]);
-  __syncthreads();
-  const uint32_t n = P.tasks[e0->task].p[1];
-  const uint64_t lo64 = static_cast<uint64_t>(e0->tile_lo) * kEwTs;
-  uint64_t hi64 = static_cast<uint64_t>(e0->tile_hi) * kEwTs;
-  if (hi64 > n) hi64 = n;
-  if (lo64 >= hi64) return;
-  const uint32_t lo = static_cast<uint32_t>(lo64), hi = static_cast<uint32_t>(hi64);
-  bool vec = true;
-  for (uint32_t j = 0; j < chain; ++j) vec = vec && (ops[j].flags & kVecPath);
-  if (vec) {
-    ew_chain_run(L, ops, chain, lo, hi);
-  } else {
-    // No forwarding on this path (the loader never sets the flags for it): one op
-    // at a time, published to the whole lane between ops.
-    for (uint32_t j = 0; j < chain; ++j) {
-      if (j) { __threadfence_block(); __syncthreads(); }
-      ew_scalar_run(L, ops[j], lo, hi);
-    }
-  }
 }
 
 }  // namespace b2

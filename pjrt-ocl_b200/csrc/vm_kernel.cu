@@ -15,6 +15,7 @@
 
 #include "dev_common.cuh"
 #include "ops_ew.cuh"
+#include "ops_ew_steps.cuh"
 #include "ops_flash.cuh"
 #include "ops_mma.cuh"
 #include "ops_move.cuh"
