@@ -124,6 +124,11 @@ b2_status b2_execute_device_async(b2_loaded *lp, void *const *dev_inputs, size_t
 b2_status b2_loaded_status(b2_loaded *lp, b2_exec_status *out, char *err, size_t err_cap);
 /* Number of kernels launched by this loaded program so far. */
 uint64_t b2_loaded_launch_count(const b2_loaded *lp);
+/* Load-time facts about how the program was mapped to the device, for tests and
+ * logs (no counterpart in the reference). `which`: 0 fused elementwise chains,
+ * 1 operands forwarded in registers, 2 intermediate stores elided, 3 matmul
+ * tasks, 4 matmul tasks on the tensor-core path. Unknown `which` returns 0. */
+uint64_t b2_loaded_stat(const b2_loaded *lp, int which);
 /* Per-wait budget of device-side bounded waits, in nanoseconds (default 2e9). */
 void b2_loaded_set_wait_budget_ns(b2_loaded *lp, uint64_t ns);
 /* Lane 0's arrival time, in ns since kernel entry, at each of the first grid

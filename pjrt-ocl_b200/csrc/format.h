@@ -151,12 +151,18 @@ struct DRegion {            // loader-built: the 8 input references (a, b, p2..p
   BufRef in[8];
 };
 
+// tc_mode bits: the operands are affine in (batch, row, k) with a unit stride along
+// k ("K-major") or along the row / column index ("MN-major"), 16-byte friendly.
+constexpr uint32_t kTcOk = 1u, kTcAmn = 2u, kTcBmn = 4u;
 struct DMma {          // loader-built
   DView va, vb;
-  uint32_t tc_mode;    // 0: CUDA-core path only; else operand layout class for the tensor-core path
+  uint32_t tc_mode;    // 0: CUDA-core path only
   uint32_t pad;
-  int64_t a_ld, b_ld;  // tensor-core path: leading dimensions (elements)
-  int64_t a_gs, b_gs;  // tensor-core path: batch strides (elements)
+  // tensor-core path, in elements: A(g,m,k) = a_off + g*a_gs + (K-major: m*a_ld + k | MN-major: k*a_ld + m),
+  // B(g,k,n) = b_off + g*b_gs + (K-major: n*b_ld + k | MN-major: k*b_ld + n)
+  int64_t a_ld, b_ld;
+  int64_t a_gs, b_gs;
+  int64_t a_off, b_off;
 };
 
 struct DFlash {        // loader-built

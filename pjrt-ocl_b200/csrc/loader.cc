@@ -100,6 +100,61 @@ bool ViewFromAux(const VmProgram &p, uint32_t aux_off, DView *v, std::string *er
   return true;
 }
 
+// Is the view, read over the row-major flat index of a [n0, n1, n2] tensor, affine
+// in the three coordinates? The view's (collapsed) dims and [n0, n1, n2] are two
+// factorisations of the same index space; walk their common refinement from the
+// innermost digit and require every piece of one coordinate to agree on that
+// coordinate's stride.
+bool AffineOverAxes(const DView &v, const int64_t n[3], int64_t stride[3], int64_t *off) {
+  *off = v.off;
+  stride[0] = stride[1] = stride[2] = 0;
+  bool have[3] = {false, false, false};
+  int a = 2, j = v.rank - 1;
+  int64_t ra = n[2], wa = 1, rv = j >= 0 ? v.dim[j] : 1, wv = 1;
+  auto next_axis = [&]() { while (a >= 0 && ra == 1) { --a; if (a >= 0) { ra = n[a]; wa = 1; } } };
+  auto next_dim = [&]() { while (j >= 0 && rv == 1) { --j; if (j >= 0) { rv = v.dim[j]; wv = 1; } } };
+  next_axis();
+  next_dim();
+  while (a >= 0 && j >= 0) {
+    const int64_t p = std::min(ra, rv);
+    if (ra % p != 0 || rv % p != 0) return false;
+    const int64_t contrib = wv * static_cast<int64_t>(v.stride[j]);   // address step of one digit of this piece
+    if (!have[a]) {
+      if (wa != 1) return false;
+      stride[a] = contrib;
+      have[a] = true;
+    } else if (contrib != wa * stride[a]) {
+      return false;
+    }
+    ra /= p; wa *= p; rv /= p; wv *= p;
+    next_axis();
+    next_dim();
+  }
+  return a < 0 && j < 0;   // both factorisations consumed: same number of elements
+}
+
+// Classify one matmul operand for the tensor-core path. rows x K operand (A: rows = M;
+// B: rows = N), given the element strides of (batch, row, k). Returns false when the
+// layout cannot be fed to the tensor cores directly.
+bool TcOperand(int64_t rows, int64_t K, int64_t sg, int64_t sr, int64_t sk, int64_t off, bool *mn_major, int64_t *ld,
+               int64_t *gs) {
+  if (off < 0 || off % 8 != 0 || sg < 0 || sg % 8 != 0) return false;
+  *gs = sg;
+  if (sk == 1 || K == 1) {                       // K-major: rows at pitch sr
+    if (rows > 1 && (sr <= 0 || sr % 8 != 0)) return false;
+    *mn_major = false;
+    *ld = rows > 1 ? sr : 8;
+    return true;
+  }
+  if (sr == 1 || rows == 1) {                    // MN-major: k rows at pitch sk
+    if (sk <= 0 || sk % 8 != 0) return false;
+    *mn_major = true;
+    *ld = sk;
+    return true;
+  }
+  return false;
+}
+
 }  // namespace
 
 bool CollapseView(const int32_t *dims, const int32_t *strides, int rank, int64_t off, DView *out) {
@@ -316,6 +371,26 @@ bool BuildDeviceTables(const VmProgram &p, uint64_t arena_base, DeviceTables *ou
             return false;
           }
         }
+        // tensor-core eligibility: 16-bit float operands in a directly loadable layout
+        if (d.adt == kBF16 || d.adt == kF16) {
+          const int64_t M = t.p0, N = t.p1, K = t.p2, G = t.p3 ? t.p3 : 1;
+          int64_t sa[3] = {M * K, K, 1}, sb[3] = {K * N, N, 1}, oa = 0, ob = 0;
+          bool ok = M > 0 && N > 0 && K > 0 && M < (1ll << 31) && N < (1ll << 31) && K < (1ll << 31);
+          const int64_t na[3] = {G, M, K}, nb[3] = {G, K, N};
+          if (ok && t.p4) ok = AffineOverAxes(m.va, na, sa, &oa);
+          if (ok && t.p5) ok = AffineOverAxes(m.vb, nb, sb, &ob);
+          if (G == 1) sa[0] = sb[0] = 0;
+          bool amn = false, bmn = false;
+          ok = ok && TcOperand(M, K, sa[0], sa[1], sa[2], oa, &amn, &m.a_ld, &m.a_gs);
+          ok = ok && TcOperand(N, K, sb[0], sb[2], sb[1], ob, &bmn, &m.b_ld, &m.b_gs);
+          if (ok) {
+            m.a_off = oa;
+            m.b_off = ob;
+            m.tc_mode = kTcOk | (amn ? kTcAmn : 0u) | (bmn ? kTcBmn : 0u);
+            ++out->n_mma_tc;
+          }
+        }
+        ++out->n_mma;
         d.desc = c.PushDesc(m);
         break;
       }

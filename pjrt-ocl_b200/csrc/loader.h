@@ -27,6 +27,8 @@ struct DeviceTables {
   uint32_t n_chains = 0;                // fused elementwise chains (length > 1)
   uint32_t n_forwarded = 0;             // operands taken from registers
   uint32_t n_dead_stores = 0;           // intermediate stores elided
+  uint32_t n_mma = 0;                   // matmul tasks
+  uint32_t n_mma_tc = 0;                // ... of which the tensor-core path takes
 };
 
 // `arena_base` is the device address of the arena (only its value is used).

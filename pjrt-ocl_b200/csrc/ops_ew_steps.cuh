@@ -34,12 +34,21 @@ enum EwStepCode : uint32_t {
   kSAffine, kSFill, kSIotaF, kSIotaI, kSSelect,
   kSCvtF2I, kSCvtF2U, kSCvtI2F, kSCvtU2F, kSCvtF2B, kSCvtI2B,
   kSBNot, kSUMax, kSUMin,
-  kSCmpF = 40,               // + predicate 0..5
-  kSCmpI = 46,
-  kSCmpU = 52,
-  kSFlt = 64,                // + Sub (float arithmetic)
-  kSInt = 128,               // + Sub (i32 / u32 / bool arithmetic)
+  kSCmpF,                    // + predicate 0..5
+  kSCmpI = kSCmpF + 6,
+  kSCmpU = kSCmpI + 6,
+  kSFlt = kSCmpU + 6,        // + ew_fcode(Sub) (float arithmetic)
+  kSInt = kSFlt + 17,        // + ew_icode(Sub) (i32 / u32 / bool arithmetic)
+  kSEnd = kSInt + 14,
 };
+// The codes are dense on purpose: the dispatch switch compiles to one jump table.
+__host__ __device__ constexpr uint32_t ew_fcode(uint32_t sub) {   // kAdd..kMin, kNeg..kSign, kGelu
+  return sub <= kMin ? sub : sub <= kSign ? sub - 2u : 16u;
+}
+__host__ __device__ constexpr uint32_t ew_icode(uint32_t sub) {
+  return sub <= kSubt ? sub : sub == kMax ? 3u : sub == kMin ? 4u : sub == kNeg ? 5u : sub == kAbs ? 6u
+         : sub <= kNot ? sub - 28u : sub - 31u;   // kAnd..kNot -> 7..10, kShl..kShrA -> 11..13
+}
 
 __device__ __forceinline__ bool ew_is_w4(uint32_t dt) { return dt == kF32 || dt == kI32 || dt == kU32; }
 
@@ -124,14 +133,14 @@ __device__ inline void ew_build_steps(EwOp *o, uint32_t smem_off_of_op) {
         else if (sub == kIotaFlat) emit(kSIotaF, nullptr, 0, 0, 0);
         else if (sub == kCopy) quant = quant && adt != kBF16;
         else if (sub <= kMin || (sub >= kNeg && sub <= kSign) || sub == kGelu) {
-          emit(kSFlt + sub, nullptr, 0, 0, 0);
+          emit(kSFlt + ew_fcode(sub), nullptr, 0, 0, 0);
           if ((sub == kNeg || sub == kAbs || sub == kMax || sub == kMin) && adt == kBF16) quant = false;
         } else ok = false;
       } else if (dt == kBool) {
         if (sub == kFill) emit(kSFill, nullptr, 0, o->p2 & 0xffu, 0);
-        else if (sub == kAnd || sub == kOr || sub == kXor) emit(kSInt + sub, nullptr, 0, 0, 0);
-        else if (sub == kMax) emit(kSInt + kOr, nullptr, 0, 0, 0);
-        else if (sub == kMin) emit(kSInt + kAnd, nullptr, 0, 0, 0);
+        else if (sub == kAnd || sub == kOr || sub == kXor) emit(kSInt + ew_icode(sub), nullptr, 0, 0, 0);
+        else if (sub == kMax) emit(kSInt + ew_icode(kOr), nullptr, 0, 0, 0);
+        else if (sub == kMin) emit(kSInt + ew_icode(kAnd), nullptr, 0, 0, 0);
         else if (sub == kNot) emit(kSBNot, nullptr, 0, 0, 0);
         else if (sub != kCopy) ok = false;
       } else if (dt == kI32 || dt == kU32) {
@@ -142,8 +151,8 @@ __device__ inline void ew_build_steps(EwOp *o, uint32_t smem_off_of_op) {
         else if (sub == kMin && uns) emit(kSUMin, nullptr, 0, 0, 0);
         else if (sub == kAdd || sub == kMul || sub == kSubt || sub == kMax || sub == kMin || sub == kNeg ||
                  (sub >= kAnd && sub <= kNot) || sub == kShl || sub == kShrL || sub == kShrA)
-          emit(kSInt + sub, nullptr, 0, 0, 0);
-        else if (sub == kAbs && !uns) emit(kSInt + kAbs, nullptr, 0, 0, 0);
+          emit(kSInt + ew_icode(sub), nullptr, 0, 0, 0);
+        else if (sub == kAbs && !uns) emit(kSInt + ew_icode(kAbs), nullptr, 0, 0, 0);
         else if (!(sub == kCopy || (sub == kAbs && uns))) ok = false;
       } else {
         ok = false;
@@ -189,7 +198,8 @@ static_assert(kSmemEwFlat + sizeof(EwFlat) <= kSmemSys, "flattened steps fit the
 __device__ __forceinline__ bool ew_step_is_cold(uint32_t c) {
   if (c >= kSFlt && c < kSInt) {
     const uint32_t f = c - kSFlt;
-    return !(f == kAdd || f == kMul || f == kSubt || f == kMax || f == kMin || f == kNeg || f == kAbs || f == kGelu);
+    return !(f == ew_fcode(kAdd) || f == ew_fcode(kMul) || f == ew_fcode(kSubt) || f == ew_fcode(kMax) ||
+             f == ew_fcode(kMin) || f == ew_fcode(kNeg) || f == ew_fcode(kAbs) || f == ew_fcode(kGelu));
   }
   return c == kSIotaF || c == kSIotaI || (c >= kSCvtF2I && c <= kSBNot) || (c >= kSLdXViewW4 && c <= kSLdYViewBf);
 }
@@ -332,18 +342,18 @@ __device__ __noinline__ void ew_steps_run(uint32_t tid, uint32_t nthr, uint32_t 
   _Pragma("unroll") for (int u = 0; u < kEwU; ++u)                     \
   _Pragma("unroll") for (int e = 0; e < 4; ++e) { __VA_ARGS__; }
 #define B2_SF(S, EXPR)                                                           \
-  case kSFlt + S:                                                                \
+  case kSFlt + ew_fcode(S):                                                              \
     B2_ALL(const float x = __uint_as_float(X[u][e]), y = __uint_as_float(Y[u][e]); \
            (void)y; X[u][e] = __float_as_uint(EXPR))                             \
     break;
 #define B2_SFC(S, EXPR)                                                          \
-  case kSFlt + S:                                                                \
+  case kSFlt + ew_fcode(S):                                                              \
     if constexpr (COLD) {                                                        \
       B2_ALL(const float x = __uint_as_float(X[u][e]); X[u][e] = __float_as_uint(EXPR)) \
     }                                                                            \
     break;
 #define B2_SI(S, EXPR)                                                           \
-  case kSInt + S:                                                                \
+  case kSInt + ew_icode(S):                                                              \
     B2_ALL(const uint32_t x = X[u][e], y = Y[u][e]; (void)y; X[u][e] = (EXPR))   \
     break;
 #define B2_SCMP(BASE, CAST)                                                                   \
@@ -433,7 +443,7 @@ __device__ __noinline__ void ew_steps_run(uint32_t tid, uint32_t nthr, uint32_t 
           B2_SF(kAdd, __fadd_rn(x, y))
           B2_SF(kMul, __fmul_rn(x, y))
           B2_SF(kSubt, __fsub_rn(x, y))
-          case kSFlt + kDiv:
+          case kSFlt + ew_fcode(kDiv):
             if constexpr (COLD) { B2_ALL(X[u][e] = __float_as_uint(__fdiv_rn(__uint_as_float(X[u][e]), __uint_as_float(Y[u][e])))) }
             break;
           B2_SF(kMax, np_max(x, y))

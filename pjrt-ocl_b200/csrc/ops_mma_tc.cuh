@@ -1,0 +1,323 @@
+// TILE_MMA on the 5th-generation tensor cores (tcgen05), bf16 / f16 operands, f32
+// accumulation in tensor memory.
+//
+// Same contract as the CUDA-core path (ops_mma.cuh; pjrt_plugin/kernels/ops/mma.cl:
+// 74-96,136-434; python/pjrt_ocl/ops/dot.py:206-293): C[g] = A[g] . B[g] on 128x128
+// output tiles numbered batch x tiles_m x tiles_n, optional operand views, optional
+// store epilogue. Taken when the loader proved both operands affine with a unit
+// stride along k or along the row / column index (DMma::tc_mode).
+//
+// One lane (CTA, 16 warps) works through its tile range in "super-tiles" of one or
+// two horizontally adjacent 128x128 tiles, i.e. a 128 x (128|256) accumulator, so a
+// block of A is fetched once for both:
+//   warps 0-7   producers: 16-byte asynchronous copies global -> shared straight into
+//               the 128-byte-swizzled operand layout the tensor core reads, 64 k per
+//               stage, kTcStages stages in flight, zero-filling rows / k beyond the edge;
+//   warp 8      lane 0 issues the tcgen05.mma instructions (4 per stage, K = 16 each)
+//               and commits them to the stage's "empty" barrier;
+//   warps 8-15  epilogue: tcgen05.ld the accumulator (each warp its 32 lanes x 64 or
+//               128 columns), micro-epilogue, convert, store.
+// Every barrier wait is bounded by the launch's wait budget and watches a lane-wide
+// failure flag; on failure the lane records a status, drains its copies, frees its
+// tensor memory and returns.
+#ifndef B2VM_OPS_MMA_TC_CUH_
+#define B2VM_OPS_MMA_TC_CUH_
+
+#include "ops_mma.cuh"
+
+namespace b2 {
+
+#if B2_HAS_TC
+
+constexpr int kTcBK = 64;                    // k per stage: 128 bytes, one swizzle row
+constexpr int kTcStages = 4;
+constexpr int kTcABytes = 128 * 128;         // 128 rows x 128 B
+constexpr int kTcBBytes = 256 * 128;         // up to 256 rows x 128 B
+constexpr int kTcStageBytes = kTcABytes + kTcBBytes;
+constexpr int kTcProducers = 256;
+constexpr uint32_t kTcCols = 256;            // tensor-memory columns held (f32 accumulator 128 x 256)
+constexpr uint32_t kStatusTcTimeout = 0x7C01u;
+
+struct TcShared {                            // lives in the reduction scratch of the system area
+  uint64_t full[kTcStages];
+  uint64_t empty[kTcStages];
+  uint64_t acc_full;
+  uint64_t acc_empty;
+  uint32_t tmem_base;
+  uint32_t failed;
+};
+static_assert(sizeof(TcShared) <= 512, "fits the scratch slot");
+
+// Shared-memory matrix descriptor, 128-byte swizzle (layout type 2), descriptor version 1.
+__device__ __forceinline__ uint64_t tc_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  return static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4) | (static_cast<uint64_t>(lbo_bytes >> 4) << 16) |
+         (static_cast<uint64_t>(sbo_bytes >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+
+// Bounded wait that also gives up when another role of the lane failed.
+__device__ __forceinline__ bool tc_wait(uint64_t *bar, uint32_t parity, volatile uint32_t *failed,
+                                        unsigned long long budget_ns) {
+  if (mbar_try_wait_parity(bar, parity)) return true;
+  const unsigned long long t0 = globaltimer_ns();
+  for (;;) {
+    for (int i = 0; i < 32; ++i)
+      if (mbar_try_wait_parity(bar, parity)) return true;
+    if (*failed) return false;
+    if (globaltimer_ns() - t0 > budget_ns) { *failed = 1u; return false; }
+  }
+}
+
+// rows x 64 block of a K-major operand (element (row, k) at src[row * ld + k]) into
+// the swizzled K-major layout: row at 128 B pitch, its 16-byte chunks XORed with row % 8.
+template <int ROWS>
+__device__ __forceinline__ void tc_load_kmajor(uint32_t sdst, const uint16_t *src, const uint16_t *safe, int64_t ld,
+                                               int64_t rows_valid, int64_t k0, int64_t K, uint32_t ptid) {
+  const uint32_t c = ptid & 7u, r = ptid >> 3;                  // 32 rows per pass
+  const int64_t k = k0 + 8 * c;
+  const uint32_t kbytes = k < K ? static_cast<uint32_t>(min(static_cast<int64_t>(16), 2 * (K - k))) : 0u;
+  const uint32_t d0 = sdst + r * 128u + ((c ^ (r & 7u)) << 4);
+#pragma unroll
+  for (int i = 0; i < ROWS / 32; ++i) {
+    const int64_t row = r + 32 * i;
+    const uint32_t bytes = row < rows_valid ? kbytes : 0u;
+    cp_async_16_zfill(d0 + static_cast<uint32_t>(i) * 4096u, bytes ? src + row * ld + k : safe, bytes);
+  }
+}
+// rows x 64 block of an MN-major operand (element (row, k) at src[k * ld + row]) into
+// the swizzled MN-major layout: 64-row blocks 8192 B apart, 8-k groups 1024 B apart,
+// inside a group one k per 128 B line with its chunks XORed with k % 8.
+template <int ROWS>
+__device__ __forceinline__ void tc_load_mnmajor(uint32_t sdst, const uint16_t *src, const uint16_t *safe, int64_t ld,
+                                                int64_t rows_valid, int64_t k0, int64_t K, uint32_t ptid) {
+  constexpr uint32_t CPR = ROWS / 8;                            // chunks per k line
+  constexpr uint32_t KPP = kTcProducers / CPR;                  // k lines per pass
+  const uint32_t cm = ptid % CPR, kr = ptid / CPR;
+  const int64_t m = 8 * static_cast<int64_t>(cm);
+  const uint32_t mbytes = m < rows_valid ? static_cast<uint32_t>(min(static_cast<int64_t>(16), 2 * (rows_valid - m))) : 0u;
+#pragma unroll
+  for (uint32_t i = 0; i < 64u / KPP; ++i) {
+    const uint32_t kk = kr + KPP * i;
+    const uint32_t bytes = k0 + kk < K ? mbytes : 0u;
+    const uint32_t d = sdst + (cm >> 3) * 8192u + (kk >> 3) * 1024u + (kk & 7u) * 128u + (((cm & 7u) ^ (kk & 7u)) << 4);
+    cp_async_16_zfill(d, bytes ? src + (k0 + kk) * ld + m : safe, bytes);
+  }
+}
+
+__device__ __forceinline__ void tc_store_row32(uint8_t *dst, uint32_t dt, int64_t idx, const float (&v)[32], int64_t ncols,
+                                               bool vec) {
+  if (vec && ncols >= 32) {
+    if (dt == kF32) {
+      float4 *q = reinterpret_cast<float4 *>(dst + idx * 4);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) q[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+    } else {
+      uint4 *q = reinterpret_cast<uint4 *>(dst + idx * 2);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        uint32_t w[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float lo = v[8 * j + 2 * e], hi = v[8 * j + 2 * e + 1];
+          w[e] = dt == kBF16 ? cvt_bf16x2(hi, lo) : (f32_to_f16_bits(lo) | (f32_to_f16_bits(hi) << 16));
+        }
+        q[j] = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+    }
+    return;
+  }
+#pragma unroll
+  for (int j = 0; j < 32; ++j)
+    if (j < ncols) storef(dst, dt, idx + j, v[j]);
+}
+
+// Returns false (nothing done) when this launch cannot use the path (misaligned
+// operand base); the caller then runs the CUDA-core path.
+__device__ __noinline__ bool mma_tc_tiles(const Lane &L, const DTask &t, uint32_t tile_lo, uint32_t tile_hi) {
+  const KParams &P = *L.P;
+  const DMma &dm = *reinterpret_cast<const DMma *>(P.desc + t.desc);
+  const int64_t M = t.p[0], N = t.p[1], K = t.p[2], G = t.p[3] ? t.p[3] : 1;
+  const uint32_t adt = t.adt, dt = t.dt;
+  uint8_t *dst = resolve(P, t.ptr[0]);
+  const uint8_t *Ab = resolve(P, t.ptr[1]);
+  const uint8_t *Bb = resolve(P, t.ptr[2]);
+  const uint8_t *res = t.p[6] ? resolve(P, t.ptr[3]) : nullptr;
+  if ((reinterpret_cast<uintptr_t>(Ab) | reinterpret_cast<uintptr_t>(Bb)) & 15u) return false;
+  if (!(dt == kF32 || dt == kBF16 || dt == kF16)) return false;
+  const uint16_t *A = reinterpret_cast<const uint16_t *>(Ab) + dm.a_off;
+  const uint16_t *B = reinterpret_cast<const uint16_t *>(Bb) + dm.b_off;
+  const bool amn = dm.tc_mode & kTcAmn, bmn = dm.tc_mode & kTcBmn;
+  const int64_t tn = (N + kMmaT - 1) / kMmaT, tm = (M + kMmaT - 1) / kMmaT, per = tm * tn;
+  const int64_t nkb = (K + kTcBK - 1) / kTcBK;
+  const bool vec_store = (reinterpret_cast<uintptr_t>(dst) & 15u) == 0 && N % 8 == 0;
+
+  B2_DYN_SMEM(sm);
+  TcShared *S = reinterpret_cast<TcShared *>(sm + kSmemRed);
+  volatile uint32_t *failed = &S->failed;
+  const uint32_t stage0 = (smem_addr(sm + kSmemSys) + 1023u) & ~1023u;
+  const uint32_t w = L.tid / kWarp, lane = L.tid % kWarp;
+  const unsigned long long budget = P.wait_budget_ns;
+
+  __syncthreads();   // the scratch slot is free
+  if (L.tid == 0) {
+    for (int s = 0; s < kTcStages; ++s) { mbar_init(&S->full[s], kTcProducers); mbar_init(&S->empty[s], 1); }
+    mbar_init(&S->acc_full, 1);
+    mbar_init(&S->acc_empty, 256);
+    S->failed = 0u;
+    fence_mbar_init();
+  }
+  if (w == 8) {
+    __syncwarp();
+    tmem_alloc(&S->tmem_base, kTcCols);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = S->tmem_base;
+
+  // Enumerate the lane's super-tiles; every role walks the same sequence.
+  auto next_super = [&](uint32_t &tile, int64_t &g, int64_t &r0, int64_t &c0, int &nt) -> bool {
+    while (tile < tile_hi) {
+      g = tile / per;
+      const int64_t loc = tile % per, ti = loc / tn, tj = loc % tn;
+      if (g >= G) { tile = tile_hi; return false; }
+      r0 = ti * kMmaT; c0 = tj * kMmaT;
+      nt = (tj + 1 < tn && tile + 1 < tile_hi) ? 2 : 1;
+      tile += nt;
+      return true;
+    }
+    return false;
+  };
+
+  if (w < 8) {
+    // ---------------- producers ----------------
+    const uint32_t ptid = L.tid;
+    uint32_t it = 0, sig = 0;                     // stages issued / stages published
+    uint32_t tile = tile_lo; int64_t g, r0, c0; int nt;
+    auto signal_oldest = [&]() {                  // the oldest unpublished stage has landed: publish it
+      fence_proxy_async_smem();
+      mbar_arrive(&S->full[sig % kTcStages]);
+      ++sig;
+    };
+    bool ok = true;
+    while (ok && next_super(tile, g, r0, c0, nt)) {
+      const uint16_t *Ag = A + g * dm.a_gs + (amn ? r0 : r0 * dm.a_ld);
+      const uint16_t *Bg = B + g * dm.b_gs + (bmn ? c0 : c0 * dm.b_ld);
+      const int64_t a_rows = min(static_cast<int64_t>(kMmaT), M - r0);
+      const int64_t b_rows = min(static_cast<int64_t>(kMmaT) * nt, N - c0);
+      for (int64_t kb = 0; kb < nkb; ++kb, ++it) {
+        const uint32_t s = it % kTcStages;
+        if (!tc_wait(&S->empty[s], ((it / kTcStages) & 1u) ^ 1u, failed, budget)) { ok = false; break; }
+        const uint32_t sa = stage0 + s * kTcStageBytes, sb = sa + kTcABytes;
+        const int64_t k0 = kb * kTcBK;
+        if (amn) tc_load_mnmajor<128>(sa, Ag, A, dm.a_ld, a_rows, k0, K, ptid);
+        else tc_load_kmajor<128>(sa, Ag, A, dm.a_ld, a_rows, k0, K, ptid);
+        if (nt == 2) {
+          if (bmn) tc_load_mnmajor<256>(sb, Bg, B, dm.b_ld, b_rows, k0, K, ptid);
+          else tc_load_kmajor<256>(sb, Bg, B, dm.b_ld, b_rows, k0, K, ptid);
+        } else {
+          if (bmn) tc_load_mnmajor<128>(sb, Bg, B, dm.b_ld, b_rows, k0, K, ptid);
+          else tc_load_kmajor<128>(sb, Bg, B, dm.b_ld, b_rows, k0, K, ptid);
+        }
+        cp_async_commit();
+        if (it + 1 - sig == kTcStages - 1) {      // the two newest stages stay in flight
+          cp_async_wait<kTcStages - 2>();
+          signal_oldest();
+        }
+      }
+    }
+    // drain: everything issued lands, the remaining stages are published in order
+    cp_async_wait<0>();
+    while (sig < it) signal_oldest();
+  } else {
+    // ---------------- MMA issue (warp 8 lane 0) + epilogue (warps 8-15) ----------------
+    const uint32_t ew = w - 8, q = ew & 3u, half = ew >> 2;
+    const uint32_t fmt = adt == kBF16 ? 1u : 0u;
+    uint32_t it = 0, tcount = 0;
+    uint32_t tile = tile_lo; int64_t g, r0, c0; int nt;
+    bool ok = true;
+    while (ok && next_super(tile, g, r0, c0, nt)) {
+      const uint32_t ninst = 128u * nt;
+      if (w == 8 && lane == 0) {
+        // the previous accumulator has been read by all eight epilogue warps
+        if (tcount && !tc_wait(&S->acc_empty, (tcount - 1u) & 1u, failed, budget)) ok = false;
+        tc_fence_after_sync();
+        const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((amn ? 1u : 0u) << 15) | ((bmn ? 1u : 0u) << 16) |
+                               ((ninst >> 3) << 17) | ((128u >> 4) << 24);
+        for (int64_t kb = 0; ok && kb < nkb; ++kb, ++it) {
+          const uint32_t s = it % kTcStages;
+          if (!tc_wait(&S->full[s], (it / kTcStages) & 1u, failed, budget)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t sa = stage0 + s * kTcStageBytes, sb = sa + kTcABytes;
+          const uint64_t da = amn ? tc_desc(sa, 8192u, 1024u) : tc_desc(sa, 16u, 1024u);
+          const uint64_t db = bmn ? tc_desc(sb, 8192u, 1024u) : tc_desc(sb, 16u, 1024u);
+          const uint64_t adv_a = amn ? (2048u >> 4) : (32u >> 4), adv_b = bmn ? (2048u >> 4) : (32u >> 4);
+#pragma unroll
+          for (uint32_t j = 0; j < kTcBK / 16; ++j)
+            tc_mma_f16(tmem, da + j * adv_a, db + j * adv_b, idesc, (kb > 0 || j > 0) ? 1u : 0u);
+          tc_commit(&S->empty[s]);                // frees the stage when these MMAs have read it
+        }
+        if (ok) tc_commit(&S->acc_full);
+      } else {
+        it += static_cast<uint32_t>(nkb);
+      }
+      __syncwarp();
+      // epilogue: wait for the accumulator, then each warp drains its lanes x columns
+      if (!tc_wait(&S->acc_full, tcount & 1u, failed, budget)) { ok = false; break; }
+      ++tcount;
+      __syncwarp();
+      tc_fence_after_sync();
+      const int64_t r = r0 + 32 * q + lane;
+      const uint32_t cols_per_warp = ninst / 2;   // two column halves
+#pragma unroll 1
+      for (uint32_t cb = 0; cb < cols_per_warp; cb += 32) {
+        const uint32_t col = half * cols_per_warp + cb;
+        uint32_t raw[32];
+        __syncwarp();   // the warp-wide tensor-memory load needs all 32 lanes back together
+                        // (rows beyond M leave the store below divergent)
+        tc_ld32(tmem + ((32u * q) << 16) + col, raw);
+        tc_wait_ld();
+        const int64_t c = c0 + col;
+        if (r < M && c < N) {
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[j]);
+          const int64_t ncols = min(static_cast<int64_t>(32), N - c);
+          if (t.p[6]) {
+#pragma unroll 1
+            for (int j = 0; j < 32; ++j)
+              if (j < ncols) v[j] = mma_epilogue(P, t, res, v[j], g, r, c + j, M, N);
+          }
+          tc_store_row32(dst, dt, (g * M + r) * N + c, v, ncols, vec_store);
+        }
+      }
+      tc_fence_before_sync();
+      mbar_arrive(&S->acc_empty);                 // this thread is done with the accumulator
+    }
+  }
+
+  // ---------------- teardown ----------------
+  tc_fence_before_sync();
+  __syncthreads();
+  if (w == 8) {
+    __syncwarp();
+    tc_fence_after_sync();
+    tmem_dealloc(tmem, kTcCols);
+  }
+  if (L.tid == 0) {
+    if (S->failed) set_status(P, kStatusTcTimeout, L.lane, tile_lo, tile_hi);
+    for (int s = 0; s < kTcStages; ++s) { mbar_inval(&S->full[s]); mbar_inval(&S->empty[s]); }
+    mbar_inval(&S->acc_full);
+    mbar_inval(&S->acc_empty);
+  }
+  __syncthreads();
+  return true;
+}
+
+#else   // no tensor-core instructions in this build
+
+__device__ __forceinline__ bool mma_tc_tiles(const Lane &, const DTask &, uint32_t, uint32_t) { return false; }
+
+#endif
+
+}  // namespace b2
+#endif

@@ -402,6 +402,17 @@ const b2_program *b2_loaded_program(const b2_loaded *lp) {
 }
 
 uint64_t b2_loaded_launch_count(const b2_loaded *lp) { return lp->launches; }
+uint64_t b2_loaded_stat(const b2_loaded *lp, int which) {
+  if (!lp) return 0;
+  switch (which) {
+    case 0: return lp->tab.n_chains;
+    case 1: return lp->tab.n_forwarded;
+    case 2: return lp->tab.n_dead_stores;
+    case 3: return lp->tab.n_mma;
+    case 4: return lp->tab.n_mma_tc;
+    default: return 0;
+  }
+}
 void b2_loaded_set_wait_budget_ns(b2_loaded *lp, uint64_t ns) { lp->wait_budget_ns = ns; }
 size_t b2_loaded_phase_ns(const b2_loaded *lp, uint64_t *out, size_t cap) {
   if (!lp || !out) return 0;

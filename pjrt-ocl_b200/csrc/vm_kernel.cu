@@ -16,6 +16,7 @@
 #include "dev_common.cuh"
 #include "ops_ew.cuh"
 #include "ops_ew_steps.cuh"
+#include "ops_mma_tc.cuh"
 #include "ops_flash.cuh"
 #include "ops_mma.cuh"
 #include "ops_move.cuh"
@@ -75,7 +76,12 @@ __device__ __forceinline__ void exec_entry(const Lane &L, const DEntry &en) {
   const KParams &P = *L.P;
   const DTask &t = P.tasks[en.task];
   switch (t.op) {
-    case kTopMma: mma_simt_tiles<NT>(L, t, en.tile_lo, en.tile_hi); break;
+    case kTopMma: {
+      const DMma &dm = *reinterpret_cast<const DMma *>(P.desc + t.desc);
+      const bool tc = NT == 512 && B2_HAS_TC && (dm.tc_mode & kTcOk) && mma_tc_tiles(L, t, en.tile_lo, en.tile_hi);
+      if (!tc) mma_simt_tiles<NT>(L, t, en.tile_lo, en.tile_hi);
+      break;
+    }
     case kTopGather: case kTopDynGather: move_tiles(L, t, en.tile_lo, en.tile_hi, false); break;
     case kTopScatter: case kTopDynScatter: move_tiles(L, t, en.tile_lo, en.tile_hi, true); break;
     case kTopRedPart: red_part_tiles(L, t, en.tile_lo, en.tile_hi); break;

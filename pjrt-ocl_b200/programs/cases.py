@@ -40,6 +40,18 @@ def c1_relu_matmul(M=256, K=128, N=64, nlanes=NLANES, dtype=F32):
                             ("normal", (K, N), DN[dtype])])
 
 
+def dot_general_square(n=8192, nlanes=NLANES, dtype=BF16, transpose_b=False):
+    """One dot_general, n x n x n, for the matmul tile-op family on its own.
+    `transpose_b`: y = x . w^T with w stored [n_out, n_in] (both operands k-contiguous)."""
+    a_ = Asm()
+    x = a_.input((n, n), dtype)
+    w = a_.input((n, n), dtype)
+    y = (a_.dot_general(x, w, lc=1, rc=1, out_dtype=dtype) if transpose_b
+         else a_.matmul(x, w, out_dtype=dtype))
+    blob, prog = a_.finish([y], nlanes=nlanes, fold_2byte_views=True)
+    return blob, prog, (3, [("normal", (n, n), DN[dtype]), ("normal", (n, n), DN[dtype], [1.0 / n ** 0.5])])
+
+
 # --------------------------------------------------------------------------
 # config 2: LayerNorm -> tanh-GELU -> softmax -> full sum ; i32 add/xor/max
 # --------------------------------------------------------------------------

@@ -516,7 +516,8 @@ class Asm:
 
     # -- finish -----------------------------------------------------------
     def finish(self, outputs: list, *, nlanes: int, costs: dict | None = None,
-               fold_2byte_views: bool = True, passes: bool = True):
+               fold_2byte_views: bool = True, passes: bool = True,
+               fold_2byte_matmul_views: bool = False):
         """Run the reference pass pipeline in its own order
         (lowering.py:3039-3090), schedule, serialize.  Returns (blob, program).
 
@@ -524,7 +525,9 @@ class Asm:
         bf16/f16 elementwise consumers (the reference gates that fold on f32,
         lowering.py:1507,1529, although the bytecode and both validators are
         dtype-agnostic): the buffers' dtype tags are masked to f32 for the
-        duration of that one pass."""
+        duration of that one pass.  `fold_2byte_matmul_views` does the same for
+        `_fuse_matmul_views` (lowering.py:2381-2452): transposes feeding a bf16/f16
+        dot_general become operand views of the matmul task instead of gathers."""
         ctx = self.ctx
         main_len = len(ctx.instrs)
         self._lower_regions()
@@ -532,7 +535,18 @@ class Asm:
         ctx.output_shapes = [o.shape for o in outputs]
         if passes:
             L._compose_affines(ctx)
-            L._fuse_matmul_views(ctx)
+            if fold_2byte_matmul_views:
+                saved = [b.dtype for b in ctx.buffers]
+                for b in ctx.buffers:
+                    if b.dtype in (F16, BF16):
+                        b.dtype = F32
+                try:
+                    L._fuse_matmul_views(ctx)
+                finally:
+                    for b, d in zip(ctx.buffers, saved):
+                        b.dtype = d
+            else:
+                L._fuse_matmul_views(ctx)
             L._fuse_views(ctx)
             if fold_2byte_views:
                 saved = [b.dtype for b in ctx.buffers]

@@ -96,7 +96,7 @@ EXPORTS = [
     "b2_program_io_rank", "b2_program_io_dim", "b2_program_load", "b2_loaded_destroy",
     "b2_loaded_program", "b2_execute_host", "b2_execute_device", "b2_execute_device_async",
     "b2_loaded_status", "b2_loaded_launch_count", "b2_loaded_set_wait_budget_ns",
-    "b2_loaded_phase_ns",
+    "b2_loaded_phase_ns", "b2_loaded_stat",
 ]
 
 
@@ -141,6 +141,7 @@ def lib():
         "b2_loaded_launch_count": (ctypes.c_uint64, [vp]),
         "b2_loaded_set_wait_budget_ns": (None, [vp, ctypes.c_uint64]),
         "b2_loaded_phase_ns": (sz, [vp, ctypes.POINTER(ctypes.c_uint64), sz]),
+        "b2_loaded_stat": (ctypes.c_uint64, [vp, ctypes.c_int]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(L, name)
@@ -347,6 +348,12 @@ class LoadedProgram:
         buf = (ctypes.c_uint64 * 64)()
         n = lib().b2_loaded_phase_ns(self._h, buf, 64)
         return [int(buf[i]) for i in range(n)]
+
+    _STATS = {"chains": 0, "forwarded": 0 + 1, "dead_stores": 2, "matmuls": 3, "tensor_core_matmuls": 4}
+
+    def stat(self, name: str) -> int:
+        """Load-time mapping facts: chains, forwarded, dead_stores, matmuls, tensor_core_matmuls."""
+        return int(lib().b2_loaded_stat(self._h, self._STATS[name]))
 
     @property
     def launch_count(self) -> int:

@@ -555,6 +555,58 @@ def _():
     return _dot_case(F16, F16, _DOT_SHAPES, 4)
 
 
+def _dot_tc_case(dtype, out_dtype, fold_views=False):
+    """Shapes whose operands are 16-byte friendly (every leading dimension a multiple
+    of 8 elements) but not multiples of the 128 tile or the 64-wide k block, in all
+    four operand layouts: plain, q k^T (both k-contiguous), x^T y (both row-contiguous),
+    batched, plus a bias + GELU + residual store epilogue."""
+    a = Asm()
+    dn = DN[dtype]
+    q = a.input((3, 200, 72), dtype)
+    k = a.input((3, 136, 72), dtype)
+    x = a.input((264, 136), dtype)
+    y = a.input((264, 152), dtype)
+    w = a.input((136, 328), dtype)
+    b = a.input((328,), dtype)
+    r = a.input((264, 328), dtype)
+    s = a.dot_general(q, k, lb=[0], lc=2, rb=[0], rc=2, out_dtype=out_dtype)       # [3,200,136]
+    kk = a.input((3, 136, 88), dtype)
+    sk = a.dot_general(a.convert(s, dtype) if out_dtype != dtype else s, kk, lb=[0], lc=2, rb=[0], rc=1,
+                       out_dtype=out_dtype)                                       # [3,200,88]
+    g = a.dot_general(x, y, lc=0, rc=0, out_dtype=out_dtype)                      # x^T y: [136,152]
+    e = a.matmul(x, w, out_dtype=dtype)                                           # [264,328] + epilogue
+    e = a.add(e, a.broadcast_in_dim(b, (264, 328), [1]))
+    e = a.gelu_tanh(e)
+    e = a.add(e, r)
+    big = a.matmul(a.input((384, 520), dtype), a.input((520, 640), dtype), out_dtype=out_dtype)
+    blob, prog = a.finish([s, sk, g, e, big], nlanes=6, fold_2byte_matmul_views=fold_views)
+    return blob, prog, (29, [N((3, 200, 72), dn, 0.5), N((3, 136, 72), dn, 0.5), N((264, 136), dn, 0.5),
+                             N((264, 152), dn, 0.5), N((136, 328), dn, 0.1), N((328,), dn), N((264, 328), dn),
+                             N((3, 136, 88), dn, 0.2), N((384, 520), dn, 0.3), N((520, 640), dn, 0.1)])
+
+
+@case("dot_tc_bf16", rtol=2e-2, atol=3e-2)
+def _():
+    return _dot_tc_case(BF16, BF16)
+
+
+@case("dot_tc_bf16_f32out", rtol=2e-2, atol=3e-2)
+def _():
+    return _dot_tc_case(BF16, F32)
+
+
+@case("dot_tc_f16", rtol=2e-2, atol=3e-2)
+def _():
+    return _dot_tc_case(F16, F16)
+
+
+@case("dot_tc_views_bf16", rtol=2e-2, atol=3e-2)
+def _():
+    """The same graph with the transposes folded into the matmul tasks as operand
+    views: k-contiguous B (q k^T) and row-contiguous A (x^T y) reach the matmul."""
+    return _dot_tc_case(BF16, BF16, fold_views=True)
+
+
 @case("dot_kat_2x2", exact=True)
 def _():
     """tests/test_ops_dot.py:56-63 known answer: [[1,2],[3,4]] @ [[5,6],[7,8]]
