@@ -43,20 +43,46 @@ N_C2 = 8192 * 4096
 
 # name -> program blob, CPU-arm sample blob (+ fraction of the full workload it is),
 # algorithmic bytes per step, metric
+def _wl(program, metric, unit, alg, scale, bound, dtype, desc, roof_alg=None, sample=None, sample_frac=0.0,
+        secondary=False):
+    """alg: algorithmic units one step processes (bytes, flops or tokens); value = alg / seconds / scale.
+    roof_alg: bytes (bound "hbm") or flops (bound "tensor") of one step, for the roofline fraction."""
+    return dict(program=program, metric=metric, unit=unit, alg=alg, scale=scale, bound=bound, dtype=dtype, desc=desc,
+                roof_alg=alg if roof_alg is None else roof_alg, sample=sample, sample_frac=sample_frac,
+                secondary=secondary)
+
+
+# config 5 block: 8 x 2048 tokens, d_model 1024, 16 heads x 64, FFN 4096
+_C5_TOK = 8 * 2048
+_C5_MM_FLOPS = 2 * _C5_TOK * (4 * 1024 * 1024 + 2 * 1024 * 4096)
+_C5_ATT_FLOPS = 2 * 2 * 8 * 16 * 2048 * 2048 * 64 // 2          # QK^T and PV, causal half
+# config 3 step: forward + dX (layers 2,3) + dW (all), batch 8192, 1024-4096-4096-1024
+_C3_FLOPS = 2 * 8192 * (1024 * 4096 + 4096 * 4096 + 4096 * 1024) * 3 - 2 * 8192 * 1024 * 4096
+
 WORKLOADS = {
-    "c2_f32": dict(
-        program="c2_chain_f32", sample="c2_chain_f32_cpu_sample", sample_frac=512 / 8192,
-        # LayerNorm r+w, GELU r+w, softmax r+w, full sum r  (f32) + gamma/beta
-        alg_bytes=7 * N_C2 * 4 + 2 * 4096 * 4, dtype="f32", metric="eltwise HBM GB/s", unit="GB/s",
-        desc="config 2: LayerNorm -> tanh-GELU -> softmax -> full sum on f32 (8192,4096)"),
-    "c2_bf16": dict(
-        program="c2_chain_bf16", sample="c2_chain_bf16_cpu_sample", sample_frac=512 / 8192,
-        alg_bytes=7 * N_C2 * 2 + 2 * 4096 * 2, dtype="bf16", metric="eltwise HBM GB/s", unit="GB/s",
-        desc="config 2 on bf16-storage copies of the same values"),
-    "c2_i32": dict(
-        program="c2_int_chain", sample="c2_int_chain_cpu_sample", sample_frac=512 / 8192,
-        alg_bytes=5 * N_C2 * 4, dtype="i32", metric="eltwise HBM GB/s", unit="GB/s",
-        desc="config 2: max((a+b)^c, d) on i32 (8192,4096), bit-exact"),
+    "c2_f32": _wl("c2_chain_f32", "eltwise HBM GB/s", "GB/s", 7 * N_C2 * 4 + 2 * 4096 * 4, 1e9, "hbm", "f32",
+                  "config 2: LayerNorm -> tanh-GELU -> softmax -> full sum on f32 (8192,4096); "
+                  "bytes = LayerNorm r+w, GELU r+w, softmax r+w, sum r, + gamma/beta",
+                  sample="c2_chain_f32_cpu_sample", sample_frac=512 / 8192),
+    "c2_bf16": _wl("c2_chain_bf16", "eltwise HBM GB/s", "GB/s", 7 * N_C2 * 2 + 2 * 4096 * 2, 1e9, "hbm", "bf16",
+                   "config 2 on bf16-storage copies of the same values",
+                   sample="c2_chain_bf16_cpu_sample", sample_frac=512 / 8192),
+    "c2_i32": _wl("c2_int_chain", "eltwise HBM GB/s", "GB/s", 5 * N_C2 * 4, 1e9, "hbm", "i32",
+                  "config 2: max((a+b)^c, d) on i32 (8192,4096), bit-exact",
+                  sample="c2_int_chain_cpu_sample", sample_frac=512 / 8192),
+    "dot_bf16_8192": _wl("dot_bf16_8192", "dot_general TFLOP/s", "TFLOP/s", 2 * 8192 ** 3, 1e12, "tensor", "bf16",
+                         "one dot_general bf16 8192 x 8192 x 8192, f32 accumulate, bf16 result"),
+    "dot_bf16_4096": _wl("dot_bf16_4096", "dot_general TFLOP/s", "TFLOP/s", 2 * 4096 ** 3, 1e12, "tensor", "bf16",
+                         "one dot_general bf16 4096 x 4096 x 4096", secondary=True),
+    "c3_mlp": _wl("c3_mlp_step_bf16", "dot_general TFLOP/s", "TFLOP/s", _C3_FLOPS, 1e12, "tensor", "bf16",
+                  "config 3: 3-layer MLP forward + grad of MSE + SGD step, batch 8192, 1024-4096-4096-1024, bf16"),
+    "c5_block": _wl("c5_block_bf16", "transformer-block tokens/s per B200", "tokens/s", _C5_TOK, 1.0, "tensor", "bf16",
+                    "config 5: pre-norm decoder block forward, batch 8 x seq 2048, d_model 1024, 16 x 64 heads, "
+                    "causal flash attention, GELU FFN 4096, bf16",
+                    roof_alg=_C5_MM_FLOPS + _C5_ATT_FLOPS),
+    "c5_decode": _wl("c5_decode_bf16", "transformer-block tokens/s per B200", "tokens/s", 32, 1.0, "hbm", "bf16",
+                     "config 5 decode step: batch 32, KV cache 2048; bytes = weights + KV cache read once",
+                     roof_alg=2 * (4 * 1024 * 1024 + 2 * 1024 * 4096) + 2 * 32 * 16 * 2048 * 64 * 2),
 }
 
 
@@ -66,9 +92,8 @@ for _stage, _bytes, _what in (
         ("affine_gelu", 2 * N_C2 * 4 + 2 * 4096 * 4, "fused chain mul(gamma view), add(beta view), GELU"),
         ("softmax", 2 * N_C2 * 4, "SOFTMAX_SEG rows of 4096 (TMA-staged)"),
         ("sum", N_C2 * 4, "full sum: RED_PART + RED_COMB")):
-    WORKLOADS[f"c2_stage_{_stage}"] = dict(
-        program=f"c2_stage_{_stage}_f32", sample=None, sample_frac=0.0, alg_bytes=_bytes, dtype="f32",
-        metric="eltwise HBM GB/s", unit="GB/s", desc=f"config 2 stage: {_what}", secondary=True)
+    WORKLOADS[f"c2_stage_{_stage}"] = _wl(f"c2_stage_{_stage}_f32", "eltwise HBM GB/s", "GB/s", _bytes, 1e9, "hbm",
+                                          "f32", f"config 2 stage: {_what}", secondary=True)
 
 
 def load_blob(name: str) -> bytes:
@@ -145,7 +170,7 @@ def cpu_arm(w: dict, steps: int, warmup: int, threads: int):
     for _ in range(steps):
         prog.execute(args, threads=threads)
     dt = (time.perf_counter() - t0) / steps
-    return w["alg_bytes"] * w["sample_frac"] / dt / 1e9, dt
+    return w["alg"] * w["sample_frac"] / dt / w["scale"], dt
 
 
 def main():
@@ -210,7 +235,7 @@ def main():
         torch.cuda.synchronize()
         ins = [t.data_ptr() for t in dev_in]
         outs = [t.data_ptr() for t in dev_out]
-        scalar = dev_out[-1][:4].view(torch.float32) if wl["dtype"] != "i32" else None
+        scalar = dev_out[-1][:4].view(torch.float32) if wl["program"].startswith("c2_chain") else None
 
         def step():
             lp.ExecuteDeviceAsync(ins, outs, stream.cuda_stream)
@@ -255,6 +280,7 @@ def main():
             dt = (time.perf_counter() - t0) / n_e2e
             e2e = {"seconds": dt, "h2d": int(sum(x.nbytes for x in host_in)),
                    "d2h": int(sum(s["bytes"] for s in lp.prog.outputs)), "steps": n_e2e}
+        st["tensor_core_matmuls"] = [lp.stat("tensor_core_matmuls"), lp.stat("matmuls")]
         lp.close()
         st["phase_ns"] = phases
         return ms / steps, launches, clocks, e2e, st
@@ -266,8 +292,9 @@ def main():
         dist.all_reduce(t_max, op=dist.ReduceOp.MAX)
         dist.all_reduce(e2e_t, op=dist.ReduceOp.MAX)
     ms_step = float(t_max.item())
-    value = w["alg_bytes"] * world / (ms_step * 1e-3) / 1e9
-    achieved = w["alg_bytes"] / (ms_step * 1e-3) / 1e9
+    value = w["alg"] * world / (ms_step * 1e-3) / w["scale"]
+    roof_scale = 1e9 if w["bound"] == "hbm" else 1e12
+    achieved = w["roof_alg"] / (ms_step * 1e-3) / roof_scale
 
     extra = {}
     if rank == 0 and world == 1 and not a.no_extra:
@@ -275,27 +302,29 @@ def main():
             if name == a.workload:
                 continue
             m, _, _, _, _ = run_workload(wl, max(5, a.steps // 2), 3, False)
-            extra[name] = {"GB/s": wl["alg_bytes"] / (m * 1e-3) / 1e9, "ms_per_step": m}
+            extra[name] = {wl["unit"]: wl["alg"] / (m * 1e-3) / wl["scale"], "ms_per_step": m}
 
     if rank == 0:
         peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+        key = "hbm_gbs" if w["bound"] == "hbm" else "bf16_tflops"
         if os.path.exists(peaks_path):
-            peak, peak_src = json.load(open(peaks_path))["hbm_gbs"], "measured (MEASURED_PEAKS.json hbm_gbs)"
+            peak, peak_src = json.load(open(peaks_path))[key], f"measured (MEASURED_PEAKS.json {key})"
         else:
-            peak, peak_src = 6650.0, "fallback"
+            peak, peak_src = (6650.0 if w["bound"] == "hbm" else 1590.0), "fallback"
         cpu = None
         if world == 1 and w["sample"]:
             cv, cdt = cpu_arm(w, 3, 1, cores)
             cpu = {"value": cv, "unit": w["unit"], "cores": cores, "kind": "port",
                    "sample": f"{w['sample']}: {w['sample_frac']:.4f} of the rows, 3 steps, {cdt:.2f} s each"}
         line = dict(base, value=value, ms_per_step=ms_step, clocks=clocks, gpu_launches=launches,
-                    e2e={"value": w["alg_bytes"] * world / float(e2e_t.item()) / 1e9, "unit": w["unit"],
+                    e2e={"value": w["alg"] * world / float(e2e_t.item()) / w["scale"], "unit": w["unit"],
                          "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"]},
-                    roofline={"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                    roofline={"bound": w["bound"], "achieved": achieved, "peak": peak,
+                              "unit": "GB/s" if w["bound"] == "hbm" else "TFLOP/s",
                               "frac": achieved / peak, "traffic": None, "peak_source": peak_src,
                               "kernel": "b2_vm<512> (one launch per step)"},
                     cpu_baseline=cpu, device_ns_per_step=st["device_ns"], grid_barriers=st["barriers"],
-                    phase_end_ns=st["phase_ns"],
+                    phase_end_ns=st["phase_ns"], tensor_core_matmuls=st["tensor_core_matmuls"],
                     other_workloads=extra)
         print(json.dumps(line))
     if world > 1:

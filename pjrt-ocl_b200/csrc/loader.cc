@@ -391,6 +391,7 @@ bool BuildDeviceTables(const VmProgram &p, uint64_t arena_base, DeviceTables *ou
           }
         }
         ++out->n_mma;
+        out->mma_flops += 2ull * (t.p3 ? t.p3 : 1u) * t.p0 * static_cast<uint64_t>(t.p1) * t.p2;
         d.desc = c.PushDesc(m);
         break;
       }

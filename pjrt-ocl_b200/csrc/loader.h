@@ -29,6 +29,7 @@ struct DeviceTables {
   uint32_t n_dead_stores = 0;           // intermediate stores elided
   uint32_t n_mma = 0;                   // matmul tasks
   uint32_t n_mma_tc = 0;                // ... of which the tensor-core path takes
+  uint64_t mma_flops = 0;               // sum over matmul tasks of 2 G M N K
 };
 
 // `arena_base` is the device address of the arena (only its value is used).

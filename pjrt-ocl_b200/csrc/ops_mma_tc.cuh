@@ -55,51 +55,93 @@ __device__ __forceinline__ uint64_t tc_desc(uint32_t saddr, uint32_t lbo_bytes, 
 }
 
 // Bounded wait that also gives up when another role of the lane failed.
+// `backoff_ns`: sleep between polls - for waits that are expected to be long (the
+// epilogue warps during the main loop), so they leave the issue slots to the producers.
 __device__ __forceinline__ bool tc_wait(uint64_t *bar, uint32_t parity, volatile uint32_t *failed,
-                                        unsigned long long budget_ns) {
+                                        unsigned long long budget_ns, uint32_t backoff_ns = 0) {
   if (mbar_try_wait_parity(bar, parity)) return true;
   const unsigned long long t0 = globaltimer_ns();
   for (;;) {
-    for (int i = 0; i < 32; ++i)
+    for (int i = 0; i < 32; ++i) {
       if (mbar_try_wait_parity(bar, parity)) return true;
+      if (backoff_ns) nanosleep_ns(backoff_ns);
+    }
     if (*failed) return false;
     if (globaltimer_ns() - t0 > budget_ns) { *failed = 1u; return false; }
   }
 }
 
-// rows x 64 block of a K-major operand (element (row, k) at src[row * ld + k]) into
-// the swizzled K-major layout: row at 128 B pitch, its 16-byte chunks XORed with row % 8.
+// A producer thread's share of one operand block (ROWS x 64 k), fixed for a whole
+// super-tile: NCH 16-byte chunks, each with a shared-memory offset inside the stage,
+// a source pointer that advances by `step` elements per k block, and the bytes of
+// the chunk that exist (rows / columns beyond the matrix edge are zero-filled).
+//   K-major operand (element (row, k) at src[row * ld + k]): row at 128 B pitch, its
+//   16-byte chunks XORed with row % 8.
+//   MN-major operand (element (row, k) at src[k * ld + row]): 64-row blocks 8192 B
+//   apart, 8-k groups 1024 B apart, inside a group one k per 128 B line with its
+//   chunks XORed with k % 8.
 template <int ROWS>
-__device__ __forceinline__ void tc_load_kmajor(uint32_t sdst, const uint16_t *src, const uint16_t *safe, int64_t ld,
-                                               int64_t rows_valid, int64_t k0, int64_t K, uint32_t ptid) {
-  const uint32_t c = ptid & 7u, r = ptid >> 3;                  // 32 rows per pass
-  const int64_t k = k0 + 8 * c;
-  const uint32_t kbytes = k < K ? static_cast<uint32_t>(min(static_cast<int64_t>(16), 2 * (K - k))) : 0u;
-  const uint32_t d0 = sdst + r * 128u + ((c ^ (r & 7u)) << 4);
+struct TcPlan {
+  static constexpr int NCH = ROWS / 32;
+  const uint16_t *src[NCH];
+  uint32_t dst[NCH];
+  uint32_t bytes[NCH];      // K-major: 16 or 0 by row; MN-major: bytes of the row chunk
+  uint32_t koff[NCH];       // k of the chunk inside the block (its validity in the last, partial block)
+  int64_t step;
+  bool mn;
+};
+
+template <int ROWS>
+__device__ __forceinline__ void tc_plan(TcPlan<ROWS> &p, bool mn, const uint16_t *src, int64_t ld, int64_t rows_valid,
+                                        uint32_t ptid) {
+  p.mn = mn;
+  if (!mn) {
+    const uint32_t c = ptid & 7u, r = ptid >> 3;                // 32 rows per pass
+    p.step = kTcBK;
 #pragma unroll
-  for (int i = 0; i < ROWS / 32; ++i) {
-    const int64_t row = r + 32 * i;
-    const uint32_t bytes = row < rows_valid ? kbytes : 0u;
-    cp_async_16_zfill(d0 + static_cast<uint32_t>(i) * 4096u, bytes ? src + row * ld + k : safe, bytes);
+    for (int i = 0; i < TcPlan<ROWS>::NCH; ++i) {
+      const int64_t row = r + 32 * i;
+      p.dst[i] = r * 128u + ((c ^ (r & 7u)) << 4) + static_cast<uint32_t>(i) * 4096u;
+      p.bytes[i] = row < rows_valid ? 16u : 0u;
+      p.src[i] = src + (row < rows_valid ? row : 0) * ld + 8 * c;
+      p.koff[i] = 8u * c;
+    }
+  } else {
+    constexpr uint32_t CPR = ROWS / 8;                          // chunks per k line
+    constexpr uint32_t KPP = kTcProducers / CPR;                // k lines per pass
+    const uint32_t cm = ptid % CPR, kr = ptid / CPR;
+    const int64_t m = 8 * static_cast<int64_t>(cm);
+    const uint32_t mbytes = m < rows_valid ? static_cast<uint32_t>(min(static_cast<int64_t>(16), 2 * (rows_valid - m))) : 0u;
+    p.step = kTcBK * ld;
+#pragma unroll
+    for (int i = 0; i < TcPlan<ROWS>::NCH; ++i) {
+      const uint32_t kk = kr + KPP * static_cast<uint32_t>(i);
+      p.dst[i] = (cm >> 3) * 8192u + (kk >> 3) * 1024u + (kk & 7u) * 128u + (((cm & 7u) ^ (kk & 7u)) << 4);
+      p.bytes[i] = mbytes;
+      p.src[i] = src + kk * ld + (mbytes ? m : 0);
+      p.koff[i] = kk;
+    }
   }
 }
-// rows x 64 block of an MN-major operand (element (row, k) at src[k * ld + row]) into
-// the swizzled MN-major layout: 64-row blocks 8192 B apart, 8-k groups 1024 B apart,
-// inside a group one k per 128 B line with its chunks XORed with k % 8.
+
+// Issue the thread's chunks of k block `kb` into the stage at `sbase`.
 template <int ROWS>
-__device__ __forceinline__ void tc_load_mnmajor(uint32_t sdst, const uint16_t *src, const uint16_t *safe, int64_t ld,
-                                                int64_t rows_valid, int64_t k0, int64_t K, uint32_t ptid) {
-  constexpr uint32_t CPR = ROWS / 8;                            // chunks per k line
-  constexpr uint32_t KPP = kTcProducers / CPR;                  // k lines per pass
-  const uint32_t cm = ptid % CPR, kr = ptid / CPR;
-  const int64_t m = 8 * static_cast<int64_t>(cm);
-  const uint32_t mbytes = m < rows_valid ? static_cast<uint32_t>(min(static_cast<int64_t>(16), 2 * (rows_valid - m))) : 0u;
+__device__ __forceinline__ void tc_issue(const TcPlan<ROWS> &p, uint32_t sbase, int64_t kb, int64_t K,
+                                         const uint16_t *safe) {
+  const int64_t k0 = kb * kTcBK;
+  if (k0 + kTcBK <= K) {                 // a full k block: validity is the row's alone
 #pragma unroll
-  for (uint32_t i = 0; i < 64u / KPP; ++i) {
-    const uint32_t kk = kr + KPP * i;
-    const uint32_t bytes = k0 + kk < K ? mbytes : 0u;
-    const uint32_t d = sdst + (cm >> 3) * 8192u + (kk >> 3) * 1024u + (kk & 7u) * 128u + (((cm & 7u) ^ (kk & 7u)) << 4);
-    cp_async_16_zfill(d, bytes ? src + (k0 + kk) * ld + m : safe, bytes);
+    for (int i = 0; i < TcPlan<ROWS>::NCH; ++i)
+      cp_async_16_zfill(sbase + p.dst[i], p.src[i] + kb * p.step, p.bytes[i]);
+    return;
+  }
+#pragma unroll
+  for (int i = 0; i < TcPlan<ROWS>::NCH; ++i) {
+    const int64_t k = k0 + p.koff[i];
+    uint32_t b = p.bytes[i];
+    if (k >= K) b = 0u;
+    else if (!p.mn) b = min(b, static_cast<uint32_t>(2 * (K - k)));
+    cp_async_16_zfill(sbase + p.dst[i], b ? p.src[i] + kb * p.step : safe, b);
   }
 }
 
@@ -174,60 +216,84 @@ __device__ __noinline__ bool mma_tc_tiles(const Lane &L, const DTask &t, uint32_
   tc_fence_after_sync();
   const uint32_t tmem = S->tmem_base;
 
+  // Rasterisation. The scheduler hands every lane a contiguous range of tile
+  // *positions* (balanced split of [0, tiles) over the lanes), and the lanes walk
+  // their ranges in step. Executing position p as tile p would make the lanes'
+  // concurrent tiles a sparse scatter over the whole matrix (every block of A and
+  // B live at once: far more than L2 holds, so the operands stream from HBM once
+  // per use). Instead positions are mapped to tiles by a bijection chosen so that
+  // what the lanes execute at the same time is a compact 2-D block of the output:
+  // positions pair up (2u, 2u+1) -> the two halves of a 128 x 256 "wide tile", and
+  // pair u of chunk j at step s gets rank s * k + j (wave-major), ranks filling the
+  // wide-tile grid in groups of kRasterRows rows, column-major inside a group. Any
+  // bijection keeps the result exact - every tile is still computed exactly once
+  // within the task's barrier phase; only the locality depends on the guess k.
+  constexpr int64_t kRasterRows = 16;
+  const int64_t total_tiles = G * per;
+  const int64_t U = per / 2, kch = min(static_cast<int64_t>(P.n_lanes), U);
+  const bool raster = G == 1 && tn % 2 == 0 && U >= 2 * static_cast<int64_t>(P.n_lanes);
+  const int64_t tnw = tn / 2;
+  auto tile_of = [&](int64_t pos) -> int64_t {
+    if (!raster) return pos;
+    const int64_t u = pos >> 1, h = pos & 1;
+    const int64_t j = ((u + 1) * kch - 1) / U;            // chunk of pair u under a balanced split
+    const int64_t lo_j = U * j / kch, st = u - lo_j, c_lo = U / kch;
+    const int64_t rank = st < c_lo ? st * kch + j : c_lo * kch + (lo_j - j * c_lo);
+    const int64_t grp = rank / (kRasterRows * tnw), o = rank % (kRasterRows * tnw);
+    const int64_t rows = min(kRasterRows, tm - grp * kRasterRows);
+    const int64_t row = grp * kRasterRows + o % rows, pc = o / rows;
+    return row * tn + 2 * pc + h;
+  };
   // Enumerate the lane's super-tiles; every role walks the same sequence.
-  auto next_super = [&](uint32_t &tile, int64_t &g, int64_t &r0, int64_t &c0, int &nt) -> bool {
-    while (tile < tile_hi) {
-      g = tile / per;
-      const int64_t loc = tile % per, ti = loc / tn, tj = loc % tn;
-      if (g >= G) { tile = tile_hi; return false; }
-      r0 = ti * kMmaT; c0 = tj * kMmaT;
-      nt = (tj + 1 < tn && tile + 1 < tile_hi) ? 2 : 1;
-      tile += nt;
-      return true;
-    }
-    return false;
+  auto next_super = [&](uint32_t &pos, int64_t &g, int64_t &r0, int64_t &c0, int &nt) -> bool {
+    if (pos >= tile_hi || pos >= total_tiles) { pos = tile_hi; return false; }
+    const int64_t tile = tile_of(pos);
+    g = tile / per;
+    const int64_t loc = tile % per, ti = loc / tn, tj = loc % tn;
+    r0 = ti * kMmaT; c0 = tj * kMmaT;
+    const bool pair = raster ? ((pos & 1u) == 0u) : (tj + 1 < tn);
+    nt = (pair && pos + 1 < tile_hi && static_cast<int64_t>(pos) + 1 < total_tiles) ? 2 : 1;
+    pos += nt;
+    return true;
   };
 
   if (w < 8) {
     // ---------------- producers ----------------
     const uint32_t ptid = L.tid;
-    uint32_t it = 0, sig = 0;                     // stages issued / stages published
+    uint32_t it = 0;                              // stages issued
     uint32_t tile = tile_lo; int64_t g, r0, c0; int nt;
-    auto signal_oldest = [&]() {                  // the oldest unpublished stage has landed: publish it
-      fence_proxy_async_smem();
-      mbar_arrive(&S->full[sig % kTcStages]);
-      ++sig;
-    };
     bool ok = true;
     while (ok && next_super(tile, g, r0, c0, nt)) {
       const uint16_t *Ag = A + g * dm.a_gs + (amn ? r0 : r0 * dm.a_ld);
       const uint16_t *Bg = B + g * dm.b_gs + (bmn ? c0 : c0 * dm.b_ld);
       const int64_t a_rows = min(static_cast<int64_t>(kMmaT), M - r0);
       const int64_t b_rows = min(static_cast<int64_t>(kMmaT) * nt, N - c0);
-      for (int64_t kb = 0; kb < nkb; ++kb, ++it) {
-        const uint32_t s = it % kTcStages;
-        if (!tc_wait(&S->empty[s], ((it / kTcStages) & 1u) ^ 1u, failed, budget)) { ok = false; break; }
-        const uint32_t sa = stage0 + s * kTcStageBytes, sb = sa + kTcABytes;
-        const int64_t k0 = kb * kTcBK;
-        if (amn) tc_load_mnmajor<128>(sa, Ag, A, dm.a_ld, a_rows, k0, K, ptid);
-        else tc_load_kmajor<128>(sa, Ag, A, dm.a_ld, a_rows, k0, K, ptid);
-        if (nt == 2) {
-          if (bmn) tc_load_mnmajor<256>(sb, Bg, B, dm.b_ld, b_rows, k0, K, ptid);
-          else tc_load_kmajor<256>(sb, Bg, B, dm.b_ld, b_rows, k0, K, ptid);
-        } else {
-          if (bmn) tc_load_mnmajor<128>(sb, Bg, B, dm.b_ld, b_rows, k0, K, ptid);
-          else tc_load_kmajor<128>(sb, Bg, B, dm.b_ld, b_rows, k0, K, ptid);
+      TcPlan<128> pa;
+      tc_plan(pa, amn, Ag, dm.a_ld, a_rows, ptid);
+      // The copies of a stage are asynchronous and so is their arrival on the stage's
+      // "full" barrier: a producer never waits for data, only for a free stage, so
+      // every free stage is in flight at once.
+      auto run = [&](auto &pb) {
+        for (int64_t kb = 0; kb < nkb; ++kb, ++it) {
+          const uint32_t s = it % kTcStages;
+          if (!tc_wait(&S->empty[s], ((it / kTcStages) & 1u) ^ 1u, failed, budget)) { ok = false; break; }
+          const uint32_t sa = stage0 + s * kTcStageBytes;
+          tc_issue(pa, sa, kb, K, A);
+          tc_issue(pb, sa + kTcABytes, kb, K, B);
+          cp_async_mbar_arrive(&S->full[s]);
         }
-        cp_async_commit();
-        if (it + 1 - sig == kTcStages - 1) {      // the two newest stages stay in flight
-          cp_async_wait<kTcStages - 2>();
-          signal_oldest();
-        }
+      };
+      if (nt == 2) {
+        TcPlan<256> pb;
+        tc_plan(pb, bmn, Bg, dm.b_ld, b_rows, ptid);
+        run(pb);
+      } else {
+        TcPlan<128> pb;
+        tc_plan(pb, bmn, Bg, dm.b_ld, b_rows, ptid);
+        run(pb);
       }
     }
-    // drain: everything issued lands, the remaining stages are published in order
-    cp_async_wait<0>();
-    while (sig < it) signal_oldest();
+    cp_async_wait_all();                          // nothing of this thread is still in flight
   } else {
     // ---------------- MMA issue (warp 8 lane 0) + epilogue (warps 8-15) ----------------
     const uint32_t ew = w - 8, q = ew & 3u, half = ew >> 2;
@@ -246,6 +312,7 @@ __device__ __noinline__ bool mma_tc_tiles(const Lane &L, const DTask &t, uint32_
         for (int64_t kb = 0; ok && kb < nkb; ++kb, ++it) {
           const uint32_t s = it % kTcStages;
           if (!tc_wait(&S->full[s], (it / kTcStages) & 1u, failed, budget)) { ok = false; break; }
+          fence_proxy_async_smem();               // the producers' (generic-proxy) writes -> the MMA's async-proxy reads
           tc_fence_after_sync();
           const uint32_t sa = stage0 + s * kTcStageBytes, sb = sa + kTcABytes;
           const uint64_t da = amn ? tc_desc(sa, 8192u, 1024u) : tc_desc(sa, 16u, 1024u);
@@ -262,7 +329,7 @@ __device__ __noinline__ bool mma_tc_tiles(const Lane &L, const DTask &t, uint32_
       }
       __syncwarp();
       // epilogue: wait for the accumulator, then each warp drains its lanes x columns
-      if (!tc_wait(&S->acc_full, tcount & 1u, failed, budget)) { ok = false; break; }
+      if (!tc_wait(&S->acc_full, tcount & 1u, failed, budget, 256u)) { ok = false; break; }
       ++tcount;
       __syncwarp();
       tc_fence_after_sync();

@@ -104,6 +104,7 @@ __device__ __forceinline__ void cp_async_8(void *smem_dst, const void *gsrc) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(smem_addr(smem_dst)), "l"(gsrc) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 // Wait until at most N of this thread's most recent groups are still in flight.
 template <int N>
 __device__ __forceinline__ void cp_async_wait() {
@@ -114,6 +115,12 @@ __device__ __forceinline__ void cp_async_wait() {
 // 16-byte asynchronous copy that reads only `src_bytes` (0..16) and zero-fills the rest.
 __device__ __forceinline__ void cp_async_16_zfill(uint32_t smem_dst, const void *gsrc, uint32_t src_bytes) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_dst), "l"(gsrc), "r"(src_bytes) : "memory");
+}
+// One arrival on the mbarrier once every asynchronous copy this thread has issued so
+// far has landed; the thread itself does not wait. (".noinc": the arrival is one of
+// the barrier's expected count.)
+__device__ __forceinline__ void cp_async_mbar_arrive(uint64_t *bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_addr(bar)) : "memory");
 }
 // Allocate `ncols` (power of two >= 32) tensor-memory columns; the base address is
 // written to *smem_dst. One full warp executes each of these. The allocation

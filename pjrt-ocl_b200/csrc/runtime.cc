@@ -410,6 +410,7 @@ uint64_t b2_loaded_stat(const b2_loaded *lp, int which) {
     case 2: return lp->tab.n_dead_stores;
     case 3: return lp->tab.n_mma;
     case 4: return lp->tab.n_mma_tc;
+    case 5: return lp->tab.mma_flops;
     default: return 0;
   }
 }

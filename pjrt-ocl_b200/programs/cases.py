@@ -49,7 +49,7 @@ def dot_general_square(n=8192, nlanes=NLANES, dtype=BF16, transpose_b=False):
     y = (a_.dot_general(x, w, lc=1, rc=1, out_dtype=dtype) if transpose_b
          else a_.matmul(x, w, out_dtype=dtype))
     blob, prog = a_.finish([y], nlanes=nlanes, fold_2byte_views=True)
-    return blob, prog, (3, [("normal", (n, n), DN[dtype]), ("normal", (n, n), DN[dtype], [1.0 / n ** 0.5])])
+    return blob, prog, (3, [("normal", (n, n), DN[dtype]), ("normal", (n, n), DN[dtype], 1.0 / n ** 0.5)])
 
 
 # --------------------------------------------------------------------------

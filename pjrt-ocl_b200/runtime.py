@@ -349,7 +349,8 @@ class LoadedProgram:
         n = lib().b2_loaded_phase_ns(self._h, buf, 64)
         return [int(buf[i]) for i in range(n)]
 
-    _STATS = {"chains": 0, "forwarded": 0 + 1, "dead_stores": 2, "matmuls": 3, "tensor_core_matmuls": 4}
+    _STATS = {"chains": 0, "forwarded": 0 + 1, "dead_stores": 2, "matmuls": 3, "tensor_core_matmuls": 4,
+              "matmul_flops": 5}
 
     def stat(self, name: str) -> int:
         """Load-time mapping facts: chains, forwarded, dead_stores, matmuls, tensor_core_matmuls."""
