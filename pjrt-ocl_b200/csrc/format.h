@@ -154,10 +154,14 @@ struct DRegion {            // loader-built: the 8 input references (a, b, p2..p
 // tc_mode bits: the operands are affine in (batch, row, k) with a unit stride along
 // k ("K-major") or along the row / column index ("MN-major"), 16-byte friendly.
 constexpr uint32_t kTcOk = 1u, kTcAmn = 2u, kTcBmn = 4u;
+// A TMA tensor map (CUtensorMap, opaque to this code), 64-byte aligned as the
+// hardware requires. Built on the host for every tensor-core matmul operand.
+struct alignas(64) DTmap { uint64_t w[16]; };
+
 struct DMma {          // loader-built
   DView va, vb;
   uint32_t tc_mode;    // 0: CUDA-core path only
-  uint32_t pad;
+  int32_t tmap;        // index of the operands' tensor maps (A at tmap, B at tmap + 1) in KParams::tmaps, or -1
   // tensor-core path, in elements: A(g,m,k) = a_off + g*a_gs + (K-major: m*a_ld + k | MN-major: k*a_ld + m),
   // B(g,k,n) = b_off + g*b_gs + (K-major: n*b_ld + k | MN-major: k*b_ld + n)
   int64_t a_ld, b_ld;
@@ -185,6 +189,7 @@ struct KParams {
   const uint64_t *desc;     // loader-built descriptor pool (views, pointers, ...)
   DSync *sync;
   uint8_t *scratch;         // per-program scratch (split reductions, tensor-core staging)
+  const DTmap *tmaps;       // tensor maps of the tensor-core matmul operands
   uint32_t n_lanes;
   uint32_t pad;
   unsigned long long wait_budget_ns;

@@ -388,11 +388,19 @@ bool BuildDeviceTables(const VmProgram &p, uint64_t arena_base, DeviceTables *ou
             m.b_off = ob;
             m.tc_mode = kTcOk | (amn ? kTcAmn : 0u) | (bmn ? kTcBmn : 0u);
             ++out->n_mma_tc;
+            m.tmap = static_cast<int32_t>(out->tmaps.size());
+            out->tmaps.push_back(TmapSpec{d.ptr[1], oa, d.adt, amn, M, K, G, m.a_ld, m.a_gs, 0u});
+            out->tmaps.push_back(TmapSpec{d.ptr[2], ob, d.adt, bmn, N, K, G, m.b_ld, m.b_gs, 0u});
           }
         }
+        if (!(m.tc_mode & kTcOk)) m.tmap = -1;
         ++out->n_mma;
         out->mma_flops += 2ull * (t.p3 ? t.p3 : 1u) * t.p0 * static_cast<uint64_t>(t.p1) * t.p2;
         d.desc = c.PushDesc(m);
+        if (m.tc_mode & kTcOk) {
+          out->tmaps[m.tmap].desc_word = d.desc;
+          out->tmaps[m.tmap + 1].desc_word = d.desc;
+        }
         break;
       }
       case kTopFlashAttn: {

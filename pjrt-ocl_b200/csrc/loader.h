@@ -16,6 +16,19 @@
 
 namespace b2 {
 
+// What the runtime needs to encode the tensor map of one tensor-core matmul operand:
+// a [batch, rows, k] tensor of 16-bit elements, unit stride along k ("K-major") or
+// along rows ("MN-major").
+struct TmapSpec {
+  BufRef base;            // operand buffer (absolute address, or an I/O port)
+  int64_t off;            // elements
+  uint32_t dtype;         // kBF16 / kF16
+  bool mn_major;
+  int64_t rows, k, batch;
+  int64_t ld, gs;         // elements
+  uint32_t desc_word;     // where the owning DMma sits in the descriptor pool (to clear DMma::tmap on failure)
+};
+
 struct DeviceTables {
   std::vector<DTask> tasks;
   std::vector<DEntry> entries;
@@ -23,6 +36,7 @@ struct DeviceTables {
   std::vector<int> input_port;          // per program input: port index or -1 (goes through the arena)
   std::vector<int> output_port;         // per program output
   int n_ports = 0;
+  std::vector<TmapSpec> tmaps;          // two per tensor-core matmul task (A, B), in DMma::tmap order
   // statistics for tests / logging
   uint32_t n_chains = 0;                // fused elementwise chains (length > 1)
   uint32_t n_forwarded = 0;             // operands taken from registers

@@ -36,7 +36,6 @@ constexpr int kTcBBytes = 256 * 128;         // up to 256 rows x 128 B
 constexpr int kTcStageBytes = kTcABytes + kTcBBytes;
 constexpr int kTcProducers = 256;
 constexpr uint32_t kTcCols = 256;            // tensor-memory columns held (f32 accumulator 128 x 256)
-constexpr uint32_t kStatusTcTimeout = 0x7C01u;
 
 struct TcShared {                            // lives in the reduction scratch of the system area
   uint64_t full[kTcStages];
@@ -191,6 +190,8 @@ __device__ __noinline__ bool mma_tc_tiles(const Lane &L, const DTask &t, uint32_
   const int64_t tn = (N + kMmaT - 1) / kMmaT, tm = (M + kMmaT - 1) / kMmaT, per = tm * tn;
   const int64_t nkb = (K + kTcBK - 1) / kTcBK;
   const bool vec_store = (reinterpret_cast<uintptr_t>(dst) & 15u) == 0 && N % 8 == 0;
+  const bool use_tma = dm.tmap >= 0;     // operands fetched by the TMA unit (else per-thread asynchronous copies)
+  const DTmap *tm_a = use_tma ? P.tmaps + dm.tmap : nullptr, *tm_b = use_tma ? tm_a + 1 : nullptr;
 
   B2_DYN_SMEM(sm);
   TcShared *S = reinterpret_cast<TcShared *>(sm + kSmemRed);
@@ -201,7 +202,7 @@ __device__ __noinline__ bool mma_tc_tiles(const Lane &L, const DTask &t, uint32_
 
   __syncthreads();   // the scratch slot is free
   if (L.tid == 0) {
-    for (int s = 0; s < kTcStages; ++s) { mbar_init(&S->full[s], kTcProducers); mbar_init(&S->empty[s], 1); }
+    for (int s = 0; s < kTcStages; ++s) { mbar_init(&S->full[s], use_tma ? 1u : static_cast<uint32_t>(kTcProducers)); mbar_init(&S->empty[s], 1); }
     mbar_init(&S->acc_full, 1);
     mbar_init(&S->acc_empty, 256);
     S->failed = 0u;
@@ -257,8 +258,40 @@ __device__ __noinline__ bool mma_tc_tiles(const Lane &L, const DTask &t, uint32_
     return true;
   };
 
-  if (w < 8) {
-    // ---------------- producers ----------------
+  if (w < 8 && use_tma) {
+    // ---------------- producer: one thread drives the TMA unit ----------------
+    // Per stage: the A block (one 128-row box, or two 64-row-wide boxes when the rows
+    // are the unit-stride dimension) and the B block likewise, each box landing as
+    // one 128-byte-swizzled [rows][64] image - exactly the layout of the per-thread
+    // path below. Boxes past the matrix edge arrive zero-filled.
+    if (L.tid == 0) {
+      uint32_t it = 0;
+      uint32_t tile = tile_lo; int64_t g, r0, c0; int nt;
+      bool ok = true;
+      while (ok && next_super(tile, g, r0, c0, nt)) {
+        const int32_t gi = static_cast<int32_t>(g), ri = static_cast<int32_t>(r0), ci = static_cast<int32_t>(c0);
+        for (int64_t kb = 0; kb < nkb; ++kb, ++it) {
+          const uint32_t s = it % kTcStages;
+          if (!tc_wait(&S->empty[s], ((it / kTcStages) & 1u) ^ 1u, failed, budget)) { ok = false; break; }
+          const uint32_t sa = stage0 + s * kTcStageBytes, sb = sa + kTcABytes;
+          const int32_t k0 = static_cast<int32_t>(kb * kTcBK);
+          if (amn) {
+            tma_load_3d(sa, tm_a, ri, k0, gi, &S->full[s]);
+            tma_load_3d(sa + 8192u, tm_a, ri + 64, k0, gi, &S->full[s]);
+          } else {
+            tma_load_3d(sa, tm_a, k0, ri, gi, &S->full[s]);
+          }
+          if (bmn) {
+            for (int b = 0; b < 2 * nt; ++b) tma_load_3d(sb + 8192u * b, tm_b, ci + 64 * b, k0, gi, &S->full[s]);
+          } else {
+            for (int b = 0; b < nt; ++b) tma_load_3d(sb + 16384u * b, tm_b, k0, ci + 128 * b, gi, &S->full[s]);
+          }
+          mbar_arrive_tx(&S->full[s], static_cast<uint32_t>(kTcABytes + 16384 * nt));
+        }
+      }
+    }
+  } else if (w < 8) {
+    // ---------------- producers: per-thread asynchronous copies ----------------
     const uint32_t ptid = L.tid;
     uint32_t it = 0;                              // stages issued
     uint32_t tile = tile_lo; int64_t g, r0, c0; int nt;
@@ -371,7 +404,7 @@ __device__ __noinline__ bool mma_tc_tiles(const Lane &L, const DTask &t, uint32_
     tmem_dealloc(tmem, kTcCols);
   }
   if (L.tid == 0) {
-    if (S->failed) set_status(P, kStatusTcTimeout, L.lane, tile_lo, tile_hi);
+    if (S->failed) set_status(P, kStTensorTimeout, L.lane, tile_lo, kTopMma);
     for (int s = 0; s < kTcStages; ++s) { mbar_inval(&S->full[s]); mbar_inval(&S->empty[s]); }
     mbar_inval(&S->acc_full);
     mbar_inval(&S->acc_empty);

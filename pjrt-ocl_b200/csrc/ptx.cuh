@@ -122,6 +122,20 @@ __device__ __forceinline__ void cp_async_16_zfill(uint32_t smem_dst, const void 
 __device__ __forceinline__ void cp_async_mbar_arrive(uint64_t *bar) {
   asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_addr(bar)) : "memory");
 }
+// TMA: one box of a rank-3 tensor (coordinates innermost first) global -> shared;
+// the mbarrier receives the box's bytes as completed transactions. The inner
+// coordinate times the element size must be a multiple of 16 bytes.
+__device__ __forceinline__ void tma_load_3d(uint32_t smem_dst, const void *tmap, int32_t x, int32_t y, int32_t z,
+                                            uint64_t *bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+      ::"r"(smem_dst), "l"(tmap), "r"(x), "r"(y), "r"(z), "r"(smem_addr(bar))
+      : "memory");
+}
+// One arrival that also announces `bytes` of transactions (issued before or after it).
+__device__ __forceinline__ void mbar_arrive_tx(uint64_t *bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
+}
 // Allocate `ncols` (power of two >= 32) tensor-memory columns; the base address is
 // written to *smem_dst. One full warp executes each of these. The allocation
 // permit is never relinquished: a lane allocates again for its next matmul task,

@@ -7,6 +7,9 @@
 // loaded program with constants uploaded once; <= 64 zero-copy I/O ports;
 // synchronous execute; size-keyed pool for result buffers.
 #include <cuda_runtime.h>
+#ifndef B2_EMU
+#include <cuda.h>   // CUtensorMap types only; the encoder is reached through the runtime's driver entry point
+#endif
 
 #include <cstdarg>
 #include <cstddef>
@@ -41,6 +44,56 @@ std::string CudaMsg(const char *what, cudaError_t e) {
 }
 
 constexpr size_t kPoolPerSize = 4;  // runtime.h:304
+
+// Encode the TMA tensor map of one tensor-core matmul operand: a rank-3 tensor
+// {inner, outer, batch} of 16-bit elements whose inner dimension is the unit-stride
+// one (k for a K-major operand, the row / column index for an MN-major one), read
+// in boxes of 64 inner elements (128 bytes: one swizzle line) x 128 or 64 outer
+// rows with the 128-byte swizzle the tensor core expects. Elements beyond the
+// tensor's edge read as zero. Returns false when the tensor cannot be described
+// (the matmul then loads with per-thread asynchronous copies instead).
+bool EncodeTmap(const b2::TmapSpec &s, const void *base, b2::DTmap *out) {
+  if (s.batch > 1 && s.gs <= 0) return false;               // a batch-broadcast operand
+  if (reinterpret_cast<uintptr_t>(base) % 16) return false;
+  const uint64_t inner = static_cast<uint64_t>(s.mn_major ? s.rows : s.k);
+  const uint64_t outer = static_cast<uint64_t>(s.mn_major ? s.k : s.rows);
+  const uint64_t stride1 = static_cast<uint64_t>(s.ld) * 2;
+  const uint64_t stride2 = s.batch > 1 ? static_cast<uint64_t>(s.gs) * 2 : stride1 * outer;
+  if (stride1 % 16 || stride2 % 16 || stride1 >= (1ull << 40) || stride2 >= (1ull << 40)) return false;
+#ifdef B2_EMU
+  // emulation: a plain record the emulated copy engine reads back
+  std::memset(out, 0, sizeof(*out));
+  out->w[0] = reinterpret_cast<uint64_t>(base);
+  out->w[1] = inner; out->w[2] = outer; out->w[3] = static_cast<uint64_t>(s.batch);
+  out->w[4] = stride1; out->w[5] = stride2;
+  out->w[6] = 64; out->w[7] = s.mn_major ? 64 : 128;
+  return true;
+#else
+  typedef CUresult (*EncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                               const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                               CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+  static EncodeFn encode = [] {
+    void *fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      fn = nullptr;
+    return reinterpret_cast<EncodeFn>(fn);
+  }();
+  if (!encode) return false;
+  static_assert(sizeof(CUtensorMap) == sizeof(b2::DTmap), "tensor map size");
+  const cuuint64_t dims[3] = {inner, outer, static_cast<cuuint64_t>(s.batch)};
+  const cuuint64_t strides[2] = {stride1, stride2};
+  const cuuint32_t box[3] = {64u, s.mn_major ? 64u : 128u, 1u};
+  const cuuint32_t estr[3] = {1u, 1u, 1u};
+  const CUresult r = encode(reinterpret_cast<CUtensorMap *>(out),
+                            s.dtype == b2::kBF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
+                            const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+#endif
+}
 
 }  // namespace
 
@@ -106,6 +159,9 @@ struct b2_loaded {
   b2::VmLane *d_lanes = nullptr;
   int32_t *d_aux = nullptr;
   uint64_t *d_desc = nullptr;
+  b2::DTmap *d_tmaps = nullptr;          // tensor maps of the tensor-core matmul operands
+  std::vector<b2::DTmap> h_tmaps;
+  std::vector<const void *> tmap_base;   // the operand address each map was encoded for
   b2::DSync *d_sync = nullptr;
   b2::DSync *h_sync = nullptr;  // pinned mirror
   uint64_t launches = 0;
@@ -116,7 +172,7 @@ struct b2_loaded {
   ~b2_loaded() {
     if (rt) rt->Bind();
     cudaFree(arena); cudaFree(d_tasks); cudaFree(d_entries); cudaFree(d_lanes);
-    cudaFree(d_aux); cudaFree(d_desc); cudaFree(d_sync);
+    cudaFree(d_aux); cudaFree(d_desc); cudaFree(d_sync); cudaFree(d_tmaps);
     if (h_sync) cudaFreeHost(h_sync);
   }
 };
@@ -144,8 +200,24 @@ b2_status Enqueue(b2_loaded *lp, const b2::IoTable &io, cudaStream_t stream, std
     if (e != cudaSuccess) { *err = CudaMsg("sync reset", e); return B2_INTERNAL; }
     lp->sync_dirty = false;
   }
+  // Tensor maps carry the operand's address: the ones over I/O ports follow the
+  // addresses bound for this launch.
+  for (size_t i = 0; i < lp->tab.tmaps.size(); ++i) {
+    const b2::TmapSpec &sp = lp->tab.tmaps[i];
+    if (!(sp.base & b2::kPortBit)) continue;
+    const uint8_t *base = static_cast<const uint8_t *>(io.p[sp.base & (b2::kMaxIoPorts - 1)]) + sp.off * 2;
+    if (base == lp->tmap_base[i]) continue;
+    if (!EncodeTmap(sp, base, &lp->h_tmaps[i])) {
+      *err = "matmul operand bound at an address the tensor map cannot describe (needs 16-byte alignment)";
+      return B2_INVALID_ARGUMENT;
+    }
+    lp->tmap_base[i] = base;
+    e = cudaMemcpyAsync(lp->d_tmaps + i, &lp->h_tmaps[i], sizeof(b2::DTmap), cudaMemcpyHostToDevice, stream);
+    if (e != cudaSuccess) { *err = CudaMsg("tensor map upload", e); return B2_INTERNAL; }
+  }
   b2::KParams kp;
   std::memset(&kp, 0, sizeof(kp));
+  kp.tmaps = lp->d_tmaps;
   kp.tasks = lp->d_tasks;
   kp.entries = lp->d_entries;
   kp.lanes = lp->d_lanes;
@@ -371,8 +443,27 @@ b2_status b2_program_load(b2_runtime *rt, b2_program *prog, b2_loaded **out, cha
     SetErr(err, err_cap, "load: " + m);
     return unimpl ? B2_UNIMPLEMENTED : B2_INVALID_ARGUMENT;
   }
+  // Tensor maps of the tensor-core matmul operands. Arena operands are final here;
+  // port operands get a placeholder (the arena) and are re-encoded at bind. A task
+  // whose operand cannot be described keeps the per-thread copy path.
+  lp->h_tmaps.resize(lp->tab.tmaps.size());
+  lp->tmap_base.assign(lp->tab.tmaps.size(), nullptr);
+  for (size_t i = 0; i + 1 < lp->tab.tmaps.size(); i += 2) {
+    bool ok = true;
+    for (size_t j = i; j < i + 2; ++j) {
+      const b2::TmapSpec &sp = lp->tab.tmaps[j];
+      const bool port = (sp.base & b2::kPortBit) != 0;
+      const uint8_t *base = port ? lp->arena : reinterpret_cast<const uint8_t *>(static_cast<uintptr_t>(sp.base)) + sp.off * 2;
+      ok = ok && EncodeTmap(sp, base, &lp->h_tmaps[j]);
+      lp->tmap_base[j] = port ? nullptr : base;
+    }
+    if (!ok) {
+      b2::DMma *m = reinterpret_cast<b2::DMma *>(&lp->tab.desc[lp->tab.tmaps[i].desc_word]);
+      m->tmap = -1;
+    }
+  }
   std::vector<int32_t> aux = p.aux;
-  if ((e = Upload(&lp->d_tasks, lp->tab.tasks)) != cudaSuccess || (e = Upload(&lp->d_entries, lp->tab.entries)) != cudaSuccess ||
+  if ((e = Upload(&lp->d_tmaps, lp->h_tmaps)) != cudaSuccess || (e = Upload(&lp->d_tasks, lp->tab.tasks)) != cudaSuccess || (e = Upload(&lp->d_entries, lp->tab.entries)) != cudaSuccess ||
       (e = Upload(&lp->d_lanes, p.lane_tab)) != cudaSuccess || (e = Upload(&lp->d_aux, aux)) != cudaSuccess ||
       (e = Upload(&lp->d_desc, lp->tab.desc)) != cudaSuccess ||
       (e = cudaMalloc(reinterpret_cast<void **>(&lp->d_sync), sizeof(b2::DSync))) != cudaSuccess ||
