@@ -44,12 +44,12 @@ N_C2 = 8192 * 4096
 # name -> program blob, CPU-arm sample blob (+ fraction of the full workload it is),
 # algorithmic bytes per step, metric
 def _wl(program, metric, unit, alg, scale, bound, dtype, desc, roof_alg=None, sample=None, sample_frac=0.0,
-        secondary=False):
+        secondary=False, plan=None):
     """alg: algorithmic units one step processes (bytes, flops or tokens); value = alg / seconds / scale.
     roof_alg: bytes (bound "hbm") or flops (bound "tensor") of one step, for the roofline fraction."""
     return dict(program=program, metric=metric, unit=unit, alg=alg, scale=scale, bound=bound, dtype=dtype, desc=desc,
                 roof_alg=alg if roof_alg is None else roof_alg, sample=sample, sample_frac=sample_frac,
-                secondary=secondary)
+                secondary=secondary, plan=plan)
 
 
 # config 5 block: 8 x 2048 tokens, d_model 1024, 16 heads x 64, FFN 4096
@@ -75,14 +75,15 @@ WORKLOADS = {
     "dot_bf16_4096": _wl("dot_bf16_4096", "dot_general TFLOP/s", "TFLOP/s", 2 * 4096 ** 3, 1e12, "tensor", "bf16",
                          "one dot_general bf16 4096 x 4096 x 4096", secondary=True),
     "c3_mlp": _wl("c3_mlp_step_bf16", "dot_general TFLOP/s", "TFLOP/s", _C3_FLOPS, 1e12, "tensor", "bf16",
-                  "config 3: 3-layer MLP forward + grad of MSE + SGD step, batch 8192, 1024-4096-4096-1024, bf16"),
+                  "config 3: 3-layer MLP forward + grad of MSE + SGD step, batch 8192, 1024-4096-4096-1024, bf16; "
+                  "on N GPUs: local-batch gradients, NCCL all-reduce, SGD program", plan="c3"),
     "c5_block": _wl("c5_block_bf16", "transformer-block tokens/s per B200", "tokens/s", _C5_TOK, 1.0, "tensor", "bf16",
                     "config 5: pre-norm decoder block forward, batch 8 x seq 2048, d_model 1024, 16 x 64 heads, "
                     "causal flash attention, GELU FFN 4096, bf16",
-                    roof_alg=_C5_MM_FLOPS + _C5_ATT_FLOPS),
+                    roof_alg=_C5_MM_FLOPS + _C5_ATT_FLOPS, plan="c5_block"),
     "c5_decode": _wl("c5_decode_bf16", "transformer-block tokens/s per B200", "tokens/s", 32, 1.0, "hbm", "bf16",
                      "config 5 decode step: batch 32, KV cache 2048; bytes = weights + KV cache read once",
-                     roof_alg=2 * (4 * 1024 * 1024 + 2 * 1024 * 4096) + 2 * 32 * 16 * 2048 * 64 * 2),
+                     roof_alg=2 * (4 * 1024 * 1024 + 2 * 1024 * 4096) + 2 * 32 * 16 * 2048 * 64 * 2, plan="c5_decode"),
 }
 
 
@@ -220,10 +221,18 @@ def main():
     stream = torch.cuda.Stream()
     torch.cuda.set_stream(stream)
 
+    dp = importlib.import_module("pjrt-ocl_b200.dataparallel")
+
     def run_workload(wl: dict, steps: int, warmup: int, want_e2e: bool):
-        man = manifest()[wl["program"]]
-        lp = vm.LoadedProgram.Load(rt, vm.VmProgram.Parse(load_blob(wl["program"])))
+        plan = dp.PLANS.get(wl["plan"]) if wl["plan"] else None
+        name = plan.rank_program(world) if plan else wl["program"]
+        man = manifest()[name]
+        lp = vm.LoadedProgram.Load(rt, vm.VmProgram.Parse(load_blob(name)))
         host_in = [np.ascontiguousarray(x) for x in gen_inputs.gen_all(man["seed"], man["items"])]
+        if plan and world > 1:
+            # inputs listed at the global batch are sliced; per-shard listings already have the local shape
+            host_in = [dp.shard_rows(x, rank, world) if (i in plan.batch_inputs and x.nbytes != lp.prog.inputs[i]["bytes"])
+                       else x for i, x in enumerate(host_in)]
         pin_in = []
         for x in host_in:
             t = torch.empty(max(x.nbytes, 1), dtype=torch.uint8, pin_memory=True)
@@ -235,12 +244,25 @@ def main():
         torch.cuda.synchronize()
         ins = [t.data_ptr() for t in dev_in]
         outs = [t.data_ptr() for t in dev_out]
-        scalar = dev_out[-1][:4].view(torch.float32) if wl["program"].startswith("c2_chain") else None
+        # the exchange step of the configuration, if it has one (NCCL, on the launching stream)
+        reduce_views, lp2, ins2, outs2, dev_out2 = [], None, None, None, None
+        if world > 1:
+            if plan and plan.reduce_outputs:
+                reduce_views = [dev_out[i][:lp.prog.outputs[i]["bytes"]].view(torch.float32) for i in plan.reduce_outputs]
+            elif wl["program"].startswith("c2_chain"):
+                reduce_views = [dev_out[-1][:4].view(torch.float32)]
+            if plan and plan.apply_program:
+                lp2 = vm.LoadedProgram.Load(rt, vm.VmProgram.Parse(load_blob(plan.apply_program)))
+                dev_out2 = [torch.empty(max(s["bytes"], 16), dtype=torch.uint8, device="cuda") for s in lp2.prog.outputs]
+                ins2 = [ins[i] for i in plan.apply_inputs] + [outs[i] for i in plan.reduce_outputs[plan.apply_skip:]]
+                outs2 = [t.data_ptr() for t in dev_out2]
 
         def step():
             lp.ExecuteDeviceAsync(ins, outs, stream.cuda_stream)
-            if world > 1 and scalar is not None:
-                dist.all_reduce(scalar)           # the only cross-GPU step of this configuration
+            for v in reduce_views:
+                dist.all_reduce(v)
+            if lp2 is not None:
+                lp2.ExecuteDeviceAsync(ins2, outs2, stream.cuda_stream)
 
         sampler = ClockSampler(local_rank)
         sampler.start()                       # nvidia-smi needs a moment to start sampling
@@ -252,7 +274,7 @@ def main():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
-        launches0 = lp.launch_count
+        launches0 = lp.launch_count + (lp2.launch_count if lp2 else 0)
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record(stream)
         for _ in range(steps):
@@ -265,21 +287,47 @@ def main():
         ms = e0.elapsed_time(e1)
         clocks = sampler.stop()
         lp.Status()
-        launches = lp.launch_count - launches0
+        launches = lp.launch_count + (lp2.launch_count if lp2 else 0) - launches0
         e2e = None
         if want_e2e:
-            np_in = [t.numpy()[:x.nbytes].view(x.dtype).reshape(x.shape) for t, x in zip(pin_in, host_in)]
-            np_out = [t.numpy()[:s["bytes"]] for t, s in zip(pin_out, lp.prog.outputs)]
-            for _ in range(2):
-                lp.Execute(np_in, out=np_out)
             n_e2e = max(3, min(steps, 10))
-            torch.cuda.synchronize()
-            t0 = time.perf_counter()
-            for _ in range(n_e2e):
-                lp.Execute(np_in, out=np_out)
-            dt = (time.perf_counter() - t0) / n_e2e
-            e2e = {"seconds": dt, "h2d": int(sum(x.nbytes for x in host_in)),
-                   "d2h": int(sum(s["bytes"] for s in lp.prog.outputs)), "steps": n_e2e}
+            h2d = int(sum(x.nbytes for x in host_in))
+            d2h = int(sum(s["bytes"] for s in lp.prog.outputs))
+            if world == 1:
+                # the call a user makes: host arrays in, host arrays out (copies inside)
+                np_in = [t.numpy()[:x.nbytes].view(x.dtype).reshape(x.shape) for t, x in zip(pin_in, host_in)]
+                np_out = [t.numpy()[:s["bytes"]] for t, s in zip(pin_out, lp.prog.outputs)]
+                for _ in range(2):
+                    lp.Execute(np_in, out=np_out)
+                torch.cuda.synchronize()
+                t0 = time.perf_counter()
+                for _ in range(n_e2e):
+                    lp.Execute(np_in, out=np_out)
+                dt = (time.perf_counter() - t0) / n_e2e
+            else:
+                # per rank: pinned inputs -> device, the data-parallel step, first result -> pinned host
+                src = dev_out2 if dev_out2 is not None else dev_out
+                pin_res = [torch.empty(d.numel(), dtype=torch.uint8, pin_memory=True) for d in src]
+
+                def e2e_step():
+                    for d, p_ in zip(dev_in, pin_in):
+                        d.copy_(p_, non_blocking=True)
+                    step()
+                    for p_, d in zip(pin_res, src):
+                        p_.copy_(d, non_blocking=True)
+                    torch.cuda.synchronize()
+                for _ in range(2):
+                    e2e_step()
+                dist.barrier()
+                t0 = time.perf_counter()
+                for _ in range(n_e2e):
+                    e2e_step()
+                dt = (time.perf_counter() - t0) / n_e2e
+                if dev_out2 is not None:
+                    d2h = int(sum(s["bytes"] for s in lp2.prog.outputs))
+            e2e = {"seconds": dt, "h2d": h2d, "d2h": d2h, "steps": n_e2e}
+        if lp2 is not None:
+            lp2.close()
         st["tensor_core_matmuls"] = [lp.stat("tensor_core_matmuls"), lp.stat("matmuls")]
         lp.close()
         st["phase_ns"] = phases
@@ -292,9 +340,17 @@ def main():
         dist.all_reduce(t_max, op=dist.ReduceOp.MAX)
         dist.all_reduce(e2e_t, op=dist.ReduceOp.MAX)
     ms_step = float(t_max.item())
-    value = w["alg"] * world / (ms_step * 1e-3) / w["scale"]
+    plan = dp.PLANS.get(w["plan"]) if w["plan"] else None
+    strong = bool(plan and plan.scaling == "strong")
+    total_alg = w["alg"] if strong else w["alg"] * world          # strong scaling: the global batch is fixed
+    value = total_alg / (ms_step * 1e-3) / w["scale"]
+    base["scaling"] = "strong" if strong else "weak"
+    base["config"]["parallelism"] = ("single GPU" if world == 1 else
+                                     f"dp{world}: {'batch shards' if strong else 'replicas'}"
+                                     + (", NCCL all-reduce between the gradient and SGD programs" if plan and plan.apply_program else
+                                        ", scalar all-reduce" if w["program"].startswith("c2_chain") else ", no exchange step"))
     roof_scale = 1e9 if w["bound"] == "hbm" else 1e12
-    achieved = w["roof_alg"] / (ms_step * 1e-3) / roof_scale
+    achieved = (w["roof_alg"] / world if strong else w["roof_alg"]) / (ms_step * 1e-3) / roof_scale   # per GPU
 
     extra = {}
     if rank == 0 and world == 1 and not a.no_extra:
@@ -317,7 +373,7 @@ def main():
             cpu = {"value": cv, "unit": w["unit"], "cores": cores, "kind": "port",
                    "sample": f"{w['sample']}: {w['sample_frac']:.4f} of the rows, 3 steps, {cdt:.2f} s each"}
         line = dict(base, value=value, ms_per_step=ms_step, clocks=clocks, gpu_launches=launches,
-                    e2e={"value": w["alg"] * world / float(e2e_t.item()) / w["scale"], "unit": w["unit"],
+                    e2e={"value": total_alg / float(e2e_t.item()) / w["scale"], "unit": w["unit"],
                          "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"]},
                     roofline={"bound": w["bound"], "achieved": achieved, "peak": peak,
                               "unit": "GB/s" if w["bound"] == "hbm" else "TFLOP/s",

@@ -140,6 +140,9 @@ struct DMove {
   DView view;          // linear side index -> strided side index (in elements)
   uint32_t esz;        // element size in bytes
   uint32_t chunk;      // elements per 16-byte chunk when vector-movable, else 0
+  uint32_t transposed; // gather whose innermost linear dim is strided on the other side while the next
+                       // one is contiguous there (a transpose): moved through shared-memory tiles
+  uint32_t pad;
   uint32_t n_idx;      // DYN_*: number of runtime start indices (rank), else 0
   uint32_t is64;       // DYN_*: start scalars are i64
   int32_t clamp_max[8];

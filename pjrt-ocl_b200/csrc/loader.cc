@@ -315,6 +315,10 @@ bool BuildDeviceTables(const VmProgram &p, uint64_t arena_base, DeviceTables *ou
         if (dyn)
           for (uint32_t k = 0; ok && k < m.n_idx; ++k) ok = true;  // base alignment is checked per launch
         m.chunk = ok ? chunk : 0u;
+        // a transpose: dst[..., r, c] = src[... + r + c * ld], 2- or 4-byte elements
+        m.transposed = (d.op == kTopGather && !m.chunk && (m.esz == 2 || m.esz == 4) && v.rank >= 2 &&
+                        v.stride[v.rank - 2] == 1 && v.stride[v.rank - 1] > 1 && v.dim[v.rank - 1] >= 32 &&
+                        v.dim[v.rank - 2] >= 8) ? 1u : 0u;
         d.desc = c.PushDesc(m);
         break;
       }
@@ -413,6 +417,13 @@ bool BuildDeviceTables(const VmProgram &p, uint64_t arena_base, DeviceTables *ou
         if (qv) { if (!ViewFromAux(p, qv - 1, &f.vq, err)) return fail_unimpl(*err); f.has_q = 1; }
         if (kv) { if (!ViewFromAux(p, kv - 1, &f.vk, err)) return fail_unimpl(*err); f.has_k = 1; }
         if (vv) { if (!ViewFromAux(p, vv - 1, &f.vv, err)) return fail_unimpl(*err); f.has_v = 1; }
+        // tensor-core eligibility: 16-bit floats, plain operands, head_dim 64, 16-byte friendly rows
+        if ((d.adt == kBF16 || d.adt == kF16) && (d.dt == kBF16 || d.dt == kF16 || d.dt == kF32) && !qv && !kv && !vv &&
+            x[3] == 64 && x[2] % 8 == 0 && x[1] >= 16 && x[2] > 0) {
+          f.tc_mode = 1;
+          ++out->n_flash_tc;
+        }
+        ++out->n_flash;
         d.desc = c.PushDesc(f);
         break;
       }

@@ -44,6 +44,7 @@ struct DeviceTables {
   uint32_t n_mma = 0;                   // matmul tasks
   uint32_t n_mma_tc = 0;                // ... of which the tensor-core path takes
   uint64_t mma_flops = 0;               // sum over matmul tasks of 2 G M N K
+  uint32_t n_flash = 0, n_flash_tc = 0; // flash-attention tasks / ... on the tensor-core path
 };
 
 // `arena_base` is the device address of the arena (only its value is used).

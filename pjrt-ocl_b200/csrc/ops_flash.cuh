@@ -38,6 +38,93 @@ __device__ __noinline__ void flash_simt_tiles(const Lane &L, const DTask &t, uin
   float *qs = reinterpret_cast<float *>(L.smem + kSmemSys) + static_cast<size_t>(w) * kFlashMaxHd;
   const int64_t hi = min(static_cast<int64_t>(tile_hi), H * T);
   __syncthreads();  // workspace handover from the previous op
+  if ((hi - static_cast<int64_t>(tile_lo)) * 2 <= static_cast<int64_t>(nw) && hd <= 128) {
+    // Few query rows for this lane (a decode step): a warp per row would leave most
+    // warps idle and each row's keys in one warp's serial loop. Instead the lane's
+    // warps split every row's keys (chunk c0 = 32 w, 32 (w + nw), ...), each keeps
+    // its own running (max, sum, accumulator), and the partial results are merged
+    // through shared memory: out = sum_w o_w e^{m_w - M} / sum_w l_w e^{m_w - M}.
+    float *q_all = reinterpret_cast<float *>(L.smem + kSmemSys);                     // [hd]
+    float *ml = q_all + kFlashMaxHd;                                                 // [nw][2]
+    float *os = ml + 2 * 32;                                                         // [nw][hd]
+    const bool plain = !df.has_q && !df.has_k && !df.has_v && (adt == kBF16 || adt == kF16);
+    for (int64_t tile = tile_lo; tile < hi; ++tile) {
+      const int64_t g = tile / T, m = tile % T;
+      const int64_t qpos = m + (C - T);
+      const int64_t c_end = causal ? min(C, qpos + 1) : C;
+      __syncthreads();
+      for (int64_t d = L.tid; d < hd; d += L.nthr) {
+        const int64_t qi = (g * T + m) * hd + d;
+        q_all[d] = loadf(Q, adt, df.has_q ? view_index(df.vq, static_cast<uint32_t>(qi)) : qi);
+      }
+      __syncthreads();
+      float m_run = -INFINITY, l_run = 0.0f;
+      float o[4] = {0.0f, 0.0f, 0.0f, 0.0f};                                        // columns l, l+32, l+64, l+96
+      for (int64_t c0 = static_cast<int64_t>(kWarp) * w; c0 < c_end; c0 += static_cast<int64_t>(kWarp) * nw) {
+        const int64_t c = c0 + l;
+        float sc = -INFINITY;
+        if (c < c_end) {
+          float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
+          if (plain) {
+            const uint16_t *kp = reinterpret_cast<const uint16_t *>(Kp) + g * hd * C + c;
+            for (int64_t d = 0; d < hd; d += 4) {        // four independent loads in flight
+              const uint32_t k0 = kp[d * C], k1 = kp[(d + 1) * C], k2 = kp[(d + 2) * C], k3 = kp[(d + 3) * C];
+              const bool bf = adt == kBF16;
+              a0 = fmaf(q_all[d], bf ? bf16_bits_to_f32(k0) : f16_bits_to_f32(k0), a0);
+              a1 = fmaf(q_all[d + 1], bf ? bf16_bits_to_f32(k1) : f16_bits_to_f32(k1), a1);
+              a2 = fmaf(q_all[d + 2], bf ? bf16_bits_to_f32(k2) : f16_bits_to_f32(k2), a2);
+              a3 = fmaf(q_all[d + 3], bf ? bf16_bits_to_f32(k3) : f16_bits_to_f32(k3), a3);
+            }
+          } else {
+            for (int64_t d = 0; d < hd; ++d) {
+              const int64_t ki = (g * hd + d) * C + c;
+              a0 = fmaf(q_all[d], loadf(Kp, adt, df.has_k ? view_index(df.vk, static_cast<uint32_t>(ki)) : ki), a0);
+            }
+          }
+          sc = ((a0 + a1) + (a2 + a3)) * scale;
+        }
+        const float cmax = warp_reduce(sc, [](float a, float b) { return fmaxf(a, b); });
+        const float m_new = fmaxf(m_run, cmax);
+        const float alpha = (m_run == -INFINITY) ? 0.0f : expf(m_run - m_new);
+        const float p = (c < c_end) ? expf(sc - m_new) : 0.0f;
+        const float psum = warp_reduce(p, [](float a, float b) { return a + b; });
+        l_run = l_run * alpha + psum;
+        m_run = m_new;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) o[j] *= alpha;
+        const int64_t cn = min(static_cast<int64_t>(kWarp), c_end - c0);
+        for (int64_t cc = 0; cc < cn; ++cc) {
+          const float pc = __shfl_sync(0xffffffffu, p, static_cast<int>(cc));
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int64_t d = l + j * kWarp;
+            if (d < hd) {
+              const int64_t vi = (g * C + c0 + cc) * hd + d;
+              o[j] = fmaf(pc, loadf(V, adt, df.has_v ? view_index(df.vv, static_cast<uint32_t>(vi)) : vi), o[j]);
+            }
+          }
+        }
+      }
+      if (l == 0) { ml[2 * w] = m_run; ml[2 * w + 1] = l_run; }
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (l + j * kWarp < hd) os[w * kFlashMaxHd + l + j * kWarp] = o[j];
+      __syncthreads();
+      for (int64_t d = L.tid; d < hd; d += L.nthr) {
+        float M = -INFINITY;
+        for (uint32_t ww = 0; ww < nw; ++ww) M = fmaxf(M, ml[2 * ww]);
+        float num = 0.0f, den = 0.0f;
+        for (uint32_t ww = 0; ww < nw; ++ww) {
+          const float e = ml[2 * ww] == -INFINITY ? 0.0f : expf(ml[2 * ww] - M);
+          num = fmaf(os[ww * kFlashMaxHd + d], e, num);
+          den = fmaf(ml[2 * ww + 1], e, den);
+        }
+        storef(out, dt, (g * T + m) * hd + d, __fdiv_rn(num, den));
+      }
+    }
+    __syncthreads();
+    return;
+  }
   for (int64_t tile = tile_lo + w; tile < hi; tile += nw) {
     const int64_t g = tile / T, m = tile % T;
     const int64_t qpos = m + (C - T);

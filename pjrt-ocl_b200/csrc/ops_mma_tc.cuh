@@ -362,9 +362,9 @@ __device__ __noinline__ bool mma_tc_tiles(const Lane &L, const DTask &t, uint32_
       }
       __syncwarp();
       // epilogue: wait for the accumulator, then each warp drains its lanes x columns
-      if (!tc_wait(&S->acc_full, tcount & 1u, failed, budget, 256u)) { ok = false; break; }
+      // (voted: the whole warp leaves together if the wait ran out)
+      if (!__all_sync(0xffffffffu, tc_wait(&S->acc_full, tcount & 1u, failed, budget, 256u))) { ok = false; break; }
       ++tcount;
-      __syncwarp();
       tc_fence_after_sync();
       const int64_t r = r0 + 32 * q + lane;
       const uint32_t cols_per_warp = ninst / 2;   // two column halves

@@ -41,6 +41,41 @@ __device__ __forceinline__ int64_t dyn_base(const KParams &P, const DMove &m) {
   return base;
 }
 
+// A transposing gather: dst rows (length cc = dim[rank-1]) walk the source with stride
+// ld, while consecutive dst rows are adjacent in the source. Element by element every
+// read would touch its own 32-byte sector. Here whole dst rows [row_a, row_b) move
+// through shared-memory tiles of up to 32 rows x 64 columns: read along the source's
+// contiguous direction (rows), write along dst's (columns), both coalesced.
+template <typename E>
+__device__ __forceinline__ void transpose_rows(const Lane &L, const DMove &m, E *dst, const E *src, int64_t row_a,
+                                               int64_t row_b) {
+  constexpr int TR = 32, TC = 64;
+  const DView &v = m.view;
+  const int64_t cc = v.dim[v.rank - 1], rr = v.dim[v.rank - 2], ld = v.stride[v.rank - 1];
+  E *tile = reinterpret_cast<E *>(L.smem + kSmemSys);             // [TC][TR + 1]
+  for (int64_t row0 = row_a; row0 < row_b;) {
+    // rows of one segment share every outer coordinate: their source addresses are consecutive
+    const int64_t r_in = row0 % rr;
+    const int nr = static_cast<int>(min(min(static_cast<int64_t>(TR), rr - r_in), row_b - row0));
+    const int64_t sbase = view_index(v, static_cast<uint32_t>(row0 * cc));
+    for (int64_t c0 = 0; c0 < cc; c0 += TC) {
+      const int nc = static_cast<int>(min(static_cast<int64_t>(TC), cc - c0));
+      __syncthreads();
+      for (int i = L.tid; i < nc * TR; i += L.nthr) {
+        const int r = i % TR, c = i / TR;
+        if (r < nr) tile[c * (TR + 1) + r] = src[sbase + (c0 + c) * ld + r];
+      }
+      __syncthreads();
+      for (int i = L.tid; i < nr * TC; i += L.nthr) {
+        const int c = i % TC, r = i / TC;
+        if (c < nc) dst[(row0 + r) * cc + c0 + c] = tile[c * (TR + 1) + r];
+      }
+    }
+    row0 += nr;
+  }
+  __syncthreads();
+}
+
 // gather: dst[i] = a[base + view(i)];  scatter: dst[base + view(i)] = a[i]
 __device__ __noinline__ void move_tiles(const Lane &L, const DTask &t, uint32_t tile_lo, uint32_t tile_hi, bool scatter) {
   const KParams &P = *L.P;
@@ -56,6 +91,19 @@ __device__ __noinline__ void move_tiles(const Lane &L, const DTask &t, uint32_t 
   const int64_t base = m.n_idx ? dyn_base(P, m) : 0;
   const uint32_t esz = m.esz;
   const bool vec = m.chunk && (base % m.chunk == 0);
+  if (m.transposed && !scatter) {
+    const int64_t cc = m.view.dim[m.view.rank - 1];
+    const int64_t row_a = (static_cast<int64_t>(lo) + cc - 1) / cc, row_b = static_cast<int64_t>(hi) / cc;
+    if (row_b > row_a) {
+      // ragged ends of the range element by element, whole rows through the tiles
+      for (uint32_t i = lo + L.tid; i < row_a * cc; i += L.nthr) copy_elem(dst, i, src, view_index(m.view, i), esz);
+      for (uint32_t i = static_cast<uint32_t>(row_b * cc) + L.tid; i < hi; i += L.nthr)
+        copy_elem(dst, i, src, view_index(m.view, i), esz);
+      if (esz == 2) transpose_rows(L, m, reinterpret_cast<uint16_t *>(dst), reinterpret_cast<const uint16_t *>(src), row_a, row_b);
+      else transpose_rows(L, m, reinterpret_cast<uint32_t *>(dst), reinterpret_cast<const uint32_t *>(src), row_a, row_b);
+      return;
+    }
+  }
   if (vec) {
     // lo is a multiple of 4096 and chunk divides 16, so chunks never straddle lo.
     const uint32_t c = m.chunk, c_lo = lo / c, c_hi = hi / c;

@@ -72,17 +72,42 @@ __device__ __noinline__ void region_tiles(const Lane &L, const DTask &t, uint32_
       const uint32_t *q = micro + m * 6u;
       const uint32_t kind = q[0], ds = q[1] & 7u, as = q[2] & 7u, bs = q[3] & 7u;
       const float s = __uint_as_float(q[4]), tt = __uint_as_float(q[5]);
-#pragma unroll
-      for (int u = 0; u < kRegionU; ++u) {
-        const uint4 a = slots[(u * kRegionSlots + as) * pitch + col];
-        const uint4 b = slots[(u * kRegionSlots + bs) * pitch + col];
-        uint4 r;
-        r.x = __float_as_uint(micro_alu(kind, __uint_as_float(a.x), __uint_as_float(b.x), s, tt));
-        r.y = __float_as_uint(micro_alu(kind, __uint_as_float(a.y), __uint_as_float(b.y), s, tt));
-        r.z = __float_as_uint(micro_alu(kind, __uint_as_float(a.z), __uint_as_float(b.z), s, tt));
-        r.w = __float_as_uint(micro_alu(kind, __uint_as_float(a.w), __uint_as_float(b.w), s, tt));
-        slots[(u * kRegionSlots + ds) * pitch + col] = r;
+      // one dispatch per micro-op, the 8 evaluations inside each case
+#define B2_RG(K, EXPR)                                                              \
+  case K:                                                                           \
+    _Pragma("unroll") for (int u = 0; u < kRegionU; ++u) {                          \
+      const uint4 a = slots[(u * kRegionSlots + as) * pitch + col];                 \
+      const uint4 b = slots[(u * kRegionSlots + bs) * pitch + col];                 \
+      uint4 r;                                                                      \
+      { const float x = __uint_as_float(a.x), y = __uint_as_float(b.x); (void)y; r.x = __float_as_uint(EXPR); } \
+      { const float x = __uint_as_float(a.y), y = __uint_as_float(b.y); (void)y; r.y = __float_as_uint(EXPR); } \
+      { const float x = __uint_as_float(a.z), y = __uint_as_float(b.z); (void)y; r.z = __float_as_uint(EXPR); } \
+      { const float x = __uint_as_float(a.w), y = __uint_as_float(b.w); (void)y; r.w = __float_as_uint(EXPR); } \
+      slots[(u * kRegionSlots + ds) * pitch + col] = r;                             \
+    }                                                                               \
+    break;
+      switch (kind) {
+        B2_RG(kAdd, __fadd_rn(x, y))
+        B2_RG(kMul, __fmul_rn(x, y))
+        B2_RG(kSubt, __fsub_rn(x, y))
+        B2_RG(kDiv, __fdiv_rn(x, y))
+        B2_RG(kMax, np_max(x, y))
+        B2_RG(kMin, np_min(x, y))
+        B2_RG(kNeg, -x)
+        B2_RG(kExp, expf(x))
+        B2_RG(kLog, logf(x))
+        B2_RG(kSqrt, __fsqrt_rn(x))
+        B2_RG(kRsqrt, __fdiv_rn(1.0f, __fsqrt_rn(x)))
+        B2_RG(kTanh, fast_tanh(x))
+        B2_RG(kAbs, fabsf(x))
+        B2_RG(kAffine, affine2(x, s, tt))
+        B2_RG(kGelu, gelu_tanh(x))
+        default:   // copy
+          _Pragma("unroll") for (int u = 0; u < kRegionU; ++u)
+            slots[(u * kRegionSlots + ds) * pitch + col] = slots[(u * kRegionSlots + as) * pitch + col];
+          break;
       }
+#undef B2_RG
     }
 #pragma unroll
     for (int u = 0; u < kRegionU; ++u) {

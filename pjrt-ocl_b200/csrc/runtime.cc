@@ -502,6 +502,8 @@ uint64_t b2_loaded_stat(const b2_loaded *lp, int which) {
     case 3: return lp->tab.n_mma;
     case 4: return lp->tab.n_mma_tc;
     case 5: return lp->tab.mma_flops;
+    case 6: return lp->tab.n_flash;
+    case 7: return lp->tab.n_flash_tc;
     default: return 0;
   }
 }

@@ -17,6 +17,7 @@
 #include "ops_ew.cuh"
 #include "ops_ew_steps.cuh"
 #include "ops_mma_tc.cuh"
+#include "ops_flash_tc.cuh"
 #include "ops_flash.cuh"
 #include "ops_mma.cuh"
 #include "ops_move.cuh"
@@ -91,7 +92,12 @@ __device__ __forceinline__ void exec_entry(const Lane &L, const DEntry &en) {
     case kTopSoftmaxSeg: rows_tiles(L, t, en.tile_lo, en.tile_hi, true); break;
     case kTopLayernormSeg: rows_tiles(L, t, en.tile_lo, en.tile_hi, false); break;
     case kTopMapRegion: region_tiles(L, t, en.tile_lo, en.tile_hi); break;
-    case kTopFlashAttn: flash_simt_tiles(L, t, en.tile_lo, en.tile_hi); break;
+    case kTopFlashAttn: {
+      const DFlash &df = *reinterpret_cast<const DFlash *>(P.desc + t.desc);
+      const bool tc = NT == 512 && B2_HAS_TC && df.tc_mode && flash_tc_tiles(L, t, en.tile_lo, en.tile_hi);
+      if (!tc) flash_simt_tiles(L, t, en.tile_lo, en.tile_hi);
+      break;
+    }
     case kTopRedStrided: red_strided_tiles(L, t, en.tile_lo, en.tile_hi); break;
     default:
       if (L.tid == 0) set_status(P, kStBadOp, L.lane, en.task, t.op);

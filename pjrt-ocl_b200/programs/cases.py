@@ -22,6 +22,12 @@ NP = {F32: np.float32, I32: np.int32, U32: np.uint32, BOOL: np.uint8,
 DN = {F32: "f32", I32: "i32", U32: "u32", BOOL: "bool", I64: "i64",
       F16: "f16", BF16: "bf16"}
 NLANES = 148
+# The scheduler's per-tile cost table (scheduler.py:116-156; the reference's runtime
+# supplies a calibrated one through PJRT_OCL_COST_TABLE) for this backend: microseconds
+# one lane spends on a 4096-element elementwise / gather / reduce tile and on a
+# 128 x 128 matmul tile of typical depth. With the all-ones default a matmul sharing a
+# phase with an elementwise op would be given a fifth of the lanes.
+B200_COSTS = {"ew_tile_us": 1.0, "gather_tile_us": 1.5, "reduce_tile_us": 1.0, "mma_tile_us": 20.0}
 
 
 # --------------------------------------------------------------------------
@@ -195,7 +201,7 @@ def c3_mlp_step(batch=8192, widths=(1024, 4096, 4096, 1024), nlanes=NLANES,
             outs.append(a_.convert(upd, dtype))
     else:
         outs = [loss, dw1, dw2, dw3]
-    blob, prog = a_.finish(outs, nlanes=nlanes)
+    blob, prog = a_.finish(outs, nlanes=nlanes, costs=B200_COSTS)
 
     # x, y are drawn at the GLOBAL batch size; a data-parallel shard takes its
     # rows of them (the caller slices), weights are replicated.
@@ -215,7 +221,7 @@ def sgd_apply(shapes, nlanes=NLANES, dtype=BF16, lr=1e-3):
     for w, g in zip(ws, gs):
         upd = a_.sub(a_.convert(w, F32), a_.mul(a_.scalar(lr, g), g))
         outs.append(a_.convert(upd, dtype))
-    blob, prog = a_.finish(outs, nlanes=nlanes)
+    blob, prog = a_.finish(outs, nlanes=nlanes, costs=B200_COSTS)
     return blob, prog, None
 
 
@@ -321,7 +327,7 @@ def c5_block(batch=8, seq=2048, d_model=1024, heads=16, d_ff=4096,
     h2 = _rmsnorm(a, x1, g2, eps)
     f = a.gelu_tanh(a.matmul(h2, w1, out_dtype=dtype))
     y = a.add(x1, a.matmul(f, w2, out_dtype=dtype))
-    blob, prog = a.finish([y], nlanes=nlanes)
+    blob, prog = a.finish([y], nlanes=nlanes, costs=B200_COSTS)
 
     d = DN[dtype]
     items = [("ones", (d_model,), d), ("normal", (n, d_model), d)]
@@ -365,7 +371,7 @@ def c5_decode(batch=32, cache=2048, d_model=1024, heads=16, d_ff=4096,
     h2 = _rmsnorm(a, x1, g2, eps)
     f = a.gelu_tanh(a.matmul(h2, w1, out_dtype=dtype))
     y = a.add(x1, a.matmul(f, w2, out_dtype=dtype))
-    blob, prog = a.finish([y, kfull, vfull], nlanes=nlanes)
+    blob, prog = a.finish([y, kfull, vfull], nlanes=nlanes, costs=B200_COSTS)
 
     d = DN[dtype]
     items = [("ones", (d_model,), d), ("normal", (batch, d_model), d),

@@ -350,7 +350,7 @@ class LoadedProgram:
         return [int(buf[i]) for i in range(n)]
 
     _STATS = {"chains": 0, "forwarded": 0 + 1, "dead_stores": 2, "matmuls": 3, "tensor_core_matmuls": 4,
-              "matmul_flops": 5}
+              "matmul_flops": 5, "flash": 6, "tensor_core_flash": 7}
 
     def stat(self, name: str) -> int:
         """Load-time mapping facts: chains, forwarded, dead_stores, matmuls, tensor_core_matmuls."""

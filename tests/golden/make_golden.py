@@ -655,12 +655,18 @@ def _():
                              N((150, 200))])
 
 
-def _flash_case(dtype, lanes):
+_FLASH_SHAPES = ((3, 40, 40, 16, True), (2, 70, 70, 64, False), (4, 1, 130, 64, True), (2, 33, 97, 32, True),
+                 (1, 200, 200, 64, True))
+# head_dim 64 and key counts that are multiples of 8 (what the tensor-core path takes),
+# query counts off the 128-row block, more keys than queries, causal and not
+_FLASH_TC_SHAPES = ((3, 200, 200, 64, True), (2, 136, 264, 64, True), (2, 72, 328, 64, False),
+                    (2, 300, 304, 64, False))
+
+
+def _flash_case(dtype, lanes, shapes=_FLASH_SHAPES):
     a = Asm()
     outs, items = [], []
-    for (H, T_, C, hd, causal) in ((3, 40, 40, 16, True), (2, 70, 70, 64, False),
-                                   (4, 1, 130, 64, True), (2, 33, 97, 32, True),
-                                   (1, 200, 200, 64, True)):
+    for (H, T_, C, hd, causal) in shapes:
         q = a.input((H, T_, hd), dtype)
         kt = a.input((H, hd, C), dtype)
         v = a.input((H, C, hd), dtype)
@@ -679,6 +685,16 @@ def _():
 @case("flash_bf16", rtol=2e-2, atol=2e-2, twin=lambda: _flash_case(F32, 4))
 def _():
     return _flash_case(BF16, 4)
+
+
+@case("flash_tc_bf16", rtol=2e-2, atol=2e-2, twin=lambda: _flash_case(F32, 5, _FLASH_TC_SHAPES))
+def _():
+    return _flash_case(BF16, 5, _FLASH_TC_SHAPES)
+
+
+@case("flash_tc_f16", rtol=2e-2, atol=2e-2, twin=lambda: _flash_case(F32, 5, _FLASH_TC_SHAPES))
+def _():
+    return _flash_case(F16, 5, _FLASH_TC_SHAPES)
 
 
 # ---------------------------------------------------------------- configs
@@ -706,6 +722,24 @@ def _():
 def _():
     return cases.c3_mlp_step(batch=160, widths=(96, 256, 192, 64), nlanes=8,
                              dtype=F32)
+
+
+@case("c3_dp2_grads_f32_small", rtol=1e-4, atol=1e-5)
+def _():
+    """Config 3's per-rank program at 2 ranks: gradients of half the batch, scaled for the global batch."""
+    blob, prog, (seed, items) = cases.c3_mlp_step(batch=80, global_batch=160, widths=(96, 256, 192, 64), nlanes=8,
+                                                  dtype=F32, apply_sgd=False)
+    # the case lists x, y at the global batch (callers slice); this fixture feeds one shard
+    items = [(k, (80,) + tuple(shp[1:]), *rest) if i < 2 else (k, shp, *rest) for i, (k, shp, *rest) in enumerate(items)]
+    return blob, prog, (seed, items)
+
+
+@case("c3_dp2_apply_f32_small", rtol=1e-5, atol=1e-6)
+def _():
+    """Config 3's post-all-reduce program: w <- w - lr g."""
+    blob, prog, _ = cases.sgd_apply([(96, 256), (256, 192), (192, 64)], nlanes=8, dtype=F32)
+    return blob, prog, (31, [N((96, 256)), N((256, 192)), N((192, 64)), N((96, 256), "f32", 0.01),
+                             N((256, 192), "f32", 0.01), N((192, 64), "f32", 0.01)])
 
 
 @case("c3_mlp_bf16_small", rtol=2e-2, atol=2e-2)
