@@ -40,8 +40,8 @@ constexpr uint32_t kTcCols = 256;            // tensor-memory columns held (f32 
 struct TcShared {                            // lives in the reduction scratch of the system area
   uint64_t full[kTcStages];
   uint64_t empty[kTcStages];
-  uint64_t acc_full;
-  uint64_t acc_empty;
+  uint64_t acc_full[2];
+  uint64_t acc_empty[2];
   uint32_t tmem_base;
   uint32_t failed;
 };
@@ -203,14 +203,14 @@ __device__ __noinline__ bool mma_tc_tiles(const Lane &L, const DTask &t, uint32_
   __syncthreads();   // the scratch slot is free
   if (L.tid == 0) {
     for (int s = 0; s < kTcStages; ++s) { mbar_init(&S->full[s], use_tma ? 1u : static_cast<uint32_t>(kTcProducers)); mbar_init(&S->empty[s], 1); }
-    mbar_init(&S->acc_full, 1);
-    mbar_init(&S->acc_empty, 256);
+    for (int b = 0; b < 2; ++b) { mbar_init(&S->acc_full[b], 1); mbar_init(&S->acc_empty[b], 256); }
     S->failed = 0u;
     fence_mbar_init();
   }
+  const uint32_t tcols = use_tma ? 2u * kTcCols : kTcCols;
   if (w == 8) {
     __syncwarp();
-    tmem_alloc(&S->tmem_base, kTcCols);
+    tmem_alloc(&S->tmem_base, tcols);
   }
   tc_fence_before_sync();
   __syncthreads();
@@ -327,44 +327,80 @@ __device__ __noinline__ bool mma_tc_tiles(const Lane &L, const DTask &t, uint32_
       }
     }
     cp_async_wait_all();                          // nothing of this thread is still in flight
-  } else {
-    // ---------------- MMA issue (warp 8 lane 0) + epilogue (warps 8-15) ----------------
+  }
+  // ---------------- MMA issue ----------------
+  // With TMA producers (one thread) warp 1 is free to issue, so the accumulator is
+  // double-buffered in tensor memory (columns 0 and 256) and the epilogue of one
+  // super-tile runs under the main loop of the next. With per-thread producers the
+  // issuing thread sits in epilogue warp 8 and there is one accumulator.
+  const uint32_t nbuf = use_tma ? 2u : 1u;
+  const uint32_t fmt = adt == kBF16 ? 1u : 0u;
+  uint32_t mma_it = 0;                               // k blocks consumed so far (issuing thread only)
+  auto issue_tile = [&](uint32_t n, int nt) -> bool {   // super-tile number n of this lane
+    const uint32_t buf = n % nbuf, use = n / nbuf, ninst = 128u * nt;
+    // the epilogue warps have drained this accumulator's previous contents
+    if (!tc_wait(&S->acc_empty[buf], (use & 1u) ^ 1u, failed, budget)) return false;
+    tc_fence_after_sync();
+    const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((amn ? 1u : 0u) << 15) | ((bmn ? 1u : 0u) << 16) |
+                           ((ninst >> 3) << 17) | ((128u >> 4) << 24);
+    for (int64_t kb = 0; kb < nkb; ++kb, ++mma_it) {
+      const uint32_t s = mma_it % kTcStages;
+      if (!tc_wait(&S->full[s], (mma_it / kTcStages) & 1u, failed, budget)) return false;
+      if (!use_tma) fence_proxy_async_smem();       // per-thread (generic-proxy) writes -> the MMA's async-proxy reads
+      tc_fence_after_sync();
+      const uint32_t sa = stage0 + s * kTcStageBytes, sb = sa + kTcABytes;
+      const uint64_t da = amn ? tc_desc(sa, 8192u, 1024u) : tc_desc(sa, 16u, 1024u);
+      const uint64_t db = bmn ? tc_desc(sb, 8192u, 1024u) : tc_desc(sb, 16u, 1024u);
+      const uint64_t adv_a = amn ? (2048u >> 4) : (32u >> 4), adv_b = bmn ? (2048u >> 4) : (32u >> 4);
+#pragma unroll
+      for (uint32_t j = 0; j < kTcBK / 16; ++j)
+        tc_mma_f16(tmem + buf * 256u, da + j * adv_a, db + j * adv_b, idesc, (kb > 0 || j > 0) ? 1u : 0u);
+      tc_commit(&S->empty[s]);                    // frees the stage when these MMAs have read it
+    }
+    tc_commit(&S->acc_full[buf]);
+    return true;
+  };
+  if (use_tma && w == 1 && lane == 0) {
+    uint32_t n = 0;
+    uint32_t tile = tile_lo; int64_t g, r0, c0; int nt;
+    while (next_super(tile, g, r0, c0, nt) && issue_tile(n, nt)) ++n;
+  }
+  if (w >= 8) {
+    // ---------------- epilogue (warps 8-15) ----------------
     const uint32_t ew = w - 8, q = ew & 3u, half = ew >> 2;
-    const uint32_t fmt = adt == kBF16 ? 1u : 0u;
-    uint32_t it = 0, tcount = 0;
+    // the store epilogue, decoded once: up to kEpiMax micro-ops {kind, operand source, s, t}
+    constexpr int kEpiMax = 4;
+    int epi_n = 0;
+    uint32_t epi_kind[kEpiMax], epi_src[kEpiMax];
+    float epi_s[kEpiMax], epi_t[kEpiMax];
+    bool epi_generic = false;
+    if (t.p[6]) {
+      const int32_t *e = P.aux + (t.p[6] - 1u);
+      epi_n = e[0];
+      if (epi_n > kEpiMax) { epi_generic = true; epi_n = 0; }
+#pragma unroll
+      for (int mi = 0; mi < kEpiMax; ++mi) {
+        const bool on = mi < epi_n;
+        epi_kind[mi] = on ? static_cast<uint32_t>(e[1 + 4 * mi]) : 0u;
+        epi_src[mi] = on ? static_cast<uint32_t>(e[2 + 4 * mi]) : 0u;
+        epi_s[mi] = on ? __int_as_float(e[3 + 4 * mi]) : 0.0f;
+        epi_t[mi] = on ? __int_as_float(e[4 + 4 * mi]) : 0.0f;
+      }
+    }
+    const uint32_t cdt = t.cdt;
+    const bool vec_res = res && (reinterpret_cast<uintptr_t>(res) & 15u) == 0 && N % 8 == 0 && (cdt == kBF16 || cdt == kF32);
+    uint32_t n = 0;
     uint32_t tile = tile_lo; int64_t g, r0, c0; int nt;
     bool ok = true;
     while (ok && next_super(tile, g, r0, c0, nt)) {
-      const uint32_t ninst = 128u * nt;
-      if (w == 8 && lane == 0) {
-        // the previous accumulator has been read by all eight epilogue warps
-        if (tcount && !tc_wait(&S->acc_empty, (tcount - 1u) & 1u, failed, budget)) ok = false;
-        tc_fence_after_sync();
-        const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((amn ? 1u : 0u) << 15) | ((bmn ? 1u : 0u) << 16) |
-                               ((ninst >> 3) << 17) | ((128u >> 4) << 24);
-        for (int64_t kb = 0; ok && kb < nkb; ++kb, ++it) {
-          const uint32_t s = it % kTcStages;
-          if (!tc_wait(&S->full[s], (it / kTcStages) & 1u, failed, budget)) { ok = false; break; }
-          fence_proxy_async_smem();               // the producers' (generic-proxy) writes -> the MMA's async-proxy reads
-          tc_fence_after_sync();
-          const uint32_t sa = stage0 + s * kTcStageBytes, sb = sa + kTcABytes;
-          const uint64_t da = amn ? tc_desc(sa, 8192u, 1024u) : tc_desc(sa, 16u, 1024u);
-          const uint64_t db = bmn ? tc_desc(sb, 8192u, 1024u) : tc_desc(sb, 16u, 1024u);
-          const uint64_t adv_a = amn ? (2048u >> 4) : (32u >> 4), adv_b = bmn ? (2048u >> 4) : (32u >> 4);
-#pragma unroll
-          for (uint32_t j = 0; j < kTcBK / 16; ++j)
-            tc_mma_f16(tmem, da + j * adv_a, db + j * adv_b, idesc, (kb > 0 || j > 0) ? 1u : 0u);
-          tc_commit(&S->empty[s]);                // frees the stage when these MMAs have read it
-        }
-        if (ok) tc_commit(&S->acc_full);
-      } else {
-        it += static_cast<uint32_t>(nkb);
+      const uint32_t buf = n % nbuf, use = n / nbuf, ninst = 128u * nt;
+      if (!use_tma) {
+        if (w == 8 && lane == 0) ok = issue_tile(n, nt);
+        __syncwarp();
       }
-      __syncwarp();
-      // epilogue: wait for the accumulator, then each warp drains its lanes x columns
-      // (voted: the whole warp leaves together if the wait ran out)
-      if (!__all_sync(0xffffffffu, tc_wait(&S->acc_full, tcount & 1u, failed, budget, 256u))) { ok = false; break; }
-      ++tcount;
+      // wait for the accumulator (voted: the whole warp leaves together if the wait ran out)
+      if (!__all_sync(0xffffffffu, tc_wait(&S->acc_full[buf], use & 1u, failed, budget, 256u))) { ok = false; break; }
+      ++n;
       tc_fence_after_sync();
       const int64_t r = r0 + 32 * q + lane;
       const uint32_t cols_per_warp = ninst / 2;   // two column halves
@@ -374,7 +410,7 @@ __device__ __noinline__ bool mma_tc_tiles(const Lane &L, const DTask &t, uint32_
         uint32_t raw[32];
         __syncwarp();   // the warp-wide tensor-memory load needs all 32 lanes back together
                         // (rows beyond M leave the store below divergent)
-        tc_ld32(tmem + ((32u * q) << 16) + col, raw);
+        tc_ld32(tmem + ((32u * q) << 16) + buf * 256u + col, raw);
         tc_wait_ld();
         const int64_t c = c0 + col;
         if (r < M && c < N) {
@@ -382,16 +418,60 @@ __device__ __noinline__ bool mma_tc_tiles(const Lane &L, const DTask &t, uint32_
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[j]);
           const int64_t ncols = min(static_cast<int64_t>(32), N - c);
-          if (t.p[6]) {
+          if (epi_generic) {
 #pragma unroll 1
             for (int j = 0; j < 32; ++j)
               if (j < ncols) v[j] = mma_epilogue(P, t, res, v[j], g, r, c + j, M, N);
+          }
+#pragma unroll
+          for (int mi = 0; mi < kEpiMax; ++mi) {
+            if (mi >= epi_n) break;
+            float y[32];
+            if (epi_src[mi]) {      // 1: the residual's element, 2: the per-column vector's
+              const int64_t yi = epi_src[mi] == 1u ? (g * M + r) * N + c : c;
+              if (vec_res && ncols == 32) {
+                if (cdt == kF32) {
+                  const float4 *yp = reinterpret_cast<const float4 *>(res + yi * 4);
+#pragma unroll
+                  for (int j = 0; j < 8; ++j) { const float4 f = yp[j]; y[4 * j] = f.x; y[4 * j + 1] = f.y; y[4 * j + 2] = f.z; y[4 * j + 3] = f.w; }
+                } else {
+                  const uint4 *yp = reinterpret_cast<const uint4 *>(res + yi * 2);
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) {
+                    const uint4 u = yp[j];
+                    y[8 * j] = bf16_bits_to_f32(u.x & 0xffffu); y[8 * j + 1] = __uint_as_float(u.x & 0xffff0000u);
+                    y[8 * j + 2] = bf16_bits_to_f32(u.y & 0xffffu); y[8 * j + 3] = __uint_as_float(u.y & 0xffff0000u);
+                    y[8 * j + 4] = bf16_bits_to_f32(u.z & 0xffffu); y[8 * j + 5] = __uint_as_float(u.z & 0xffff0000u);
+                    y[8 * j + 6] = bf16_bits_to_f32(u.w & 0xffffu); y[8 * j + 7] = __uint_as_float(u.w & 0xffff0000u);
+                  }
+                }
+              } else {
+#pragma unroll 1
+                for (int j = 0; j < 32; ++j) y[j] = j < ncols ? loadf(res, cdt, yi + j) : 0.0f;
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) y[j] = v[j];
+            }
+            const float es = epi_s[mi], et = epi_t[mi];
+            switch (epi_kind[mi]) {     // one dispatch, the 32 evaluations inside
+              case kAdd: _Pragma("unroll") for (int j = 0; j < 32; ++j) v[j] = __fadd_rn(v[j], y[j]); break;
+              case kMul: _Pragma("unroll") for (int j = 0; j < 32; ++j) v[j] = __fmul_rn(v[j], y[j]); break;
+              case kSubt: _Pragma("unroll") for (int j = 0; j < 32; ++j) v[j] = __fsub_rn(v[j], y[j]); break;
+              case kMax: _Pragma("unroll") for (int j = 0; j < 32; ++j) v[j] = np_max(v[j], y[j]); break;
+              case kGelu: _Pragma("unroll") for (int j = 0; j < 32; ++j) v[j] = gelu_tanh(v[j]); break;
+              case kAffine: _Pragma("unroll") for (int j = 0; j < 32; ++j) v[j] = affine2(v[j], es, et); break;
+              default:
+#pragma unroll 1
+                for (int j = 0; j < 32; ++j) v[j] = micro_alu(epi_kind[mi], v[j], y[j], es, et);
+                break;
+            }
           }
           tc_store_row32(dst, dt, (g * M + r) * N + c, v, ncols, vec_store);
         }
       }
       tc_fence_before_sync();
-      mbar_arrive(&S->acc_empty);                 // this thread is done with the accumulator
+      mbar_arrive(&S->acc_empty[buf]);            // this thread is done with the accumulator
     }
   }
 
@@ -401,13 +481,12 @@ __device__ __noinline__ bool mma_tc_tiles(const Lane &L, const DTask &t, uint32_
   if (w == 8) {
     __syncwarp();
     tc_fence_after_sync();
-    tmem_dealloc(tmem, kTcCols);
+    tmem_dealloc(tmem, tcols);
   }
   if (L.tid == 0) {
     if (S->failed) set_status(P, kStTensorTimeout, L.lane, tile_lo, kTopMma);
     for (int s = 0; s < kTcStages; ++s) { mbar_inval(&S->full[s]); mbar_inval(&S->empty[s]); }
-    mbar_inval(&S->acc_full);
-    mbar_inval(&S->acc_empty);
+    for (int b = 0; b < 2; ++b) { mbar_inval(&S->acc_full[b]); mbar_inval(&S->acc_empty[b]); }
   }
   __syncthreads();
   return true;
