@@ -74,6 +74,9 @@ WORKLOADS = {
                          "one dot_general bf16 8192 x 8192 x 8192, f32 accumulate, bf16 result"),
     "dot_bf16_4096": _wl("dot_bf16_4096", "dot_general TFLOP/s", "TFLOP/s", 2 * 4096 ** 3, 1e12, "tensor", "bf16",
                          "one dot_general bf16 4096 x 4096 x 4096", secondary=True),
+    "flash_bf16": _wl("flash_bf16_c5", "flash-attention TFLOP/s", "TFLOP/s", _C5_ATT_FLOPS, 1e12, "tensor", "bf16",
+                      "config 5's attention alone: 128 heads x 2048 x 2048, head_dim 64, causal (flops count the "
+                      "causal half)", secondary=True),
     "c3_mlp": _wl("c3_mlp_step_bf16", "dot_general TFLOP/s", "TFLOP/s", _C3_FLOPS, 1e12, "tensor", "bf16",
                   "config 3: 3-layer MLP forward + grad of MSE + SGD step, batch 8192, 1024-4096-4096-1024, bf16; "
                   "on N GPUs: local-batch gradients, NCCL all-reduce, SGD program", plan="c3"),

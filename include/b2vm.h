@@ -134,8 +134,8 @@ uint64_t b2_loaded_launch_count(const b2_loaded *lp);
 uint64_t b2_loaded_stat(const b2_loaded *lp, int which);
 /* Per-wait budget of device-side bounded waits, in nanoseconds (default 2e9). */
 void b2_loaded_set_wait_budget_ns(b2_loaded *lp, uint64_t ns);
-/* Lane 0's arrival time, in ns since kernel entry, at each of the first grid
- * barriers of the last execute (what the reference prints under
+/* The time, in ns since kernel entry, at which each of the first grid barriers of
+ * the last execute released (every lane had arrived, seen from lane 0) (what the reference prints under
  * PJRT_OCL_PHASE_TS, runtime.cc:2196-2240). Writes at most `cap` values and
  * returns how many were written. */
 size_t b2_loaded_phase_ns(const b2_loaded *lp, uint64_t *out, size_t cap);

@@ -29,6 +29,8 @@ enum EwStepCode : uint32_t {
   kSLdXRowBf, kSLdYRowBf,
   kSLdXViewW4, kSLdYViewW4,  // any vector-friendly view
   kSLdXViewBf, kSLdYViewBf,
+  kSLdXColW4, kSLdYColW4,    // a column vector broadcast along rows: index = off + (i / d) * stride
+  kSLdXColBf, kSLdYColBf,
   kSStW4, kSStBf, kSStB1,
   kSQuantBf,
   kSAffine, kSFill, kSIotaF, kSIotaI, kSSelect,
@@ -85,6 +87,8 @@ __device__ inline void ew_build_steps(EwOp *o, uint32_t smem_off_of_op) {
       emit((w4 ? kSLdXW4 : kSLdXBf) + is_y, p + v.off * static_cast<int64_t>(esz), 0, 0, 0);
     } else if (v.rank == 2 && v.stride[0] == 0 && v.inner_stride == 1 && v.aligned4) {
       emit((w4 ? kSLdXRowW4 : kSLdXRowBf) + is_y, p, voff, 0, 0);
+    } else if (v.rank == 2 && v.inner_stride == 0) {
+      emit((w4 ? kSLdXColW4 : kSLdXColBf) + is_y, p, voff, 0, 0);
     } else {
       emit((w4 ? kSLdXViewW4 : kSLdXViewBf) + is_y, p, voff, 0, 0);
     }
@@ -332,6 +336,19 @@ __device__ __noinline__ void ew_steps_run(uint32_t tid, uint32_t nthr, uint32_t 
         else B2_SET(R, ldg_v4(p + static_cast<size_t>(c) * 4))
       }
     };
+    // one value per row, the same for the 4 elements of a group (a group never straddles a row)
+    auto ld_col = [&](uint32_t (&R)[kEwU][4], const EwStep &st, bool bf) {
+      const DView &v = *reinterpret_cast<const DView *>(sm + st.voff);
+      const uint32_t mg = v.magic[1], sh = v.shift[1];
+      const int64_t off = v.off, s0 = v.stride[0];
+      B2_GROUPS {
+        const uint32_t n = eb + u * estep, mh = __umulhi(n, mg);
+        const uint32_t row = (((n - mh) >> 1) + mh) >> sh;
+        const int64_t idx = off + row * s0;
+        const uint32_t val = bf ? (ldg_u16(st.ptr + idx * 2) << 16) : ldg_u32(st.ptr + idx * 4);
+        R[u][0] = R[u][1] = R[u][2] = R[u][3] = val;
+      }
+    };
     auto ld_view = [&](uint32_t (&R)[kEwU][4], const EwStep &st, bool bf) {
       const DView &v = *reinterpret_cast<const DView *>(sm + st.voff);
       const bool bcast = v.inner_stride == 0, al4 = v.aligned4 != 0;
@@ -378,6 +395,10 @@ __device__ __noinline__ void ew_steps_run(uint32_t tid, uint32_t nthr, uint32_t 
           case kSLdYRowW4: ld_row(Y, st, false); break;
           case kSLdXRowBf: ld_row(X, st, true); break;
           case kSLdYRowBf: ld_row(Y, st, true); break;
+          case kSLdXColW4: ld_col(X, st, false); break;
+          case kSLdYColW4: ld_col(Y, st, false); break;
+          case kSLdXColBf: ld_col(X, st, true); break;
+          case kSLdYColBf: ld_col(Y, st, true); break;
           case kSLdXViewW4: if constexpr (COLD) ld_view(X, st, false); break;
           case kSLdYViewW4: if constexpr (COLD) ld_view(Y, st, false); break;
           case kSLdXViewBf: if constexpr (COLD) ld_view(X, st, true); break;

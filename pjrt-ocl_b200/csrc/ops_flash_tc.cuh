@@ -123,7 +123,7 @@ __device__ __noinline__ bool flash_tc_tiles(const Lane &L, const DTask &t, uint3
       }
       for (int64_t j = 0; j < nkb; ++j) {
         const uint32_t kvpos = kvit + static_cast<uint32_t>(j), s = kvpos % kFaStages;
-        if (!tc_wait(&S->kv_empty[s], ((kvpos / kFaStages) & 1u) ^ 1u, failed, budget)) break;
+        if (!tc_wait_warp(&S->kv_empty[s], ((kvpos / kFaStages) & 1u) ^ 1u, failed, budget, 32u)) break;
         const uint32_t ks = kv_s + s * kFaKvBytes, vs = ks + 128 * 128;
         const int64_t n0 = j * 128;
         {   // K^T block: element (d, key) at KT[(g*hd + d)*C + key]: keys are the unit-stride ("MN") dimension
@@ -205,47 +205,64 @@ __device__ __noinline__ bool flash_tc_tiles(const Lane &L, const DTask &t, uint3
         const uint32_t jj = jt + static_cast<uint32_t>(j);
         float alpha = 1.0f;
         if (j < nkb) {
-          // (the outcome is voted on so that the whole warp leaves together if a wait ran out)
-          if (!__all_sync(0xffffffffu, tc_wait(&S->s_full[jj & 1u], (jj >> 1) & 1u, failed, budget))) { ok = false; break; }
+          if (!tc_wait_warp(&S->s_full[jj & 1u], (jj >> 1) & 1u, failed, budget)) { ok = false; break; }
           tc_fence_after_sync();
-          const int64_t n0 = j * 128;
+          // valid columns of this block for this row (keys n0 .. n0 + lim - 1)
+          const int lim = static_cast<int>(max(static_cast<int64_t>(0), min(static_cast<int64_t>(128), c_end - j * 128)));
+          const uint32_t s_addr = tmem + ((32u * q4) << 16) + (jj & 1u) * 128u;
           // pass 1: the row's maximum over this block
           float mx = -INFINITY;
 #pragma unroll 1
-          for (uint32_t cb = 0; cb < 128; cb += 32) {
+          for (int cb = 0; cb < 128; cb += 32) {
             uint32_t raw[32];
             __syncwarp();
-            tc_ld32(tmem + ((32u * q4) << 16) + (jj & 1u) * 128u + cb, raw);
+            tc_ld32(s_addr + cb, raw);
             tc_wait_ld();
+            if (cb + 32 <= lim) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i)
-              if (n0 + cb + i < c_end) mx = fmaxf(mx, __uint_as_float(raw[i]) * sl2);
+              for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(raw[i]) * sl2);
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                if (cb + i < lim) mx = fmaxf(mx, __uint_as_float(raw[i]) * sl2);
+            }
           }
           const float m_new = fmaxf(m_run, mx);
           alpha = m_run == -INFINITY ? (m_new == -INFINITY ? 1.0f : 0.0f) : fast_ex2(m_run - m_new);
+          const float neg_m = m_new == -INFINITY ? 0.0f : -m_new;
           // pass 2: p = 2^(s - m_new), written as the 16-bit A operand of the second matmul
           float psum = 0.0f;
           const uint32_t pb = p_s + (jj & 1u) * kFaPBytes;
+          const bool bf = adt == kBF16;
 #pragma unroll 1
-          for (uint32_t cb = 0; cb < 128; cb += 32) {
-            uint32_t raw[32];
+          for (int cb = 0; cb < 128; cb += 16) {
+            uint32_t raw[16];
             __syncwarp();
-            tc_ld32(tmem + ((32u * q4) << 16) + (jj & 1u) * 128u + cb, raw);
+            tc_ld16(s_addr + cb, raw);
             tc_wait_ld();
-            uint32_t pk[16];
+            float pv[16];
+            if (cb + 16 <= lim) {
 #pragma unroll
-            for (int i = 0; i < 32; i += 2) {
-              float p0 = 0.0f, p1 = 0.0f;
-              if (n0 + cb + i < c_end) p0 = fast_ex2(__uint_as_float(raw[i]) * sl2 - m_new);
-              if (n0 + cb + i + 1 < c_end) p1 = fast_ex2(__uint_as_float(raw[i + 1]) * sl2 - m_new);
-              psum += p0 + p1;
-              pk[i >> 1] = adt == kBF16 ? cvt_bf16x2(p1, p0) : (f32_to_f16_bits(p0) | (f32_to_f16_bits(p1) << 16));
+              for (int i = 0; i < 16; ++i) pv[i] = fast_ex2(fmaf(__uint_as_float(raw[i]), sl2, neg_m));
+            } else {
+#pragma unroll
+              for (int i = 0; i < 16; ++i) pv[i] = cb + i < lim ? fast_ex2(fmaf(__uint_as_float(raw[i]), sl2, neg_m)) : 0.0f;
             }
-            // 32 keys = 4 chunks of 8; sub-tile = cb / 64, chunk inside it = (cb % 64) / 8 + q
-            const uint32_t sub = pb + (cb >> 6) * 16384u + r * 128u;
+            uint32_t pk[8];
+            if (bf) {
 #pragma unroll
-            for (uint32_t q = 0; q < 4; ++q) {
-              const uint32_t ch = ((cb & 63u) >> 3) + q;
+              for (int i = 0; i < 8; ++i) pk[i] = cvt_bf16x2(pv[2 * i + 1], pv[2 * i]);
+            } else {
+#pragma unroll
+              for (int i = 0; i < 8; ++i) pk[i] = f32_to_f16_bits(pv[2 * i]) | (f32_to_f16_bits(pv[2 * i + 1]) << 16);
+            }
+#pragma unroll
+            for (int i = 0; i < 16; ++i) psum += pv[i];
+            // 16 keys = 2 chunks of 8; sub-tile = cb / 64, chunk inside it = (cb % 64) / 8 + q
+            const uint32_t sub = pb + (static_cast<uint32_t>(cb) >> 6) * 16384u + r * 128u;
+#pragma unroll
+            for (uint32_t q = 0; q < 2; ++q) {
+              const uint32_t ch = ((static_cast<uint32_t>(cb) & 63u) >> 3) + q;
               uint4 *dstp = reinterpret_cast<uint4 *>(sm + (sub + ((ch ^ (r & 7u)) << 4) - smem_addr(sm)));
               *dstp = make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
             }
@@ -259,7 +276,7 @@ __device__ __noinline__ bool flash_tc_tiles(const Lane &L, const DTask &t, uint3
         if (j > 0) {
           // fold O(j-1) in: acc = (acc + O(j-1)) * alpha(j)
           const uint32_t pj = jj - 1u;
-          if (!__all_sync(0xffffffffu, tc_wait(&S->o_full[pj & 1u], (pj >> 1) & 1u, failed, budget))) { ok = false; break; }
+          if (!tc_wait_warp(&S->o_full[pj & 1u], (pj >> 1) & 1u, failed, budget)) { ok = false; break; }
           tc_fence_after_sync();
 #pragma unroll
           for (uint32_t cb = 0; cb < 64; cb += 32) {

@@ -70,6 +70,17 @@ __device__ __forceinline__ bool tc_wait(uint64_t *bar, uint32_t parity, volatile
   }
 }
 
+// A whole warp waits, but only lane 0 polls: the other lanes sit at the warp
+// barrier without taking issue slots from the warps that have work. Every lane
+// gets lane 0's outcome (so the warp stays together when a wait ran out), and the
+// warp barrier orders lane 0's acquire before the other lanes' later accesses.
+__device__ __forceinline__ bool tc_wait_warp(uint64_t *bar, uint32_t parity, volatile uint32_t *failed,
+                                             unsigned long long budget_ns, uint32_t backoff_ns = 0) {
+  uint32_t ok = 1u;
+  if ((threadIdx.x & 31u) == 0u) ok = tc_wait(bar, parity, failed, budget_ns, backoff_ns) ? 1u : 0u;
+  return __shfl_sync(0xffffffffu, ok, 0) != 0u;
+}
+
 // A producer thread's share of one operand block (ROWS x 64 k), fixed for a whole
 // super-tile: NCH 16-byte chunks, each with a shared-memory offset inside the stage,
 // a source pointer that advances by `step` elements per k block, and the bytes of
@@ -309,7 +320,7 @@ __device__ __noinline__ bool mma_tc_tiles(const Lane &L, const DTask &t, uint32_
       auto run = [&](auto &pb) {
         for (int64_t kb = 0; kb < nkb; ++kb, ++it) {
           const uint32_t s = it % kTcStages;
-          if (!tc_wait(&S->empty[s], ((it / kTcStages) & 1u) ^ 1u, failed, budget)) { ok = false; break; }
+          if (!tc_wait_warp(&S->empty[s], ((it / kTcStages) & 1u) ^ 1u, failed, budget)) { ok = false; break; }
           const uint32_t sa = stage0 + s * kTcStageBytes;
           tc_issue(pa, sa, kb, K, A);
           tc_issue(pb, sa + kTcABytes, kb, K, B);
@@ -399,7 +410,7 @@ __device__ __noinline__ bool mma_tc_tiles(const Lane &L, const DTask &t, uint32_
         __syncwarp();
       }
       // wait for the accumulator (voted: the whole warp leaves together if the wait ran out)
-      if (!__all_sync(0xffffffffu, tc_wait(&S->acc_full[buf], use & 1u, failed, budget, 256u))) { ok = false; break; }
+      if (!tc_wait_warp(&S->acc_full[buf], use & 1u, failed, budget, 64u)) { ok = false; break; }
       ++n;
       tc_fence_after_sync();
       const int64_t r = r0 + 32 * q + lane;

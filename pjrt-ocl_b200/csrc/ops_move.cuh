@@ -49,7 +49,7 @@ __device__ __forceinline__ int64_t dyn_base(const KParams &P, const DMove &m) {
 template <typename E>
 __device__ __forceinline__ void transpose_rows(const Lane &L, const DMove &m, E *dst, const E *src, int64_t row_a,
                                                int64_t row_b) {
-  constexpr int TR = 32, TC = 64;
+  constexpr int TR = 64, TC = 256;   // 16K elements per tile: 32 independent loads per thread in flight
   const DView &v = m.view;
   const int64_t cc = v.dim[v.rank - 1], rr = v.dim[v.rank - 2], ld = v.stride[v.rank - 1];
   E *tile = reinterpret_cast<E *>(L.smem + kSmemSys);             // [TC][TR + 1]
@@ -61,14 +61,30 @@ __device__ __forceinline__ void transpose_rows(const Lane &L, const DMove &m, E 
     for (int64_t c0 = 0; c0 < cc; c0 += TC) {
       const int nc = static_cast<int>(min(static_cast<int64_t>(TC), cc - c0));
       __syncthreads();
-      for (int i = L.tid; i < nc * TR; i += L.nthr) {
-        const int r = i % TR, c = i / TR;
-        if (r < nr) tile[c * (TR + 1) + r] = src[sbase + (c0 + c) * ld + r];
+      const E *sp = src + sbase + c0 * ld;
+      // loads first, into registers, then the shared-memory stores: written as one loop the
+      // compiler must assume the two pointers alias and would wait out each load in turn
+      constexpr int U = 8;
+      for (int i0 = L.tid; i0 < nc * TR; i0 += U * static_cast<int>(L.nthr)) {
+        E val[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const int i = i0 + u * static_cast<int>(L.nthr);
+          const int r = i % TR, c = i / TR;
+          val[u] = (i < nc * TR && r < nr) ? sp[static_cast<int64_t>(c) * ld + r] : E(0);
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const int i = i0 + u * static_cast<int>(L.nthr);
+          if (i < nc * TR) tile[(i / TR) * (TR + 1) + i % TR] = val[u];
+        }
       }
       __syncthreads();
+      E *dp = dst + row0 * cc + c0;
+#pragma unroll 8
       for (int i = L.tid; i < nr * TC; i += L.nthr) {
         const int c = i % TC, r = i / TC;
-        if (c < nc) dst[(row0 + r) * cc + c0 + c] = tile[c * (TR + 1) + r];
+        if (c < nc) dp[static_cast<int64_t>(r) * cc + c] = tile[c * (TR + 1) + r];
       }
     }
     row0 += nr;
@@ -107,7 +123,25 @@ __device__ __noinline__ void move_tiles(const Lane &L, const DTask &t, uint32_t 
   if (vec) {
     // lo is a multiple of 4096 and chunk divides 16, so chunks never straddle lo.
     const uint32_t c = m.chunk, c_lo = lo / c, c_hi = hi / c;
-    for (uint32_t k = c_lo + L.tid; k < c_hi; k += L.nthr) {
+    // four chunks per thread per trip: the four loads are independent and in flight together
+    constexpr uint32_t U = 4;
+    uint32_t k = c_lo + L.tid;
+    for (; k + (U - 1) * L.nthr < c_hi; k += U * L.nthr) {
+      int64_t s[U];
+      uint4 w[U];
+#pragma unroll
+      for (uint32_t u = 0; u < U; ++u) s[u] = base + view_index(m.view, (k + u * L.nthr) * c);
+#pragma unroll
+      for (uint32_t u = 0; u < U; ++u)
+        w[u] = scatter ? *reinterpret_cast<const uint4 *>(src + static_cast<int64_t>(k + u * L.nthr) * 16)
+                       : *reinterpret_cast<const uint4 *>(src + s[u] * esz);
+#pragma unroll
+      for (uint32_t u = 0; u < U; ++u) {
+        if (scatter) *reinterpret_cast<uint4 *>(dst + s[u] * esz) = w[u];
+        else *reinterpret_cast<uint4 *>(dst + static_cast<int64_t>(k + u * L.nthr) * 16) = w[u];
+      }
+    }
+    for (; k < c_hi; k += L.nthr) {
       const int64_t s = base + view_index(m.view, k * c);
       if (scatter)
         *reinterpret_cast<uint4 *>(dst + s * esz) = *reinterpret_cast<const uint4 *>(src + static_cast<int64_t>(k) * 16);

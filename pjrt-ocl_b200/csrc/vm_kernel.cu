@@ -39,7 +39,6 @@ __device__ __forceinline__ bool grid_barrier(const Lane &L, uint32_t barrier_ind
   if (L.tid == 0) {
     bool ok = true;
     DSync *s = P.sync;
-    if (L.lane == 0 && barrier_index < kPhaseSlots) s->phase_ns[barrier_index] = globaltimer_ns() - t_start;
     const uint32_t gen = ld_relaxed_gpu(&s->gen);
     __threadfence();  // release this lane's stores (made visible to thread 0 by the CTA barrier above)
     const uint32_t prev = atom_add_acq_rel_gpu(&s->arrive, 1u);
@@ -64,6 +63,8 @@ __device__ __forceinline__ bool grid_barrier(const Lane &L, uint32_t barrier_ind
         }
       }
     }
+    // when the phase ended for everybody: the barrier's release as lane 0 sees it
+    if (L.lane == 0 && barrier_index < kPhaseSlots) s->phase_ns[barrier_index] = globaltimer_ns() - t_start;
     __threadfence();  // acquire: later plain loads of this CTA see every lane's stores
     if (ok && ld_relaxed_gpu(&s->abort)) ok = false;
     ok_flag = ok ? 1u : 0u;

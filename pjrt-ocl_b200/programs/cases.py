@@ -58,6 +58,18 @@ def dot_general_square(n=8192, nlanes=NLANES, dtype=BF16, transpose_b=False):
     return blob, prog, (3, [("normal", (n, n), DN[dtype]), ("normal", (n, n), DN[dtype], 1.0 / n ** 0.5)])
 
 
+def flash_only(H=128, T=2048, hd=64, causal=True, nlanes=NLANES, dtype=BF16):
+    """Config 5's attention on its own: H = batch x heads, q [H,T,hd], k^T [H,hd,T], v [H,T,hd]."""
+    a_ = Asm()
+    q = a_.input((H, T, hd), dtype)
+    kt = a_.input((H, hd, T), dtype)
+    v = a_.input((H, T, hd), dtype)
+    o = a_.flash_attn(q, kt, v, 1.0 / math.sqrt(hd), causal)
+    blob, prog = a_.finish([o], nlanes=nlanes, costs=B200_COSTS)
+    return blob, prog, (5, [("normal", (H, T, hd), DN[dtype]), ("normal", (H, hd, T), DN[dtype]),
+                            ("normal", (H, T, hd), DN[dtype])])
+
+
 # --------------------------------------------------------------------------
 # config 2: LayerNorm -> tanh-GELU -> softmax -> full sum ; i32 add/xor/max
 # --------------------------------------------------------------------------

@@ -53,6 +53,7 @@ PROGRAMS["c3_sgd_apply_bf16"] = lambda: cases.sgd_apply(
 # the matmul tile-op family on its own
 PROGRAMS["dot_bf16_8192"] = lambda: cases.dot_general_square(8192)
 PROGRAMS["dot_bf16_4096"] = lambda: cases.dot_general_square(4096)
+PROGRAMS["flash_bf16_c5"] = lambda: cases.flash_only()
 
 
 def main():
