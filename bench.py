@@ -44,12 +44,14 @@ N_C2 = 8192 * 4096
 # name -> program blob, CPU-arm sample blob (+ fraction of the full workload it is),
 # algorithmic bytes per step, metric
 def _wl(program, metric, unit, alg, scale, bound, dtype, desc, roof_alg=None, sample=None, sample_frac=0.0,
-        secondary=False, plan=None):
+        secondary=False, plan=None, traffic=None):
     """alg: algorithmic units one step processes (bytes, flops or tokens); value = alg / seconds / scale.
-    roof_alg: bytes (bound "hbm") or flops (bound "tensor") of one step, for the roofline fraction."""
+    roof_alg: bytes (bound "hbm") or flops (bound "tensor") of one step, for the roofline fraction.
+    traffic: dram__bytes_read.sum + dram__bytes_write.sum of one launch from the ncu capture summarised under
+    profiles/ (bytes), where one was taken."""
     return dict(program=program, metric=metric, unit=unit, alg=alg, scale=scale, bound=bound, dtype=dtype, desc=desc,
                 roof_alg=alg if roof_alg is None else roof_alg, sample=sample, sample_frac=sample_frac,
-                secondary=secondary, plan=plan)
+                secondary=secondary, plan=plan, traffic=traffic)
 
 
 # config 5 block: 8 x 2048 tokens, d_model 1024, 16 heads x 64, FFN 4096
@@ -63,7 +65,7 @@ WORKLOADS = {
     "c2_f32": _wl("c2_chain_f32", "eltwise HBM GB/s", "GB/s", 7 * N_C2 * 4 + 2 * 4096 * 4, 1e9, "hbm", "f32",
                   "config 2: LayerNorm -> tanh-GELU -> softmax -> full sum on f32 (8192,4096); "
                   "bytes = LayerNorm r+w, GELU r+w, softmax r+w, sum r, + gamma/beta",
-                  sample="c2_chain_f32_cpu_sample", sample_frac=512 / 8192),
+                  sample="c2_chain_f32_cpu_sample", sample_frac=512 / 8192, traffic=945.1e6),
     "c2_bf16": _wl("c2_chain_bf16", "eltwise HBM GB/s", "GB/s", 7 * N_C2 * 2 + 2 * 4096 * 2, 1e9, "hbm", "bf16",
                    "config 2 on bf16-storage copies of the same values",
                    sample="c2_chain_bf16_cpu_sample", sample_frac=512 / 8192),
@@ -73,10 +75,10 @@ WORKLOADS = {
     "dot_bf16_8192": _wl("dot_bf16_8192", "dot_general TFLOP/s", "TFLOP/s", 2 * 8192 ** 3, 1e12, "tensor", "bf16",
                          "one dot_general bf16 8192 x 8192 x 8192, f32 accumulate, bf16 result"),
     "dot_bf16_4096": _wl("dot_bf16_4096", "dot_general TFLOP/s", "TFLOP/s", 2 * 4096 ** 3, 1e12, "tensor", "bf16",
-                         "one dot_general bf16 4096 x 4096 x 4096", secondary=True),
+                         "one dot_general bf16 4096 x 4096 x 4096", secondary=True, traffic=156.8e6),
     "flash_bf16": _wl("flash_bf16_c5", "flash-attention TFLOP/s", "TFLOP/s", _C5_ATT_FLOPS, 1e12, "tensor", "bf16",
                       "config 5's attention alone: 128 heads x 2048 x 2048, head_dim 64, causal (flops count the "
-                      "causal half)", secondary=True),
+                      "causal half)", secondary=True, traffic=147.0e6),
     "c3_mlp": _wl("c3_mlp_step_bf16", "dot_general TFLOP/s", "TFLOP/s", _C3_FLOPS, 1e12, "tensor", "bf16",
                   "config 3: 3-layer MLP forward + grad of MSE + SGD step, batch 8192, 1024-4096-4096-1024, bf16; "
                   "on N GPUs: local-batch gradients, NCCL all-reduce, SGD program", plan="c3"),
@@ -356,12 +358,21 @@ def main():
     achieved = (w["roof_alg"] / world if strong else w["roof_alg"]) / (ms_step * 1e-3) / roof_scale   # per GPU
 
     extra = {}
-    if rank == 0 and world == 1 and not a.no_extra:
-        for name, wl in WORKLOADS.items():
-            if name == a.workload:
-                continue
-            m, _, _, _, _ = run_workload(wl, max(5, a.steps // 2), 3, False)
-            extra[name] = {wl["unit"]: wl["alg"] / (m * 1e-3) / wl["scale"], "ms_per_step": m}
+    if not a.no_extra:
+        # N = 1: every other workload; N > 1: the two batch-sharded configurations (all ranks take part)
+        names = [n for n in WORKLOADS if n != a.workload] if world == 1 else \
+                [n for n in ("c5_block", "c3_mlp") if n != a.workload]
+        for name in names:
+            wl = WORKLOADS[name]
+            m, _, _, _, _ = run_workload(wl, max(5, min(a.steps // 2, 100)), 3, False)
+            tm = torch.tensor([m], device="cuda")
+            if world > 1:
+                dist.all_reduce(tm, op=dist.ReduceOp.MAX)
+            m = float(tm.item())
+            pl = dp.PLANS.get(wl["plan"]) if wl["plan"] else None
+            tot = wl["alg"] if (pl and pl.scaling == "strong") else wl["alg"] * world
+            extra[name] = {wl["unit"]: tot / (m * 1e-3) / wl["scale"], "ms_per_step": m,
+                           "scaling": "strong" if (pl and pl.scaling == "strong") else "weak"}
 
     if rank == 0:
         peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
@@ -380,7 +391,7 @@ def main():
                          "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"]},
                     roofline={"bound": w["bound"], "achieved": achieved, "peak": peak,
                               "unit": "GB/s" if w["bound"] == "hbm" else "TFLOP/s",
-                              "frac": achieved / peak, "traffic": None, "peak_source": peak_src,
+                              "frac": achieved / peak, "traffic": w["traffic"], "peak_source": peak_src,
                               "kernel": "b2_vm<512> (one launch per step)"},
                     cpu_baseline=cpu, device_ns_per_step=st["device_ns"], grid_barriers=st["barriers"],
                     phase_end_ns=st["phase_ns"], tensor_core_matmuls=st["tensor_core_matmuls"],

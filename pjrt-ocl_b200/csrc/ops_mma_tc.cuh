@@ -398,6 +398,10 @@ __device__ __noinline__ bool mma_tc_tiles(const Lane &L, const DTask &t, uint32_
         epi_t[mi] = on ? __int_as_float(e[4 + 4 * mi]) : 0.0f;
       }
     }
+    // staging slab of this warp for coalesced stores (32 rows x 16 words, pitch 17), after the stages
+    const uint32_t stg_off = stage0 - smem_addr(sm) + kTcStages * kTcStageBytes + ew * (32u * 17u * 4u);
+    uint32_t *stg = reinterpret_cast<uint32_t *>(sm + stg_off);
+    const bool coalesce = vec_store && stg_off + 32u * 17u * 4u <= L.smem_bytes;
     const uint32_t cdt = t.cdt;
     const bool vec_res = res && (reinterpret_cast<uintptr_t>(res) & 15u) == 0 && N % 8 == 0 && (cdt == kBF16 || cdt == kF32);
     uint32_t n = 0;
@@ -424,10 +428,10 @@ __device__ __noinline__ bool mma_tc_tiles(const Lane &L, const DTask &t, uint32_
         tc_ld32(tmem + ((32u * q) << 16) + buf * 256u + col, raw);
         tc_wait_ld();
         const int64_t c = c0 + col;
-        if (r < M && c < N) {
-          float v[32];
+        float v[32];
 #pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[j]);
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[j]);
+        if (r < M && c < N) {
           const int64_t ncols = min(static_cast<int64_t>(32), N - c);
           if (epi_generic) {
 #pragma unroll 1
@@ -478,7 +482,40 @@ __device__ __noinline__ bool mma_tc_tiles(const Lane &L, const DTask &t, uint32_
                 break;
             }
           }
-          tc_store_row32(dst, dt, (g * M + r) * N + c, v, ncols, vec_store);
+          if (!(coalesce && c + 32 <= N)) tc_store_row32(dst, dt, (g * M + r) * N + c, v, ncols, vec_store);
+        }
+        if (coalesce && c + 32 <= N) {
+          // Each thread holds 32 consecutive columns of ONE row: stored directly, a warp
+          // instruction would touch 32 rows with 16 bytes each (half-filled sectors). The
+          // warp's 32 x 32 block goes through its staging slab instead and leaves as
+          // 64-byte row segments, 4 lanes per row, 8 rows per instruction.
+          const uint32_t esz = dt == kF32 ? 4u : 2u;
+#pragma unroll
+          for (uint32_t h = 0; h < 2; ++h) {          // f32: two 16-column halves; 2-byte types: one pass
+            if (h == 1 && esz == 2u) break;
+            __syncwarp();
+            if (esz == 4u) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) stg[lane * 17u + j] = __float_as_uint(v[16 * h + j]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                const float lo = v[2 * j], hi = v[2 * j + 1];
+                stg[lane * 17u + j] = dt == kBF16 ? cvt_bf16x2(hi, lo) : (f32_to_f16_bits(lo) | (f32_to_f16_bits(hi) << 16));
+              }
+            }
+            __syncwarp();
+#pragma unroll
+            for (uint32_t pass = 0; pass < 4; ++pass) {
+              const uint32_t row = pass * 8u + (lane >> 2), ch = lane & 3u;
+              const int64_t rr = r0 + 32 * q + row;
+              if (rr < M) {
+                const uint32_t *sp = stg + row * 17u + ch * 4u;
+                uint8_t *gp = dst + ((g * M + rr) * N + c) * esz + h * 64u + ch * 16u;
+                *reinterpret_cast<uint4 *>(gp) = make_uint4(sp[0], sp[1], sp[2], sp[3]);
+              }
+            }
+          }
         }
       }
       tc_fence_before_sync();
