@@ -10,15 +10,17 @@
 // A lane's range of query rows is covered by 128-row blocks aligned inside a head
 // (rows outside the lane's range are computed and dropped: a block that straddles
 // two lanes' ranges is computed by both). Per block, over 128-key blocks:
-//   warps 0-7   producers: Q once, then K^T / V blocks through a 3-stage ring,
+//   warps 0-3   producers: Q once, then K^T / V blocks through a 3-stage ring,
 //               16-byte asynchronous copies into the swizzled operand layouts;
-//   warp 12     lane 0 issues S(j) = Q K(j)^T  (M 128, N 128, K 64) into one of two
+//   warp 4      lane 0 issues S(j) = Q K(j)^T  (M 128, N 128, K 64) into one of two
 //               S buffers, and O(j) = P(j) V(j) (M 128, N 64, K 128) into one of two O
 //               buffers, S(j+1) being issued ahead of O(j);
-//   warps 8-11  softmax: thread r owns query row r (= its tensor-memory lane): reads
-//               S(j), masks, updates the running maximum / sum, writes P(j) as bf16
-//               into shared memory for the second matmul, then folds O(j-1) into its
-//               register accumulator with the rescale factor; finally out = acc / sum.
+//   warps 8-15  softmax: two threads per query row (row = tensor-memory lane, the pair
+//               splits the 128 key columns and the 64 output columns): read S(j), mask,
+//               exchange the half-row maxima through shared memory, write P(j) as
+//               16-bit values into shared memory for the second matmul, then fold
+//               O(j-1) into the register accumulator with the rescale factor; finally
+//               out = acc / (sum of the two half-row sums).
 // Scores are handled in the log2 domain (one ex2 per score). Every wait is bounded.
 #ifndef B2VM_OPS_FLASH_TC_CUH_
 #define B2VM_OPS_FLASH_TC_CUH_
@@ -43,6 +45,8 @@ struct FaShared {
   uint64_t s_full[2];
   uint64_t p_full[2];
   uint64_t o_full[2];
+  uint64_t mx_full[2];      // both halves of every row have published their block maximum
+  uint64_t l_full;          // ... their final row sums
   uint32_t tmem_base;
   uint32_t failed;
 };
@@ -79,13 +83,16 @@ __device__ __noinline__ bool flash_tc_tiles(const Lane &L, const DTask &t, uint3
 
   __syncthreads();   // the scratch slot and the workspace are free
   if (L.tid == 0) {
-    mbar_init(&S->q_full, 256);
-    for (int s = 0; s < kFaStages; ++s) { mbar_init(&S->kv_full[s], 256); mbar_init(&S->kv_empty[s], 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(&S->s_full[b], 1); mbar_init(&S->p_full[b], 128); mbar_init(&S->o_full[b], 1); }
+    mbar_init(&S->q_full, 128);
+    for (int s = 0; s < kFaStages; ++s) { mbar_init(&S->kv_full[s], 128); mbar_init(&S->kv_empty[s], 1); }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&S->s_full[b], 1); mbar_init(&S->p_full[b], 256); mbar_init(&S->o_full[b], 1); mbar_init(&S->mx_full[b], 256);
+    }
+    mbar_init(&S->l_full, 256);
     S->failed = 0u;
     fence_mbar_init();
   }
-  if (w == 12) {
+  if (w == 4) {
     __syncwarp();
     tmem_alloc(&S->tmem_base, kFaCols);
   }
@@ -107,14 +114,14 @@ __device__ __noinline__ bool flash_tc_tiles(const Lane &L, const DTask &t, uint3
     const int64_t c_max = causal ? min(C, m0 + rows_q - 1 + (C - T) + 1) : C;
     const int64_t nkb = (c_max + 127) / 128;
 
-    if (w < 8) {
-      // ---------------- producers ----------------
+    if (w < 4) {
+      // ---------------- producers (128 threads) ----------------
       const uint32_t ptid = L.tid;
       {   // Q block, K-major: row (query) at 128 B pitch, chunks XORed with row % 8
         const uint32_t c = ptid & 7u, r = ptid >> 3;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int64_t row = r + 32 * i;
+        for (int i = 0; i < 8; ++i) {
+          const int64_t row = r + 16 * i;
           const bool okr = row < rows_q;
           cp_async_16_zfill(q_s + static_cast<uint32_t>(row) * 128u + ((c ^ (static_cast<uint32_t>(row) & 7u)) << 4),
                             okr ? Q + ((g * T + m0 + row) * hd + 8 * c) : Q, okr ? 16u : 0u);
@@ -123,25 +130,25 @@ __device__ __noinline__ bool flash_tc_tiles(const Lane &L, const DTask &t, uint3
       }
       for (int64_t j = 0; j < nkb; ++j) {
         const uint32_t kvpos = kvit + static_cast<uint32_t>(j), s = kvpos % kFaStages;
-        if (!tc_wait_warp(&S->kv_empty[s], ((kvpos / kFaStages) & 1u) ^ 1u, failed, budget, 32u)) break;
+        if (!tc_wait_warp(&S->kv_empty[s], ((kvpos / kFaStages) & 1u) ^ 1u, failed, budget, 64u)) break;
         const uint32_t ks = kv_s + s * kFaKvBytes, vs = ks + 128 * 128;
         const int64_t n0 = j * 128;
         {   // K^T block: element (d, key) at KT[(g*hd + d)*C + key]: keys are the unit-stride ("MN") dimension
-          const uint32_t cm = ptid & 15u, dr = ptid >> 4;            // 16 key chunks x 16 d lines per pass
+          const uint32_t cm = ptid & 15u, dr = ptid >> 4;            // 16 key chunks x 8 d lines per pass
           const int64_t key = n0 + 8 * cm;
           const uint32_t kbytes = key < C ? static_cast<uint32_t>(min(static_cast<int64_t>(16), 2 * (C - key))) : 0u;
 #pragma unroll
-          for (uint32_t i = 0; i < 4; ++i) {
-            const uint32_t d = dr + 16u * i;
+          for (uint32_t i = 0; i < 8; ++i) {
+            const uint32_t d = dr + 8u * i;
             const uint32_t dst = ks + (cm >> 3) * 8192u + (d >> 3) * 1024u + (d & 7u) * 128u + (((cm & 7u) ^ (d & 7u)) << 4);
             cp_async_16_zfill(dst, kbytes ? KT + ((g * hd + d) * C + key) : KT, kbytes);
           }
         }
         {   // V block: element (key, d) at V[(g*C + key)*hd + d]: d is the unit-stride ("MN") dimension, keys are k
-          const uint32_t cd = ptid & 7u, kr = ptid >> 3;             // 8 d chunks x 32 keys per pass
+          const uint32_t cd = ptid & 7u, kr = ptid >> 3;             // 8 d chunks x 16 keys per pass
 #pragma unroll
-          for (uint32_t i = 0; i < 4; ++i) {
-            const uint32_t kk = kr + 32u * i;
+          for (uint32_t i = 0; i < 8; ++i) {
+            const uint32_t kk = kr + 16u * i;
             const int64_t key = n0 + kk;
             const uint32_t dst = vs + (kk >> 3) * 1024u + (kk & 7u) * 128u + ((cd ^ (kk & 7u)) << 4);
             cp_async_16_zfill(dst, key < C ? V + ((g * C + key) * hd + 8 * cd) : V, key < C ? 16u : 0u);
@@ -150,7 +157,7 @@ __device__ __noinline__ bool flash_tc_tiles(const Lane &L, const DTask &t, uint3
         cp_async_mbar_arrive(&S->kv_full[s]);
       }
       cp_async_wait_all();
-    } else if (w == 12) {
+    } else if (w == 4) {
       // ---------------- MMA issue ----------------
       if (lane == 0) {
         const uint32_t fmt = adt == kBF16 ? 1u : 0u;
@@ -190,16 +197,17 @@ __device__ __noinline__ bool flash_tc_tiles(const Lane &L, const DTask &t, uint3
         }
       }
       __syncwarp();
-    } else if (w >= 8 && w < 12) {
-      // ---------------- softmax + output: thread = query row ----------------
-      const uint32_t q4 = w - 8, r = 32u * q4 + lane;
+    } else if (w >= 8) {
+      // ---------------- softmax + output: two threads per query row ----------------
+      const uint32_t q4 = w & 3u, hf = (w - 8u) >> 2, r = 32u * q4 + lane;
+      float *xch = reinterpret_cast<float *>(sm + kSmemChain);          // [2 parities][2 halves][128 rows], then [2][128] sums
       const int64_t m = m0 + r, grow = g * T + m;
       const bool row_ok = m < T && grow >= first && grow < rows_end;
       const int64_t c_end = causal ? min(C, m + (C - T) + 1) : C;   // keys this row may see
       float m_run = -INFINITY, l_run = 0.0f;
-      float acc[64];
+      float acc[32];                                                  // output columns 32 hf .. 32 hf + 31
 #pragma unroll
-      for (int d = 0; d < 64; ++d) acc[d] = 0.0f;
+      for (int d = 0; d < 32; ++d) acc[d] = 0.0f;
       bool ok = true;
       for (int64_t j = 0; ok && j <= nkb; ++j) {
         const uint32_t jj = jt + static_cast<uint32_t>(j);
@@ -207,13 +215,13 @@ __device__ __noinline__ bool flash_tc_tiles(const Lane &L, const DTask &t, uint3
         if (j < nkb) {
           if (!tc_wait_warp(&S->s_full[jj & 1u], (jj >> 1) & 1u, failed, budget)) { ok = false; break; }
           tc_fence_after_sync();
-          // valid columns of this block for this row (keys n0 .. n0 + lim - 1)
-          const int lim = static_cast<int>(max(static_cast<int64_t>(0), min(static_cast<int64_t>(128), c_end - j * 128)));
-          const uint32_t s_addr = tmem + ((32u * q4) << 16) + (jj & 1u) * 128u;
-          // pass 1: the row's maximum over this block
+          // valid columns of this thread's half (keys n0 + 64 hf .. + lim - 1)
+          const int lim = static_cast<int>(max(static_cast<int64_t>(0), min(static_cast<int64_t>(64), c_end - j * 128 - 64 * hf)));
+          const uint32_t s_addr = tmem + ((32u * q4) << 16) + (jj & 1u) * 128u + 64u * hf;
+          // pass 1: the half row's maximum over this block, then the row's through shared memory
           float mx = -INFINITY;
 #pragma unroll 1
-          for (int cb = 0; cb < 128; cb += 32) {
+          for (int cb = 0; cb < 64; cb += 32) {
             uint32_t raw[32];
             __syncwarp();
             tc_ld32(s_addr + cb, raw);
@@ -227,15 +235,19 @@ __device__ __noinline__ bool flash_tc_tiles(const Lane &L, const DTask &t, uint3
                 if (cb + i < lim) mx = fmaxf(mx, __uint_as_float(raw[i]) * sl2);
             }
           }
+          xch[((jj & 1u) * 2u + hf) * 128u + r] = mx;
+          mbar_arrive(&S->mx_full[jj & 1u]);
+          if (!tc_wait_warp(&S->mx_full[jj & 1u], (jj >> 1) & 1u, failed, budget)) { ok = false; break; }
+          mx = fmaxf(mx, xch[((jj & 1u) * 2u + (hf ^ 1u)) * 128u + r]);
           const float m_new = fmaxf(m_run, mx);
           alpha = m_run == -INFINITY ? (m_new == -INFINITY ? 1.0f : 0.0f) : fast_ex2(m_run - m_new);
           const float neg_m = m_new == -INFINITY ? 0.0f : -m_new;
           // pass 2: p = 2^(s - m_new), written as the 16-bit A operand of the second matmul
           float psum = 0.0f;
-          const uint32_t pb = p_s + (jj & 1u) * kFaPBytes;
+          const uint32_t prow = p_s + (jj & 1u) * kFaPBytes + hf * 16384u + r * 128u;   // 64 keys = one sub-tile
           const bool bf = adt == kBF16;
 #pragma unroll 1
-          for (int cb = 0; cb < 128; cb += 16) {
+          for (int cb = 0; cb < 64; cb += 16) {
             uint32_t raw[16];
             __syncwarp();
             tc_ld16(s_addr + cb, raw);
@@ -258,12 +270,10 @@ __device__ __noinline__ bool flash_tc_tiles(const Lane &L, const DTask &t, uint3
             }
 #pragma unroll
             for (int i = 0; i < 16; ++i) psum += pv[i];
-            // 16 keys = 2 chunks of 8; sub-tile = cb / 64, chunk inside it = (cb % 64) / 8 + q
-            const uint32_t sub = pb + (static_cast<uint32_t>(cb) >> 6) * 16384u + r * 128u;
 #pragma unroll
-            for (uint32_t q = 0; q < 2; ++q) {
-              const uint32_t ch = ((static_cast<uint32_t>(cb) & 63u) >> 3) + q;
-              uint4 *dstp = reinterpret_cast<uint4 *>(sm + (sub + ((ch ^ (r & 7u)) << 4) - smem_addr(sm)));
+            for (uint32_t q = 0; q < 2; ++q) {                      // 16 keys = 2 chunks of 8
+              const uint32_t ch = (static_cast<uint32_t>(cb) >> 3) + q;
+              uint4 *dstp = reinterpret_cast<uint4 *>(sm + (prow + ((ch ^ (r & 7u)) << 4) - smem_addr(sm)));
               *dstp = make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
             }
           }
@@ -278,29 +288,28 @@ __device__ __noinline__ bool flash_tc_tiles(const Lane &L, const DTask &t, uint3
           const uint32_t pj = jj - 1u;
           if (!tc_wait_warp(&S->o_full[pj & 1u], (pj >> 1) & 1u, failed, budget)) { ok = false; break; }
           tc_fence_after_sync();
+          uint32_t raw[32];
+          __syncwarp();
+          tc_ld32(tmem + ((32u * q4) << 16) + 256u + (pj & 1u) * 64u + 32u * hf, raw);
+          tc_wait_ld();
 #pragma unroll
-          for (uint32_t cb = 0; cb < 64; cb += 32) {
-            uint32_t raw[32];
-            __syncwarp();
-            tc_ld32(tmem + ((32u * q4) << 16) + 256u + (pj & 1u) * 64u + cb, raw);
-            tc_wait_ld();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) acc[cb + i] = (acc[cb + i] + __uint_as_float(raw[i])) * alpha;
-          }
+          for (int i = 0; i < 32; ++i) acc[i] = (acc[i] + __uint_as_float(raw[i])) * alpha;
         } else {
 #pragma unroll
-          for (int d = 0; d < 64; ++d) acc[d] *= alpha;
+          for (int d = 0; d < 32; ++d) acc[d] *= alpha;
         }
       }
+      // the row's sum is the two halves' (they share the running maximum)
+      float *lx = xch + 512;
+      lx[hf * 128u + r] = l_run;
+      mbar_arrive(&S->l_full);
+      if (ok && !tc_wait_warp(&S->l_full, qn & 1u, failed, budget)) ok = false;
       if (ok && row_ok) {
-        const float inv = 1.0f / l_run;
+        const float inv = 1.0f / (l_run + lx[(hf ^ 1u) * 128u + r]);
         float v[32];
 #pragma unroll
-        for (uint32_t cb = 0; cb < 64; cb += 32) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = acc[cb + i] * inv;
-          tc_store_row32(out, dt, grow * hd + cb, v, 32, true);
-        }
+        for (int i = 0; i < 32; ++i) v[i] = acc[i] * inv;
+        tc_store_row32(out, dt, grow * hd + 32 * hf, v, 32, true);
       }
     }
     kvit += static_cast<uint32_t>(nkb);
@@ -316,7 +325,7 @@ __device__ __noinline__ bool flash_tc_tiles(const Lane &L, const DTask &t, uint3
   // ---------------- teardown ----------------
   tc_fence_before_sync();
   __syncthreads();
-  if (w == 12) {
+  if (w == 4) {
     __syncwarp();
     tc_fence_after_sync();
     tmem_dealloc(tmem, kFaCols);
@@ -325,7 +334,10 @@ __device__ __noinline__ bool flash_tc_tiles(const Lane &L, const DTask &t, uint3
     if (S->failed) set_status(P, kStTensorTimeout, L.lane, tile_lo, kTopFlashAttn);
     mbar_inval(&S->q_full);
     for (int s = 0; s < kFaStages; ++s) { mbar_inval(&S->kv_full[s]); mbar_inval(&S->kv_empty[s]); }
-    for (int b = 0; b < 2; ++b) { mbar_inval(&S->s_full[b]); mbar_inval(&S->p_full[b]); mbar_inval(&S->o_full[b]); }
+    for (int b = 0; b < 2; ++b) {
+      mbar_inval(&S->s_full[b]); mbar_inval(&S->p_full[b]); mbar_inval(&S->o_full[b]); mbar_inval(&S->mx_full[b]);
+    }
+    mbar_inval(&S->l_full);
   }
   __syncthreads();
   return true;
