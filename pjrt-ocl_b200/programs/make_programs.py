@@ -21,23 +21,29 @@ sys.path.insert(0, HERE)
 import cases  # noqa: E402
 from vmasm import BF16, F32  # noqa: E402
 
+# Programs whose phases hold several equal units (the three q/k/v projections, the three
+# head transposes): the scheduler gives each unit ceil(lanes * share) chunks, which for
+# 148 lanes and three units is 150 chunks - two lanes would run two chunks and the phase
+# twice as long. 144 divides by 2, 3, 4, 6 and 8.
+MULTI_UNIT_LANES = 144
+
 PROGRAMS = {
     "c1_relu_matmul": lambda: cases.c1_relu_matmul(),
     "c2_chain_f32": lambda: cases.c2_chain(dtype=F32),
     "c2_chain_bf16": lambda: cases.c2_chain(dtype=BF16),
     "c2_chain_f32_decomposed": lambda: cases.c2_chain(dtype=F32, fused=False),
     "c2_int_chain": lambda: cases.c2_int_chain(),
-    "c3_mlp_step_bf16": lambda: cases.c3_mlp_step(),
+    "c3_mlp_step_bf16": lambda: cases.c3_mlp_step(nlanes=MULTI_UNIT_LANES),
     "c4_nbody": lambda: cases.c4_nbody(),
-    "c5_block_bf16": lambda: cases.c5_block(),
-    "c5_decode_bf16": lambda: cases.c5_decode(),
+    "c5_block_bf16": lambda: cases.c5_block(nlanes=MULTI_UNIT_LANES),
+    "c5_decode_bf16": lambda: cases.c5_decode(nlanes=MULTI_UNIT_LANES),
 }
 # data-parallel shards of config 3 / 5 (batch split over 2, 4, 8 GPUs)
 for g in (2, 4, 8):
     PROGRAMS[f"c3_mlp_grads_bf16_dp{g}"] = (
-        lambda g=g: cases.c3_mlp_step(batch=8192 // g, global_batch=8192, apply_sgd=False))
-    PROGRAMS[f"c5_block_bf16_dp{g}"] = lambda g=g: cases.c5_block(batch=8 // g)
-    PROGRAMS[f"c5_decode_bf16_dp{g}"] = lambda g=g: cases.c5_decode(batch=32 // g)
+        lambda g=g: cases.c3_mlp_step(batch=8192 // g, global_batch=8192, apply_sgd=False, nlanes=MULTI_UNIT_LANES))
+    PROGRAMS[f"c5_block_bf16_dp{g}"] = lambda g=g: cases.c5_block(batch=8 // g, nlanes=MULTI_UNIT_LANES)
+    PROGRAMS[f"c5_decode_bf16_dp{g}"] = lambda g=g: cases.c5_decode(batch=32 // g, nlanes=MULTI_UNIT_LANES)
 # the four stages of config 2 as programs of their own (one tile-op family each),
 # for per-family roofline numbers and ncu captures
 for stage in ("layernorm", "affine_gelu", "softmax", "sum"):
