@@ -343,8 +343,8 @@ class LoadedProgram:
                 "barriers": st.barriers, "device_ns": st.device_ns}
 
     def PhaseTimes(self) -> list:
-        """ns since kernel entry at which lane 0 reached each grid barrier of the
-        last execute (first 64 barriers)."""
+        """ns since kernel entry at which each grid barrier of the last execute
+        released (first 64 barriers): the end of each phase for every lane."""
         buf = (ctypes.c_uint64 * 64)()
         n = lib().b2_loaded_phase_ns(self._h, buf, 64)
         return [int(buf[i]) for i in range(n)]

@@ -1,0 +1,86 @@
+"""Full-size configurations on the GPU, checked through size-independent properties
+and sampled exact recomputation (the oracle would take minutes at these sizes):
+  * config 2 i32 chain: bit-exact against numpy on all 33.5 M elements;
+  * config 2 f32 chain: softmax rows are non-negative and sum to 1, the scalar equals
+    their sum (= the row count);
+  * dot_general bf16 4096^3: sampled rows against a float64 dot of the same bf16 inputs;
+  * config 5's attention (128 heads x 2048 x 2048, causal, bf16): sampled query rows
+    against a float64 softmax(QK^T)V.
+Tolerances: integer exact; f32 rel 1e-5 class; bf16 rel 2e-2."""
+import gzip
+import json
+import os
+import sys
+
+import ml_dtypes
+import numpy as np
+import pytest
+
+from conftest import package
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+PROG = os.path.join(ROOT, "pjrt-ocl_b200", "programs")
+sys.path.insert(0, PROG)
+import inputs as gen_inputs  # noqa: E402
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def rt():
+    vm = package()
+    r = vm.Runtime.Create(0)
+    yield r
+    r.close()
+
+
+def _run(rt, name):
+    vm = package()
+    man = json.load(open(os.path.join(PROG, "manifest.json")))[name]
+    with gzip.open(os.path.join(PROG, name + ".vmprog.gz"), "rb") as f:
+        blob = f.read()
+    args = gen_inputs.gen_all(man["seed"], man["items"])
+    lp = vm.LoadedProgram.Load(rt, vm.VmProgram.Parse(blob))
+    outs = lp.Execute(args)
+    st = lp.Status()
+    lp.close()
+    assert st["code"] == 0
+    return args, outs
+
+
+def test_config2_int_chain_is_bit_exact_at_full_size(rt):
+    (a, b, c, d), (out,) = _run(rt, "c2_int_chain")
+    want = np.maximum((a + b) ^ c, d)
+    got = np.asarray(out).view(np.int32).reshape(want.shape)
+    assert np.array_equal(got, want)
+
+
+def test_config2_f32_chain_properties_at_full_size(rt):
+    _, outs = _run(rt, "c2_chain_f32")
+    sm = np.asarray(outs[0]).view(np.float32).reshape(8192, 4096)
+    total = float(np.asarray(outs[1]).view(np.float32).reshape(-1)[0])
+    assert np.isfinite(sm).all() and (sm >= 0).all()
+    rows = sm.astype(np.float64).sum(axis=1)
+    assert np.max(np.abs(rows - 1.0)) < 1e-4          # every softmax row sums to 1
+    assert abs(total - rows.sum()) / 8192.0 < 1e-5     # the full sum is the sum of the rows (~8192)
+
+
+def test_dot_bf16_4096_sampled_rows(rt):
+    (x, w), (y,) = _run(rt, "dot_bf16_4096")
+    got = np.asarray(y).view(ml_dtypes.bfloat16).reshape(4096, 4096).astype(np.float64)
+    rows = np.random.default_rng(7).choice(4096, size=16, replace=False)
+    want = x[rows].astype(np.float64) @ w.astype(np.float64)
+    err = np.abs(got[rows] - want)
+    assert np.max(err / (np.abs(want) + 2e-2)) < 2e-2
+
+
+def test_flash_attention_c5_sampled_rows(rt):
+    (q, kt, v), (o,) = _run(rt, "flash_bf16_c5")
+    H, T, hd = q.shape
+    got = np.asarray(o).view(ml_dtypes.bfloat16).reshape(H, T, hd).astype(np.float64)
+    rng = np.random.default_rng(11)
+    for h, m in zip(rng.integers(0, H, 12), list(rng.integers(0, T, 10)) + [0, T - 1]):
+        s = (q[h, m].astype(np.float64) @ kt[h].astype(np.float64))[: m + 1] / np.sqrt(hd)   # causal: keys 0..m
+        p = np.exp(s - s.max())
+        want = (p / p.sum()) @ v[h, : m + 1].astype(np.float64)
+        assert np.max(np.abs(got[h, m] - want) / (np.abs(want) + 2e-2)) < 2e-2, (h, m)
