@@ -188,24 +188,47 @@ __device__ __forceinline__ uint32_t view_mod(const DView &v, int k, uint32_t n) 
 // trip loop is a single counted loop; lives after the EwOp array.
 struct EwFlat {
   uint32_t n;
-  uint32_t cold;            // some step is outside the hot set (see ew_step_is_cold)
+  uint32_t tier;            // smallest EwTier that has every step of the chain
   EwStep s[kChainMax * kEwMaxSteps];
 };
 constexpr int kSmemEwFlat = kSmemChain + static_cast<int>(sizeof(EwOp)) * kChainMax;
 static_assert(kSmemEwFlat + sizeof(EwFlat) <= kSmemSys, "flattened steps fit the system area");
 
-// Steps with long bodies (division, transcendentals, rounding, conversions,
-// loads through a general strided view). The
-// trip loop is compiled twice: once with only the short bodies - where the
-// register banks are not squeezed by code that almost never runs - and once with
-// everything, for chains that contain a cold step.
-__device__ __forceinline__ bool ew_step_is_cold(uint32_t c) {
-  if (c >= kSFlt && c < kSInt) {
-    const uint32_t f = c - kSFlt;
-    return !(f == ew_fcode(kAdd) || f == ew_fcode(kMul) || f == ew_fcode(kSubt) || f == ew_fcode(kMax) ||
-             f == ew_fcode(kMin) || f == ew_fcode(kNeg) || f == ew_fcode(kAbs) || f == ew_fcode(kGelu));
-  }
-  return c == kSIotaF || c == kSIotaI || (c >= kSCvtF2I && c <= kSBNot) || (c >= kSLdXViewW4 && c <= kSLdYViewBf);
+// The trip loop is compiled five times ("tiers"), each containing only some of the step
+// bodies: the compiler's code for the common steps is markedly better (fewer register
+// moves around the dispatch, no spills) when the rarely used, long or register-hungry
+// bodies are not in the same function. A chain runs in the smallest tier that has all
+// its steps:
+//   kTierF32  4-byte contiguous / row-vector loads, 4-byte store, float add mul sub max min neg abs
+//             gelu, affine, fill
+//   kTierBf   the same with bf16 loads / stores / rounding added
+//   kTierInt  4-byte loads / stores and the integer ops
+//   kTierHot  every short body
+//   kTierAll  everything (division, transcendentals, rounding, conversions, general strided and
+//             column-broadcast loads)
+enum EwTier : int { kTierF32 = 0, kTierBf, kTierInt, kTierHot, kTierAll };
+
+__host__ __device__ constexpr bool ew_is_cheap_float(uint32_t c) {
+  return c >= kSFlt && c < kSInt &&
+         (c - kSFlt == ew_fcode(kAdd) || c - kSFlt == ew_fcode(kMul) || c - kSFlt == ew_fcode(kSubt) ||
+          c - kSFlt == ew_fcode(kMax) || c - kSFlt == ew_fcode(kMin) || c - kSFlt == ew_fcode(kNeg) ||
+          c - kSFlt == ew_fcode(kAbs) || c - kSFlt == ew_fcode(kGelu));
+}
+__host__ __device__ constexpr bool ew_step_is_cold(uint32_t c) {
+  return (c >= kSFlt && c < kSInt && !ew_is_cheap_float(c)) || c == kSIotaF || c == kSIotaI ||
+         (c >= kSCvtF2I && c <= kSBNot) || (c >= kSLdXViewW4 && c <= kSLdYColBf);
+}
+__host__ __device__ constexpr bool ew_tier_has(int tier, uint32_t c) {
+  if (tier == kTierAll) return true;
+  if (tier == kTierHot) return !ew_step_is_cold(c);
+  const bool f32core = c == kSMovYX || c == kSLdXW4 || c == kSLdYW4 || c == kSLdXRowW4 || c == kSLdYRowW4 ||
+                       c == kSStW4 || c == kSAffine || c == kSFill || ew_is_cheap_float(c);
+  if (tier == kTierF32) return f32core;
+  if (tier == kTierBf)
+    return f32core || c == kSLdXBf || c == kSLdYBf || c == kSLdXRowBf || c == kSLdYRowBf || c == kSStBf || c == kSQuantBf;
+  // kTierInt
+  return c == kSMovYX || c == kSLdXW4 || c == kSLdYW4 || c == kSStW4 || c == kSFill || c == kSUMax || c == kSUMin ||
+         (c >= kSInt && c < kSEnd);
 }
 
 // One thread, after every op's steps are built.
@@ -216,7 +239,8 @@ __device__ __forceinline__ bool ew_step_is_cold(uint32_t c) {
 // entry instead (p2 = 1, p3 = byte offset) when they fit.
 __device__ inline void ew_plan(EwOp *ops, uint32_t k, EwFlat *fl, uint32_t smem_bytes) {
   const uint8_t *sm = reinterpret_cast<const uint8_t *>(ops) - kSmemChain;
-  uint32_t n = 0, used = 0, cold = 0;
+  uint32_t n = 0, used = 0;
+  bool in_tier[5] = {true, true, true, true, true};
   const uint32_t avail = smem_bytes > static_cast<uint32_t>(kSmemSys) ? smem_bytes - kSmemSys : 0u;
   for (uint32_t j = 0; j < k && ops[j].nsteps != kEwNoSteps; ++j)
     for (uint32_t si = 0; si < ops[j].nsteps; ++si) {
@@ -227,11 +251,11 @@ __device__ inline void ew_plan(EwOp *ops, uint32_t k, EwFlat *fl, uint32_t smem_
         const uint32_t b = (v.dim[1] * esz + 15u) & ~15u;
         if (used + b <= avail) { st.p2 = 1u; st.p3 = kSmemSys + used; used += b; }
       }
-      if (ew_step_is_cold(st.code)) cold = 1u;
+      for (int tr = 0; tr < 5; ++tr) in_tier[tr] = in_tier[tr] && ew_tier_has(tr, st.code);
       fl->s[n++] = st;
     }
   fl->n = n;
-  fl->cold = cold;
+  fl->tier = in_tier[0] ? 0u : in_tier[1] ? 1u : in_tier[2] ? 2u : in_tier[3] ? 3u : 4u;
 }
 
 // Copy the cached row vectors in (all threads of the lane; 8-byte words, which is
@@ -256,9 +280,9 @@ __device__ __forceinline__ void ew_stage_rows(const Lane &L, const EwFlat *fl) {
 // element `lo`. Per trip a thread owns kEwU groups (group g0 + u * nthr), held in
 // the register banks X and Y across the steps; each step body is the 16
 // evaluations, fully unrolled. FULL: every trip has all kEwU groups (ge - gb is a
-// multiple of nthr * kEwU), so no access is predicated. COLD: the bodies of the
-// cold steps are compiled in.
-template <bool FULL, bool COLD>
+// multiple of nthr * kEwU), so no access is predicated. TIER: which step bodies are
+// compiled in (ew_tier_has).
+template <bool FULL, int TIER>
 __device__ __noinline__ void ew_steps_run(uint32_t tid, uint32_t nthr, uint32_t lo, uint32_t gb, uint32_t ge) {
   B2_DYN_SMEM(sm);
   const EwFlat &fl = *reinterpret_cast<const EwFlat *>(sm + kSmemEwFlat);
@@ -360,85 +384,91 @@ __device__ __noinline__ void ew_steps_run(uint32_t tid, uint32_t nthr, uint32_t 
   _Pragma("unroll") for (int e = 0; e < 4; ++e) { __VA_ARGS__; }
 #define B2_SF(S, EXPR)                                                           \
   case kSFlt + ew_fcode(S):                                                              \
-    B2_ALL(const float x = __uint_as_float(X[u][e]), y = __uint_as_float(Y[u][e]); \
-           (void)y; X[u][e] = __float_as_uint(EXPR))                             \
+    if constexpr (ew_tier_has(TIER, kSFlt + ew_fcode(S))) {                      \
+      B2_ALL(const float x = __uint_as_float(X[u][e]), y = __uint_as_float(Y[u][e]); \
+             (void)y; X[u][e] = __float_as_uint(EXPR))                           \
+    }                                                                            \
     break;
 #define B2_SFC(S, EXPR)                                                          \
   case kSFlt + ew_fcode(S):                                                              \
-    if constexpr (COLD) {                                                        \
+    if constexpr (ew_tier_has(TIER, kSFlt + ew_fcode(S))) {                      \
       B2_ALL(const float x = __uint_as_float(X[u][e]); X[u][e] = __float_as_uint(EXPR)) \
     }                                                                            \
     break;
 #define B2_SI(S, EXPR)                                                           \
   case kSInt + ew_icode(S):                                                              \
-    B2_ALL(const uint32_t x = X[u][e], y = Y[u][e]; (void)y; X[u][e] = (EXPR))   \
+    if constexpr (ew_tier_has(TIER, kSInt + ew_icode(S))) {                      \
+      B2_ALL(const uint32_t x = X[u][e], y = Y[u][e]; (void)y; X[u][e] = (EXPR)) \
+    }                                                                            \
     break;
 #define B2_SCMP(BASE, CAST)                                                                   \
-  case BASE + 0: B2_ALL(X[u][e] = (CAST(X[u][e]) == CAST(Y[u][e])) ? 1u : 0u) break;         \
-  case BASE + 1: B2_ALL(X[u][e] = (CAST(X[u][e]) != CAST(Y[u][e])) ? 1u : 0u) break;         \
-  case BASE + 2: B2_ALL(X[u][e] = (CAST(X[u][e]) < CAST(Y[u][e])) ? 1u : 0u) break;          \
-  case BASE + 3: B2_ALL(X[u][e] = (CAST(X[u][e]) <= CAST(Y[u][e])) ? 1u : 0u) break;         \
-  case BASE + 4: B2_ALL(X[u][e] = (CAST(X[u][e]) > CAST(Y[u][e])) ? 1u : 0u) break;          \
-  case BASE + 5: B2_ALL(X[u][e] = (CAST(X[u][e]) >= CAST(Y[u][e])) ? 1u : 0u) break;
+  case BASE + 0: if constexpr (ew_tier_has(TIER, BASE + 0)) { B2_ALL(X[u][e] = (CAST(X[u][e]) == CAST(Y[u][e])) ? 1u : 0u) } break;         \
+  case BASE + 1: if constexpr (ew_tier_has(TIER, BASE + 1)) { B2_ALL(X[u][e] = (CAST(X[u][e]) != CAST(Y[u][e])) ? 1u : 0u) } break;         \
+  case BASE + 2: if constexpr (ew_tier_has(TIER, BASE + 2)) { B2_ALL(X[u][e] = (CAST(X[u][e]) < CAST(Y[u][e])) ? 1u : 0u) } break;          \
+  case BASE + 3: if constexpr (ew_tier_has(TIER, BASE + 3)) { B2_ALL(X[u][e] = (CAST(X[u][e]) <= CAST(Y[u][e])) ? 1u : 0u) } break;         \
+  case BASE + 4: if constexpr (ew_tier_has(TIER, BASE + 4)) { B2_ALL(X[u][e] = (CAST(X[u][e]) > CAST(Y[u][e])) ? 1u : 0u) } break;          \
+  case BASE + 5: if constexpr (ew_tier_has(TIER, BASE + 5)) { B2_ALL(X[u][e] = (CAST(X[u][e]) >= CAST(Y[u][e])) ? 1u : 0u) } break;
 
     for (uint32_t si = 0; si < nsteps; ++si) {
       const EwStep &st = fl.s[si];
       switch (st.code) {
-          case kSMovYX: B2_ALL(Y[u][e] = X[u][e]) break;
-          case kSLdXW4: ld_w4(X, st); break;
-          case kSLdYW4: ld_w4(Y, st); break;
-          case kSLdXBf: ld_bf(X, st); break;
-          case kSLdYBf: ld_bf(Y, st); break;
-          case kSLdXB1: ld_b1(X, st); break;
-          case kSLdYB1: ld_b1(Y, st); break;
-          case kSLdXRowW4: ld_row(X, st, false); break;
-          case kSLdYRowW4: ld_row(Y, st, false); break;
-          case kSLdXRowBf: ld_row(X, st, true); break;
-          case kSLdYRowBf: ld_row(Y, st, true); break;
-          case kSLdXColW4: ld_col(X, st, false); break;
-          case kSLdYColW4: ld_col(Y, st, false); break;
-          case kSLdXColBf: ld_col(X, st, true); break;
-          case kSLdYColBf: ld_col(Y, st, true); break;
-          case kSLdXViewW4: if constexpr (COLD) ld_view(X, st, false); break;
-          case kSLdYViewW4: if constexpr (COLD) ld_view(Y, st, false); break;
-          case kSLdXViewBf: if constexpr (COLD) ld_view(X, st, true); break;
-          case kSLdYViewBf: if constexpr (COLD) ld_view(Y, st, true); break;
-          case kSStW4: {
+          case kSMovYX: if constexpr (ew_tier_has(TIER, kSMovYX)) { B2_ALL(Y[u][e] = X[u][e]) } break;
+          case kSLdXW4: if constexpr (ew_tier_has(TIER, kSLdXW4)) { ld_w4(X, st); } break;
+          case kSLdYW4: if constexpr (ew_tier_has(TIER, kSLdYW4)) { ld_w4(Y, st); } break;
+          case kSLdXBf: if constexpr (ew_tier_has(TIER, kSLdXBf)) { ld_bf(X, st); } break;
+          case kSLdYBf: if constexpr (ew_tier_has(TIER, kSLdYBf)) { ld_bf(Y, st); } break;
+          case kSLdXB1: if constexpr (ew_tier_has(TIER, kSLdXB1)) { ld_b1(X, st); } break;
+          case kSLdYB1: if constexpr (ew_tier_has(TIER, kSLdYB1)) { ld_b1(Y, st); } break;
+          case kSLdXRowW4: if constexpr (ew_tier_has(TIER, kSLdXRowW4)) { ld_row(X, st, false); } break;
+          case kSLdYRowW4: if constexpr (ew_tier_has(TIER, kSLdYRowW4)) { ld_row(Y, st, false); } break;
+          case kSLdXRowBf: if constexpr (ew_tier_has(TIER, kSLdXRowBf)) { ld_row(X, st, true); } break;
+          case kSLdYRowBf: if constexpr (ew_tier_has(TIER, kSLdYRowBf)) { ld_row(Y, st, true); } break;
+          case kSLdXColW4: if constexpr (TIER == kTierAll) ld_col(X, st, false); break;
+          case kSLdYColW4: if constexpr (TIER == kTierAll) ld_col(Y, st, false); break;
+          case kSLdXColBf: if constexpr (TIER == kTierAll) ld_col(X, st, true); break;
+          case kSLdYColBf: if constexpr (TIER == kTierAll) ld_col(Y, st, true); break;
+          case kSLdXViewW4: if constexpr (TIER == kTierAll) ld_view(X, st, false); break;
+          case kSLdYViewW4: if constexpr (TIER == kTierAll) ld_view(Y, st, false); break;
+          case kSLdXViewBf: if constexpr (TIER == kTierAll) ld_view(X, st, true); break;
+          case kSLdYViewBf: if constexpr (TIER == kTierAll) ld_view(Y, st, true); break;
+          case kSStW4: if constexpr (ew_tier_has(TIER, kSStW4)) {
             uint8_t *q = const_cast<uint8_t *>(st.ptr) + static_cast<size_t>(eb) * 4;
             B2_GROUPS stg_v4(q + static_cast<size_t>(u) * estep * 4, make_uint4(X[u][0], X[u][1], X[u][2], X[u][3]));
             break;
           }
-          case kSStBf: {   // X holds bf16-representable values here
+          case kSStBf: if constexpr (ew_tier_has(TIER, kSStBf)) {   // X holds bf16-representable values here
             uint8_t *q = const_cast<uint8_t *>(st.ptr) + static_cast<size_t>(eb) * 2;
             B2_GROUPS stg_v2(q + static_cast<size_t>(u) * estep * 2,
                              make_uint2((X[u][0] >> 16) | (X[u][1] & 0xffff0000u), (X[u][2] >> 16) | (X[u][3] & 0xffff0000u)));
             break;
           }
-          case kSStB1: {
+          case kSStB1: if constexpr (ew_tier_has(TIER, kSStB1)) {
             uint8_t *q = const_cast<uint8_t *>(st.ptr) + eb;
             B2_GROUPS stg_u32(q + static_cast<size_t>(u) * estep,
                               (X[u][0] & 0xffu) | ((X[u][1] & 0xffu) << 8) | ((X[u][2] & 0xffu) << 16) | (X[u][3] << 24));
             break;
           }
           case kSQuantBf:
+            if constexpr (ew_tier_has(TIER, kSQuantBf)) {
 #pragma unroll
-            for (int u = 0; u < kEwU; ++u)
+              for (int u = 0; u < kEwU; ++u)
 #pragma unroll
-              for (int e = 0; e < 4; e += 2) {
-                const uint32_t w = cvt_bf16x2(__uint_as_float(X[u][e + 1]), __uint_as_float(X[u][e]));
-                X[u][e] = w << 16;
-                X[u][e + 1] = w & 0xffff0000u;
-              }
+                for (int e = 0; e < 4; e += 2) {
+                  const uint32_t w = cvt_bf16x2(__uint_as_float(X[u][e + 1]), __uint_as_float(X[u][e]));
+                  X[u][e] = w << 16;
+                  X[u][e + 1] = w & 0xffff0000u;
+                }
+            }
             break;
-          case kSAffine: {
+          case kSAffine: if constexpr (ew_tier_has(TIER, kSAffine)) {
             const float sc = __uint_as_float(st.p2), sh = __uint_as_float(st.p3);
             B2_ALL(X[u][e] = __float_as_uint(affine2(__uint_as_float(X[u][e]), sc, sh)))
             break;
           }
-          case kSFill: { const uint32_t f = st.p2; B2_ALL(X[u][e] = f) break; }
-          case kSIotaF: if constexpr (COLD) { B2_ALL(X[u][e] = __float_as_uint(static_cast<float>(eb + u * estep + e))) } break;
-          case kSIotaI: if constexpr (COLD) { B2_ALL(X[u][e] = eb + u * estep + e) } break;
-          case kSSelect: {
+          case kSFill: if constexpr (ew_tier_has(TIER, kSFill)) { const uint32_t f = st.p2; B2_ALL(X[u][e] = f) } break;
+          case kSIotaF: if constexpr (TIER == kTierAll) { B2_ALL(X[u][e] = __float_as_uint(static_cast<float>(eb + u * estep + e))) } break;
+          case kSIotaI: if constexpr (TIER == kTierAll) { B2_ALL(X[u][e] = eb + u * estep + e) } break;
+          case kSSelect: if constexpr (ew_tier_has(TIER, kSSelect)) {
             const uint8_t *q = st.ptr + eb;
             B2_GROUPS {
               const uint32_t w = ldg_u32(q + static_cast<size_t>(u) * estep);
@@ -449,15 +479,15 @@ __device__ __noinline__ void ew_steps_run(uint32_t tid, uint32_t nthr, uint32_t 
             }
             break;
           }
-          case kSCvtF2I: if constexpr (COLD) { B2_ALL(X[u][e] = static_cast<uint32_t>(static_cast<int32_t>(truncf(__uint_as_float(X[u][e]))))) } break;
-          case kSCvtF2U: if constexpr (COLD) { B2_ALL(X[u][e] = static_cast<uint32_t>(static_cast<long long>(truncf(__uint_as_float(X[u][e]))))) } break;
-          case kSCvtF2B: if constexpr (COLD) { B2_ALL(X[u][e] = static_cast<uint32_t>(static_cast<long long>(truncf(__uint_as_float(X[u][e])))) & 0xffu) } break;
-          case kSCvtI2F: if constexpr (COLD) { B2_ALL(X[u][e] = __float_as_uint(static_cast<float>(static_cast<int32_t>(X[u][e])))) } break;
-          case kSCvtU2F: if constexpr (COLD) { B2_ALL(X[u][e] = __float_as_uint(static_cast<float>(X[u][e]))) } break;
-          case kSCvtI2B: if constexpr (COLD) { B2_ALL(X[u][e] &= 0xffu) } break;
-          case kSBNot: if constexpr (COLD) { B2_ALL(X[u][e] = X[u][e] == 0u ? 1u : 0u) } break;
-          case kSUMax: B2_ALL(X[u][e] = max(X[u][e], Y[u][e])) break;
-          case kSUMin: B2_ALL(X[u][e] = min(X[u][e], Y[u][e])) break;
+          case kSCvtF2I: if constexpr (TIER == kTierAll) { B2_ALL(X[u][e] = static_cast<uint32_t>(static_cast<int32_t>(truncf(__uint_as_float(X[u][e]))))) } break;
+          case kSCvtF2U: if constexpr (TIER == kTierAll) { B2_ALL(X[u][e] = static_cast<uint32_t>(static_cast<long long>(truncf(__uint_as_float(X[u][e]))))) } break;
+          case kSCvtF2B: if constexpr (TIER == kTierAll) { B2_ALL(X[u][e] = static_cast<uint32_t>(static_cast<long long>(truncf(__uint_as_float(X[u][e])))) & 0xffu) } break;
+          case kSCvtI2F: if constexpr (TIER == kTierAll) { B2_ALL(X[u][e] = __float_as_uint(static_cast<float>(static_cast<int32_t>(X[u][e])))) } break;
+          case kSCvtU2F: if constexpr (TIER == kTierAll) { B2_ALL(X[u][e] = __float_as_uint(static_cast<float>(X[u][e]))) } break;
+          case kSCvtI2B: if constexpr (TIER == kTierAll) { B2_ALL(X[u][e] &= 0xffu) } break;
+          case kSBNot: if constexpr (TIER == kTierAll) { B2_ALL(X[u][e] = X[u][e] == 0u ? 1u : 0u) } break;
+          case kSUMax: if constexpr (ew_tier_has(TIER, kSUMax)) { B2_ALL(X[u][e] = max(X[u][e], Y[u][e])) } break;
+          case kSUMin: if constexpr (ew_tier_has(TIER, kSUMin)) { B2_ALL(X[u][e] = min(X[u][e], Y[u][e])) } break;
           B2_SCMP(kSCmpF, __uint_as_float)
           B2_SCMP(kSCmpI, static_cast<int32_t>)
           B2_SCMP(kSCmpU, static_cast<uint32_t>)
@@ -465,7 +495,7 @@ __device__ __noinline__ void ew_steps_run(uint32_t tid, uint32_t nthr, uint32_t 
           B2_SF(kMul, __fmul_rn(x, y))
           B2_SF(kSubt, __fsub_rn(x, y))
           case kSFlt + ew_fcode(kDiv):
-            if constexpr (COLD) { B2_ALL(X[u][e] = __float_as_uint(__fdiv_rn(__uint_as_float(X[u][e]), __uint_as_float(Y[u][e])))) }
+            if constexpr (TIER == kTierAll) { B2_ALL(X[u][e] = __float_as_uint(__fdiv_rn(__uint_as_float(X[u][e]), __uint_as_float(Y[u][e])))) }
             break;
           B2_SF(kMax, np_max(x, y))
           B2_SF(kMin, np_min(x, y))
@@ -535,12 +565,18 @@ __device__ __forceinline__ void ew_entries(const Lane &L, const DEntry *e0, uint
     const uint32_t ngroups = (hi - lo) >> 2;
     const uint32_t trip = L.nthr * kEwU, nfull = ngroups / trip * trip;
     if (ngroups) ew_stage_rows(L, fl);
-    if (fl->cold) {
-      if (nfull) ew_steps_run<true, true>(L.tid, L.nthr, lo, 0u, nfull);
-      if (nfull < ngroups) ew_steps_run<false, true>(L.tid, L.nthr, lo, nfull, ngroups);
-    } else {
-      if (nfull) ew_steps_run<true, false>(L.tid, L.nthr, lo, 0u, nfull);
-      if (nfull < ngroups) ew_steps_run<false, false>(L.tid, L.nthr, lo, nfull, ngroups);
+    switch (fl->tier) {
+#define B2_TIER(T)                                                                              \
+  case T:                                                                                       \
+    if (nfull) ew_steps_run<true, T>(L.tid, L.nthr, lo, 0u, nfull);                             \
+    if (nfull < ngroups) ew_steps_run<false, T>(L.tid, L.nthr, lo, nfull, ngroups);             \
+    break;
+      B2_TIER(kTierF32) B2_TIER(kTierBf) B2_TIER(kTierInt) B2_TIER(kTierHot)
+      default:
+        if (nfull) ew_steps_run<true, kTierAll>(L.tid, L.nthr, lo, 0u, nfull);
+        if (nfull < ngroups) ew_steps_run<false, kTierAll>(L.tid, L.nthr, lo, nfull, ngroups);
+        break;
+#undef B2_TIER
     }
     if (lo + (ngroups << 2) < hi) ew_chain_run(L, ops, chain, lo + (ngroups << 2), hi);
   } else if (vec) {

@@ -252,6 +252,14 @@ __device__ __noinline__ void red_part_tiles(const Lane &L, const DTask &t, uint3
   for (uint32_t tile = tile_lo; tile < tile_hi; ++tile) {
     const int64_t lo = tile * chunk, hi = min(lo + chunk, n);
     if (lo >= hi) continue;
+    if (tile + 1 < tile_hi) {
+      // the lane's next tile is pulled into L2 while this one is reduced, so the load
+      // pipeline that drains at the block reduction refills from L2 rather than HBM
+      const uint32_t esz = dt_size(dt);
+      const int64_t nb = (min(hi + chunk, n) - hi) * esz;
+      const uint8_t *q = a + hi * esz;
+      for (int64_t b = static_cast<int64_t>(L.tid) * 128; b < nb; b += static_cast<int64_t>(L.nthr) * 128) prefetch_l2(q + b);
+    }
     Acc acc = reduce_run(a, dt, kind, lo, hi, L.tid, L.nthr, nullptr, 0);
     acc = acc_block_reduce(L, kind, dt, acc);
     if (L.tid == 0) acc_store(dst, dt, tile, acc);

@@ -159,6 +159,69 @@ __device__ __forceinline__ void rows_staged(const Lane &L, const DTask &t, uint3
           o4[g] = v;
         }
       }
+    } else if (adt == kBF16 && dt == kBF16 && (seg & 7u) == 0u) {
+      // bf16 in, bf16 out: 8 elements per 16-byte word, f32 arithmetic, hardware ex2.
+      const uint4 *r8 = reinterpret_cast<const uint4 *>(rowp);
+      uint4 *o8 = reinterpret_cast<uint4 *>(outp);
+      const uint32_t ng8 = seg >> 3;
+      auto unpack8 = [](const uint4 w, float (&f)[8]) {
+        f[0] = __uint_as_float(w.x << 16); f[1] = __uint_as_float(w.x & 0xffff0000u);
+        f[2] = __uint_as_float(w.y << 16); f[3] = __uint_as_float(w.y & 0xffff0000u);
+        f[4] = __uint_as_float(w.z << 16); f[5] = __uint_as_float(w.z & 0xffff0000u);
+        f[6] = __uint_as_float(w.w << 16); f[7] = __uint_as_float(w.w & 0xffff0000u);
+      };
+      auto pack8 = [](const float (&f)[8]) {
+        return make_uint4(cvt_bf16x2(f[1], f[0]), cvt_bf16x2(f[3], f[2]), cvt_bf16x2(f[5], f[4]), cvt_bf16x2(f[7], f[6]));
+      };
+      if (softmax) {
+        float m = -INFINITY;
+        for (uint32_t g = gl; g < ng8; g += kRowGroupThreads) {
+          float f[8];
+          unpack8(r8[g], f);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) m = fmaxf(m, f[e]);
+        }
+        m = group_reduce(m, [](float a, float c) { return fmaxf(a, c); }, slot, bid, gl);
+        constexpr float kLog2e = 1.4426950408889634f;
+        const float mb = m * kLog2e;
+        float sum = 0.0f;
+        for (uint32_t g = gl; g < ng8; g += kRowGroupThreads) {
+          float f[8];
+          unpack8(r8[g], f);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) sum += fast_ex2(fmaf(f[e], kLog2e, -mb));
+        }
+        sum = group_reduce(sum, [](float a, float c) { return a + c; }, slot, bid, gl);
+        const float rs = __fdiv_rn(1.0f, sum);
+        for (uint32_t g = gl; g < ng8; g += kRowGroupThreads) {
+          float f[8];
+          unpack8(r8[g], f);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) f[e] = fast_ex2(fmaf(f[e], kLog2e, -mb)) * rs;
+          o8[g] = pack8(f);
+        }
+      } else {
+        float sum = 0.0f, s2 = 0.0f;
+        for (uint32_t g = gl; g < ng8; g += kRowGroupThreads) {
+          float f[8];
+          unpack8(r8[g], f);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) { sum += f[e]; s2 = fmaf(f[e], f[e], s2); }
+        }
+        sum = group_reduce(sum, [](float a, float c) { return a + c; }, slot, bid, gl);
+        s2 = group_reduce(s2, [](float a, float c) { return a + c; }, slot, bid, gl);
+        const float inv_n = 1.0f / static_cast<float>(seg);
+        const float mu = sum * inv_n;
+        const float var = __fsub_rn(s2 * inv_n, __fmul_rn(mu, mu));
+        const float rden = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(var, eps)));
+        for (uint32_t g = gl; g < ng8; g += kRowGroupThreads) {
+          float f[8];
+          unpack8(r8[g], f);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) f[e] = (f[e] - mu) * rden;
+          o8[g] = pack8(f);
+        }
+      }
     } else if (softmax) {
       float m = -INFINITY;
       for (uint32_t g = gl; g < ng; g += kRowGroupThreads) {
