@@ -167,6 +167,26 @@ __device__ __forceinline__ uint32_t reduce_vec32(const uint8_t *p, uint32_t dt, 
   for (int u = 0; u < U; ++u) acc[u] = ident;
   int64_t g = g_lo + rank;
   const int64_t step = nthreads;
+  if (!DOT && dt_size(dt) == 4u && g + (U - 1) * step < g_hi) {
+    // 4-byte elements: software-pipelined, the next trip's U loads are issued before
+    // this trip's values are combined, so 2 U loads per thread are in flight
+    const uint4 *q = reinterpret_cast<const uint4 *>(p);
+    uint4 a[U], b[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) a[u] = q[g + u * step];
+    g += U * step;
+    for (; g + (U - 1) * step < g_hi; g += U * step) {
+#pragma unroll
+      for (int u = 0; u < U; ++u) b[u] = q[g + u * step];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        acc[u] = C::f(C::f(acc[u], a[u].x), C::f(a[u].y, C::f(a[u].z, a[u].w)));
+        a[u] = b[u];
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) acc[u] = C::f(C::f(acc[u], a[u].x), C::f(a[u].y, C::f(a[u].z, a[u].w)));
+  }
   for (; g + (U - 1) * step < g_hi; g += U * step) {
     uint32_t v[U][4], w[U][4];
 #pragma unroll
@@ -242,6 +262,79 @@ __device__ __forceinline__ Acc reduce_run(const uint8_t *p, uint32_t dt, uint32_
   return acc;
 }
 
+// RED_PART for 4-byte elements, streamed: the lane's tiles are one contiguous byte range;
+// it flows through a ring of kStreamBufs 16 KB shared-memory buffers filled by bulk
+// asynchronous copies (one thread issues, mbarrier completion), so ~100 KB per SM are in
+// flight independent of registers; every thread folds its 32 bytes of each buffer, and at
+// each tile boundary the lane reduces and stores that tile's partial.
+constexpr uint32_t kStreamChunk = 16384, kStreamBufs = 8;
+
+template <typename C>
+__device__ __forceinline__ bool red_part_stream(const Lane &L, const DTask &t, uint32_t tile_lo, uint32_t tile_hi,
+                                                uint32_t kind, uint32_t dt) {
+  const KParams &P = *L.P;
+  uint8_t *dst = resolve(P, t.ptr[0]);
+  const uint8_t *a = resolve(P, t.ptr[1]);
+  const int64_t n = t.p[0], chunk = t.p[1];
+  const int64_t lo = static_cast<int64_t>(tile_lo) * chunk, hi = min(static_cast<int64_t>(tile_hi) * chunk, n);
+  if (lo >= hi) return true;
+  const uint32_t tile_bytes = static_cast<uint32_t>(chunk) * 4u;
+  if ((reinterpret_cast<uintptr_t>(a) & 15u) || tile_bytes % kStreamChunk || ((hi - lo) & 3) ||
+      L.smem_bytes < kSmemSys + 1024u + kStreamBufs * kStreamChunk)
+    return false;
+  const uint8_t *src = a + lo * 4;
+  const uint64_t total = static_cast<uint64_t>(hi - lo) * 4u;
+  const uint32_t nchunks = static_cast<uint32_t>((total + kStreamChunk - 1) / kStreamChunk), per_tile = tile_bytes / kStreamChunk;
+  uint64_t *bar = reinterpret_cast<uint64_t *>(L.smem + kSmemSys);
+  uint8_t *bufs = L.smem + kSmemSys + 1024;
+  auto bytes_of = [&](uint32_t c) { return static_cast<uint32_t>(min<uint64_t>(kStreamChunk, total - static_cast<uint64_t>(c) * kStreamChunk)); };
+  __syncthreads();
+  if (L.tid == 0) {
+    for (uint32_t i = 0; i < kStreamBufs; ++i) mbar_init(&bar[i], 1);
+    fence_mbar_init();
+    for (uint32_t c = 0; c + 1 < kStreamBufs && c < nchunks; ++c) {
+      mbar_arrive_expect_tx(&bar[c], bytes_of(c));
+      bulk_g2s(bufs + c * kStreamChunk, src + static_cast<size_t>(c) * kStreamChunk, bytes_of(c), &bar[c]);
+    }
+  }
+  __syncthreads();
+  const uint32_t ident = static_cast<uint32_t>(acc_identity(kind, dt).bits);
+  uint32_t acc = ident;
+  bool fine = true;
+  for (uint32_t c = 0; c < nchunks; ++c) {
+    const uint32_t b = c % kStreamBufs;
+    bool ok = mbar_wait_bounded(&bar[b], (c / kStreamBufs) & 1u, P.wait_budget_ns);
+    if (!ok) set_status(P, kStTensorTimeout, L.lane, c, t.op);
+    // lane-wide: nobody is still reading the buffer consumed last trip; a lost copy ends the op for all
+    if (!__syncthreads_and(ok)) { fine = false; break; }
+    const uint32_t nx = c + kStreamBufs - 1u;
+    if (L.tid == 0 && nx < nchunks) {
+      fence_proxy_async_smem();
+      mbar_arrive_expect_tx(&bar[nx % kStreamBufs], bytes_of(nx));
+      bulk_g2s(bufs + (nx % kStreamBufs) * kStreamChunk, src + static_cast<size_t>(nx) * kStreamChunk, bytes_of(nx), &bar[nx % kStreamBufs]);
+    }
+    const uint32_t nb = bytes_of(c);
+    const uint4 *q = reinterpret_cast<const uint4 *>(bufs + b * kStreamChunk);
+    for (uint32_t o = L.tid; o < nb / 16u; o += L.nthr) {
+      const uint4 v = q[o];
+      acc = C::f(C::f(acc, v.x), C::f(v.y, C::f(v.z, v.w)));
+    }
+    if ((c + 1u) % per_tile == 0u || c + 1u == nchunks) {     // a tile is complete
+      Acc r;
+      r.bits = acc;
+      r = acc_block_reduce(L, kind, dt, r);
+      if (L.tid == 0) acc_store(dst, dt, tile_lo + c / per_tile, r);
+      acc = ident;
+    }
+  }
+  __syncthreads();
+  if (L.tid == 0)
+    for (uint32_t i = 0; i < kStreamBufs; ++i) mbar_inval(&bar[i]);
+  __syncthreads();
+  (void)fine;
+  return true;
+}
+
 // RED_PART: tile t reduces in[t*chunk, min((t+1)*chunk, n)) into partials[t].
 __device__ __noinline__ void red_part_tiles(const Lane &L, const DTask &t, uint32_t tile_lo, uint32_t tile_hi) {
   const KParams &P = *L.P;
@@ -249,6 +342,10 @@ __device__ __noinline__ void red_part_tiles(const Lane &L, const DTask &t, uint3
   const uint8_t *a = resolve(P, t.ptr[1]);
   const int64_t n = t.p[0], chunk = t.p[1];
   const uint32_t kind = t.p[2], dt = t.dt;
+  if (dt == kF32 && kind == kSum && red_part_stream<RFSum>(L, t, tile_lo, tile_hi, kind, dt)) return;
+  if (dt == kF32 && kind == kRMax && red_part_stream<RFMax>(L, t, tile_lo, tile_hi, kind, dt)) return;
+  if (dt == kF32 && kind == kRMin && red_part_stream<RFMin>(L, t, tile_lo, tile_hi, kind, dt)) return;
+  if ((dt == kI32 || dt == kU32) && kind == kSum && red_part_stream<RISum>(L, t, tile_lo, tile_hi, kind, dt)) return;
   for (uint32_t tile = tile_lo; tile < tile_hi; ++tile) {
     const int64_t lo = tile * chunk, hi = min(lo + chunk, n);
     if (lo >= hi) continue;
