@@ -218,27 +218,22 @@ __device__ __noinline__ bool flash_tc_tiles(const Lane &L, const DTask &t, uint3
           // valid columns of this thread's half (keys n0 + 64 hf .. + lim - 1)
           const int lim = static_cast<int>(max(static_cast<int64_t>(0), min(static_cast<int64_t>(64), c_end - j * 128 - 64 * hf)));
           const uint32_t s_addr = tmem + ((32u * q4) << 16) + (jj & 1u) * 128u + 64u * hf;
-          // the thread's 64 scores, read from tensor memory once (both loads in flight together)
-          uint32_t raw[64];
-          __syncwarp();
-          tc_ld32(s_addr, *reinterpret_cast<uint32_t(*)[32]>(&raw[0]));
-          tc_ld32(s_addr + 32u, *reinterpret_cast<uint32_t(*)[32]>(&raw[32]));
-          tc_wait_ld();
-          // the half row's maximum over this block, then the row's through shared memory
+          // pass 1: the half row's maximum over this block, then the row's through shared memory
           float mx = -INFINITY;
-          if (lim == 64) {
+#pragma unroll 1
+          for (int cb = 0; cb < 64; cb += 32) {
+            uint32_t raw[32];
+            __syncwarp();
+            tc_ld32(s_addr + cb, raw);
+            tc_wait_ld();
+            if (cb + 32 <= lim) {
 #pragma unroll
-            for (int i = 0; i < 64; ++i) mx = fmaxf(mx, __uint_as_float(raw[i]));
-          } else {
+              for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(raw[i]) * sl2);
+            } else {
 #pragma unroll
-            for (int i = 0; i < 64; ++i)
-              if (i < lim) mx = fmaxf(mx, __uint_as_float(raw[i]));
-          }
-          mx = sl2 >= 0.0f ? mx * sl2 : -INFINITY;          // (a negative scale falls back below)
-          if (sl2 < 0.0f) {
-#pragma unroll
-            for (int i = 0; i < 64; ++i)
-              if (i < lim) mx = fmaxf(mx, __uint_as_float(raw[i]) * sl2);
+              for (int i = 0; i < 32; ++i)
+                if (cb + i < lim) mx = fmaxf(mx, __uint_as_float(raw[i]) * sl2);
+            }
           }
           xch[((jj & 1u) * 2u + hf) * 128u + r] = mx;
           mbar_arrive(&S->mx_full[jj & 1u]);
@@ -247,25 +242,40 @@ __device__ __noinline__ bool flash_tc_tiles(const Lane &L, const DTask &t, uint3
           const float m_new = fmaxf(m_run, mx);
           alpha = m_run == -INFINITY ? (m_new == -INFINITY ? 1.0f : 0.0f) : fast_ex2(m_run - m_new);
           const float neg_m = m_new == -INFINITY ? 0.0f : -m_new;
-          // p = 2^(s - m_new), written as the 16-bit A operand of the second matmul
+          // pass 2: p = 2^(s - m_new), written as the 16-bit A operand of the second matmul
           float psum = 0.0f;
           const uint32_t prow = p_s + (jj & 1u) * kFaPBytes + hf * 16384u + r * 128u;   // 64 keys = one sub-tile
           const bool bf = adt == kBF16;
+#pragma unroll 1
+          for (int cb = 0; cb < 64; cb += 16) {
+            uint32_t raw[16];
+            __syncwarp();
+            tc_ld16(s_addr + cb, raw);
+            tc_wait_ld();
+            float pv[16];
+            if (cb + 16 <= lim) {
 #pragma unroll
-          for (int cb = 0; cb < 64; cb += 8) {
-            float pv[8];
+              for (int i = 0; i < 16; ++i) pv[i] = fast_ex2(fmaf(__uint_as_float(raw[i]), sl2, neg_m));
+            } else {
 #pragma unroll
-            for (int i = 0; i < 8; ++i)
-              pv[i] = (lim == 64 || cb + i < lim) ? fast_ex2(fmaf(__uint_as_float(raw[cb + i]), sl2, neg_m)) : 0.0f;
-            uint32_t pk[4];
+              for (int i = 0; i < 16; ++i) pv[i] = cb + i < lim ? fast_ex2(fmaf(__uint_as_float(raw[i]), sl2, neg_m)) : 0.0f;
+            }
+            uint32_t pk[8];
+            if (bf) {
 #pragma unroll
-            for (int i = 0; i < 4; ++i)
-              pk[i] = bf ? cvt_bf16x2(pv[2 * i + 1], pv[2 * i]) : (f32_to_f16_bits(pv[2 * i]) | (f32_to_f16_bits(pv[2 * i + 1]) << 16));
+              for (int i = 0; i < 8; ++i) pk[i] = cvt_bf16x2(pv[2 * i + 1], pv[2 * i]);
+            } else {
 #pragma unroll
-            for (int i = 0; i < 8; ++i) psum += pv[i];
-            const uint32_t ch = static_cast<uint32_t>(cb) >> 3;
-            uint4 *dstp = reinterpret_cast<uint4 *>(sm + (prow + ((ch ^ (r & 7u)) << 4) - smem_addr(sm)));
-            *dstp = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+              for (int i = 0; i < 8; ++i) pk[i] = f32_to_f16_bits(pv[2 * i]) | (f32_to_f16_bits(pv[2 * i + 1]) << 16);
+            }
+#pragma unroll
+            for (int i = 0; i < 16; ++i) psum += pv[i];
+#pragma unroll
+            for (uint32_t q = 0; q < 2; ++q) {                      // 16 keys = 2 chunks of 8
+              const uint32_t ch = (static_cast<uint32_t>(cb) >> 3) + q;
+              uint4 *dstp = reinterpret_cast<uint4 *>(sm + (prow + ((ch ^ (r & 7u)) << 4) - smem_addr(sm)));
+              *dstp = make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
+            }
           }
           l_run = l_run * alpha + psum;
           m_run = m_new;

@@ -49,88 +49,42 @@ __device__ __forceinline__ int64_t dyn_base(const KParams &P, const DMove &m) {
 template <typename E>
 __device__ __forceinline__ void transpose_rows(const Lane &L, const DMove &m, E *dst, const E *src, int64_t row_a,
                                                int64_t row_b) {
-  constexpr int TR = 64, TC = 256;          // 16K elements per tile
-  constexpr int P = TR + 8;                 // tile pitch in elements: keeps 8-byte words aligned
-  constexpr int W = 8 / sizeof(E);          // elements per 8-byte word (4 for 2-byte, 2 for 4-byte types)
+  constexpr int TR = 64, TC = 256;   // 16K elements per tile: 32 independent loads per thread in flight
   const DView &v = m.view;
   const int64_t cc = v.dim[v.rank - 1], rr = v.dim[v.rank - 2], ld = v.stride[v.rank - 1];
-  E *tile = reinterpret_cast<E *>(L.smem + kSmemSys);             // [TC][P]
-  const bool dst_wide = (reinterpret_cast<uintptr_t>(dst) % 8 == 0) && cc % W == 0;
+  E *tile = reinterpret_cast<E *>(L.smem + kSmemSys);             // [TC][TR + 1]
   for (int64_t row0 = row_a; row0 < row_b;) {
     // rows of one segment share every outer coordinate: their source addresses are consecutive
     const int64_t r_in = row0 % rr;
-    int nr = static_cast<int>(min(min(static_cast<int64_t>(TR), rr - r_in), row_b - row0));
+    const int nr = static_cast<int>(min(min(static_cast<int64_t>(TR), rr - r_in), row_b - row0));
     const int64_t sbase = view_index(v, static_cast<uint32_t>(row0 * cc));
-    // a segment that starts off an 8-byte boundary is cut short so that the next one starts on it
-    const int mis = static_cast<int>((reinterpret_cast<uintptr_t>(src + sbase) / sizeof(E)) % W);
-    if (mis) nr = min(nr, W - mis);
-    else if (nr > W) nr -= nr % W;
-    // 8-byte source words when every column's run starts on an 8-byte boundary
-    const bool src_wide = (reinterpret_cast<uintptr_t>(src + sbase) % 8 == 0) && ld % W == 0 && nr % W == 0;
     for (int64_t c0 = 0; c0 < cc; c0 += TC) {
       const int nc = static_cast<int>(min(static_cast<int64_t>(TC), cc - c0));
       __syncthreads();
       const E *sp = src + sbase + c0 * ld;
-      // Loads first, into registers, then the shared-memory stores: written as one loop the
-      // compiler must assume the two pointers alias and would wait out each load in turn.
-      // The words are 8 bytes where alignment allows: with 2-byte loads a thread's eight
-      // loads in flight are 16 bytes, far too few to cover the memory latency.
+      // loads first, into registers, then the shared-memory stores: written as one loop the
+      // compiler must assume the two pointers alias and would wait out each load in turn
       constexpr int U = 8;
-      if (src_wide) {
-        constexpr int TRW = TR / W;
-        for (int i0 = L.tid; i0 < nc * TRW; i0 += U * static_cast<int>(L.nthr)) {
-          uint2 val[U];
+      for (int i0 = L.tid; i0 < nc * TR; i0 += U * static_cast<int>(L.nthr)) {
+        E val[U];
 #pragma unroll
-          for (int u = 0; u < U; ++u) {
-            const int i = i0 + u * static_cast<int>(L.nthr);
-            const int rw = i % TRW, c = i / TRW;
-            val[u] = (i < nc * TRW && rw * W < nr) ? *reinterpret_cast<const uint2 *>(sp + static_cast<int64_t>(c) * ld + rw * W)
-                                                   : make_uint2(0u, 0u);
-          }
-#pragma unroll
-          for (int u = 0; u < U; ++u) {
-            const int i = i0 + u * static_cast<int>(L.nthr);
-            if (i < nc * TRW) *reinterpret_cast<uint2 *>(tile + (i / TRW) * P + (i % TRW) * W) = val[u];
-          }
+        for (int u = 0; u < U; ++u) {
+          const int i = i0 + u * static_cast<int>(L.nthr);
+          const int r = i % TR, c = i / TR;
+          val[u] = (i < nc * TR && r < nr) ? sp[static_cast<int64_t>(c) * ld + r] : E(0);
         }
-      } else {
-        for (int i0 = L.tid; i0 < nc * TR; i0 += U * static_cast<int>(L.nthr)) {
-          E val[U];
 #pragma unroll
-          for (int u = 0; u < U; ++u) {
-            const int i = i0 + u * static_cast<int>(L.nthr);
-            const int r = i % TR, c = i / TR;
-            val[u] = (i < nc * TR && r < nr) ? sp[static_cast<int64_t>(c) * ld + r] : E(0);
-          }
-#pragma unroll
-          for (int u = 0; u < U; ++u) {
-            const int i = i0 + u * static_cast<int>(L.nthr);
-            if (i < nc * TR) tile[(i / TR) * P + i % TR] = val[u];
-          }
+        for (int u = 0; u < U; ++u) {
+          const int i = i0 + u * static_cast<int>(L.nthr);
+          if (i < nc * TR) tile[(i / TR) * (TR + 1) + i % TR] = val[u];
         }
       }
       __syncthreads();
       E *dp = dst + row0 * cc + c0;
-      if (dst_wide && nc % W == 0) {
-        // W consecutive columns of one row per thread: one 8-byte store
-        constexpr int TCW = TC / W;
-        for (int i = L.tid; i < nr * TCW; i += L.nthr) {
-          const int cw = i % TCW, r = i / TCW;
-          if (cw * W < nc) {
-            E e[W];
-#pragma unroll
-            for (int k = 0; k < W; ++k) e[k] = tile[(cw * W + k) * P + r];
-            uint2 w2;
-            memcpy(&w2, e, 8);
-            *reinterpret_cast<uint2 *>(dp + static_cast<int64_t>(r) * cc + cw * W) = w2;
-          }
-        }
-      } else {
 #pragma unroll 8
-        for (int i = L.tid; i < nr * TC; i += L.nthr) {
-          const int c = i % TC, r = i / TC;
-          if (c < nc) dp[static_cast<int64_t>(r) * cc + c] = tile[c * P + r];
-        }
+      for (int i = L.tid; i < nr * TC; i += L.nthr) {
+        const int c = i % TC, r = i / TC;
+        if (c < nc) dp[static_cast<int64_t>(r) * cc + c] = tile[c * (TR + 1) + r];
       }
     }
     row0 += nr;

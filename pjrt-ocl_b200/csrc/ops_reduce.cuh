@@ -287,7 +287,10 @@ __device__ __forceinline__ bool red_part_stream(const Lane &L, const DTask &t, u
   const uint32_t nchunks = static_cast<uint32_t>((total + kStreamChunk - 1) / kStreamChunk), per_tile = tile_bytes / kStreamChunk;
   uint64_t *bar = reinterpret_cast<uint64_t *>(L.smem + kSmemSys);
   uint8_t *bufs = L.smem + kSmemSys + 1024;
-  auto bytes_of = [&](uint32_t c) { return static_cast<uint32_t>(min<uint64_t>(kStreamChunk, total - static_cast<uint64_t>(c) * kStreamChunk)); };
+  auto bytes_of = [&](uint32_t c) {
+    const uint64_t left = total - static_cast<uint64_t>(c) * kStreamChunk;
+    return left < kStreamChunk ? static_cast<uint32_t>(left) : kStreamChunk;
+  };
   __syncthreads();
   if (L.tid == 0) {
     for (uint32_t i = 0; i < kStreamBufs; ++i) mbar_init(&bar[i], 1);
