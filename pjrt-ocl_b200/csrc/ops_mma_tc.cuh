@@ -214,7 +214,8 @@ __device__ __noinline__ bool mma_tc_tiles(const Lane &L, const DTask &t, uint32_
   __syncthreads();   // the scratch slot is free
   if (L.tid == 0) {
     for (int s = 0; s < kTcStages; ++s) { mbar_init(&S->full[s], use_tma ? 1u : static_cast<uint32_t>(kTcProducers)); mbar_init(&S->empty[s], 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(&S->acc_full[b], 1); mbar_init(&S->acc_empty[b], 256); }
+    // epilogue threads: warps 4-15 with TMA producers (twelve warps, three per lane quarter), else warps 8-15
+    for (int b = 0; b < 2; ++b) { mbar_init(&S->acc_full[b], 1); mbar_init(&S->acc_empty[b], use_tma ? 384u : 256u); }
     S->failed = 0u;
     fence_mbar_init();
   }
@@ -376,9 +377,12 @@ __device__ __noinline__ bool mma_tc_tiles(const Lane &L, const DTask &t, uint32_
     uint32_t tile = tile_lo; int64_t g, r0, c0; int nt;
     while (next_super(tile, g, r0, c0, nt) && issue_tile(n, nt)) ++n;
   }
-  if (w >= 8) {
-    // ---------------- epilogue (warps 8-15) ----------------
-    const uint32_t ew = w - 8, q = ew & 3u, half = ew >> 2;
+  const uint32_t epi_first = use_tma ? 4u : 8u;      // first epilogue warp
+  if (w >= epi_first) {
+    // ---------------- epilogue ----------------
+    // warp w reads tensor-memory lanes 32 (w % 4) .. +31; the warps sharing a lane quarter
+    // split the accumulator's 32-column chunks round-robin
+    const uint32_t ew = w - epi_first, q = w & 3u, slot = ew >> 2, nslots = (16u - epi_first) >> 2;
     // the store epilogue, decoded once: up to kEpiMax micro-ops {kind, operand source, s, t}
     constexpr int kEpiMax = 4;
     int epi_n = 0;
@@ -418,10 +422,8 @@ __device__ __noinline__ bool mma_tc_tiles(const Lane &L, const DTask &t, uint32_
       ++n;
       tc_fence_after_sync();
       const int64_t r = r0 + 32 * q + lane;
-      const uint32_t cols_per_warp = ninst / 2;   // two column halves
 #pragma unroll 1
-      for (uint32_t cb = 0; cb < cols_per_warp; cb += 32) {
-        const uint32_t col = half * cols_per_warp + cb;
+      for (uint32_t col = 32u * slot; col < ninst; col += 32u * nslots) {
         uint32_t raw[32];
         __syncwarp();   // the warp-wide tensor-memory load needs all 32 lanes back together
                         // (rows beyond M leave the store below divergent)
