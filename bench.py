@@ -44,14 +44,14 @@ N_C2 = 8192 * 4096
 # name -> program blob, CPU-arm sample blob (+ fraction of the full workload it is),
 # algorithmic bytes per step, metric
 def _wl(program, metric, unit, alg, scale, bound, dtype, desc, roof_alg=None, sample=None, sample_frac=0.0,
-        secondary=False, plan=None, traffic=None):
+        secondary=False, plan=None, traffic=None, max_steps=None):
     """alg: algorithmic units one step processes (bytes, flops or tokens); value = alg / seconds / scale.
     roof_alg: bytes (bound "hbm") or flops (bound "tensor") of one step, for the roofline fraction.
     traffic: dram__bytes_read.sum + dram__bytes_write.sum of one launch from the ncu capture summarised under
-    profiles/ (bytes), where one was taken."""
+    profiles/ (bytes), where one was taken. max_steps: cap on timed steps where one step runs for a second or so."""
     return dict(program=program, metric=metric, unit=unit, alg=alg, scale=scale, bound=bound, dtype=dtype, desc=desc,
                 roof_alg=alg if roof_alg is None else roof_alg, sample=sample, sample_frac=sample_frac,
-                secondary=secondary, plan=plan, traffic=traffic)
+                secondary=secondary, plan=plan, traffic=traffic, max_steps=max_steps)
 
 
 # config 5 block: 8 x 2048 tokens, d_model 1024, 16 heads x 64, FFN 4096
@@ -86,6 +86,13 @@ WORKLOADS = {
                     "config 5: pre-norm decoder block forward, batch 8 x seq 2048, d_model 1024, 16 x 64 heads, "
                     "causal flash attention, GELU FFN 4096, bf16",
                     roof_alg=_C5_MM_FLOPS + _C5_ATT_FLOPS, plan="c5_block"),
+    "c4_nbody": _wl("c4_nbody", "n-body pair interactions/s", "G interactions/s", 4096 * 4096 * 4 * 200, 1e9, "hbm",
+                    "f32", "config 4: 4096 bodies, RK4, 200 steps in one FOR loop (one system per GPU), executed as "
+                    "the decomposed bytecode, whose (N,N,3) intermediates make it HBM-bound; bytes per step = the "
+                    "tile ops' inputs + outputs over the four acceleration evaluations, A = 201 MB (N,N,3) and "
+                    "B = 67 MB (N,N) tensors: 28 A + 16 B",
+                    roof_alg=(28 * 4096 * 4096 * 3 * 4 + 16 * 4096 * 4096 * 4) * 200, secondary=True, plan="c4",
+                    max_steps=3),
     "c5_decode": _wl("c5_decode_bf16", "transformer-block tokens/s per B200", "tokens/s", 32, 1.0, "hbm", "bf16",
                      "config 5 decode step: batch 32, KV cache 2048; bytes = weights + KV cache read once",
                      roof_alg=2 * (4 * 1024 * 1024 + 2 * 1024 * 4096) + 2 * 32 * 16 * 2048 * 64 * 2, plan="c5_decode"),
@@ -192,6 +199,8 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     w = WORKLOADS[a.workload]
+    if w["max_steps"]:
+        a.steps, a.warmup = min(a.steps, w["max_steps"]), min(a.warmup, 3)
     cores = os.cpu_count() or 1
     base = {"metric": w["metric"], "unit": w["unit"], "n_gpus": a.gpus, "steps": a.steps,
             "warmup": a.warmup, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
@@ -233,7 +242,7 @@ def main():
         name = plan.rank_program(world) if plan else wl["program"]
         man = manifest()[name]
         lp = vm.LoadedProgram.Load(rt, vm.VmProgram.Parse(load_blob(name)))
-        host_in = [np.ascontiguousarray(x) for x in gen_inputs.gen_all(man["seed"], man["items"])]
+        host_in = [np.ascontiguousarray(x) for x in gen_inputs.gen_all(man["seed"] + (rank if plan and plan.seed_per_rank else 0), man["items"])]
         if plan and world > 1:
             # inputs listed at the global batch are sliced; per-shard listings already have the local shape
             host_in = [dp.shard_rows(x, rank, world) if (i in plan.batch_inputs and x.nbytes != lp.prog.inputs[i]["bytes"])
@@ -364,7 +373,8 @@ def main():
                 [n for n in ("c5_block", "c3_mlp") if n != a.workload]
         for name in names:
             wl = WORKLOADS[name]
-            m, _, _, _, _ = run_workload(wl, max(5, min(a.steps // 2, 100)), 3, False)
+            m, _, _, _, _ = run_workload(wl, min(max(5, min(a.steps // 2, 100)), wl["max_steps"] or 100),
+                                         1 if wl["max_steps"] else 3, False)
             tm = torch.tensor([m], device="cuda")
             if world > 1:
                 dist.all_reduce(tm, op=dist.ReduceOp.MAX)

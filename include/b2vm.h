@@ -129,8 +129,9 @@ uint64_t b2_loaded_launch_count(const b2_loaded *lp);
  * 1 operands forwarded in registers, 2 intermediate stores elided, 3 matmul
  * tasks, 4 matmul tasks on the tensor-core path, 5 floating-point operations of
  * all matmul tasks per execute (2 G M N K each; a task inside a loop body counts
- * once), 6 flash-attention tasks, 7 flash-attention tasks on the tensor-core path.
- * Unknown `which` returns 0. */
+ * once), 6 flash-attention tasks, 7 flash-attention tasks on the tensor-core path,
+ * 8 strided-reduction phases whose few output tiles were re-cut by rows over all
+ * lanes. Unknown `which` returns 0. */
 uint64_t b2_loaded_stat(const b2_loaded *lp, int which);
 /* Per-wait budget of device-side bounded waits, in nanoseconds (default 2e9). */
 void b2_loaded_set_wait_budget_ns(b2_loaded *lp, uint64_t ns);

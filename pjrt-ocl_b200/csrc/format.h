@@ -39,6 +39,21 @@ enum Sub : uint32_t {
 // reduction kinds (python/pjrt_ocl/ops/reduce.py:56)
 enum RedKind : uint32_t { kSum = 0, kRMax, kRMin, kProd, kRAnd, kROr, kRXor };
 
+#if defined(__CUDACC__)
+#define B2_HOST_DEVICE __host__ __device__
+#else
+#define B2_HOST_DEVICE
+#endif
+
+// RED_STRIDED tasks the device reduces row by row (a warp streams the red*inner
+// contiguous elements of one row): f32, inner axis of 2..4, rows of whole 16-byte
+// words and at least 1 KB, sum / max / min. The loader spreads such a task over
+// all lanes when its output tiles are few; both sides use this one rule.
+B2_HOST_DEVICE inline bool red_strided_rows_ok(uint32_t dt, int64_t red, int64_t inner, uint32_t kind) {
+  return dt == kF32 && inner >= 2 && inner <= 4 && (red * inner) % 4 == 0 && red * inner >= 256 &&
+         kind <= kRMin;
+}
+
 // entry sentinels (scheduler.py:80-85)
 constexpr uint32_t kEntNop = 0xFFFFFFFFu;
 constexpr uint32_t kEntBarrier = 0xFFFFFFFEu;
@@ -110,7 +125,8 @@ static_assert(sizeof(DTask) == 96, "DTask layout");
 // A device entry: the wire entry with control cond buffers resolved and chain
 // annotations added by the loader.
 struct DEntry {
-  uint32_t task, tile_lo, tile_hi, a, b;  // a/b: wait_flag / wait_count of the wire entry
+  uint32_t task, tile_lo, tile_hi, a, b;  // a/b: wait_flag / wait_count of the wire entry (control ranges, trip counts);
+                                          // on a RED_STRIDED entry the loader spread over the lanes: rows [a, b)
   uint32_t chain;        // number of consecutive EW entries (this one included) to run as one fused chain; 0/1 = alone
   BufRef cond;           // WHILE / IF: address of the 4-byte condition word
 };

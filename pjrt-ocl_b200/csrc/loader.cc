@@ -155,6 +155,142 @@ bool TcOperand(int64_t rows, int64_t K, int64_t sg, int64_t sr, int64_t sk, int6
   return false;
 }
 
+// ---- spreading strided reductions over the lanes ----
+//
+// The scheduler tiles RED_STRIDED by outputs, EW_TS per tile (scheduler.py:178-197),
+// so a reduction over a long interior axis with few outputs (config 4: 12288
+// outputs of 4096 terms each) lands on 3 lanes while the others wait at the
+// barrier. Where such a task is alone in its owners' runs the loader re-cuts it by rows:
+// every lane gets an entry naming a row range (DEntry::a, b) instead of output
+// tiles, and the original entries become NOPs. The new entries are inserted into
+// the lanes' streams, so control ranges and the lane table are re-indexed.
+//
+// A lane's stream is a set of contiguous ranges: the root walk [0, root_len) and
+// the cond / body / branch ranges of its control entries, in stream order.
+// Barrier entries split a range into runs; run k is the same phase on every lane
+// (the parser checked that barrier counts agree; range and run counts are
+// compared again here and the pass backs off when they differ).
+struct StreamRun {
+  uint32_t range, start, end;   // entries [start, end) of the lane's stream, no barrier inside
+  bool at_range_start, in_empty_range;
+};
+
+void LaneRuns(const VmProgram &p, const VmLane &l, std::vector<StreamRun> *runs) {
+  std::vector<std::pair<uint32_t, uint32_t>> ranges;
+  ranges.push_back({0u, l.root_len});
+  for (uint32_t e = 0; e < l.count; ++e) {
+    const VmEntry &en = p.entries[l.off + e];
+    if (en.task == kEntFor || en.task == kEntWhile || en.task == kEntIf) ranges.push_back({en.tile_lo, en.tile_hi});
+    if (en.task == kEntWhile || en.task == kEntIf) ranges.push_back({en.wait_flag, en.wait_count});
+  }
+  for (uint32_t r = 0; r < ranges.size(); ++r) {
+    const uint32_t s = ranges[r].first, e = s + ranges[r].second;
+    uint32_t run_start = s;
+    for (uint32_t i = s; i <= e; ++i) {
+      if (i == e || p.entries[l.off + i].task == kEntBarrier) {
+        runs->push_back({r, run_start, i, run_start == s, s == e});
+        run_start = i + 1;
+      }
+    }
+  }
+}
+
+void SpreadStridedReductions(const VmProgram &p, DeviceTables *out) {
+  const uint32_t n_lanes = static_cast<uint32_t>(p.lane_tab.size());
+  if (n_lanes < 4) return;
+  std::vector<std::vector<StreamRun>> runs(n_lanes);
+  for (uint32_t l = 0; l < n_lanes; ++l) LaneRuns(p, p.lane_tab[l], &runs[l]);
+  for (uint32_t l = 1; l < n_lanes; ++l) {
+    if (runs[l].size() != runs[0].size()) return;
+    for (size_t k = 0; k < runs[0].size(); ++k)
+      if (runs[l][k].range != runs[0][k].range) return;
+  }
+  struct Insert { uint32_t pos; bool at_start; DEntry e; };
+  std::vector<std::vector<Insert>> ins(n_lanes);
+  for (size_t k = 0; k < runs[0].size(); ++k) {
+    // One eligible RED_STRIDED task in this phase, alone in the runs of the lanes that
+    // own it (entries of one lane run in order and may depend on each other; entries
+    // of different lanes in one phase never do, so its rows can be appended to any
+    // lane's run).
+    int64_t task = -1;
+    uint64_t tiles = 0;
+    bool ok = true;
+    for (uint32_t l = 0; l < n_lanes && ok; ++l) {
+      const StreamRun &r = runs[l][k];
+      if (r.in_empty_range) ok = false;
+      uint32_t mine = 0, others = 0;
+      for (uint32_t i = r.start; i < r.end && ok; ++i) {
+        const VmEntry &en = p.entries[p.lane_tab[l].off + i];
+        if (en.task == kEntNop) continue;
+        if (en.task >= p.tasks.size()) { ok = false; break; }          // a control entry inside the run
+        if ((p.tasks[en.task].tile_op & 0xFFu) != kTopRedStrided) { ++others; continue; }
+        if (task >= 0 && task != static_cast<int64_t>(en.task)) { ok = false; break; }
+        task = en.task;
+        ++mine;
+        tiles += en.tile_hi > en.tile_lo ? en.tile_hi - en.tile_lo : 0u;
+      }
+      if (mine && others) ok = false;
+    }
+    if (!ok || task < 0) continue;
+    const VmTask &t = p.tasks[task];
+    const uint32_t dt = (t.tile_op >> 8) & 0xFFu;
+    const int64_t n_out = t.p0, red = t.p1, inner = t.p2;
+    if (!red_strided_rows_ok(dt, red, inner, t.p3) || n_out % inner != 0) continue;
+    const uint64_t nt = (static_cast<uint64_t>(n_out) + kEwTs - 1) / kEwTs;
+    if (tiles != nt || nt * 2 > n_lanes) continue;
+    const int64_t rows = n_out / inner;
+    for (uint32_t l = 0; l < n_lanes; ++l) {
+      const StreamRun &r = runs[l][k];
+      for (uint32_t i = r.start; i < r.end; ++i)
+        if (p.entries[p.lane_tab[l].off + i].task == static_cast<uint32_t>(task)) out->entries[p.lane_tab[l].off + i].task = kEntNop;
+      const int64_t lo = rows * l / n_lanes, hi = rows * (l + 1) / n_lanes;
+      if (hi <= lo) continue;
+      DEntry e;
+      std::memset(&e, 0, sizeof(e));
+      e.task = static_cast<uint32_t>(task);
+      e.a = static_cast<uint32_t>(lo);
+      e.b = static_cast<uint32_t>(hi);
+      const bool empty_at_start = r.start == r.end && r.at_range_start;
+      ins[l].push_back({r.end, empty_at_start, e});
+    }
+    out->n_spread++;
+  }
+  if (!out->n_spread) return;
+  std::vector<DEntry> rebuilt;
+  rebuilt.reserve(out->entries.size() + static_cast<size_t>(out->n_spread) * n_lanes);
+  for (uint32_t l = 0; l < n_lanes; ++l) {
+    const VmLane &ln = p.lane_tab[l];
+    const uint32_t new_off = static_cast<uint32_t>(rebuilt.size());
+    // boundary[i]: new index where old position i starts, after the entries that
+    // close the run ending at i and before those that open a range at i
+    std::vector<uint32_t> boundary(ln.count + 1);
+    for (uint32_t i = 0; i <= ln.count; ++i) {
+      for (const Insert &x : ins[l])
+        if (x.pos == i && !x.at_start) rebuilt.push_back(x.e);
+      boundary[i] = static_cast<uint32_t>(rebuilt.size()) - new_off;
+      for (const Insert &x : ins[l])
+        if (x.pos == i && x.at_start) rebuilt.push_back(x.e);
+      if (i < ln.count) rebuilt.push_back(out->entries[ln.off + i]);
+    }
+    const uint32_t new_count = static_cast<uint32_t>(rebuilt.size()) - new_off;
+    for (uint32_t i = new_off; i < new_off + new_count; ++i) {
+      DEntry &d = rebuilt[i];
+      if (d.task == kEntFor || d.task == kEntWhile || d.task == kEntIf) {
+        const uint32_t s = d.tile_lo, n = d.tile_hi;
+        d.tile_lo = boundary[s];
+        d.tile_hi = boundary[s + n] - boundary[s];
+      }
+      if (d.task == kEntWhile || d.task == kEntIf) {
+        const uint32_t s = d.a, n = d.b;
+        d.a = boundary[s];
+        d.b = boundary[s + n] - boundary[s];
+      }
+    }
+    out->lanes[l] = VmLane{new_off, new_count, boundary[ln.root_len], 0u};
+  }
+  out->entries.swap(rebuilt);
+}
+
 }  // namespace
 
 bool CollapseView(const int32_t *dims, const int32_t *strides, int rank, int64_t off, DView *out) {
@@ -441,7 +577,9 @@ bool BuildDeviceTables(const VmProgram &p, uint64_t arena_base, DeviceTables *ou
     const VmEntry &e = p.entries[i];
     DEntry &d = out->entries[i];
     std::memset(&d, 0, sizeof(d));
-    d.task = e.task; d.tile_lo = e.tile_lo; d.tile_hi = e.tile_hi; d.a = e.wait_flag; d.b = e.wait_count;
+    d.task = e.task; d.tile_lo = e.tile_lo; d.tile_hi = e.tile_hi;
+    const bool control = e.task == kEntWhile || e.task == kEntIf || e.task == kEntFor;
+    if (control) { d.a = e.wait_flag; d.b = e.wait_count; }   // tile entries: the reserved words stay 0
     if (e.task == kEntWhile || e.task == kEntIf) d.cond = c.Ref(e.signal_flag);
   }
 
@@ -547,6 +685,8 @@ bool BuildDeviceTables(const VmProgram &p, uint64_t arena_base, DeviceTables *ou
       i += n - 1;
     }
   }
+  out->lanes = p.lane_tab;
+  SpreadStridedReductions(p, out);
   return true;
 }
 

@@ -32,6 +32,8 @@ struct TmapSpec {
 struct DeviceTables {
   std::vector<DTask> tasks;
   std::vector<DEntry> entries;
+  std::vector<VmLane> lanes;            // per lane: its span of `entries` (the program's table, or the rebuilt one
+                                        // when strided reductions were spread over the lanes)
   std::vector<uint64_t> desc;           // descriptor pool (word 0 reserved: offset 0 = none)
   std::vector<int> input_port;          // per program input: port index or -1 (goes through the arena)
   std::vector<int> output_port;         // per program output
@@ -45,6 +47,7 @@ struct DeviceTables {
   uint32_t n_mma_tc = 0;                // ... of which the tensor-core path takes
   uint64_t mma_flops = 0;               // sum over matmul tasks of 2 G M N K
   uint32_t n_flash = 0, n_flash_tc = 0; // flash-attention tasks / ... on the tensor-core path
+  uint32_t n_spread = 0;                // strided-reduction phases spread over all lanes
 };
 
 // `arena_base` is the device address of the arena (only its value is used).

@@ -154,7 +154,26 @@ __device__ __noinline__ void move_tiles(const Lane &L, const DTask &t, uint32_t 
     }
     return;
   }
-  for (uint32_t i = lo + L.tid; i < hi; i += L.nthr) {
+  uint32_t i = lo + L.tid;
+  if (!scatter && esz == 4) {
+    // eight elements per thread per trip, loads first: a broadcast whose innermost run
+    // is shorter than 16 bytes (an (N, 3) table repeated along a middle axis) comes
+    // through here, and one dependent load -> store per trip leaves the lane idle
+    constexpr uint32_t U = 8;
+    const uint32_t *s32 = reinterpret_cast<const uint32_t *>(src);
+    uint32_t *d32 = reinterpret_cast<uint32_t *>(dst);
+    for (; static_cast<uint64_t>(i) + (U - 1) * L.nthr < hi; i += U * L.nthr) {
+      int64_t s[U];
+      uint32_t w[U];
+#pragma unroll
+      for (uint32_t u = 0; u < U; ++u) s[u] = base + view_index(m.view, i + u * L.nthr);
+#pragma unroll
+      for (uint32_t u = 0; u < U; ++u) w[u] = s32[s[u]];
+#pragma unroll
+      for (uint32_t u = 0; u < U; ++u) d32[i + u * L.nthr] = w[u];
+    }
+  }
+  for (; i < hi; i += L.nthr) {
     const int64_t s = base + view_index(m.view, i);
     if (scatter) copy_elem(dst, s, src, i, esz); else copy_elem(dst, i, src, s, esz);
   }

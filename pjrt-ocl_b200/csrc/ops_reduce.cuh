@@ -378,6 +378,56 @@ __device__ __noinline__ void red_comb_tiles(const Lane &L, const DTask &t, uint3
   if (L.tid == 0) acc_store(dst, dt, 0, acc);
 }
 
+
+// RED_SEG on f32 with segments of 2..8 elements (a trailing axis of 3 in an
+// (N, N, 3) tensor): a thread per segment reads 4 bytes at a stride of `seg`
+// words and the load pipeline never fills. Here a warp takes 128 consecutive
+// segments (128 * seg contiguous floats) with `seg` coalesced 16-byte loads per
+// thread, parks them in its shared-memory slab, and each thread folds segments
+// l, l+32, l+64, l+96 from there; results leave as 128-byte rows. Elements of a
+// segment are folded in index order, like the per-thread loop.
+template <uint32_t KIND>
+__device__ __forceinline__ void red_seg_small_f32(const Lane &L, float *dst, const float *a, uint32_t lo, uint32_t hi,
+                                                  uint32_t seg) {
+  constexpr uint32_t kSpan = 128, kMaxSeg = 8;
+  const uint32_t w = L.tid / kWarp, l = L.tid % kWarp, nw = L.nthr / kWarp;
+  float *stage = reinterpret_cast<float *>(L.smem + kSmemSys) + static_cast<size_t>(w) * kSpan * kMaxSeg;
+  auto one = [&](uint32_t o) {
+    const float *p = a + static_cast<int64_t>(o) * seg;
+    float r = p[0];
+    for (uint32_t i = 1; i < seg; ++i) r = red_f(KIND, r, p[i]);
+    dst[o] = r;
+  };
+  const uint32_t o_al = min(hi, (lo + 3u) & ~3u);          // 16-byte alignment of the first full span
+  for (uint32_t o = lo + L.tid; o < o_al; o += L.nthr) one(o);
+  const uint32_t nsteps = (hi - o_al) / kSpan;
+  const uint32_t span_lines = (kSpan * seg * 4u + 127u) / 128u;
+  for (uint32_t s = w; s < nsteps; s += nw) {
+    const uint32_t o0 = o_al + s * kSpan;
+    const float *p = a + static_cast<int64_t>(o0) * seg;
+    uint4 v[kMaxSeg];
+#pragma unroll
+    for (uint32_t j = 0; j < kMaxSeg; ++j)
+      if (j < seg) v[j] = ldg_v4(p + (j * kWarp + l) * 4u);
+    if (s + nw < nsteps && l < span_lines)                   // the warp's next span, into L2
+      prefetch_l2(reinterpret_cast<const uint8_t *>(p + static_cast<int64_t>(nw) * kSpan * seg) + l * 128u);
+#pragma unroll
+    for (uint32_t j = 0; j < kMaxSeg; ++j)
+      if (j < seg) *reinterpret_cast<uint4 *>(stage + (j * kWarp + l) * 4u) = v[j];
+    __syncwarp();
+#pragma unroll
+    for (uint32_t q = 0; q < kSpan / kWarp; ++q) {
+      const uint32_t si = l + q * kWarp;
+      const float *sp = stage + si * seg;
+      float r = sp[0];
+      for (uint32_t i = 1; i < seg; ++i) r = red_f(KIND, r, sp[i]);
+      dst[o0 + si] = r;
+    }
+    __syncwarp();
+  }
+  for (uint32_t o = o_al + nsteps * kSpan + L.tid; o < hi; o += L.nthr) one(o);
+}
+
 // RED_SEG: out[o] = reduce(in[o*seg, (o+1)*seg)), one segment per tile index;
 // p3 = 1: dot mode, out[o] = sum_j in[o*seg+j] * b[j].
 __device__ __noinline__ void red_seg_tiles(const Lane &L, const DTask &t, uint32_t tile_lo, uint32_t tile_hi) {
@@ -389,6 +439,15 @@ __device__ __noinline__ void red_seg_tiles(const Lane &L, const DTask &t, uint32
   const uint32_t dt = t.p[3] ? t.adt : t.dt;  // reduce keeps the input dtype; dot mode reads adt
   const uint8_t *vecb = t.p[3] ? resolve(P, t.ptr[2]) : nullptr;
   const uint32_t hi = min(tile_hi, n_out);
+  if (!t.p[3] && dt == kF32 && t.dt == kF32 && seg >= 2 && seg <= 8 && hi > tile_lo &&
+      (reinterpret_cast<uintptr_t>(a) & 15u) == 0 && (kind == kSum || kind == kRMax || kind == kRMin)) {
+    float *d = reinterpret_cast<float *>(dst);
+    const float *s = reinterpret_cast<const float *>(a);
+    if (kind == kSum) red_seg_small_f32<kSum>(L, d, s, tile_lo, hi, static_cast<uint32_t>(seg));
+    else if (kind == kRMax) red_seg_small_f32<kRMax>(L, d, s, tile_lo, hi, static_cast<uint32_t>(seg));
+    else red_seg_small_f32<kRMin>(L, d, s, tile_lo, hi, static_cast<uint32_t>(seg));
+    return;
+  }
   if (seg <= 16) {  // thread per segment
     for (uint32_t o = tile_lo + L.tid; o < hi; o += L.nthr) {
       Acc acc = reduce_run(a, dt, kind, o * seg, (o + 1) * seg, 0, 1, vecb, 0);
@@ -410,16 +469,126 @@ __device__ __noinline__ void red_seg_tiles(const Lane &L, const DTask &t, uint32
   }
 }
 
+// RED_STRIDED on f32 with a short inner axis (2..4) and a long reduced axis:
+// out[row*INNER + c] = reduce_r in[(row*red + r)*INNER + c]. A row's red*INNER
+// elements are contiguous, so a warp streams one row with coalesced 16-byte
+// loads. A step covers 32*INNER loads = 128*INNER elements, a multiple of INNER,
+// so register (j, k) of a thread (load j of the step, element k of its 16 bytes)
+// sees the same output column c = (128 j + 4 l + k) mod INNER in every step:
+// the loop adds into INNER*4 fixed accumulators and the columns are sorted out
+// once per row.
+template <int INNER, uint32_t KIND>
+__device__ __forceinline__ void red_strided_rows_f32(const Lane &L, float *dst, const float *a, const float *a_end,
+                                                     int64_t row_lo, int64_t row_hi, int64_t red, int64_t out_lo,
+                                                     int64_t out_hi) {
+  const uint32_t w = L.tid / kWarp, l = L.tid % kWarp, nw = L.nthr / kWarp;
+  const int64_t row_f4 = red * INNER / 4;                    // 16-byte words per row
+  constexpr int64_t kStep = static_cast<int64_t>(kWarp) * INNER;
+  const int64_t full = row_f4 / kStep;
+  const float ident = red_f_identity(KIND);
+  auto put = [&](float (&res)[INNER], int c, float x) {
+#pragma unroll
+    for (int cc = 0; cc < INNER; ++cc) res[cc] = (c == cc) ? red_f(KIND, res[cc], x) : res[cc];
+  };
+  for (int64_t row = row_lo + w; row < row_hi; row += nw) {
+    const float *rp = a + row * red * INNER;
+    float acc[INNER][4];
+#pragma unroll
+    for (int j = 0; j < INNER; ++j)
+#pragma unroll
+      for (int k = 0; k < 4; ++k) acc[j][k] = ident;
+    int64_t s = 0;
+    for (; s + 2 <= full; s += 2) {                          // two steps' loads in flight
+      uint4 v[2][INNER];
+#pragma unroll
+      for (int h = 0; h < 2; ++h)
+#pragma unroll
+        for (int j = 0; j < INNER; ++j) v[h][j] = ldg_v4(rp + ((s + h) * kStep + j * kWarp + l) * 4);
+      const float *pf = rp + (s + 8) * kStep * 4 + l * 32;   // 2 steps = 24*INNER/3 lines of 128 B, 8 steps ahead
+      if (l < (2 * kStep * 16 + 127) / 128 && pf < a_end) prefetch_l2(pf);
+#pragma unroll
+      for (int h = 0; h < 2; ++h)
+#pragma unroll
+        for (int j = 0; j < INNER; ++j) {
+          acc[j][0] = red_f(KIND, acc[j][0], __uint_as_float(v[h][j].x));
+          acc[j][1] = red_f(KIND, acc[j][1], __uint_as_float(v[h][j].y));
+          acc[j][2] = red_f(KIND, acc[j][2], __uint_as_float(v[h][j].z));
+          acc[j][3] = red_f(KIND, acc[j][3], __uint_as_float(v[h][j].w));
+        }
+    }
+    for (; s < full; ++s) {
+#pragma unroll
+      for (int j = 0; j < INNER; ++j) {
+        const uint4 v = ldg_v4(rp + (s * kStep + j * kWarp + l) * 4);
+        acc[j][0] = red_f(KIND, acc[j][0], __uint_as_float(v.x));
+        acc[j][1] = red_f(KIND, acc[j][1], __uint_as_float(v.y));
+        acc[j][2] = red_f(KIND, acc[j][2], __uint_as_float(v.z));
+        acc[j][3] = red_f(KIND, acc[j][3], __uint_as_float(v.w));
+      }
+    }
+    float res[INNER];
+#pragma unroll
+    for (int c = 0; c < INNER; ++c) res[c] = ident;
+#pragma unroll
+    for (int j = 0; j < INNER; ++j)
+#pragma unroll
+      for (int k = 0; k < 4; ++k) put(res, static_cast<int>((128u * j + 4u * l + k) % INNER), acc[j][k]);
+    for (int64_t f = full * kStep + l; f < row_f4; f += kWarp) {   // the row's ragged end
+      const uint4 v = ldg_v4(rp + f * 4);
+      const int c0 = static_cast<int>((f * 4) % INNER);
+      put(res, c0 % INNER, __uint_as_float(v.x));
+      put(res, (c0 + 1) % INNER, __uint_as_float(v.y));
+      put(res, (c0 + 2) % INNER, __uint_as_float(v.z));
+      put(res, (c0 + 3) % INNER, __uint_as_float(v.w));
+    }
+#pragma unroll
+    for (int c = 0; c < INNER; ++c) {
+#pragma unroll
+      for (int o = kWarp / 2; o > 0; o >>= 1) res[c] = red_f(KIND, res[c], __shfl_xor_sync(0xffffffffu, res[c], o));
+      const int64_t g = row * INNER + c;
+      if (l == 0 && g >= out_lo && g < out_hi) dst[g] = res[c];
+    }
+  }
+}
+
+template <uint32_t KIND>
+__device__ __forceinline__ void red_strided_rows_kind(const Lane &L, float *dst, const float *a, const float *a_end,
+                                                      int64_t row_lo, int64_t row_hi, int64_t red, int64_t inner,
+                                                      int64_t out_lo, int64_t out_hi) {
+  if (inner == 2) red_strided_rows_f32<2, KIND>(L, dst, a, a_end, row_lo, row_hi, red, out_lo, out_hi);
+  else if (inner == 3) red_strided_rows_f32<3, KIND>(L, dst, a, a_end, row_lo, row_hi, red, out_lo, out_hi);
+  else red_strided_rows_f32<4, KIND>(L, dst, a, a_end, row_lo, row_hi, red, out_lo, out_hi);
+}
+
 // RED_STRIDED: out[o*inner + i] = reduce_r in[(o*red + r)*inner + i]; EW-style
-// tiling of the outputs. Consecutive threads own consecutive outputs (coalesced
-// along `inner`), each keeps kQ independent outputs in flight.
-__device__ __noinline__ void red_strided_tiles(const Lane &L, const DTask &t, uint32_t tile_lo, uint32_t tile_hi) {
+// tiling of the outputs. An entry either names output tiles [tile_lo, tile_hi)
+// or, when the loader spread a task with few tiles over all lanes, whole rows
+// [row_lo, row_hi) (row_hi > row_lo; a row = the `inner` outputs of one o).
+// General path: consecutive threads own consecutive outputs (coalesced along
+// `inner`), each keeps kQ independent outputs in flight.
+__device__ __noinline__ void red_strided_tiles(const Lane &L, const DTask &t, uint32_t tile_lo, uint32_t tile_hi,
+                                               uint32_t row_lo, uint32_t row_hi) {
   const KParams &P = *L.P;
   uint8_t *dst = resolve(P, t.ptr[0]);
   const uint8_t *a = resolve(P, t.ptr[1]);
   const int64_t n_out = t.p[0], red = t.p[1], inner = t.p[2];
   const uint32_t kind = t.p[3], dt = t.dt;
-  const int64_t lo = static_cast<int64_t>(tile_lo) * kEwTs, hi = min(static_cast<int64_t>(tile_hi) * kEwTs, n_out);
+  const bool by_rows = row_hi > row_lo;
+  const int64_t lo = by_rows ? static_cast<int64_t>(row_lo) * inner : static_cast<int64_t>(tile_lo) * kEwTs;
+  const int64_t hi = min(by_rows ? static_cast<int64_t>(row_hi) * inner : static_cast<int64_t>(tile_hi) * kEwTs, n_out);
+  if (lo >= hi) return;
+  if (red_strided_rows_ok(dt, red, inner, kind) && (reinterpret_cast<uintptr_t>(a) & 15u) == 0) {
+    // rows that intersect [lo, hi); a row cut by a tile boundary is reduced by both
+    // neighbours and each stores its own outputs
+    const int64_t r0 = lo / inner, r1 = (hi + inner - 1) / inner;
+    float *d = reinterpret_cast<float *>(dst);
+    const float *s = reinterpret_cast<const float *>(a);
+    const float *s_end = s + (n_out / inner) * red * inner;
+    if (kind == kSum) red_strided_rows_kind<kSum>(L, d, s, s_end, r0, r1, red, inner, lo, hi);
+    else if (kind == kRMax) red_strided_rows_kind<kRMax>(L, d, s, s_end, r0, r1, red, inner, lo, hi);
+    else red_strided_rows_kind<kRMin>(L, d, s, s_end, r0, r1, red, inner, lo, hi);
+    return;
+  }
   constexpr int kQ = 8;
   for (int64_t g0 = lo + L.tid; g0 < hi; g0 += static_cast<int64_t>(L.nthr) * kQ) {
     Acc acc[kQ];

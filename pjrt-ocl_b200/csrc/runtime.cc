@@ -464,7 +464,7 @@ b2_status b2_program_load(b2_runtime *rt, b2_program *prog, b2_loaded **out, cha
   }
   std::vector<int32_t> aux = p.aux;
   if ((e = Upload(&lp->d_tmaps, lp->h_tmaps)) != cudaSuccess || (e = Upload(&lp->d_tasks, lp->tab.tasks)) != cudaSuccess || (e = Upload(&lp->d_entries, lp->tab.entries)) != cudaSuccess ||
-      (e = Upload(&lp->d_lanes, p.lane_tab)) != cudaSuccess || (e = Upload(&lp->d_aux, aux)) != cudaSuccess ||
+      (e = Upload(&lp->d_lanes, lp->tab.lanes)) != cudaSuccess || (e = Upload(&lp->d_aux, aux)) != cudaSuccess ||
       (e = Upload(&lp->d_desc, lp->tab.desc)) != cudaSuccess ||
       (e = cudaMalloc(reinterpret_cast<void **>(&lp->d_sync), sizeof(b2::DSync))) != cudaSuccess ||
       (e = cudaMallocHost(reinterpret_cast<void **>(&lp->h_sync), sizeof(b2::DSync))) != cudaSuccess) {
@@ -504,6 +504,7 @@ uint64_t b2_loaded_stat(const b2_loaded *lp, int which) {
     case 5: return lp->tab.mma_flops;
     case 6: return lp->tab.n_flash;
     case 7: return lp->tab.n_flash_tc;
+    case 8: return lp->tab.n_spread;
     default: return 0;
   }
 }

@@ -99,7 +99,7 @@ __device__ __forceinline__ void exec_entry(const Lane &L, const DEntry &en) {
       if (!tc) flash_simt_tiles(L, t, en.tile_lo, en.tile_hi);
       break;
     }
-    case kTopRedStrided: red_strided_tiles(L, t, en.tile_lo, en.tile_hi); break;
+    case kTopRedStrided: red_strided_tiles(L, t, en.tile_lo, en.tile_hi, en.a, en.b); break;
     default:
       if (L.tid == 0) set_status(P, kStBadOp, L.lane, en.task, t.op);
       break;

@@ -39,6 +39,7 @@ class DpPlan:
     apply_program: program run after the reduction (None: none); its inputs are
                    `apply_inputs` (indices into the per-rank INPUTS) followed by the
                    reduced outputs in `reduce_outputs[apply_skip:]` order
+    seed_per_rank: every rank draws its own inputs (seed + rank): independent units, nothing shared
     """
     program: str
     dp_program: Optional[str] = None
@@ -48,6 +49,7 @@ class DpPlan:
     apply_inputs: Sequence[int] = ()
     apply_skip: int = 0
     scaling: str = "weak"
+    seed_per_rank: bool = False
 
     def rank_program(self, world: int) -> str:
         if world == 1 or self.dp_program is None:
@@ -61,6 +63,8 @@ PLANS = {
     # config 3: gradients of the local batch, summed, then one SGD step on every rank
     "c3": DpPlan("c3_mlp_step_bf16", "c3_mlp_grads_bf16_dp{n}", batch_inputs=(0, 1), reduce_outputs=(0, 1, 2, 3),
                  apply_program="c3_sgd_apply_bf16", apply_inputs=(2, 3, 4), apply_skip=1, scaling="strong"),
+    # config 4: one independent system (seed) per GPU, no exchange
+    "c4": DpPlan("c4_nbody", seed_per_rank=True, scaling="weak"),
     # config 5: batch shards, no exchange
     "c5_block": DpPlan("c5_block_bf16", "c5_block_bf16_dp{n}", scaling="strong"),
     "c5_decode": DpPlan("c5_decode_bf16", "c5_decode_bf16_dp{n}", scaling="strong"),

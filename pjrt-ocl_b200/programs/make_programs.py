@@ -57,6 +57,9 @@ PROGRAMS["c3_sgd_apply_bf16"] = lambda: cases.sgd_apply(
 
 
 # the matmul tile-op family on its own
+# config 4 at its full 4096 bodies but two RK4 steps: small enough in time for a float64
+# recomputation on the host (the full-size parity case; the 200-step program is the bench)
+PROGRAMS["c4_nbody_2steps"] = lambda: cases.c4_nbody(steps=2)
 PROGRAMS["dot_bf16_8192"] = lambda: cases.dot_general_square(8192)
 PROGRAMS["dot_bf16_4096"] = lambda: cases.dot_general_square(4096)
 PROGRAMS["flash_bf16_c5"] = lambda: cases.flash_only()

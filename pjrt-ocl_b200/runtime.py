@@ -350,10 +350,10 @@ class LoadedProgram:
         return [int(buf[i]) for i in range(n)]
 
     _STATS = {"chains": 0, "forwarded": 0 + 1, "dead_stores": 2, "matmuls": 3, "tensor_core_matmuls": 4,
-              "matmul_flops": 5, "flash": 6, "tensor_core_flash": 7}
+              "matmul_flops": 5, "flash": 6, "tensor_core_flash": 7, "spread_reductions": 8}
 
     def stat(self, name: str) -> int:
-        """Load-time mapping facts: chains, forwarded, dead_stores, matmuls, tensor_core_matmuls."""
+        """Load-time mapping facts, by name (see `_STATS`)."""
         return int(lib().b2_loaded_stat(self._h, self._STATS[name]))
 
     @property

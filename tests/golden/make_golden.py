@@ -753,6 +753,14 @@ def _():
     return cases.c4_nbody(n=96, steps=3, nlanes=8)
 
 
+# 256 bodies on 8 lanes: the axis-1 force sum is one output tile, so the loader spreads it
+# over the lanes by rows (two full 96-load steps per 768-element row), and the
+# trailing-axis sum has 65536 segments of 3 (the warp-cooperative small-segment path)
+@case("c4_nbody_mid", rtol=1e-4, atol=1e-5)
+def _():
+    return cases.c4_nbody(n=256, steps=2, nlanes=8)
+
+
 @case("c5_block_f32_small", rtol=1e-4, atol=1e-4)
 def _():
     return cases.c5_block(batch=2, seq=48, d_model=128, heads=4, d_ff=256,

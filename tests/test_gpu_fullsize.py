@@ -5,7 +5,9 @@ and sampled exact recomputation (the oracle would take minutes at these sizes):
     their sum (= the row count);
   * dot_general bf16 4096^3: sampled rows against a float64 dot of the same bf16 inputs;
   * config 5's attention (128 heads x 2048 x 2048, causal, bf16): sampled query rows
-    against a float64 softmax(QK^T)V.
+    against a float64 softmax(QK^T)V;
+  * config 4 (4096 bodies): two RK4 steps against a float64 recomputation; 200 steps
+    conserve total momentum (pair forces are antisymmetric) and stay finite.
 Tolerances: integer exact; f32 rel 1e-5 class; bf16 rel 2e-2."""
 import gzip
 import json
@@ -84,3 +86,47 @@ def test_flash_attention_c5_sampled_rows(rt):
         p = np.exp(s - s.max())
         want = (p / p.sum()) @ v[h, : m + 1].astype(np.float64)
         assert np.max(np.abs(got[h, m] - want) / (np.abs(want) + 2e-2)) < 2e-2, (h, m)
+
+
+def _nbody_accel64(pos, mass, soft=1e-2, block=512):
+    acc = np.empty_like(pos)
+    for i0 in range(0, pos.shape[0], block):
+        d = pos[None, :, :] - pos[i0:i0 + block, None, :]              # d[i, j] = pos[j] - pos[i]
+        r2 = (d * d).sum(axis=2) + soft * soft
+        w = r2 ** -1.5 * mass[None, :]
+        acc[i0:i0 + block] = (d * w[:, :, None]).sum(axis=1)
+    return acc
+
+
+def _nbody_rk4_64(pos, vel, mass, steps, dt=1e-3):
+    for _ in range(steps):
+        k1v, k1x = _nbody_accel64(pos, mass), vel
+        k2v, k2x = _nbody_accel64(pos + dt / 2 * k1x, mass), vel + dt / 2 * k1v
+        k3v, k3x = _nbody_accel64(pos + dt / 2 * k2x, mass), vel + dt / 2 * k2v
+        k4v, k4x = _nbody_accel64(pos + dt * k3x, mass), vel + dt * k3v
+        pos = pos + dt / 6 * (k1x + 2 * k2x + 2 * k3x + k4x)
+        vel = vel + dt / 6 * (k1v + 2 * k2v + 2 * k3v + k4v)
+    return pos, vel
+
+
+def test_config4_two_steps_match_float64_at_full_size(rt):
+    (pos0, vel0, mass), outs = _run(rt, "c4_nbody_2steps")
+    pos = np.asarray(outs[0]).view(np.float32).reshape(4096, 3)
+    vel = np.asarray(outs[1]).view(np.float32).reshape(4096, 3)
+    want_p, want_v = _nbody_rk4_64(pos0.astype(np.float64), vel0.astype(np.float64), mass.astype(np.float64), 2)
+    # f32 sums of 4096 pair terms per body: rel 1e-5 class on the accelerations, which enter
+    # the velocities scaled by dt = 1e-3
+    np.testing.assert_allclose(pos, want_p, rtol=1e-5, atol=1e-6)
+    np.testing.assert_allclose(vel, want_v, rtol=1e-4, atol=1e-5 * np.abs(want_v).max())
+
+
+def test_config4_200_steps_conserve_momentum(rt):
+    (pos0, vel0, mass), outs = _run(rt, "c4_nbody")
+    pos = np.asarray(outs[0]).view(np.float32).reshape(4096, 3).astype(np.float64)
+    vel = np.asarray(outs[1]).view(np.float32).reshape(4096, 3).astype(np.float64)
+    assert np.isfinite(pos).all() and np.isfinite(vel).all()
+    m = mass.astype(np.float64)[:, None]
+    p0, p1 = (m * vel0).sum(axis=0), (m * vel).sum(axis=0)
+    scale = np.abs(m * vel).sum(axis=0)
+    assert np.all(np.abs(p1 - p0) <= 1e-3 * scale), (p0, p1, scale)
+    assert np.abs(pos - pos0).max() > 1e-3          # the system moved
