@@ -386,10 +386,13 @@ __device__ __noinline__ void red_comb_tiles(const Lane &L, const DTask &t, uint3
 // thread, parks them in its shared-memory slab, and each thread folds segments
 // l, l+32, l+64, l+96 from there; results leave as 128-byte rows. Elements of a
 // segment are folded in index order, like the per-thread loop.
-template <uint32_t KIND>
+// SEG > 0: the segment length as a constant (its loads sit in exactly SEG registers);
+// SEG == 0: any length up to 8.
+template <uint32_t KIND, uint32_t SEG>
 __device__ __forceinline__ void red_seg_small_f32(const Lane &L, float *dst, const float *a, uint32_t lo, uint32_t hi,
-                                                  uint32_t seg) {
-  constexpr uint32_t kSpan = 128, kMaxSeg = 8;
+                                                  uint32_t seg_rt) {
+  constexpr uint32_t kSpan = 128, kMaxSeg = SEG ? SEG : 8;
+  const uint32_t seg = SEG ? SEG : seg_rt;
   const uint32_t w = L.tid / kWarp, l = L.tid % kWarp, nw = L.nthr / kWarp;
   float *stage = reinterpret_cast<float *>(L.smem + kSmemSys) + static_cast<size_t>(w) * kSpan * kMaxSeg;
   auto one = [&](uint32_t o) {
@@ -443,9 +446,13 @@ __device__ __noinline__ void red_seg_tiles(const Lane &L, const DTask &t, uint32
       (reinterpret_cast<uintptr_t>(a) & 15u) == 0 && (kind == kSum || kind == kRMax || kind == kRMin)) {
     float *d = reinterpret_cast<float *>(dst);
     const float *s = reinterpret_cast<const float *>(a);
-    if (kind == kSum) red_seg_small_f32<kSum>(L, d, s, tile_lo, hi, static_cast<uint32_t>(seg));
-    else if (kind == kRMax) red_seg_small_f32<kRMax>(L, d, s, tile_lo, hi, static_cast<uint32_t>(seg));
-    else red_seg_small_f32<kRMin>(L, d, s, tile_lo, hi, static_cast<uint32_t>(seg));
+    const uint32_t sg = static_cast<uint32_t>(seg);
+    if (kind == kSum && sg == 3) red_seg_small_f32<kSum, 3>(L, d, s, tile_lo, hi, sg);
+    else if (kind == kSum && sg == 2) red_seg_small_f32<kSum, 2>(L, d, s, tile_lo, hi, sg);
+    else if (kind == kSum && sg == 4) red_seg_small_f32<kSum, 4>(L, d, s, tile_lo, hi, sg);
+    else if (kind == kSum) red_seg_small_f32<kSum, 0>(L, d, s, tile_lo, hi, sg);
+    else if (kind == kRMax) red_seg_small_f32<kRMax, 0>(L, d, s, tile_lo, hi, sg);
+    else red_seg_small_f32<kRMin, 0>(L, d, s, tile_lo, hi, sg);
     return;
   }
   if (seg <= 16) {  // thread per segment

@@ -145,6 +145,52 @@ def kat_for_zero_trip_and_if():
     return b.serialize(), x, out
 
 
+def kat_strided_reduce_in_control_ranges():
+    """An interior-axis reduction owned by one lane inside a FOR body and inside an IF
+    branch, with the other lanes' runs empty at a range start, empty at a range end, or
+    holding NOPs: the layout a loader that re-cuts the reduction over all lanes has to
+    re-index. z accumulates sum_r x[row, r, c] twice; w = max_r x if flag else y - y.
+    Integer-valued inputs, so every summation order gives the same f32."""
+    rows, red, inner = 8, 128, 3
+    n_out = rows * inner
+    b = Builder(4)
+    bx, bflag, bz, by, bw = b.buf(rows * red * inner), b.buf(1), b.buf(n_out), b.buf(n_out), b.buf(n_out)
+    b.inputs, b.outputs = [bx, bflag, bz], [bz, bw]
+    b.in_dims, b.out_dims = [[rows, red, inner], [], [rows, inner]], [[rows, inner], [rows, inner]]
+    RED_STRIDED = 15
+    tsum = b.task(RED_STRIDED, by, bx, bx, n_out, red, inner, 0)
+    tmax = b.task(RED_STRIDED, bw, bx, bx, n_out, red, inner, 1)
+    tacc = b.task(EW, bz, bz, by, 0, n_out)
+    tzero = b.task(EW, bw, by, by, 2, n_out)
+    # lane 0: owner of both reductions
+    b.ent(0, FOR, 3, 3, 2); b.ent(0, BARRIER); b.ent(0, IF, 6, 1, 7, 1, bflag)
+    b.ent(0, tsum, 0, 1); b.ent(0, BARRIER); b.ent(0, NOP)
+    b.ent(0, tmax, 0, 1)
+    b.ent(0, tzero, 0, 1)
+    # lane 1: the body starts with its barrier (an empty run at the range start), then accumulates
+    b.ent(1, FOR, 3, 2, 2); b.ent(1, BARRIER); b.ent(1, IF, 5, 1, 6, 1, bflag)
+    b.ent(1, BARRIER); b.ent(1, tacc, 0, 1)
+    b.ent(1, NOP)
+    b.ent(1, NOP)
+    # lane 2: NOPs everywhere
+    b.ent(2, FOR, 3, 3, 2); b.ent(2, BARRIER); b.ent(2, IF, 6, 1, 7, 1, bflag)
+    b.ent(2, NOP); b.ent(2, BARRIER); b.ent(2, NOP)
+    b.ent(2, NOP)
+    b.ent(2, NOP)
+    # lane 3: the body is the barrier alone (empty runs at both ends of the range)
+    b.ent(3, FOR, 3, 1, 2); b.ent(3, BARRIER); b.ent(3, IF, 4, 1, 5, 1, bflag)
+    b.ent(3, BARRIER)
+    b.ent(3, NOP)
+    b.ent(3, NOP)
+    b.root_lens = [3, 3, 3, 3]
+    rng = np.random.default_rng(7)
+    x = rng.integers(-8, 9, size=(rows, red, inner)).astype(np.float32)
+    z0 = rng.integers(-4, 5, size=(rows, inner)).astype(np.float32)
+    y = x.sum(axis=1)
+    out = {1.0: [z0 + 2 * y, x.max(axis=1)], 0.0: [z0 + 2 * y, np.zeros_like(y)]}
+    return b.serialize(), [x, z0], out
+
+
 ALL = {
     "A_two_level": kat_a_two_level, "B_while": kat_b_while, "C_region_gelu": kat_c_region_gelu,
     "while_counter": kat_while_counter, "int_div_zero": kat_int_div_zero,

@@ -90,6 +90,26 @@ def test_for_zero_trip_and_if(rt, flag):
         np.testing.assert_array_equal(o.reshape(e.shape), e)
 
 
+@pytest.mark.parametrize("flag", [1.0, 0.0])
+def test_strided_reduce_spread_over_lanes_in_control_ranges(rt, flag):
+    """The loader re-cuts both reductions by rows over the four lanes (inserting entries
+    into FOR-body and IF-branch ranges); results equal the oracle's known answer."""
+    vm = package()
+    blob, (x, z0), expected = K.kat_strided_reduce_in_control_ranges()
+    lp = vm.LoadedProgram.Load(rt, vm.VmProgram.Parse(blob))
+    assert lp.stat("spread_reductions") == 2
+    out = lp.Execute([x, np.float32(flag), z0])
+    for o, e in zip(out, expected[flag]):
+        np.testing.assert_array_equal(np.asarray(o).view(np.float32).reshape(e.shape), e)
+
+
+def test_config4_reductions_are_spread_over_lanes(rt):
+    vm = package()
+    from conftest import Golden
+    lp = vm.LoadedProgram.Load(rt, vm.VmProgram.Parse(Golden("c4_nbody_mid").blob))
+    assert lp.stat("spread_reductions") == 4      # one axis-1 sum per acceleration evaluation
+
+
 def test_lanes_beyond_residency_are_refused_at_load(rt):
     vm = package()
     from blobs import Builder

@@ -27,3 +27,9 @@ def test_kat_on_oracle(name):
 def test_for_zero_trip_and_if_on_oracle(flag):
     blob, x, expected = K.kat_for_zero_trip_and_if()
     _check(vmoracle.Program(blob).execute([x, np.float32(flag)]), expected[flag])
+
+
+@pytest.mark.parametrize("flag", [1.0, 0.0])
+def test_strided_reduce_in_control_ranges_on_oracle(flag):
+    blob, (x, z0), expected = K.kat_strided_reduce_in_control_ranges()
+    _check(vmoracle.Program(blob).execute([x, np.float32(flag), z0]), expected[flag])
