@@ -47,11 +47,11 @@ enum RedKind : uint32_t { kSum = 0, kRMax, kRMin, kProd, kRAnd, kROr, kRXor };
 
 // RED_STRIDED tasks the device reduces row by row (a warp streams the red*inner
 // contiguous elements of one row): f32, inner axis of 2..4, rows of whole 16-byte
-// words and at least 1 KB, sum / max / min. The loader spreads such a task over
+// words and at least 1 KB, sums. The loader spreads such a task over
 // all lanes when its output tiles are few; both sides use this one rule.
 B2_HOST_DEVICE inline bool red_strided_rows_ok(uint32_t dt, int64_t red, int64_t inner, uint32_t kind) {
   return dt == kF32 && inner >= 2 && inner <= 4 && (red * inner) % 4 == 0 && red * inner >= 256 &&
-         kind <= kRMin;
+         kind == kSum;
 }
 
 // entry sentinels (scheduler.py:80-85)

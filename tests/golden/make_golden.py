@@ -754,8 +754,8 @@ def _():
 
 
 # 256 bodies on 8 lanes: the axis-1 force sum is one output tile, so the loader spreads it
-# over the lanes by rows (two full 96-load steps per 768-element row), and the
-# trailing-axis sum has 65536 segments of 3 (the warp-cooperative small-segment path)
+# over the lanes by rows (two full 96-load steps per 768-element row); the trailing-axis
+# sum has 65536 segments of 3
 @case("c4_nbody_mid", rtol=1e-4, atol=1e-5)
 def _():
     return cases.c4_nbody(n=256, steps=2, nlanes=8)

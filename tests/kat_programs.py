@@ -149,7 +149,7 @@ def kat_strided_reduce_in_control_ranges():
     """An interior-axis reduction owned by one lane inside a FOR body and inside an IF
     branch, with the other lanes' runs empty at a range start, empty at a range end, or
     holding NOPs: the layout a loader that re-cuts the reduction over all lanes has to
-    re-index. z accumulates sum_r x[row, r, c] twice; w = max_r x if flag else y - y.
+    re-index. z accumulates y = sum_r x[row, r, c] twice; w = y (summed again) if flag else y - y.
     Integer-valued inputs, so every summation order gives the same f32."""
     rows, red, inner = 8, 128, 3
     n_out = rows * inner
@@ -159,7 +159,7 @@ def kat_strided_reduce_in_control_ranges():
     b.in_dims, b.out_dims = [[rows, red, inner], [], [rows, inner]], [[rows, inner], [rows, inner]]
     RED_STRIDED = 15
     tsum = b.task(RED_STRIDED, by, bx, bx, n_out, red, inner, 0)
-    tmax = b.task(RED_STRIDED, bw, bx, bx, n_out, red, inner, 1)
+    tmax = b.task(RED_STRIDED, bw, bx, bx, n_out, red, inner, 0)       # the same sums again, into w
     tacc = b.task(EW, bz, bz, by, 0, n_out)
     tzero = b.task(EW, bw, by, by, 2, n_out)
     # lane 0: owner of both reductions
@@ -187,7 +187,7 @@ def kat_strided_reduce_in_control_ranges():
     x = rng.integers(-8, 9, size=(rows, red, inner)).astype(np.float32)
     z0 = rng.integers(-4, 5, size=(rows, inner)).astype(np.float32)
     y = x.sum(axis=1)
-    out = {1.0: [z0 + 2 * y, x.max(axis=1)], 0.0: [z0 + 2 * y, np.zeros_like(y)]}
+    out = {1.0: [z0 + 2 * y, y], 0.0: [z0 + 2 * y, np.zeros_like(y)]}
     return b.serialize(), [x, z0], out
 
 
