@@ -360,7 +360,7 @@ def main():
     value = total_alg / (ms_step * 1e-3) / w["scale"]
     base["scaling"] = "strong" if strong else "weak"
     base["config"]["parallelism"] = ("single GPU" if world == 1 else
-                                     f"dp{world}: {'batch shards' if strong else 'replicas'}"
+                                     f"dp{world}: {'batch shards' if strong else 'one independently seeded system per GPU' if plan and plan.seed_per_rank else 'replicas'}"
                                      + (", NCCL all-reduce between the gradient and SGD programs" if plan and plan.apply_program else
                                         ", scalar all-reduce" if w["program"].startswith("c2_chain") else ", no exchange step"))
     roof_scale = 1e9 if w["bound"] == "hbm" else 1e12
