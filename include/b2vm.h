@@ -117,7 +117,15 @@ b2_status b2_execute_device(b2_loaded *lp, void *const *dev_inputs, size_t n_inp
  * launch is enqueued on `cuda_stream` (a cudaStream_t; NULL = the runtime's own
  * stream) WITHOUT waiting for it: the asynchronous form a CUDA-stream-aware
  * caller uses to overlap copies, collectives and execution. b2_loaded_status
- * waits for that stream and reports the device status of the last launch. */
+ * waits for that stream and reports the device status of the last launch.
+ * A loaded program owns ONE arena and ONE barrier block: its launches must run
+ * one after another (enqueue them on one stream, or order the streams with
+ * events); two launches of the same loaded program in flight at once corrupt
+ * each other. Launches may be queued back to back without fetching the status;
+ * if one of them fails on the device (a wait ran out), the launches queued
+ * behind it find the abort flag set, return at their first barrier without
+ * writing results, and b2_loaded_status reports the first failure - so fetch
+ * the status before trusting the results of a pipelined batch. */
 b2_status b2_execute_device_async(b2_loaded *lp, void *const *dev_inputs, size_t n_inputs,
                                   void *const *dev_outputs, size_t n_outputs,
                                   void *cuda_stream, char *err, size_t err_cap);

@@ -18,12 +18,12 @@ struct Ctx {
   BufRef Ref(uint32_t id) const {
     auto it = port_of.find(id);
     if (it != port_of.end()) return kPortBit | static_cast<uint64_t>(it->second);
-    return arena_base + p.buffers[id].arena_byte_offset;
+    return arena_base + p.buffers[id].offset;
   }
   // Arena buffers are 64-byte aligned by the format; port addresses are checked at execute.
   bool Aligned16(uint32_t id) const {
     if (port_of.count(id)) return true;
-    return (arena_base + p.buffers[id].arena_byte_offset) % 16 == 0;
+    return (arena_base + p.buffers[id].offset) % 16 == 0;
   }
   template <typename T>
   uint32_t PushDesc(const T &v) {
@@ -354,9 +354,9 @@ bool BuildDeviceTables(const VmProgram &p, uint64_t arena_base, DeviceTables *ou
 
   // ---- zero-copy I/O ports (runtime.cc:798-821): a buffer that is only an input
   // or only an output, is not a constant, and is among the first kMaxIoPorts such.
-  std::set<uint32_t> in_ids(p.inputs.begin(), p.inputs.end()), out_ids(p.outputs.begin(), p.outputs.end());
+  std::set<uint32_t> in_ids(p.args.ids.begin(), p.args.ids.end()), out_ids(p.results.ids.begin(), p.results.ids.end());
   std::set<uint32_t> const_ids;
-  for (const auto &k : p.consts) const_ids.insert(k.first);
+  for (const auto &k : p.consts) const_ids.insert(k.buffer);
   auto assign_port = [&](uint32_t id) -> int {
     if (in_ids.count(id) && out_ids.count(id)) return -1;
     if (const_ids.count(id)) return -1;
@@ -369,11 +369,11 @@ bool BuildDeviceTables(const VmProgram &p, uint64_t arena_base, DeviceTables *ou
   // data) has to come out of the arena.
   std::set<uint32_t> written;
   for (const VmTask &t : p.tasks) written.insert(t.dst);
-  out->input_port.assign(p.inputs.size(), -1);
-  out->output_port.assign(p.outputs.size(), -1);
-  for (size_t i = 0; i < p.inputs.size(); ++i) out->input_port[i] = assign_port(p.inputs[i]);
-  for (size_t o = 0; o < p.outputs.size(); ++o)
-    out->output_port[o] = written.count(p.outputs[o]) ? assign_port(p.outputs[o]) : -1;
+  out->input_port.assign(p.args.ids.size(), -1);
+  out->output_port.assign(p.results.ids.size(), -1);
+  for (size_t i = 0; i < p.args.ids.size(); ++i) out->input_port[i] = assign_port(p.args.ids[i]);
+  for (size_t o = 0; o < p.results.ids.size(); ++o)
+    out->output_port[o] = written.count(p.results.ids[o]) ? assign_port(p.results.ids[o]) : -1;
 
   // ---- tasks ----
   out->tasks.resize(p.tasks.size());
@@ -448,8 +448,6 @@ bool BuildDeviceTables(const VmProgram &p, uint64_t arena_base, DeviceTables *ou
         bool ok = c.Aligned16(t.dst) && c.Aligned16(t.a) && v.rank >= 1 && v.stride[v.rank - 1] == 1 &&
                   v.dim[v.rank - 1] % chunk == 0 && v.off % chunk == 0;
         for (int k = 0; ok && k < v.rank - 1; ++k) ok = v.stride[k] % static_cast<int32_t>(chunk) == 0;
-        if (dyn)
-          for (uint32_t k = 0; ok && k < m.n_idx; ++k) ok = true;  // base alignment is checked per launch
         m.chunk = ok ? chunk : 0u;
         // a transpose: dst[..., r, c] = src[... + r + c * ld], 2- or 4-byte elements
         m.transposed = (d.op == kTopGather && !m.chunk && (m.esz == 2 || m.esz == 4) && v.rank >= 2 &&
@@ -636,7 +634,7 @@ bool BuildDeviceTables(const VmProgram &p, uint64_t arena_base, DeviceTables *ou
     for (uint32_t id : r)
       if (id < p.buffers.size()) readers[id].insert(static_cast<uint32_t>(ti));
   }
-  std::set<uint32_t> pinned(p.outputs.begin(), p.outputs.end());
+  std::set<uint32_t> pinned(p.results.ids.begin(), p.results.ids.end());
   for (const VmEntry &e : p.entries)
     if (e.task == kEntWhile || e.task == kEntIf) pinned.insert(e.signal_flag);
   // Two buffer ids may share arena bytes (liveness reuse, lowering.py:2813-2973).

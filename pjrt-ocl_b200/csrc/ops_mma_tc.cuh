@@ -528,15 +528,27 @@ __device__ __noinline__ bool mma_tc_tiles(const Lane &L, const DTask &t, uint32_
   // ---------------- teardown ----------------
   tc_fence_before_sync();
   __syncthreads();
+  // A wait that ran out leaves copies and MMAs of other roles possibly still in flight
+  // towards the stages, their barriers and the accumulator. They all complete within
+  // microseconds on their own (nothing they wait for is outstanding), so the failed
+  // path gives them that time before tensor memory goes back, and leaves the barriers
+  // valid instead of invalidating words a late completion may still signal.
+  const bool gave_up = S->failed != 0u;
+  if (gave_up) {
+    const unsigned long long t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 50000ull) nanosleep_ns(1000);
+  }
   if (w == 8) {
     __syncwarp();
     tc_fence_after_sync();
     tmem_dealloc(tmem, tcols);
   }
   if (L.tid == 0) {
-    if (S->failed) set_status(P, kStTensorTimeout, L.lane, tile_lo, kTopMma);
-    for (int s = 0; s < kTcStages; ++s) { mbar_inval(&S->full[s]); mbar_inval(&S->empty[s]); }
-    for (int b = 0; b < 2; ++b) { mbar_inval(&S->acc_full[b]); mbar_inval(&S->acc_empty[b]); }
+    if (gave_up) set_status(P, kStTensorTimeout, L.lane, tile_lo, kTopMma);
+    if (!gave_up) {
+      for (int s = 0; s < kTcStages; ++s) { mbar_inval(&S->full[s]); mbar_inval(&S->empty[s]); }
+      for (int b = 0; b < 2; ++b) { mbar_inval(&S->acc_full[b]); mbar_inval(&S->acc_empty[b]); }
+    }
   }
   __syncthreads();
   return true;

@@ -7,9 +7,7 @@
 // loaded program with constants uploaded once; <= 64 zero-copy I/O ports;
 // synchronous execute; size-keyed pool for result buffers.
 #include <cuda_runtime.h>
-#ifndef B2_EMU
 #include <cuda.h>   // CUtensorMap types only; the encoder is reached through the runtime's driver entry point
-#endif
 
 #include <cstdarg>
 #include <cstddef>
@@ -60,15 +58,6 @@ bool EncodeTmap(const b2::TmapSpec &s, const void *base, b2::DTmap *out) {
   const uint64_t stride1 = static_cast<uint64_t>(s.ld) * 2;
   const uint64_t stride2 = s.batch > 1 ? static_cast<uint64_t>(s.gs) * 2 : stride1 * outer;
   if (stride1 % 16 || stride2 % 16 || stride1 >= (1ull << 40) || stride2 >= (1ull << 40)) return false;
-#ifdef B2_EMU
-  // emulation: a plain record the emulated copy engine reads back
-  std::memset(out, 0, sizeof(*out));
-  out->w[0] = reinterpret_cast<uint64_t>(base);
-  out->w[1] = inner; out->w[2] = outer; out->w[3] = static_cast<uint64_t>(s.batch);
-  out->w[4] = stride1; out->w[5] = stride2;
-  out->w[6] = 64; out->w[7] = s.mn_major ? 64 : 128;
-  return true;
-#else
   typedef CUresult (*EncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
                                CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -92,7 +81,6 @@ bool EncodeTmap(const b2::TmapSpec &s, const void *base, b2::DTmap *out) {
                             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
-#endif
 }
 
 }  // namespace
@@ -162,6 +150,7 @@ struct b2_loaded {
   b2::DTmap *d_tmaps = nullptr;          // tensor maps of the tensor-core matmul operands
   std::vector<b2::DTmap> h_tmaps;
   std::vector<const void *> tmap_base;   // the operand address each map was encoded for
+  std::vector<char> tmap_off;            // the owning matmul could not be described at load: per-thread copies instead
   b2::DSync *d_sync = nullptr;
   b2::DSync *h_sync = nullptr;  // pinned mirror
   uint64_t launches = 0;
@@ -204,7 +193,7 @@ b2_status Enqueue(b2_loaded *lp, const b2::IoTable &io, cudaStream_t stream, std
   // addresses bound for this launch.
   for (size_t i = 0; i < lp->tab.tmaps.size(); ++i) {
     const b2::TmapSpec &sp = lp->tab.tmaps[i];
-    if (!(sp.base & b2::kPortBit)) continue;
+    if (!(sp.base & b2::kPortBit) || lp->tmap_off[i]) continue;   // fixed address, or the task loads without tensor maps
     const uint8_t *base = static_cast<const uint8_t *>(io.p[sp.base & (b2::kMaxIoPorts - 1)]) + sp.off * 2;
     if (base == lp->tmap_base[i]) continue;
     if (!EncodeTmap(sp, base, &lp->h_tmaps[i])) {
@@ -294,10 +283,6 @@ b2_status b2_runtime_create(int device_ordinal, b2_runtime **out, char *err, siz
     SetErr(err, err_cap, std::string("device ") + rt->prop.name + " is sm_" + std::to_string(rt->prop.major) +
                              std::to_string(rt->prop.minor) + "; this backend is built for sm_100a only");
     return B2_FAILED_PRECONDITION;
-  }
-  if (const char *t = std::getenv("B2VM_THREADS")) {
-    const int v = std::atoi(t);
-    if (v == 128 || v == 512) rt->threads = v;
   }
   // All of the opt-in shared memory of one CTA per SM, minus a margin for the
   // runtime's own reservation.
@@ -391,29 +376,29 @@ b2_status b2_program_parse(const uint8_t *blob, size_t len, b2_program **out, ch
   return B2_OK;
 }
 void b2_program_destroy(b2_program *prog) { delete prog; }
-uint32_t b2_program_num_inputs(const b2_program *p) { return static_cast<uint32_t>(p->prog.inputs.size()); }
-uint32_t b2_program_num_outputs(const b2_program *p) { return static_cast<uint32_t>(p->prog.outputs.size()); }
+uint32_t b2_program_num_inputs(const b2_program *p) { return static_cast<uint32_t>(p->prog.args.ids.size()); }
+uint32_t b2_program_num_outputs(const b2_program *p) { return static_cast<uint32_t>(p->prog.results.ids.size()); }
 uint32_t b2_program_num_lanes(const b2_program *p) { return p->prog.n_lanes; }
 uint32_t b2_program_num_tasks(const b2_program *p) { return static_cast<uint32_t>(p->prog.tasks.size()); }
 uint64_t b2_program_arena_bytes(const b2_program *p) { return p->prog.arena_bytes; }
-static const b2::VmBuffer *IoBuf(const b2_program *p, int is_output, uint32_t i) {
-  const auto &ids = is_output ? p->prog.outputs : p->prog.inputs;
+static const b2::BufferSlot *IoBuf(const b2_program *p, int is_output, uint32_t i) {
+  const auto &ids = is_output ? p->prog.results.ids : p->prog.args.ids;
   return i < ids.size() ? &p->prog.buffers[ids[i]] : nullptr;
 }
 uint64_t b2_program_io_bytes(const b2_program *p, int is_output, uint32_t i) {
-  const b2::VmBuffer *b = IoBuf(p, is_output, i);
-  return b ? b->size_bytes : 0;
+  const b2::BufferSlot *b = IoBuf(p, is_output, i);
+  return b ? b->bytes : 0;
 }
 uint32_t b2_program_io_dtype(const b2_program *p, int is_output, uint32_t i) {
-  const b2::VmBuffer *b = IoBuf(p, is_output, i);
+  const b2::BufferSlot *b = IoBuf(p, is_output, i);
   return b ? b->dtype : 0;
 }
 uint32_t b2_program_io_rank(const b2_program *p, int is_output, uint32_t i) {
-  const auto &d = is_output ? p->prog.output_dims : p->prog.input_dims;
+  const auto &d = is_output ? p->prog.results.dims : p->prog.args.dims;
   return i < d.size() ? static_cast<uint32_t>(d[i].size()) : 0;
 }
 int64_t b2_program_io_dim(const b2_program *p, int is_output, uint32_t i, uint32_t k) {
-  const auto &d = is_output ? p->prog.output_dims : p->prog.input_dims;
+  const auto &d = is_output ? p->prog.results.dims : p->prog.args.dims;
   return (i < d.size() && k < d[i].size()) ? d[i][k] : 0;
 }
 
@@ -448,6 +433,7 @@ b2_status b2_program_load(b2_runtime *rt, b2_program *prog, b2_loaded **out, cha
   // whose operand cannot be described keeps the per-thread copy path.
   lp->h_tmaps.resize(lp->tab.tmaps.size());
   lp->tmap_base.assign(lp->tab.tmaps.size(), nullptr);
+  lp->tmap_off.assign(lp->tab.tmaps.size(), 0);
   for (size_t i = 0; i + 1 < lp->tab.tmaps.size(); i += 2) {
     bool ok = true;
     for (size_t j = i; j < i + 2; ++j) {
@@ -460,6 +446,7 @@ b2_status b2_program_load(b2_runtime *rt, b2_program *prog, b2_loaded **out, cha
     if (!ok) {
       b2::DMma *m = reinterpret_cast<b2::DMma *>(&lp->tab.desc[lp->tab.tmaps[i].desc_word]);
       m->tmap = -1;
+      lp->tmap_off[i] = lp->tmap_off[i + 1] = 1;
     }
   }
   std::vector<int32_t> aux = p.aux;
@@ -474,8 +461,8 @@ b2_status b2_program_load(b2_runtime *rt, b2_program *prog, b2_loaded **out, cha
   }
   std::memset(lp->h_sync, 0, sizeof(b2::DSync));
   for (const auto &k : p.consts) {  // constants are uploaded once (runtime.cc:1064-1072)
-    if (k.second.empty()) continue;
-    e = cudaMemcpy(lp->arena + p.buffers[k.first].arena_byte_offset, k.second.data(), k.second.size(), cudaMemcpyHostToDevice);
+    if (k.data.empty()) continue;
+    e = cudaMemcpy(lp->arena + p.buffers[k.buffer].offset, k.data.data(), k.data.size(), cudaMemcpyHostToDevice);
     if (e != cudaSuccess) { SetErr(err, err_cap, CudaMsg("constant upload", e)); return B2_INTERNAL; }
   }
   lp->prog = std::move(prog->prog);
@@ -511,6 +498,7 @@ uint64_t b2_loaded_stat(const b2_loaded *lp, int which) {
 void b2_loaded_set_wait_budget_ns(b2_loaded *lp, uint64_t ns) { lp->wait_budget_ns = ns; }
 size_t b2_loaded_phase_ns(const b2_loaded *lp, uint64_t *out, size_t cap) {
   if (!lp || !out) return 0;
+  std::lock_guard<std::mutex> g(lp->rt->mu);
   size_t n = std::min<size_t>(std::min<size_t>(lp->h_sync->barriers, b2::kPhaseSlots), cap);
   for (size_t i = 0; i < n; ++i) out[i] = lp->h_sync->phase_ns[i];
   return n;
@@ -546,28 +534,28 @@ static b2_status BindAndRun(b2_loaded *lp, void *const *dev_in, void *const *dev
   b2::IoTable io;
   std::memset(&io, 0, sizeof(io));
   cudaError_t e;
-  for (size_t i = 0; i < p.inputs.size(); ++i) {
-    const auto &b = p.buffers[p.inputs[i]];
-    if (!b.size_bytes) continue;
+  for (size_t i = 0; i < p.args.ids.size(); ++i) {
+    const auto &b = p.buffers[p.args.ids[i]];
+    if (!b.bytes) continue;
     if (lp->tab.input_port[i] >= 0) {
       if (reinterpret_cast<uintptr_t>(dev_in[i]) % 16) { *err = "argument " + std::to_string(i) + " is not 16-byte aligned"; return B2_INVALID_ARGUMENT; }
       io.p[lp->tab.input_port[i]] = dev_in[i];
-    } else if ((e = cudaMemcpyAsync(lp->arena + b.arena_byte_offset, dev_in[i], b.size_bytes, cudaMemcpyDeviceToDevice, stream)) != cudaSuccess) {
+    } else if ((e = cudaMemcpyAsync(lp->arena + b.offset, dev_in[i], b.bytes, cudaMemcpyDeviceToDevice, stream)) != cudaSuccess) {
       *err = CudaMsg("argument copy into the arena", e);
       return B2_INTERNAL;
     }
   }
-  for (size_t o = 0; o < p.outputs.size(); ++o) {
-    if (lp->tab.output_port[o] < 0 || !p.buffers[p.outputs[o]].size_bytes) continue;
+  for (size_t o = 0; o < p.results.ids.size(); ++o) {
+    if (lp->tab.output_port[o] < 0 || !p.buffers[p.results.ids[o]].bytes) continue;
     if (reinterpret_cast<uintptr_t>(dev_out[o]) % 16) { *err = "result " + std::to_string(o) + " is not 16-byte aligned"; return B2_INVALID_ARGUMENT; }
     io.p[lp->tab.output_port[o]] = dev_out[o];
   }
   const b2_status st = Enqueue(lp, io, stream, err);
   if (st != B2_OK) return st;
-  for (size_t o = 0; o < p.outputs.size(); ++o) {
-    const auto &b = p.buffers[p.outputs[o]];
-    if (lp->tab.output_port[o] >= 0 || !b.size_bytes) continue;
-    if ((e = cudaMemcpyAsync(dev_out[o], lp->arena + b.arena_byte_offset, b.size_bytes, cudaMemcpyDeviceToDevice, stream)) != cudaSuccess) {
+  for (size_t o = 0; o < p.results.ids.size(); ++o) {
+    const auto &b = p.buffers[p.results.ids[o]];
+    if (lp->tab.output_port[o] >= 0 || !b.bytes) continue;
+    if ((e = cudaMemcpyAsync(dev_out[o], lp->arena + b.offset, b.bytes, cudaMemcpyDeviceToDevice, stream)) != cudaSuccess) {
       *err = CudaMsg("result copy out of the arena", e);
       return B2_INTERNAL;
     }
@@ -586,9 +574,9 @@ b2_status b2_execute_device_async(b2_loaded *lp, void *const *dev_inputs, size_t
                                   size_t n_outputs, void *cuda_stream, char *err, size_t err_cap) {
   if (!lp) return B2_INVALID_ARGUMENT;
   const b2::VmProgram &p = lp->prog;
-  if (n_inputs != p.inputs.size() || n_outputs != p.outputs.size()) {
+  if (n_inputs != p.args.ids.size() || n_outputs != p.results.ids.size()) {
     SetErr(err, err_cap, "execute: got " + std::to_string(n_inputs) + " args / " + std::to_string(n_outputs) +
-                             " results, want " + std::to_string(p.inputs.size()) + " / " + std::to_string(p.outputs.size()));
+                             " results, want " + std::to_string(p.args.ids.size()) + " / " + std::to_string(p.results.ids.size()));
     return B2_INVALID_ARGUMENT;
   }
   std::lock_guard<std::mutex> g(lp->rt->mu);
@@ -604,9 +592,9 @@ b2_status b2_execute_device(b2_loaded *lp, void *const *dev_inputs, size_t n_inp
                             size_t n_outputs, char *err, size_t err_cap) {
   if (!lp) return B2_INVALID_ARGUMENT;
   const b2::VmProgram &p = lp->prog;
-  if (n_inputs != p.inputs.size() || n_outputs != p.outputs.size()) {
+  if (n_inputs != p.args.ids.size() || n_outputs != p.results.ids.size()) {
     SetErr(err, err_cap, "execute: got " + std::to_string(n_inputs) + " args / " + std::to_string(n_outputs) +
-                             " results, want " + std::to_string(p.inputs.size()) + " / " + std::to_string(p.outputs.size()));
+                             " results, want " + std::to_string(p.args.ids.size()) + " / " + std::to_string(p.results.ids.size()));
     return B2_INVALID_ARGUMENT;
   }
   std::lock_guard<std::mutex> g(lp->rt->mu);
@@ -614,9 +602,9 @@ b2_status b2_execute_device(b2_loaded *lp, void *const *dev_inputs, size_t n_inp
   std::string m;
   for (size_t o = 0; o < n_outputs; ++o) dev_outputs[o] = nullptr;
   for (size_t o = 0; o < n_outputs; ++o) {
-    dev_outputs[o] = lp->rt->PoolAlloc(p.buffers[p.outputs[o]].size_bytes, &m);
+    dev_outputs[o] = lp->rt->PoolAlloc(p.buffers[p.results.ids[o]].bytes, &m);
     if (!dev_outputs[o]) {
-      for (size_t k = 0; k < o; ++k) lp->rt->PoolFree(dev_outputs[k], p.buffers[p.outputs[k]].size_bytes);
+      for (size_t k = 0; k < o; ++k) lp->rt->PoolFree(dev_outputs[k], p.buffers[p.results.ids[k]].bytes);
       SetErr(err, err_cap, m);
       return B2_RESOURCE_EXHAUSTED;
     }
@@ -624,7 +612,7 @@ b2_status b2_execute_device(b2_loaded *lp, void *const *dev_inputs, size_t n_inp
   const b2_status st = BindAndRun(lp, dev_inputs, dev_outputs, lp->rt->stream, true, &m);
   if (st != B2_OK) {
     for (size_t o = 0; o < n_outputs; ++o) {
-      lp->rt->PoolFree(dev_outputs[o], p.buffers[p.outputs[o]].size_bytes);
+      lp->rt->PoolFree(dev_outputs[o], p.buffers[p.results.ids[o]].bytes);
       dev_outputs[o] = nullptr;
     }
     SetErr(err, err_cap, m);
@@ -636,8 +624,8 @@ b2_status b2_execute_host(b2_loaded *lp, const void *const *inputs, size_t n_inp
                           size_t n_outputs, char *err, size_t err_cap) {
   if (!lp) return B2_INVALID_ARGUMENT;
   const b2::VmProgram &p = lp->prog;
-  if (n_inputs != p.inputs.size() || n_outputs != p.outputs.size()) {
-    SetErr(err, err_cap, "Execute: got " + std::to_string(n_inputs) + " args, want " + std::to_string(p.inputs.size()));
+  if (n_inputs != p.args.ids.size() || n_outputs != p.results.ids.size()) {
+    SetErr(err, err_cap, "Execute: got " + std::to_string(n_inputs) + " args, want " + std::to_string(p.args.ids.size()));
     return B2_INVALID_ARGUMENT;
   }
   std::lock_guard<std::mutex> g(lp->rt->mu);
@@ -646,13 +634,13 @@ b2_status b2_execute_host(b2_loaded *lp, const void *const *inputs, size_t n_inp
   std::string m;
   std::vector<void *> din(n_inputs, nullptr), dout(n_outputs, nullptr);
   auto cleanup = [&] {
-    for (size_t i = 0; i < n_inputs; ++i) rt->PoolFree(din[i], p.buffers[p.inputs[i]].size_bytes);
-    for (size_t o = 0; o < n_outputs; ++o) rt->PoolFree(dout[o], p.buffers[p.outputs[o]].size_bytes);
+    for (size_t i = 0; i < n_inputs; ++i) rt->PoolFree(din[i], p.buffers[p.args.ids[i]].bytes);
+    for (size_t o = 0; o < n_outputs; ++o) rt->PoolFree(dout[o], p.buffers[p.results.ids[o]].bytes);
   };
   b2_status st = B2_OK;
   cudaError_t e = cudaSuccess;
   for (size_t i = 0; i < n_inputs && st == B2_OK; ++i) {
-    const size_t bytes = p.buffers[p.inputs[i]].size_bytes;
+    const size_t bytes = p.buffers[p.args.ids[i]].bytes;
     din[i] = rt->PoolAlloc(bytes, &m);
     if (!din[i]) { st = B2_RESOURCE_EXHAUSTED; break; }
     if (bytes && (e = cudaMemcpyAsync(din[i], inputs[i], bytes, cudaMemcpyHostToDevice, rt->stream)) != cudaSuccess) {
@@ -661,13 +649,13 @@ b2_status b2_execute_host(b2_loaded *lp, const void *const *inputs, size_t n_inp
     }
   }
   for (size_t o = 0; o < n_outputs && st == B2_OK; ++o) {
-    dout[o] = rt->PoolAlloc(p.buffers[p.outputs[o]].size_bytes, &m);
+    dout[o] = rt->PoolAlloc(p.buffers[p.results.ids[o]].bytes, &m);
     if (!dout[o]) st = B2_RESOURCE_EXHAUSTED;
   }
   if (st == B2_OK) st = BindAndRun(lp, din.data(), dout.data(), rt->stream, false, &m);
   if (st == B2_OK) st = FetchStatus(lp, rt->stream, &m);
   for (size_t o = 0; o < n_outputs && st == B2_OK; ++o) {
-    const size_t bytes = p.buffers[p.outputs[o]].size_bytes;
+    const size_t bytes = p.buffers[p.results.ids[o]].bytes;
     if (bytes && (e = cudaMemcpyAsync(outputs[o], dout[o], bytes, cudaMemcpyDeviceToHost, rt->stream)) != cudaSuccess) {
       m = CudaMsg("Execute: output read", e);
       st = B2_INTERNAL;

@@ -27,6 +27,7 @@
 
 namespace b2 {
 
+constexpr int kVmThreads = 512;   // threads per lane: the one instantiation the library carries
 struct Frame { uint32_t pc, end, widx, phase; };  // phase: 0 while-cond, 1 while-body, 2 if, FOR: trips left
 constexpr uint32_t kRoot = 0xFFFFFFFFu;
 
@@ -207,15 +208,15 @@ __global__ void __launch_bounds__(NT, 1) b2_vm(const __grid_constant__ KParams P
 cudaError_t LaunchVm(const KParams &params, uint32_t n_lanes, int threads, uint32_t smem_bytes,
                      cudaStream_t stream) {
   void *args[2] = {const_cast<KParams *>(&params), &smem_bytes};
-  const void *fn = threads == 512 ? reinterpret_cast<const void *>(&b2_vm<512>)
-                                  : reinterpret_cast<const void *>(&b2_vm<128>);
+  if (threads != kVmThreads) return cudaErrorInvalidValue;
+  const void *fn = reinterpret_cast<const void *>(&b2_vm<kVmThreads>);
   return cudaLaunchCooperativeKernel(fn, dim3(n_lanes), dim3(threads), args, smem_bytes, stream);
 }
 
 // Co-resident CTAs of the megakernel at `threads` per lane and `smem_bytes` of dynamic shared memory.
 cudaError_t VmResidency(int device, int threads, uint32_t smem_bytes, int *max_lanes) {
-  const void *fn = threads == 512 ? reinterpret_cast<const void *>(&b2_vm<512>)
-                                  : reinterpret_cast<const void *>(&b2_vm<128>);
+  if (threads != kVmThreads) return cudaErrorInvalidValue;
+  const void *fn = reinterpret_cast<const void *>(&b2_vm<kVmThreads>);
   cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_bytes));
   if (e != cudaSuccess) return e;
   int per_sm = 0, sms = 0;

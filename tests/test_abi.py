@@ -53,6 +53,40 @@ def test_parse_rejects_malformed_blobs():
         vm.VmProgram.Parse(b"")
 
 
+def test_byte_layout_golden_parses_field_by_field():
+    """The reference's byte-layout known answer (tests/test_lowering.py:109-171):
+    b3 = (b0 + b1) - [1, 2, 3] on 8 lanes. The blob the reference serializer wrote
+    (fixture) must equal the bytes spelled out here from the format description,
+    and the parser must report every count and shape in it."""
+    vm = package()
+    blob = Golden("golden_layout_kat").blob
+    none, barrier = 0xFFFFFFFF, 0xFFFFFFFE
+    want = struct.pack("<IIIIIIIIIIQ", 0x314D5056, 3, 4, 2, 1, 2, 2, 1, 0, 0, 256)
+    for off in (0, 64, 128, 192):
+        want += struct.pack("<QQII", off, 12, 0, 0)
+    want += struct.pack("<II", 0, 1) + struct.pack("<I", 3) + b"\0" * 4
+    want += struct.pack("<IIQ", 1, 0, 3) * 3
+    want += struct.pack("<II", 2, 12) + np.array([1.0, 2.0, 3.0], "<f4").tobytes() + b"\0" * 4
+    want += struct.pack("<8I", 1, 3, 0, 1, 3, 0, 0, 0) + struct.pack("<8I", 3, 3, 3, 2, 3, 0, 0, 0)
+    assert len(want) == 296 and blob[:296] == want
+    n_tasks, n_entries, n_flags, n_lanes = struct.unpack_from("<IIII", blob, 296)
+    assert (n_tasks, n_entries, n_flags, n_lanes) == (2, 10, 0, 8)
+    assert struct.unpack_from("<12I", blob, 312) == (0, 3, 0, 1, 0, 3, 0, 0, 0, 0, 0, 0)
+    ent = 312 + 48 * 2 + 16 * 8
+    assert struct.unpack_from("<8I", blob, ent) == (0, 0, 1, none, 0, none, 0, 0)
+    assert struct.unpack_from("<8I", blob, ent + 32) == (barrier, 0, 0, none, 0, none, 0, 0)
+    assert len(blob) == ent + 32 * 10
+    p = vm.VmProgram.Parse(blob)
+    assert (p.n_inputs, p.n_outputs, p.n_lanes, p.n_tasks, p.arena_bytes) == (2, 1, 8, 2, 256)
+    for spec in p.inputs + p.outputs:
+        assert spec["bytes"] == 12 and spec["shape"] == (3,) and spec["dtype"] == np.dtype("<f4")
+    # a buffer that is not on a multiple of its element size is refused on the host
+    bad = bytearray(blob)
+    struct.pack_into("<QQII", bad, 48 + 24, 68, 8, 4, 0)        # buffer 1: i64 at offset 68
+    with pytest.raises(vm.InvalidArgument, match="misaligned"):
+        vm.VmProgram.Parse(bytes(bad))
+
+
 def test_parse_rejects_schedule_errors():
     vm = package()
     from blobs import BARRIER, Builder
