@@ -149,6 +149,24 @@ void b2_loaded_set_wait_budget_ns(b2_loaded *lp, uint64_t ns);
  * returns how many were written. */
 size_t b2_loaded_phase_ns(const b2_loaded *lp, uint64_t *out, size_t cap);
 
+/* ---- allocation-free full sum (no counterpart in the reference) ------------ */
+/* out[0] = sum of the n_elems f32 values at dev_in, for hosts that cannot
+ * allocate device memory: a process whose own allocator already holds all of
+ * HBM (cudaMalloc - hence b2_program_load - fails there), or a latency path that
+ * cannot take the device-wide stall of cudaMalloc / cudaFree. The caller passes
+ * input and output; the partial sums live in a fixed 16.3 KB array inside the
+ * library (held by every GPU that loads it, until exit), which limits n_elems to
+ * b2_sum_f32_static_max_elems() = 536 870 912; more is B2_INVALID_ARGUMENT.
+ * Calls no cudaMalloc / cudaFree. Enqueued on `cuda_stream` (NULL = the default
+ * stream) and waited for before returning. All calls on one GPU share the array:
+ * calls that overlap on the GPU (other threads, other streams) race. The first
+ * call on each GPU looks the array's device address up; make it before any
+ * stream capture begins. Buffers 4-byte aligned (16-byte aligned input is
+ * fastest). */
+b2_status b2_sum_f32_static(int device_ordinal, const void *dev_in, uint64_t n_elems, void *dev_out,
+                            void *cuda_stream, char *err, size_t err_cap);
+uint64_t b2_sum_f32_static_max_elems(void);
+
 #ifdef __cplusplus
 }
 #endif

@@ -13,7 +13,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "build")
-SOURCES = ["vm_kernel.cu", "runtime.cc", "loader.cc", "vmprog.cc"]
+SOURCES = ["vm_kernel.cu", "runtime.cc", "loader.cc", "vmprog.cc", "static_sum.cu"]
 OUT = os.path.join(HERE, "libb2vm.so")
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 

@@ -96,7 +96,7 @@ EXPORTS = [
     "b2_program_io_rank", "b2_program_io_dim", "b2_program_load", "b2_loaded_destroy",
     "b2_loaded_program", "b2_execute_host", "b2_execute_device", "b2_execute_device_async",
     "b2_loaded_status", "b2_loaded_launch_count", "b2_loaded_set_wait_budget_ns",
-    "b2_loaded_phase_ns", "b2_loaded_stat",
+    "b2_loaded_phase_ns", "b2_loaded_stat", "b2_sum_f32_static", "b2_sum_f32_static_max_elems",
 ]
 
 
@@ -142,6 +142,8 @@ def lib():
         "b2_loaded_set_wait_budget_ns": (None, [vp, ctypes.c_uint64]),
         "b2_loaded_phase_ns": (sz, [vp, ctypes.POINTER(ctypes.c_uint64), sz]),
         "b2_loaded_stat": (ctypes.c_uint64, [vp, ctypes.c_int]),
+        "b2_sum_f32_static": (ctypes.c_int, [ctypes.c_int, vp, ctypes.c_uint64, vp, vp, cp, sz]),
+        "b2_sum_f32_static_max_elems": (ctypes.c_uint64, []),
     }
     for name, (res, args) in sig.items():
         fn = getattr(L, name)
@@ -252,6 +254,15 @@ class Runtime:
         _check(lib().b2_d2h(self._h, ctypes.c_void_p(out.ctypes.data), ctypes.c_void_p(dev_ptr),
                             nbytes, err, _ERRCAP), err)
         return out[:nbytes]
+
+    def SumF32Static(self, dev_in: int, n_elems: int, dev_out: int, stream: int = 0) -> None:
+        """out[0] = sum of n_elems f32 at dev_in, through the entry point that
+        allocates nothing (its scratch is an array built into the library; see
+        include/b2vm.h for who needs that and for the size limit). Returns once
+        the result is in dev_out."""
+        err = _errbuf()
+        _check(lib().b2_sum_f32_static(self.device_ordinal, ctypes.c_void_p(dev_in), n_elems,
+                                       ctypes.c_void_p(dev_out), ctypes.c_void_p(stream), err, _ERRCAP), err)
 
     def close(self):
         if self._h:
