@@ -3,19 +3,20 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
 
-A step = one Execute of one loaded VMProgram (one megakernel launch) on synthetic
-inputs of the configuration's shapes and distributions (seeded; see
-pjrt-ocl_b200/programs/cases.py). `value` is measured with the arguments already
+A step = one Execute of one loaded VMProgram (one megakernel launch; config 3 on N > 1
+GPUs: gradient program, NCCL all-reduce, SGD program) on synthetic inputs of the
+configuration's shapes and distributions (seeded; see pjrt-ocl_b200/programs/cases.py).
+The default workload is the headline metric: config 5's pre-norm transformer block,
+tokens/s, batch-sharded over the GPUs. `value` is measured with the arguments already
 resident in HBM (CUDA events on the launching stream); `e2e` goes through the
-host-buffer Execute call (pinned host -> device, launch, device -> host every
-step). Multi-GPU runs are weak-scaling replicas (one process per GPU, nothing on
-the data path crosses GPUs for this configuration; the scalar results are
-all-reduced once per step over NCCL).
+host-buffer Execute call (pinned host -> device, launch, device -> host every step).
+After the timed loop one step's results are copied back and checked by value
+(tests/fullsize_refs.py): the line carries `"verified": true|false`.
 
-`--impl reference` times the CPU arm: the reference's device kernels are OpenCL
-C and cannot be built or run on this box, so the arm is the C restatement of the
-reference's per-phase host walk and CPU tile bodies (oracle/), on all host cores,
-on a bounded sample of the same workload.
+`--impl reference` times the CPU arm: the reference's device kernels are OpenCL C and
+cannot be built or run on this box, so the arm is the C restatement of the reference's
+per-phase host walk and CPU tile bodies (oracle/), on all host cores, one bounded
+sample of the workload per step (the sample is named in the line's `config`).
 """
 from __future__ import annotations
 
@@ -44,14 +45,14 @@ N_C2 = 8192 * 4096
 # name -> program blob, CPU-arm sample blob (+ fraction of the full workload it is),
 # algorithmic bytes per step, metric
 def _wl(program, metric, unit, alg, scale, bound, dtype, desc, roof_alg=None, sample=None, sample_frac=0.0,
-        secondary=False, plan=None, traffic=None, max_steps=None):
+        secondary=False, plan=None, traffic=None, max_steps=None, sample_what=""):
     """alg: algorithmic units one step processes (bytes, flops or tokens); value = alg / seconds / scale.
     roof_alg: bytes (bound "hbm") or flops (bound "tensor") of one step, for the roofline fraction.
     traffic: dram__bytes_read.sum + dram__bytes_write.sum of one launch from the ncu capture summarised under
     profiles/ (bytes), where one was taken. max_steps: cap on timed steps where one step runs for a second or so."""
     return dict(program=program, metric=metric, unit=unit, alg=alg, scale=scale, bound=bound, dtype=dtype, desc=desc,
                 roof_alg=alg if roof_alg is None else roof_alg, sample=sample, sample_frac=sample_frac,
-                secondary=secondary, plan=plan, traffic=traffic, max_steps=max_steps)
+                secondary=secondary, plan=plan, traffic=traffic, max_steps=max_steps, sample_what=sample_what)
 
 
 # config 5 block: 8 x 2048 tokens, d_model 1024, 16 heads x 64, FFN 4096
@@ -65,13 +66,14 @@ WORKLOADS = {
     "c2_f32": _wl("c2_chain_f32", "eltwise HBM GB/s", "GB/s", 7 * N_C2 * 4 + 2 * 4096 * 4, 1e9, "hbm", "f32",
                   "config 2: LayerNorm -> tanh-GELU -> softmax -> full sum on f32 (8192,4096); "
                   "bytes = LayerNorm r+w, GELU r+w, softmax r+w, sum r, + gamma/beta",
-                  sample="c2_chain_f32_cpu_sample", sample_frac=512 / 8192, traffic=945.1e6),
+                  sample="c2_chain_f32_cpu_sample", sample_frac=512 / 8192, traffic=945.1e6,
+                  sample_what="512 of the 8192 rows"),
     "c2_bf16": _wl("c2_chain_bf16", "eltwise HBM GB/s", "GB/s", 7 * N_C2 * 2 + 2 * 4096 * 2, 1e9, "hbm", "bf16",
                    "config 2 on bf16-storage copies of the same values",
-                   sample="c2_chain_bf16_cpu_sample", sample_frac=512 / 8192),
+                   sample="c2_chain_bf16_cpu_sample", sample_frac=512 / 8192, sample_what="512 of the 8192 rows"),
     "c2_i32": _wl("c2_int_chain", "eltwise HBM GB/s", "GB/s", 5 * N_C2 * 4, 1e9, "hbm", "i32",
                   "config 2: max((a+b)^c, d) on i32 (8192,4096), bit-exact",
-                  sample="c2_int_chain_cpu_sample", sample_frac=512 / 8192),
+                  sample="c2_int_chain_cpu_sample", sample_frac=512 / 8192, sample_what="512 of the 8192 rows"),
     "dot_bf16_8192": _wl("dot_bf16_8192", "dot_general TFLOP/s", "TFLOP/s", 2 * 8192 ** 3, 1e12, "tensor", "bf16",
                          "one dot_general bf16 8192 x 8192 x 8192, f32 accumulate, bf16 result"),
     "dot_bf16_4096": _wl("dot_bf16_4096", "dot_general TFLOP/s", "TFLOP/s", 2 * 4096 ** 3, 1e12, "tensor", "bf16",
@@ -85,7 +87,9 @@ WORKLOADS = {
     "c5_block": _wl("c5_block_bf16", "transformer-block tokens/s per B200", "tokens/s", _C5_TOK, 1.0, "tensor", "bf16",
                     "config 5: pre-norm decoder block forward, batch 8 x seq 2048, d_model 1024, 16 x 64 heads, "
                     "causal flash attention, GELU FFN 4096, bf16",
-                    roof_alg=_C5_MM_FLOPS + _C5_ATT_FLOPS, plan="c5_block"),
+                    roof_alg=_C5_MM_FLOPS + _C5_ATT_FLOPS, plan="c5_block",
+                    sample="c5_block_bf16_cpu_sample", sample_frac=512 / _C5_TOK,
+                    sample_what="one sequence of 512 tokens through the same block (8 x 2048 in the workload)"),
     "c4_nbody": _wl("c4_nbody", "n-body pair interactions/s", "G interactions/s", 4096 * 4096 * 4 * 200, 1e9, "hbm",
                     "f32", "config 4: 4096 bodies, RK4, 200 steps in one FOR loop (one system per GPU), executed as "
                     "the decomposed bytecode, whose (N,N,3) intermediates make it HBM-bound; bytes per step = the "
@@ -132,7 +136,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "25",
                  "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -169,21 +173,35 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
-def cpu_arm(w: dict, steps: int, warmup: int, threads: int):
-    """Time the oracle on the bounded sample; returns (metric value, seconds/step)."""
+def cpu_arm(w: dict, steps: int, warmup: int, threads: int, budget_s: float = 200.0):
+    """Time the CPU arm on the workload's bounded sample: every step executes the whole
+    sample program once. Returns (metric value, seconds per step, steps actually timed).
+    The steps are cut short (and the count returned says so) only if they would not fit
+    `budget_s` seconds."""
     sys.path.insert(0, os.path.join(ROOT, "oracle"))
     import vmoracle
     man = manifest()[w["sample"]]
     blob = load_blob(w["sample"])
     args = gen_inputs.gen_all(man["seed"], man["items"])
     prog = vmoracle.Program(blob)
-    for _ in range(warmup):
+    t0 = time.perf_counter()
+    prog.execute(args, threads=threads)                      # first call also builds / loads the library
+    first = time.perf_counter() - t0
+    for _ in range(max(0, min(warmup, int(budget_s * 0.2 / max(first, 1e-6))) - 1)):
         prog.execute(args, threads=threads)
+    steps = max(1, min(steps, int(budget_s * 0.8 / max(first, 1e-6))))
     t0 = time.perf_counter()
     for _ in range(steps):
         prog.execute(args, threads=threads)
     dt = (time.perf_counter() - t0) / steps
-    return w["alg"] * w["sample_frac"] / dt / w["scale"], dt
+    return w["alg"] * w["sample_frac"] / dt / w["scale"], dt, steps
+
+
+def oracle_rows(sample_program, x_rows, gamma, beta):
+    """Config 2 on a row sample through the C oracle (the checker of `verified`)."""
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import vmoracle
+    return vmoracle.Program(load_blob(sample_program)).execute([np.ascontiguousarray(x_rows), gamma, beta])
 
 
 def main():
@@ -191,9 +209,10 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=300)
     ap.add_argument("--warmup", type=int, default=10)
-    ap.add_argument("--workload", default="c2_f32", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="c5_block", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-extra", action="store_true", help="skip the secondary workloads")
+    ap.add_argument("--no-verify", action="store_true", help="skip the value check of the last step's results")
     a = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -206,20 +225,25 @@ def main():
             "warmup": a.warmup, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": w["dtype"], "data": "synthetic",
             "config": {"workload": a.workload, "what": w["desc"], "program": w["program"],
-                       "lanes": 148, "ew_tile": 4096, "l2": "inputs larger than L2 (>= 128 MiB per operand)"}}
+                       "lanes": 148, "ew_tile": 4096, "l2": ""}}
 
     if a.impl == "reference":
         if rank != 0:
             return
-        steps = max(1, min(a.steps, 5))
-        val, dt = cpu_arm(w, steps, min(a.warmup, 1), cores)
-        sample = f"{w['sample']}: {w['sample_frac']:.4f} of the rows, {steps} steps"
-        line = dict(base, impl="reference", value=val, steps=steps, ms_per_step=dt * 1e3 / w["sample_frac"],
+        if not w["sample"]:
+            print(json.dumps({"impl": "reference", "unavailable": f"no bounded CPU sample is defined for workload {a.workload}"}))
+            return
+        val, dt, steps = cpu_arm(w, a.steps, a.warmup, cores)
+        sample = f"{w['sample']}: {w['sample_what']}; every step runs the whole sample once ({dt:.2f} s)"
+        cfg = dict(base["config"], sample=sample)
+        line = dict(base, config=cfg, impl="reference", value=val, steps=steps, ms_per_step=dt * 1e3,
                     cpu_baseline={"value": val, "unit": w["unit"], "cores": cores, "kind": "port", "sample": sample},
                     e2e={"value": val, "unit": w["unit"], "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
                     gpu_launches=0,
-                    note="reference device kernels are OpenCL C (no OpenCL runtime on this box): "
-                         "CPU arm = C restatement of its CPU tile bodies, OpenMP over all host cores")
+                    note="reference device kernels are OpenCL C (no OpenCL runtime, no jax on this box): the CPU arm is the "
+                         "C restatement of its per-phase host walk and CPU tile bodies, OpenMP over all host cores; "
+                         "the full workload does not fit a sensible time on it, so a step is the bounded sample named in config"
+                         + ("" if steps == a.steps else f"; {steps} of the {a.steps} requested steps fit the time budget"))
         print(json.dumps(line))
         return
 
@@ -237,6 +261,8 @@ def main():
 
     dp = importlib.import_module("pjrt-ocl_b200.dataparallel")
 
+    l2_note = [""]
+
     def run_workload(wl: dict, steps: int, warmup: int, want_e2e: bool):
         plan = dp.PLANS.get(wl["plan"]) if wl["plan"] else None
         name = plan.rank_program(world) if plan else wl["program"]
@@ -253,7 +279,18 @@ def main():
             t[:x.nbytes] = torch.from_numpy(x.reshape(-1).view(np.uint8))
             pin_in.append(t)
         dev_in = [t.cuda(non_blocking=True) for t in pin_in]
-        dev_out = [torch.empty(max(s["bytes"], 16), dtype=torch.uint8, device="cuda") for s in lp.prog.outputs]
+        # results of a data-parallel step that are summed over ranks live back to back in ONE buffer,
+        # so the exchange is a single all-reduce (16-byte aligned slots; the program writes into them)
+        bucket, bucket_slots = None, {}
+        if world > 1 and plan and len(plan.reduce_outputs) > 1:
+            off = 0
+            for i in plan.reduce_outputs:
+                bucket_slots[i] = off
+                off += (lp.prog.outputs[i]["bytes"] + 15) // 16 * 16
+            bucket = torch.zeros(off, dtype=torch.uint8, device="cuda")
+        dev_out = [bucket[bucket_slots[i]:bucket_slots[i] + max(s["bytes"], 16)] if i in bucket_slots
+                   else torch.empty(max(s["bytes"], 16), dtype=torch.uint8, device="cuda")
+                   for i, s in enumerate(lp.prog.outputs)]
         pin_out = [torch.empty(max(s["bytes"], 1), dtype=torch.uint8, pin_memory=True) for s in lp.prog.outputs]
         torch.cuda.synchronize()
         ins = [t.data_ptr() for t in dev_in]
@@ -261,7 +298,9 @@ def main():
         # the exchange step of the configuration, if it has one (NCCL, on the launching stream)
         reduce_views, lp2, ins2, outs2, dev_out2 = [], None, None, None, None
         if world > 1:
-            if plan and plan.reduce_outputs:
+            if bucket is not None:
+                reduce_views = [bucket.view(torch.float32)]          # padding between slots is zero on every rank
+            elif plan and plan.reduce_outputs:
                 reduce_views = [dev_out[i][:lp.prog.outputs[i]["bytes"]].view(torch.float32) for i in plan.reduce_outputs]
             elif wl["program"].startswith("c2_chain"):
                 reduce_views = [dev_out[-1][:4].view(torch.float32)]
@@ -279,29 +318,108 @@ def main():
                 lp2.ExecuteDeviceAsync(ins2, outs2, stream.cuda_stream)
 
         sampler = ClockSampler(local_rank)
-        sampler.start()                       # nvidia-smi needs a moment to start sampling
+        sampler.start()
         for _ in range(warmup):
             step()
         torch.cuda.synchronize()
+        if want_e2e:
+            # nvidia-smi needs most of a second before its first sample: keep the same load running until it
+            # reports, so that the clock record covers the timed region that follows
+            t_soak = time.perf_counter()
+            while not sampler.lines and time.perf_counter() - t_soak < 2.0:
+                for _ in range(8):
+                    step()
+                torch.cuda.synchronize()
         st = lp.Status()
         phases = lp.PhaseTimes()
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
         launches0 = lp.launch_count + (lp2.launch_count if lp2 else 0)
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(stream)
-        for _ in range(steps):
-            step()
-        e1.record(stream)
-        torch.cuda.synchronize()
+        # L2 hygiene: a workload whose arguments fit the 126 MB L2 gets the cache flushed between timed
+        # steps (a 256 MB fill), each step then timed by its own pair of events; larger ones run back to back
+        in_bytes = sum(x.nbytes for x in host_in)
+        flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device="cuda") if in_bytes < (252 << 20) else None
+        l2_note[0] = ("flushed between timed steps (256 MB fill; arguments total %.0f MB)" % (in_bytes / 1e6)
+                      if flush_buf is not None else "arguments larger than L2 (%.0f MB), steps back to back" % (in_bytes / 1e6))
+        if flush_buf is None:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(steps):
+                step()
+            e1.record(stream)
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1)
+        else:
+            evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+            for b0, b1 in evs:
+                flush_buf.fill_(1)
+                b0.record(stream)
+                step()
+                b1.record(stream)
+            torch.cuda.synchronize()
+            ms = sum(b0.elapsed_time(b1) for b0, b1 in evs)
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
-        ms = e0.elapsed_time(e1)
-        clocks = sampler.stop()
+        del flush_buf
         lp.Status()
         launches = lp.launch_count + (lp2.launch_count if lp2 else 0) - launches0
+        if want_e2e:
+            # the timed region of a short run fits between two samples: the same steps continue (untimed)
+            # until the sampler has seen at least 0.3 s of this load
+            t_soak = time.perf_counter()
+            while time.perf_counter() - t_soak < max(0.0, 0.3 - ms * 1e-3):
+                for _ in range(8):
+                    step()
+                torch.cuda.synchronize()
+        clocks = sampler.stop()
+        clocks["window"] = "timed region + identical untimed continuation to >= 0.3 s under load"
+        # where one step's time goes: CUDA events around the program(s) and the exchange
+        stages = None
+        if want_e2e and world > 1 and (reduce_views or lp2 is not None):
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+            ev[0].record(stream)
+            lp.ExecuteDeviceAsync(ins, outs, stream.cuda_stream)
+            ev[1].record(stream)
+            for v in reduce_views:
+                dist.all_reduce(v)
+            ev[2].record(stream)
+            if lp2 is not None:
+                lp2.ExecuteDeviceAsync(ins2, outs2, stream.cuda_stream)
+            ev[3].record(stream)
+            torch.cuda.synchronize()
+            stages = {"program_ms": ev[0].elapsed_time(ev[1]), "all_reduce_ms": ev[1].elapsed_time(ev[2]),
+                      "apply_program_ms": ev[2].elapsed_time(ev[3]),
+                      "all_reduce_bytes": int(sum(v.numel() * 4 for v in reduce_views))}
+        # value check of the last step's results (this rank's shard)
+        verified, verified_what = None, ""
+        if want_e2e and not a.no_verify:
+            sys.path.insert(0, os.path.join(ROOT, "tests"))
+            import fullsize_refs
+            torch.cuda.synchronize()
+            try:
+                if lp2 is None:
+                    host_out = [d.cpu().numpy()[:s["bytes"]] for d, s in zip(dev_out, lp.prog.outputs)]
+                    verified_what = fullsize_refs.verify_workload(name, host_in, host_out, oracle_rows)
+                else:
+                    # config 3 on N GPUs: every rank must hold the same updated weights, and they must be
+                    # what the single-GPU step gives on the global batch (checked on rank 0)
+                    host_out = [d.cpu().numpy()[:s["bytes"]] for d, s in zip(dev_out2, lp2.prog.outputs)]
+                    crc = torch.tensor([float(int(np.bitwise_xor.reduce(np.concatenate([h.view(np.uint8) for h in host_out]).view(np.uint32))))],
+                                       dtype=torch.float64, device="cuda")
+                    lo_, hi_ = crc.clone(), crc.clone()
+                    dist.all_reduce(lo_, op=dist.ReduceOp.MIN)
+                    dist.all_reduce(hi_, op=dist.ReduceOp.MAX)
+                    assert float(lo_.item()) == float(hi_.item()), "ranks disagree on the updated weights"
+                    if rank == 0:
+                        full_in = [np.ascontiguousarray(x) for x in gen_inputs.gen_all(man["seed"], man["items"])]
+                        loss = dev_out[0][:4].cpu().numpy()
+                        verified_what = fullsize_refs.verify_workload("c3_mlp_step", full_in, [loss] + host_out)
+                    verified_what = (verified_what or "as rank 0") + "; all ranks hold identical weights"
+                verified = bool(verified_what)
+            except AssertionError as e:
+                verified, verified_what = False, str(e)[:300]
         e2e = None
         if want_e2e:
             n_e2e = max(3, min(steps, 10))
@@ -345,9 +463,13 @@ def main():
         st["tensor_core_matmuls"] = [lp.stat("tensor_core_matmuls"), lp.stat("matmuls")]
         lp.close()
         st["phase_ns"] = phases
+        st["stages"] = stages
+        st["verified"] = verified
+        st["verified_what"] = verified_what
         return ms / steps, launches, clocks, e2e, st
 
     ms_step, launches, clocks, e2e, st = run_workload(w, a.steps, a.warmup, True)
+    base["config"]["l2"] = l2_note[0]
     t_max = torch.tensor([ms_step], device="cuda")
     e2e_t = torch.tensor([e2e["seconds"]], device="cuda")
     if world > 1:
@@ -381,21 +503,33 @@ def main():
             m = float(tm.item())
             pl = dp.PLANS.get(wl["plan"]) if wl["plan"] else None
             tot = wl["alg"] if (pl and pl.scaling == "strong") else wl["alg"] * world
+            strong_x = bool(pl and pl.scaling == "strong")
+            ach = (wl["roof_alg"] / world if strong_x else wl["roof_alg"]) / (m * 1e-3) / (1e9 if wl["bound"] == "hbm" else 1e12)
             extra[name] = {wl["unit"]: tot / (m * 1e-3) / wl["scale"], "ms_per_step": m,
-                           "scaling": "strong" if (pl and pl.scaling == "strong") else "weak"}
+                           "scaling": "strong" if strong_x else "weak",
+                           "roofline": {"bound": wl["bound"], "achieved": ach, "unit": "GB/s" if wl["bound"] == "hbm" else "TFLOP/s"}}
 
+    ver = torch.tensor([1.0 if st["verified"] else 0.0 if st["verified"] is not None else 2.0], device="cuda")
+    if world > 1:
+        dist.all_reduce(ver, op=dist.ReduceOp.MIN)
+    verified = None if float(ver.item()) == 2.0 else float(ver.item()) == 1.0
     if rank == 0:
         peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
         key = "hbm_gbs" if w["bound"] == "hbm" else "bf16_tflops"
         if os.path.exists(peaks_path):
-            peak, peak_src = json.load(open(peaks_path))[key], f"measured (MEASURED_PEAKS.json {key})"
+            pk = json.load(open(peaks_path))
+            peak, peak_src = pk[key], f"measured (MEASURED_PEAKS.json {key})"
+            for e in extra.values():
+                e["roofline"]["frac"] = e["roofline"]["achieved"] / pk["hbm_gbs" if e["roofline"]["bound"] == "hbm" else "bf16_tflops"]
         else:
             peak, peak_src = (6650.0 if w["bound"] == "hbm" else 1590.0), "fallback"
+            for e in extra.values():
+                e["roofline"]["frac"] = e["roofline"]["achieved"] / (6650.0 if e["roofline"]["bound"] == "hbm" else 1590.0)
         cpu = None
         if world == 1 and w["sample"]:
-            cv, cdt = cpu_arm(w, 3, 1, cores)
+            cv, cdt, csteps = cpu_arm(w, 3, 1, cores, budget_s=40.0)
             cpu = {"value": cv, "unit": w["unit"], "cores": cores, "kind": "port",
-                   "sample": f"{w['sample']}: {w['sample_frac']:.4f} of the rows, 3 steps, {cdt:.2f} s each"}
+                   "sample": f"{w['sample']}: {w['sample_what']}, {csteps} steps, {cdt:.2f} s each"}
         line = dict(base, value=value, ms_per_step=ms_step, clocks=clocks, gpu_launches=launches,
                     e2e={"value": total_alg / float(e2e_t.item()) / w["scale"], "unit": w["unit"],
                          "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"]},
@@ -405,6 +539,7 @@ def main():
                               "kernel": "b2_vm<512> (one launch per step)"},
                     cpu_baseline=cpu, device_ns_per_step=st["device_ns"], grid_barriers=st["barriers"],
                     phase_end_ns=st["phase_ns"], tensor_core_matmuls=st["tensor_core_matmuls"],
+                    verified=verified, verified_what=st["verified_what"], stages_ms=st["stages"],
                     other_workloads=extra)
         print(json.dumps(line))
     if world > 1:

@@ -139,7 +139,12 @@ uint64_t b2_loaded_launch_count(const b2_loaded *lp);
  * all matmul tasks per execute (2 G M N K each; a task inside a loop body counts
  * once), 6 flash-attention tasks, 7 flash-attention tasks on the tensor-core path,
  * 8 strided-reduction phases whose few output tiles were re-cut by rows over all
- * lanes. Unknown `which` returns 0. */
+ * lanes, 9 index of the megakernel build the program runs on (0 = the smallest;
+ * the library carries several builds, each holding a subset of the tile-op
+ * families, and a program runs on the smallest one that has all it uses),
+ * 10 bit mask of the tile-op families the program uses, 11 full reductions
+ * (RED_PART + RED_COMB) re-cut evenly over all lanes with the combine folded into
+ * the same phase. Unknown `which` returns 0. */
 uint64_t b2_loaded_stat(const b2_loaded *lp, int which);
 /* Per-wait budget of device-side bounded waits, in nanoseconds (default 2e9). */
 void b2_loaded_set_wait_budget_ns(b2_loaded *lp, uint64_t ns);
@@ -148,6 +153,16 @@ void b2_loaded_set_wait_budget_ns(b2_loaded *lp, uint64_t ns);
  * PJRT_OCL_PHASE_TS, runtime.cc:2196-2240). Writes at most `cap` values and
  * returns how many were written. */
 size_t b2_loaded_phase_ns(const b2_loaded *lp, uint64_t *out, size_t cap);
+/* Per-lane timing, off by default (the reference's per-lane barrier timestamps,
+ * VMO_TS_REC in vm_common.cl:258-282, read back and summarised by
+ * runtime.cc:2196-2240). When on, every lane records its start, its exit and its
+ * ARRIVAL at each of the first 64 grid barriers (globaltimer nanoseconds), which
+ * is what shows straggler idle: a phase ends at its last arrival, every other
+ * lane waited since its own. b2_loaded_lane_times waits for the last launch and
+ * copies lanes x 66 values, lane-major: [start, exit, arrival 0 .. arrival 63];
+ * returns the number of values written (0 when timing is off). */
+b2_status b2_loaded_lane_timing(b2_loaded *lp, int on, char *err, size_t err_cap);
+size_t b2_loaded_lane_times(b2_loaded *lp, uint64_t *out, size_t cap);
 
 /* ---- allocation-free full sum (no counterpart in the reference) ------------ */
 /* out[0] = sum of the n_elems f32 values at dev_in, for hosts that cannot

@@ -13,11 +13,12 @@
  *                the per-phase host order of runtime.cc:1546-1602
  *                (LaunchHostDispatch) / vmreader.py:655-773 (_run_control)
  *   tile ops     pjrt_plugin/kernels/ops/{ew,gather,reduce,mma,iota,scatter,
- *                dynslice,region,attention}.cl with the numeric conventions of
- *                the numpy validators in python/pjrt_ocl/ops/{elementwise.py,reduce.py,dot.py,attention.py,
- *                region.py,shape.py,making.py,bitcast.py,dynslice.py,
- *                concat.py} where the two differ (the validators are what the
- *                reference's own tests pin).
+ *                dynslice,region,attention,reduce_window,conv}.cl with the numeric
+ *                conventions of the numpy validators in python/pjrt_ocl/ops/
+ *                {elementwise,reduce,dot,attention,region,shape,making,bitcast,
+ *                dynslice,concat,reduce_window,gather_index,scatter_index,conv}.py
+ *                where the two differ (the validators are what the reference's
+ *                own tests pin).
  *
  * Pinning: tests/test_oracle.py replays every fixture of tests/golden/ (blobs
  * assembled by the reference's lowering + scheduler, outputs produced by BOTH
@@ -279,7 +280,8 @@ int vmo_parse(const uint8_t *data, size_t len, uint32_t ew_ts, uint32_t mma_t, v
       PFAIL("region input buffer id out of range");
     if (op == TOP_EW && t->p0 == SUB_SELECT && t->p3 >= p->n_buffers) PFAIL("select pred id out of range");
     if ((op == TOP_GATHER || op == TOP_IOTA_DIM || op == TOP_DYN_GATHER || op == TOP_DYN_SCATTER ||
-         op == TOP_RED_WINDOW || op == TOP_GATHER_INDEX || op == TOP_SCATTER_INDEX) && t->p0 >= p->n_aux)
+         op == TOP_RED_WINDOW || op == TOP_GATHER_INDEX || op == TOP_SCATTER_INDEX || op == TOP_SCATTER ||
+         op == TOP_CONV) && t->p0 >= p->n_aux)
       PFAIL("task aux offset out of range");
     if (op == TOP_MMA && (t->p4 > p->n_aux || t->p5 > p->n_aux)) PFAIL("mma view aux offset out of range");
     if (op == TOP_FLASH_ATTN && (t->p0 >= p->n_buffers || (uint64_t)t->p3 + 9 > p->n_aux))
@@ -883,6 +885,108 @@ static int exec_tiles(vmo_prog *p, const vmo_task *t, uint32_t tlo, uint32_t thi
           stf(dst, dt, (g * T_ + m) * hd + d, (float)o);
         }
         free(sc);
+      }
+      return 0;
+    }
+    case TOP_RED_WINDOW: { /* reduce_window.cl:19-70; ops/reduce_window.py:160-200 */
+      const int32_t *x = p->aux + t->p0;
+      const int kind = x[0], rank = x[1];
+      const int32_t *od = x + 2, *wd = od + rank, *ws = wd + rank, *pl = ws + rank, *id = pl + rank, *is = id + rank;
+      int64_t n = t->p1, lo = (int64_t)tlo * TS, hi = (int64_t)thi * TS, wcount = 1;
+      if (hi > n) hi = n;
+      if (rank > 16) return failf(err, cap, "reduce_window rank %d", rank);
+      for (int d = 0; d < rank; d++) wcount *= wd[d];
+#pragma omp parallel for schedule(static) if ((hi - lo) * wcount > 65536)
+      for (int64_t i = lo; i < hi; i++) {
+        int64_t oc[16], rem = i;
+        for (int d = rank - 1; d >= 0; --d) { oc[d] = rem % od[d]; rem /= od[d]; }
+        acc_t acc; int nan = 0;
+        acc_init(&acc, (uint32_t)kind, dt);   /* kinds 0 sum, 1 max, 2 min: the reduce kinds */
+        for (int64_t w = 0; w < wcount; w++) {
+          int64_t rw = w, off = 0; int inb = 1;
+          for (int d = rank - 1; d >= 0; --d) {
+            int64_t wc = rw % wd[d]; rw /= wd[d];
+            int64_t ic = oc[d] * ws[d] + wc - pl[d];
+            if (ic < 0 || ic >= id[d]) inb = 0;
+            off += ic * is[d];
+          }
+          if (inb) acc_step(&acc, (uint32_t)kind, dt, a, off, &nan);   /* padding = the identity: skipped */
+        }
+        acc_store(&acc, (uint32_t)kind, dt, dst, i, nan);
+      }
+      return 0;
+    }
+    case TOP_GATHER_INDEX: case TOP_SCATTER_INDEX: {
+      /* gather.cl:84-152, scatter.cl:81-179; ops/gather_index.py:154-186, ops/scatter_index.py:216-260 */
+      const int scat = op == TOP_SCATTER_INDEX;
+      const int32_t *x = p->aux + t->p0;
+      const int rank = x[0], nidx = x[1], vstride = x[2], is64 = x[3], kind = scat ? x[6] : 0;
+      const uint32_t idx_buf = (uint32_t)x[5];
+      const int32_t *dims = x + (scat ? 7 : 6), *ops = dims + rank, *sis = ops + rank, *ios = sis + rank, *cmax = ios + nidx;
+      if (idx_buf >= p->n_buffers) return failf(err, cap, "index buffer id out of range");
+      const uint8_t *ib = BUF(p, idx_buf);
+      int64_t n = t->p1, lo = (int64_t)tlo * TS, hi = (int64_t)thi * TS;
+      if (hi > n) hi = n;
+      /* sequential on purpose: with duplicate indices the update order is the element order
+         (np.add.at / maximum.at / minimum.at; plain assignment keeps the last writer) */
+      for (int64_t i = lo; i < hi; i++) {
+        int64_t rem = i, off = 0, sb = 0;
+        for (int e = rank - 1; e >= 0; --e) { int64_t c = rem % dims[e]; rem /= dims[e]; off += c * ops[e]; sb += c * sis[e]; }
+        for (int k = 0; k < nidx; k++) {
+          int64_t at = sb + (int64_t)k * vstride;
+          int64_t sv = is64 ? ((const int64_t *)ib)[at] : ((const int32_t *)ib)[at];
+          sv = sv < 0 ? 0 : (sv > cmax[k] ? cmax[k] : sv);
+          off += sv * ios[k];
+        }
+        if (!scat) { copy_elem(dst, i, a, off, es); continue; }
+        if (kind == 0) { copy_elem(dst, off, a, i, es); continue; }
+        if (dt == DT_F32) {
+          float *d = (float *)dst; const float v = ((const float *)a)[i];
+          d[off] = kind == 1 ? d[off] + v : kind == 2 ? np_max(d[off], v) : np_min(d[off], v);
+        } else if (dt == DT_U32) {
+          uint32_t *d = (uint32_t *)dst; const uint32_t v = ((const uint32_t *)a)[i];
+          d[off] = kind == 1 ? d[off] + v : kind == 2 ? (d[off] > v ? d[off] : v) : (d[off] < v ? d[off] : v);
+        } else if (dt == DT_I32) {
+          int32_t *d = (int32_t *)dst; const int32_t v = ((const int32_t *)a)[i];
+          d[off] = kind == 1 ? (int32_t)((uint32_t)d[off] + (uint32_t)v) : kind == 2 ? (d[off] > v ? d[off] : v) : (d[off] < v ? d[off] : v);
+        } else {
+          return failf(err, cap, "scatter combine on dtype %u", dt);
+        }
+      }
+      return 0;
+    }
+    case TOP_CONV: { /* conv.cl:23-72; ops/conv.py:160-208: f32, accumulate in double */
+      const int32_t *x = p->aux + t->p0;
+      const int sdim = x[0], Cin = x[1], Cout = x[2];
+      const int32_t *osp = x + 3, *win = osp + sdim, *st = win + sdim, *pl = st + sdim, *dil = pl + sdim, *isp = dil + sdim;
+      if (sdim < 1 || sdim > 4) return failf(err, cap, "conv spatial rank %d", sdim);
+      int64_t istr[4], acc = Cin, wcount = 1;
+      for (int d = sdim - 1; d >= 0; --d) { istr[d] = acc; acc *= isp[d]; }
+      const int64_t ibatch = acc;
+      for (int d = 0; d < sdim; d++) wcount *= win[d];
+      int64_t n = t->p1, lo = (int64_t)tlo * TS, hi = (int64_t)thi * TS;
+      if (hi > n) hi = n;
+      const float *in = (const float *)a, *wt = (const float *)b;
+#pragma omp parallel for schedule(static) if ((hi - lo) * wcount * Cin > 65536)
+      for (int64_t i = lo; i < hi; i++) {
+        int64_t rem = i, oc[4];
+        const int64_t co = rem % Cout; rem /= Cout;
+        for (int d = sdim - 1; d >= 0; --d) { oc[d] = rem % osp[d]; rem /= osp[d]; }
+        const int64_t bi = rem;
+        double sum = 0.0;
+        for (int64_t w = 0; w < wcount; w++) {
+          int64_t rw = w, ioff = bi * ibatch; int inb = 1;
+          for (int d = sdim - 1; d >= 0; --d) {
+            int64_t wc = rw % win[d]; rw /= win[d];
+            int64_t ic = oc[d] * st[d] + wc * dil[d] - pl[d];
+            if (ic < 0 || ic >= isp[d]) inb = 0;
+            ioff += ic * istr[d];
+          }
+          if (!inb) continue;
+          const int64_t wb = w * Cin * Cout + co;
+          for (int c = 0; c < Cin; c++) sum += (double)(in[ioff + c] * wt[wb + (int64_t)c * Cout]);
+        }
+        ((float *)dst)[i] = (float)sum;
       }
       return 0;
     }

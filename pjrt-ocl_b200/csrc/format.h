@@ -17,6 +17,12 @@ namespace b2 {
 constexpr uint32_t kMagic = 0x314D5056u;  // "VPM1"
 constexpr uint32_t kVersion = 3;
 
+#if defined(__CUDACC__)
+#define B2_HOST_DEVICE __host__ __device__
+#else
+#define B2_HOST_DEVICE
+#endif
+
 // dtype enum (lowering.py:59-68)
 enum Dtype : uint32_t { kF32 = 0, kI32, kU32, kBool, kI64, kF64, kF16, kBF16, kDtMax = kBF16 };
 
@@ -28,6 +34,32 @@ enum TileOp : uint32_t {
   kTopMax = kTopScatterIndex
 };
 
+// Tile-op families: the unit in which code is compiled into a build of the
+// megakernel (variants.h). Every tile op belongs to exactly one.
+enum Family : uint32_t {
+  kFamEw = 1u << 0,      // TILE_EW
+  kFamMove = 1u << 1,    // GATHER, SCATTER, DYN_GATHER, DYN_SCATTER, IOTA_DIM
+  kFamRed = 1u << 2,     // RED_PART, RED_COMB, RED_SEG, RED_STRIDED
+  kFamRows = 1u << 3,    // SOFTMAX_SEG, LAYERNORM_SEG
+  kFamRegion = 1u << 4,  // MAP_REGION
+  kFamMma = 1u << 5,     // TILE_MMA
+  kFamFlash = 1u << 6,   // FLASH_ATTN
+  kFamIndex = 1u << 7,   // RED_WINDOW, GATHER_INDEX, SCATTER_INDEX, CONV
+  kFamAll = 0xFFFFFFFFu
+};
+B2_HOST_DEVICE inline uint32_t family_of(uint32_t tile_op) {
+  switch (tile_op) {
+    case kTopEw: return kFamEw;
+    case kTopGather: case kTopScatter: case kTopDynGather: case kTopDynScatter: case kTopIotaDim: return kFamMove;
+    case kTopRedPart: case kTopRedComb: case kTopRedSeg: case kTopRedStrided: return kFamRed;
+    case kTopSoftmaxSeg: case kTopLayernormSeg: return kFamRows;
+    case kTopMapRegion: return kFamRegion;
+    case kTopMma: return kFamMma;
+    case kTopFlashAttn: return kFamFlash;
+    default: return kFamIndex;
+  }
+}
+
 // elementwise subops (pjrt_plugin/kernels/vm_common.cl:118-146)
 enum Sub : uint32_t {
   kAdd = 0, kMul, kSubt, kDiv, kMax, kMin, kPow, kCopy, kNeg, kExp, kLog, kSqrt, kRsqrt, kTanh,
@@ -38,12 +70,6 @@ enum Sub : uint32_t {
 
 // reduction kinds (python/pjrt_ocl/ops/reduce.py:56)
 enum RedKind : uint32_t { kSum = 0, kRMax, kRMin, kProd, kRAnd, kROr, kRXor };
-
-#if defined(__CUDACC__)
-#define B2_HOST_DEVICE __host__ __device__
-#else
-#define B2_HOST_DEVICE
-#endif
 
 // RED_STRIDED tasks the device reduces row by row (a warp streams the red*inner
 // contiguous elements of one row): f32, inner axis of 2..4, rows of whole 16-byte
@@ -110,6 +136,18 @@ enum TaskFlags : uint32_t {
   kViewB = 1u << 4,
   kVecPath = 1u << 5,   // every pointer 16-byte aligned and dtypes on the 4-wide path
   kFwdC = 1u << 6,      // select predicate forwarded
+  kRedFused = 1u << 7,  // RED_PART re-cut over all lanes with the combine folded in: entries carry word
+                        // ranges, ptr[3] is the final result, lane totals meet in KParams::scratch
+};
+
+// Scratch of a loaded program (KParams::scratch): where the lanes of a re-cut full
+// reduction leave their totals. `arrived` returns to 0 after every use.
+constexpr uint32_t kMaxWorkSlots = 6;
+struct RedScratch {
+  uint32_t arrived;
+  uint32_t pad[3];
+  uint32_t work[2 * kMaxWorkSlots];   // {next unit, lanes done} per dynamically distributed task; at rest 0
+  unsigned long long total[1];        // [n_lanes]
 };
 
 struct DTask {
@@ -192,10 +230,58 @@ struct DFlash {        // loader-built
   DView vq, vk, vv;
   uint32_t has_q, has_k, has_v;   // operand is read through its view
   uint32_t tc_mode;               // 0: CUDA-core path only
-  // tensor-core path: element strides of Q[h,t,d], K[h,c,d] (d contiguous), V[h,c,d]
-  int64_t q_h1, q_h0, q_t, k_h1, k_h0, k_c, v_h1, v_h0, v_c;
-  uint32_t h0_size;               // h = h1 * h0_size + h0
+  // Tensor-core path. The operands are reached through three TMA tensor maps (Q, K, V at
+  // KParams::tmaps[tmap .. tmap + 2]) of rank 4 {inner, rows, h0, h1}: head h is
+  // (h1, h0) = (h / h0_size, h % h0_size), which lets a [batch, seq, heads, hd] tensor
+  // be read in place as [batch * heads, seq, hd].
+  int32_t tmap;
+  uint32_t h0_size;
+  uint32_t k_mn;                  // K: keys are the unit-stride dimension (the plain [H, hd, C] operand), else d is
+  // Dynamic work distribution: when every lane that owns a share of the task enters it
+  // exactly once per phase, the lanes draw 256-row units from one counter pair in the
+  // program's scratch (heaviest first) instead of keeping their static ranges.
+  uint32_t work_slot;             // index of the {next, done} pair in the scratch, or kNoWorkSlot
+  uint32_t n_owner_lanes;
   uint32_t pad;
+};
+constexpr uint32_t kNoWorkSlot = 0xFFFFFFFFu;
+
+// RED_WINDOW (aux layout: pjrt_plugin/kernels/ops/reduce_window.cl:10-13), with the
+// divisions by the output dims prepared.
+constexpr int kWinDims = 8;
+struct DWindow {       // loader-built
+  uint32_t kind, rank, wcount;
+  uint32_t vec4;       // the innermost axis is not windowed, strided or padded and is a multiple of 4
+                       // (4-byte elements, aligned): 4 outputs per thread from one 16-byte load per tap
+  uint32_t odim[kWinDims], wdim[kWinDims], wstr[kWinDims], idim[kWinDims];
+  int32_t plow[kWinDims], istr[kWinDims];
+  uint32_t omagic[kWinDims], oshift[kWinDims];
+};
+
+// GATHER_INDEX / SCATTER_INDEX (aux layouts: ops/gather.cl:90-107, ops/scatter.cl:95-104):
+// the output's (gather) or the updates' (scatter) dims with the operand / index strides each
+// adds, and per index component its operand stride and clamp.
+constexpr int kIdxDims = 8;
+struct DIndexed {      // loader-built
+  uint32_t rank, nidx, is64, kind;      // kind: scatter combiner 0 set 1 add 2 max 3 min
+  int32_t vec_stride;
+  uint32_t esz;
+  uint32_t chunk;      // elements per 16-byte word when the innermost dim is a contiguous run on both
+                       // sides made of whole words, else 0
+  uint32_t pad;
+  BufRef idx;          // the start-indices buffer
+  uint32_t dim[kIdxDims];
+  int32_t op_stride[kIdxDims], si_stride[kIdxDims];
+  uint32_t magic[kIdxDims], shift[kIdxDims];
+  int32_t idx_op_stride[kIdxDims], clamp_max[kIdxDims];
+};
+
+// CONV (aux layout: ops/conv.cl:15-20), input strides precomputed.
+struct DConv {         // loader-built
+  uint32_t sdim, cin, cout, wcount;
+  uint32_t osp[4], win[4], str[4], dil[4], isp[4];
+  int32_t plow[4];
+  int64_t istr[4], ibatch;
 };
 
 struct IoTable { void *p[kMaxIoPorts]; };
@@ -212,8 +298,14 @@ struct KParams {
   uint32_t n_lanes;
   uint32_t pad;
   unsigned long long wait_budget_ns;
+  // Optional per-lane timing (null = off): kLaneTsSlots words per lane - [0] the lane's
+  // start, [1] its exit, [2 + i] its ARRIVAL at grid barrier i (first kPhaseSlots
+  // barriers), all in globaltimer nanoseconds. What the reference records under
+  // VMO_TS_REC (pjrt_plugin/kernels/vm_common.cl:258-282).
+  unsigned long long *lane_ts;
   IoTable io;
 };
+constexpr uint32_t kLaneTsSlots = kPhaseSlots + 2;
 
 }  // namespace b2
 #endif

@@ -77,6 +77,14 @@ void TaskReads(const VmProgram &p, const VmTask &t, std::vector<uint32_t> *r) {
     case kTopScatter:
       r->push_back(t.a); r->push_back(t.dst);
       break;
+    case kTopGatherIndex: case kTopScatterIndex:
+      r->push_back(t.a);
+      if (static_cast<size_t>(t.p0) + 5 < p.aux.size()) r->push_back(static_cast<uint32_t>(p.aux[t.p0 + 5]));
+      if (op == kTopScatterIndex) r->push_back(t.dst);  // combines into / partially overwrites what is there
+      break;
+    case kTopRedWindow:
+      r->push_back(t.a);
+      break;
     case kTopIotaDim:
       break;
     default:
@@ -105,12 +113,12 @@ bool ViewFromAux(const VmProgram &p, uint32_t aux_off, DView *v, std::string *er
 // factorisations of the same index space; walk their common refinement from the
 // innermost digit and require every piece of one coordinate to agree on that
 // coordinate's stride.
-bool AffineOverAxes(const DView &v, const int64_t n[3], int64_t stride[3], int64_t *off) {
+bool AffineOverAxesN(const DView &v, const int64_t *n, int naxes, int64_t *stride, int64_t *off) {
   *off = v.off;
-  stride[0] = stride[1] = stride[2] = 0;
-  bool have[3] = {false, false, false};
-  int a = 2, j = v.rank - 1;
-  int64_t ra = n[2], wa = 1, rv = j >= 0 ? v.dim[j] : 1, wv = 1;
+  bool have[8] = {false, false, false, false, false, false, false, false};
+  for (int k = 0; k < naxes; ++k) stride[k] = 0;
+  int a = naxes - 1, j = v.rank - 1;
+  int64_t ra = n[a], wa = 1, rv = j >= 0 ? v.dim[j] : 1, wv = 1;
   auto next_axis = [&]() { while (a >= 0 && ra == 1) { --a; if (a >= 0) { ra = n[a]; wa = 1; } } };
   auto next_dim = [&]() { while (j >= 0 && rv == 1) { --j; if (j >= 0) { rv = v.dim[j]; wv = 1; } } };
   next_axis();
@@ -131,6 +139,9 @@ bool AffineOverAxes(const DView &v, const int64_t n[3], int64_t stride[3], int64
     next_dim();
   }
   return a < 0 && j < 0;   // both factorisations consumed: same number of elements
+}
+bool AffineOverAxes(const DView &v, const int64_t n[3], int64_t stride[3], int64_t *off) {
+  return AffineOverAxesN(v, n, 3, stride, off);
 }
 
 // Classify one matmul operand for the tensor-core path. rows x K operand (A: rows = M;
@@ -195,7 +206,15 @@ void LaneRuns(const VmProgram &p, const VmLane &l, std::vector<StreamRun> *runs)
   }
 }
 
-void SpreadStridedReductions(const VmProgram &p, DeviceTables *out) {
+// The same pass re-cuts a full reduction (RED_PART whose partials only its RED_COMB
+// reads; `fused_comb[task]` = that RED_COMB) over all lanes: the scheduler's
+// ceil(n / chunk) partial tiles rarely divide evenly by the lane count (config 2:
+// 256 tiles on 148 lanes, so 108 lanes reduce twice what the other 40 do), and the
+// combine is a serial phase of its own. Re-cut, every lane reduces an equal share
+// of 16-byte words (DEntry::a, b), leaves its total in the program's scratch, and
+// the lane that arrives last folds the lanes' totals in lane order into the
+// RED_COMB's result; the RED_COMB entry becomes a NOP.
+void SpreadReductions(const VmProgram &p, const std::vector<int> &fused_comb, DeviceTables *out) {
   const uint32_t n_lanes = static_cast<uint32_t>(p.lane_tab.size());
   if (n_lanes < 4) return;
   std::vector<std::vector<StreamRun>> runs(n_lanes);
@@ -223,7 +242,8 @@ void SpreadStridedReductions(const VmProgram &p, DeviceTables *out) {
         const VmEntry &en = p.entries[p.lane_tab[l].off + i];
         if (en.task == kEntNop) continue;
         if (en.task >= p.tasks.size()) { ok = false; break; }          // a control entry inside the run
-        if ((p.tasks[en.task].tile_op & 0xFFu) != kTopRedStrided) { ++others; continue; }
+        const uint32_t eop = p.tasks[en.task].tile_op & 0xFFu;
+        if (!(eop == kTopRedStrided || (eop == kTopRedPart && fused_comb[en.task] >= 0))) { ++others; continue; }
         if (task >= 0 && task != static_cast<int64_t>(en.task)) { ok = false; break; }
         task = en.task;
         ++mine;
@@ -234,17 +254,25 @@ void SpreadStridedReductions(const VmProgram &p, DeviceTables *out) {
     if (!ok || task < 0) continue;
     const VmTask &t = p.tasks[task];
     const uint32_t dt = (t.tile_op >> 8) & 0xFFu;
-    const int64_t n_out = t.p0, red = t.p1, inner = t.p2;
-    if (!red_strided_rows_ok(dt, red, inner, t.p3) || n_out % inner != 0) continue;
-    const uint64_t nt = (static_cast<uint64_t>(n_out) + kEwTs - 1) / kEwTs;
-    if (tiles != nt || nt * 2 > n_lanes) continue;
-    const int64_t rows = n_out / inner;
+    const bool full = (t.tile_op & 0xFFu) == kTopRedPart;
+    int64_t rows;   // units split over the lanes: rows of a strided reduction, 16-byte words of a full one
+    if (full) {
+      const uint64_t nt = (static_cast<uint64_t>(t.p0) + t.p1 - 1) / t.p1;
+      if (tiles != nt) continue;
+      rows = t.p0 / 4;
+    } else {
+      const int64_t n_out = t.p0, red = t.p1, inner = t.p2;
+      if (!red_strided_rows_ok(dt, red, inner, t.p3) || n_out % inner != 0) continue;
+      const uint64_t nt = (static_cast<uint64_t>(n_out) + kEwTs - 1) / kEwTs;
+      if (tiles != nt || nt * 2 > n_lanes) continue;
+      rows = n_out / inner;
+    }
     for (uint32_t l = 0; l < n_lanes; ++l) {
       const StreamRun &r = runs[l][k];
       for (uint32_t i = r.start; i < r.end; ++i)
         if (p.entries[p.lane_tab[l].off + i].task == static_cast<uint32_t>(task)) out->entries[p.lane_tab[l].off + i].task = kEntNop;
       const int64_t lo = rows * l / n_lanes, hi = rows * (l + 1) / n_lanes;
-      if (hi <= lo) continue;
+      if (hi <= lo && !full) continue;   // a full reduction counts every lane in, also one with nothing to add
       DEntry e;
       std::memset(&e, 0, sizeof(e));
       e.task = static_cast<uint32_t>(task);
@@ -252,6 +280,16 @@ void SpreadStridedReductions(const VmProgram &p, DeviceTables *out) {
       e.b = static_cast<uint32_t>(hi);
       const bool empty_at_start = r.start == r.end && r.at_range_start;
       ins[l].push_back({r.end, empty_at_start, e});
+    }
+    if (full) {
+      DTask &dp = out->tasks[task];
+      const int comb = fused_comb[task];
+      dp.flags |= kRedFused;
+      dp.ptr[3] = out->tasks[comb].ptr[0];        // where the RED_COMB would have put the result
+      for (DEntry &e : out->entries)
+        if (e.task == static_cast<uint32_t>(comb)) e.task = kEntNop;
+      out->n_fused_reduce++;
+      out->needs_scratch = true;
     }
     out->n_spread++;
   }
@@ -293,6 +331,25 @@ void SpreadStridedReductions(const VmProgram &p, DeviceTables *out) {
 
 }  // namespace
 
+// Branch-free division by d >= 2 for every 32-bit n: q = umulhi(n, magic);
+// (((n - q) >> 1) + q) >> shift.
+void MagicDivider(uint32_t d, uint32_t *magic, uint32_t *shift) {
+  uint32_t sh = 31;
+  while (!(d >> sh)) --sh;                        // floor(log2(d))
+  if ((d & (d - 1)) == 0) {
+    *magic = 0;
+    *shift = sh - 1;
+    return;
+  }
+  const unsigned __int128 two = static_cast<unsigned __int128>(1) << (32 + sh);
+  uint64_t m = static_cast<uint64_t>(two / d);
+  const uint64_t rem = static_cast<uint64_t>(two - static_cast<unsigned __int128>(m) * d);
+  m *= 2;
+  if (rem * 2 >= d) m += 1;
+  *magic = static_cast<uint32_t>(m + 1);
+  *shift = sh;
+}
+
 bool CollapseView(const int32_t *dims, const int32_t *strides, int rank, int64_t off, DView *out) {
   std::vector<int64_t> d, s;
   for (int k = 0; k < rank; ++k) {
@@ -314,22 +371,7 @@ bool CollapseView(const int32_t *dims, const int32_t *strides, int rank, int64_t
     if (d[k] > 0xFFFFFFFFll) return false;
     out->dim[k] = static_cast<uint32_t>(d[k]);
     out->stride[k] = static_cast<int32_t>(s[k]);
-    // branch-free magic-number division by dim[k] (>= 2 here: size-1 axes were dropped)
-    const uint32_t dv = out->dim[k];
-    uint32_t sh = 31;
-    while (!(dv >> sh)) --sh;                       // floor(log2(dv))
-    if ((dv & (dv - 1)) == 0) {
-      out->magic[k] = 0;
-      out->shift[k] = sh - 1;
-    } else {
-      const unsigned __int128 two = static_cast<unsigned __int128>(1) << (32 + sh);
-      uint64_t m = static_cast<uint64_t>(two / dv);
-      const uint64_t rem = static_cast<uint64_t>(two - static_cast<unsigned __int128>(m) * dv);
-      m *= 2;
-      if (rem * 2 >= dv) m += 1;
-      out->magic[k] = static_cast<uint32_t>(m + 1);
-      out->shift[k] = sh;
-    }
+    MagicDivider(out->dim[k], &out->magic[k], &out->shift[k]);   // dim >= 2 here: size-1 axes were dropped
   }
   if (out->rank == 0) {
     out->vec_ok = 1;
@@ -384,6 +426,7 @@ bool BuildDeviceTables(const VmProgram &p, uint64_t arena_base, DeviceTables *ou
     d.op = t.tile_op & 0xFFu;
     d.dt = (t.tile_op >> 8) & 0xFFu;
     d.adt = (t.tile_op >> 16) & 0xFFu;
+    out->families |= family_of(d.op);
     const uint32_t raw[8] = {t.p0, t.p1, t.p2, t.p3, t.p4, t.p5, t.p6, t.p7};
     std::memcpy(d.p, raw, sizeof(raw));
     d.ptr[0] = c.Ref(t.dst);
@@ -527,8 +570,24 @@ bool BuildDeviceTables(const VmProgram &p, uint64_t arena_base, DeviceTables *ou
             m.tc_mode = kTcOk | (amn ? kTcAmn : 0u) | (bmn ? kTcBmn : 0u);
             ++out->n_mma_tc;
             m.tmap = static_cast<int32_t>(out->tmaps.size());
-            out->tmaps.push_back(TmapSpec{d.ptr[1], oa, d.adt, amn, M, K, G, m.a_ld, m.a_gs, 0u});
-            out->tmaps.push_back(TmapSpec{d.ptr[2], ob, d.adt, bmn, N, K, G, m.b_ld, m.b_gs, 0u});
+            // rank-3 maps {inner, outer, batch}: the inner dimension is the unit-stride one (k for a
+            // K-major operand, the row / column index for an MN-major one), boxes of 64 inner elements
+            // (one 128-byte swizzle line) x 128 or 64 outer rows
+            auto mm_spec = [&](BufRef base, int64_t off, bool mn, int64_t rows, int64_t ld, int64_t gs) {
+              TmapSpec sp;
+              std::memset(&sp, 0, sizeof(sp));
+              sp.base = base; sp.off = off; sp.dtype = d.adt; sp.rank = 3;
+              sp.dims[0] = static_cast<uint64_t>(mn ? rows : K);
+              sp.dims[1] = static_cast<uint64_t>(mn ? K : rows);
+              sp.dims[2] = static_cast<uint64_t>(G);
+              sp.strides[0] = ld;
+              sp.strides[1] = G > 1 ? gs : ld * static_cast<int64_t>(sp.dims[1]);
+              sp.box[0] = 64u; sp.box[1] = mn ? 64u : 128u; sp.box[2] = 1u;
+              sp.valid = !(G > 1 && gs <= 0);           // a batch-broadcast operand has no stride to give
+              return sp;
+            };
+            out->tmaps.push_back(mm_spec(d.ptr[1], oa, amn, M, m.a_ld, m.a_gs));
+            out->tmaps.push_back(mm_spec(d.ptr[2], ob, bmn, N, m.b_ld, m.b_gs));
           }
         }
         if (!(m.tc_mode & kTcOk)) m.tmap = -1;
@@ -551,19 +610,171 @@ bool BuildDeviceTables(const VmProgram &p, uint64_t arena_base, DeviceTables *ou
         if (qv) { if (!ViewFromAux(p, qv - 1, &f.vq, err)) return fail_unimpl(*err); f.has_q = 1; }
         if (kv) { if (!ViewFromAux(p, kv - 1, &f.vk, err)) return fail_unimpl(*err); f.has_k = 1; }
         if (vv) { if (!ViewFromAux(p, vv - 1, &f.vv, err)) return fail_unimpl(*err); f.has_v = 1; }
-        // tensor-core eligibility: 16-bit floats, plain operands, head_dim 64, 16-byte friendly rows
-        if ((d.adt == kBF16 || d.adt == kF16) && (d.dt == kBF16 || d.dt == kF16 || d.dt == kF32) && !qv && !kv && !vv &&
-            x[3] == 64 && x[2] % 8 == 0 && x[1] >= 16 && x[2] > 0) {
-          f.tc_mode = 1;
-          ++out->n_flash_tc;
+        float scale_f;
+        std::memcpy(&scale_f, &x[4], 4);
+        const bool scale_positive = scale_f > 0.0f && scale_f < 1e30f;   // the row maximum is taken before scaling
+        // Tensor-core eligibility: 16-bit floats, head_dim 64, and every operand affine over
+        // (h1, h0, row, column) with a unit stride along d (Q, V; K along d or along the keys) and
+        // 16-byte friendly outer strides, so that three rank-4 tensor maps describe them.
+        f.tmap = -1;
+        f.work_slot = kNoWorkSlot;
+        if ((d.adt == kBF16 || d.adt == kF16) && (d.dt == kBF16 || d.dt == kF16 || d.dt == kF32) &&
+            x[3] == 64 && x[0] > 0 && x[1] >= 16 && x[2] > 0 && c.Aligned16(t.dst) && scale_positive) {
+          const int64_t H = x[0], T = x[1], C = x[2];
+          for (int64_t h0 = H; h0 >= 1 && !f.tc_mode; --h0) {
+            if (H % h0) continue;
+            const int64_t nq[4] = {H / h0, h0, T, 64}, nk[4] = {H / h0, h0, 64, C}, nv[4] = {H / h0, h0, C, 64};
+            int64_t sq[4] = {h0 * T * 64, T * 64, 64, 1}, sk[4] = {h0 * 64 * C, 64 * C, C, 1}, sv[4] = {h0 * C * 64, C * 64, 64, 1};
+            int64_t oq = 0, ok_ = 0, ov = 0;
+            bool ok = true;
+            if (qv) ok = ok && AffineOverAxesN(f.vq, nq, 4, sq, &oq);
+            if (kv) ok = ok && AffineOverAxesN(f.vk, nk, 4, sk, &ok_);
+            if (vv) ok = ok && AffineOverAxesN(f.vv, nv, 4, sv, &ov);
+            if (H / h0 == 1) sq[0] = sk[0] = sv[0] = 8;   // a size-1 axis: any legal stride
+            if (h0 == 1) sq[1] = sk[1] = sv[1] = 8;
+            const bool k_dmajor = sk[2] == 1 && sk[3] != 1;          // d contiguous, keys strided
+            auto good = [](int64_t st) { return st > 0 && st % 8 == 0; };
+            ok = ok && sq[3] == 1 && sv[3] == 1 && (k_dmajor || sk[3] == 1) && oq >= 0 && ok_ >= 0 && ov >= 0 &&
+                 oq % 8 == 0 && ok_ % 8 == 0 && ov % 8 == 0 && good(sq[0]) && good(sq[1]) && good(sq[2]) &&
+                 good(sk[0]) && good(sk[1]) && good(k_dmajor ? sk[3] : sk[2]) && good(sv[0]) && good(sv[1]) && good(sv[2]);
+            if (!ok) continue;
+            auto fa_spec = [&](BufRef base, int64_t off, uint64_t inner, uint64_t rows, int64_t s_row, int64_t s_h0, int64_t s_h1,
+                               uint32_t box_rows) {
+              TmapSpec sp;
+              std::memset(&sp, 0, sizeof(sp));
+              sp.base = base; sp.off = off; sp.dtype = d.adt; sp.rank = 4;
+              sp.dims[0] = inner; sp.dims[1] = rows; sp.dims[2] = static_cast<uint64_t>(h0); sp.dims[3] = static_cast<uint64_t>(H / h0);
+              sp.strides[0] = s_row; sp.strides[1] = s_h0; sp.strides[2] = s_h1;
+              sp.box[0] = 64u; sp.box[1] = box_rows; sp.box[2] = 1u; sp.box[3] = 1u;
+              sp.owner_is_flash = 1u;
+              sp.valid = true;
+              return sp;
+            };
+            f.tc_mode = 1;
+            f.h0_size = static_cast<uint32_t>(h0);
+            f.k_mn = k_dmajor ? 0u : 1u;
+            f.tmap = static_cast<int32_t>(out->tmaps.size());
+            out->tmaps.push_back(fa_spec(d.ptr[1], oq, 64, static_cast<uint64_t>(T), sq[2], sq[1], sq[0], 128u));
+            if (k_dmajor) out->tmaps.push_back(fa_spec(d.ptr[2], ok_, 64, static_cast<uint64_t>(C), sk[3], sk[1], sk[0], 128u));
+            else out->tmaps.push_back(fa_spec(d.ptr[2], ok_, static_cast<uint64_t>(C), 64, sk[2], sk[1], sk[0], 64u));
+            out->tmaps.push_back(fa_spec(d.ptr[3], ov, 64, static_cast<uint64_t>(C), sv[2], sv[1], sv[0], 128u));
+            ++out->n_flash_tc;
+          }
         }
         ++out->n_flash;
         d.desc = c.PushDesc(f);
+        if (f.tmap >= 0)
+          for (int k = 0; k < 3; ++k) out->tmaps[f.tmap + k].desc_word = d.desc;
         break;
       }
       case kTopRedPart: case kTopRedComb: case kTopRedSeg: case kTopRedStrided:
       case kTopSoftmaxSeg: case kTopLayernormSeg:
         break;
+      case kTopRedWindow: {
+        const size_t x = t.p0;
+        if (x + 2 > p.aux.size()) { *err = "reduce-window descriptor out of the aux pool"; return false; }
+        const int32_t kind = p.aux[x], rank = p.aux[x + 1];
+        if (rank < 0 || x + 2 + 6 * static_cast<size_t>(rank) > p.aux.size()) { *err = "reduce-window descriptor out of the aux pool"; return false; }
+        if (rank > kWinDims) return fail_unimpl("reduce_window of rank > " + std::to_string(kWinDims));
+        if (kind < 0 || kind > 2) return fail_unimpl("reduce_window kind " + std::to_string(kind));
+        if (!(d.dt == kF32 || d.dt == kI32 || d.dt == kU32)) return fail_unimpl("reduce_window on dtype " + std::to_string(d.dt));
+        DWindow w;
+        std::memset(&w, 0, sizeof(w));
+        w.kind = static_cast<uint32_t>(kind);
+        w.rank = static_cast<uint32_t>(rank);
+        uint64_t wcount = 1, n_in = 1;
+        const int32_t *od = &p.aux[x + 2], *wd = od + rank, *ws = wd + rank, *pl = ws + rank, *id = pl + rank, *is = id + rank;
+        for (int32_t k = 0; k < rank; ++k) {
+          if (od[k] <= 0 || wd[k] <= 0 || ws[k] <= 0 || id[k] <= 0 || pl[k] < 0 || is[k] < 0) { *err = "reduce-window descriptor has a non-positive extent"; return false; }
+          w.odim[k] = od[k]; w.wdim[k] = wd[k]; w.wstr[k] = ws[k]; w.idim[k] = id[k]; w.plow[k] = pl[k]; w.istr[k] = is[k];
+          if (od[k] >= 2) MagicDivider(w.odim[k], &w.omagic[k], &w.oshift[k]);
+          wcount *= static_cast<uint32_t>(wd[k]);
+          n_in = std::max<uint64_t>(n_in, static_cast<uint64_t>(id[k]) * static_cast<uint64_t>(is[k]));
+        }
+        if (wcount > 0xFFFFFFFFull) return fail_unimpl("reduce_window with more than 2^32 taps");
+        if (n_in * 4 > p.buffers[t.a].bytes) { *err = "reduce-window input dims exceed the operand buffer"; return false; }
+        w.wcount = static_cast<uint32_t>(wcount);
+        if (rank >= 1) {
+          const int32_t l = rank - 1;
+          bool v = wd[l] == 1 && ws[l] == 1 && pl[l] == 0 && od[l] == id[l] && is[l] == 1 && od[l] % 4 == 0 &&
+                   c.Aligned16(t.dst) && c.Aligned16(t.a);
+          for (int32_t k = 0; v && k < l; ++k) v = is[k] % 4 == 0;
+          w.vec4 = v ? 1u : 0u;
+        }
+        d.desc = c.PushDesc(w);
+        break;
+      }
+      case kTopGatherIndex: case kTopScatterIndex: {
+        const bool scat = d.op == kTopScatterIndex;
+        const size_t x = t.p0, head = scat ? 7 : 6;
+        if (x + head > p.aux.size()) { *err = "indexed-move descriptor out of the aux pool"; return false; }
+        const int32_t rank = p.aux[x], nidx = p.aux[x + 1];
+        if (rank < 0 || nidx < 0 || x + head + 3 * static_cast<size_t>(rank) + 2 * static_cast<size_t>(nidx) > p.aux.size()) {
+          *err = "indexed-move descriptor out of the aux pool";
+          return false;
+        }
+        if (rank > kIdxDims || nidx > kIdxDims) return fail_unimpl("indexed gather / scatter of rank > " + std::to_string(kIdxDims));
+        const uint32_t idx_id = static_cast<uint32_t>(p.aux[x + 5]);
+        if (idx_id >= p.buffers.size()) { *err = "start-indices buffer id out of range"; return false; }
+        DIndexed g;
+        std::memset(&g, 0, sizeof(g));
+        g.rank = static_cast<uint32_t>(rank);
+        g.nidx = static_cast<uint32_t>(nidx);
+        g.vec_stride = p.aux[x + 2];
+        g.is64 = p.aux[x + 3] ? 1u : 0u;
+        g.kind = scat ? static_cast<uint32_t>(p.aux[x + 6]) : 0u;
+        g.esz = static_cast<uint32_t>(DtypeSize(d.dt));
+        g.idx = c.Ref(idx_id);
+        if (g.kind > 3u) return fail_unimpl("scatter combiner " + std::to_string(g.kind));
+        if (g.kind != 0u && !(d.dt == kF32 || d.dt == kI32 || d.dt == kU32))
+          return fail_unimpl("scatter add / max / min on dtype " + std::to_string(d.dt));
+        if (DtypeSize(p.buffers[idx_id].dtype) != (g.is64 ? 8u : 4u)) { *err = "start-indices buffer width disagrees with the descriptor"; return false; }
+        const int32_t *dims = &p.aux[x + head], *ops = dims + rank, *sis = ops + rank, *ios = sis + rank, *cmax = ios + nidx;
+        for (int32_t k = 0; k < rank; ++k) {
+          if (dims[k] <= 0) { *err = "indexed-move descriptor has a non-positive extent"; return false; }
+          g.dim[k] = dims[k]; g.op_stride[k] = ops[k]; g.si_stride[k] = sis[k];
+          if (dims[k] >= 2) MagicDivider(g.dim[k], &g.magic[k], &g.shift[k]);
+        }
+        for (int32_t k = 0; k < nidx; ++k) { g.idx_op_stride[k] = ios[k]; g.clamp_max[k] = cmax[k]; }
+        // 16-byte words along the innermost dim: it walks the operand with stride 1, selects no
+        // new index, and every run starts on a word boundary of the linear side
+        if (rank >= 1 && g.esz <= 8) {
+          const uint32_t chunk = 16u / g.esz;
+          if (ops[rank - 1] == 1 && sis[rank - 1] == 0 && static_cast<uint32_t>(dims[rank - 1]) % chunk == 0) g.chunk = chunk;
+        }
+        d.desc = c.PushDesc(g);
+        break;
+      }
+      case kTopConv: {
+        const size_t x = t.p0;
+        if (x + 3 > p.aux.size()) { *err = "convolution descriptor out of the aux pool"; return false; }
+        const int32_t sdim = p.aux[x];
+        if (sdim < 1 || sdim > 4) return fail_unimpl("convolution with " + std::to_string(sdim) + " spatial dims");
+        if (x + 3 + 6 * static_cast<size_t>(sdim) > p.aux.size()) { *err = "convolution descriptor out of the aux pool"; return false; }
+        if (d.dt != kF32) return fail_unimpl("convolution on dtype " + std::to_string(d.dt));
+        DConv k;
+        std::memset(&k, 0, sizeof(k));
+        k.sdim = static_cast<uint32_t>(sdim);
+        k.cin = static_cast<uint32_t>(p.aux[x + 1]);
+        k.cout = static_cast<uint32_t>(p.aux[x + 2]);
+        const int32_t *osp = &p.aux[x + 3], *win = osp + sdim, *st = win + sdim, *pl = st + sdim, *dil = pl + sdim, *isp = dil + sdim;
+        if (p.aux[x + 1] <= 0 || p.aux[x + 2] <= 0) { *err = "convolution descriptor has a non-positive extent"; return false; }
+        uint64_t wcount = 1;
+        int64_t acc = k.cin;
+        for (int32_t q = sdim - 1; q >= 0; --q) {
+          if (osp[q] <= 0 || win[q] <= 0 || st[q] <= 0 || dil[q] <= 0 || isp[q] <= 0 || pl[q] < 0) { *err = "convolution descriptor has a non-positive extent"; return false; }
+          k.osp[q] = osp[q]; k.win[q] = win[q]; k.str[q] = st[q]; k.dil[q] = dil[q]; k.isp[q] = isp[q]; k.plow[q] = pl[q];
+          k.istr[q] = acc;
+          acc *= isp[q];
+          wcount *= static_cast<uint32_t>(win[q]);
+        }
+        k.ibatch = acc;
+        if (wcount > 0xFFFFFFFFull) return fail_unimpl("convolution with more than 2^32 taps");
+        k.wcount = static_cast<uint32_t>(wcount);
+        if (wcount * k.cin * k.cout * 4 > p.buffers[t.b].bytes) { *err = "convolution weights exceed their buffer"; return false; }
+        d.desc = c.PushDesc(k);
+        break;
+      }
       default:
         return fail_unimpl("tile op " + std::to_string(d.op) + " is not implemented by this backend");
     }
@@ -684,7 +895,75 @@ bool BuildDeviceTables(const VmProgram &p, uint64_t arena_base, DeviceTables *ou
     }
   }
   out->lanes = p.lane_tab;
-  SpreadStridedReductions(p, out);
+  // Full reductions the lanes can share evenly: 4-byte elements, enough of them, and
+  // partials that nothing but the combine reads.
+  std::vector<int> fused_comb(p.tasks.size(), -1);
+  for (size_t ti = 0; ti < p.tasks.size(); ++ti) {
+    const VmTask &tp = p.tasks[ti];
+    if ((tp.tile_op & 0xFFu) != kTopRedPart || tp.p1 == 0 || tp.p0 < 65536) continue;
+    const uint32_t dt = (tp.tile_op >> 8) & 0xFFu;
+    if (!(dt == kF32 || dt == kI32 || dt == kU32) || tp.p2 > kRXor) continue;
+    const auto &rs = readers[tp.dst];
+    if (rs.size() != 1 || pinned.count(tp.dst) || in_ids.count(tp.dst) || const_ids.count(tp.dst)) continue;
+    const uint32_t ci = *rs.begin();
+    const VmTask &tc = p.tasks[ci];
+    const uint64_t nt = (static_cast<uint64_t>(tp.p0) + tp.p1 - 1) / tp.p1;
+    if ((tc.tile_op & 0xFFu) != kTopRedComb || tc.a != tp.dst || tc.p1 != tp.p2 || tc.p0 != nt ||
+        ((tc.tile_op >> 8) & 0xFFu) != dt || tc.dst == tp.dst || tc.dst == tp.a)
+      continue;
+    uint32_t writers = 0;
+    for (const VmTask &o : p.tasks) writers += o.dst == tp.dst ? 1u : 0u;
+    if (writers != 1) continue;
+    // The result is now written one phase earlier than the schedule says. Arena slots are
+    // shared between buffers whose live ranges are phase-disjoint (lowering.py:2824-2853), so
+    // the result buffer may share bytes with something still being read in the RED_PART's
+    // phase: only a result with bytes of its own (an I/O port, or an unshared slot) qualifies.
+    if (!c.port_of.count(tc.dst)) {
+      const BufferSlot &rb = p.buffers[tc.dst];
+      bool shared = false;
+      for (size_t j = 0; j < p.buffers.size() && !shared; ++j) {
+        const BufferSlot &ob = p.buffers[j];
+        if (j == tc.dst || !ob.bytes || c.port_of.count(static_cast<uint32_t>(j))) continue;
+        shared = ob.offset < rb.offset + rb.bytes && rb.offset < ob.offset + ob.bytes;
+      }
+      if (shared) continue;
+    }
+    fused_comb[ti] = static_cast<int>(ci);
+  }
+  SpreadReductions(p, fused_comb, out);
+  // Dynamic work distribution for tensor-core attention tasks: allowed when the task's
+  // entries cover all its query rows, no lane holds more than one of them, and they
+  // sit outside the sub-ranges of WHILE / IF entries (where lanes may not all arrive).
+  {
+    uint32_t slots = 0;
+    for (size_t ti = 0; ti < p.tasks.size() && slots < kMaxWorkSlots; ++ti) {
+      DTask &d = out->tasks[ti];
+      if (d.op != kTopFlashAttn || !d.desc) continue;
+      DFlash *f = reinterpret_cast<DFlash *>(&out->desc[d.desc]);
+      if (!f->tc_mode) continue;
+      const int32_t *x = &p.aux[p.tasks[ti].p3];
+      const uint64_t rows = static_cast<uint64_t>(x[0]) * static_cast<uint64_t>(x[1]);
+      uint64_t covered = 0;
+      uint32_t owners = 0;
+      bool ok = true;
+      for (const VmLane &l : out->lanes) {
+        uint32_t mine = 0;
+        for (uint32_t e = 0; e < l.count; ++e) {
+          const DEntry &en = out->entries[l.off + e];
+          if (en.task != ti) continue;
+          ++mine;
+          if (e >= l.root_len) ok = false;          // inside a control range: keep the static split
+          covered += std::min<uint64_t>(en.tile_hi, rows) - std::min<uint64_t>(en.tile_lo, rows);
+        }
+        if (mine > 1) ok = false;
+        owners += mine ? 1u : 0u;
+      }
+      if (!ok || covered != rows || owners == 0) continue;
+      f->work_slot = slots++;
+      f->n_owner_lanes = owners;
+      out->needs_scratch = true;
+    }
+  }
   return true;
 }
 

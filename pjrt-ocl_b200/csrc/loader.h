@@ -16,17 +16,21 @@
 
 namespace b2 {
 
-// What the runtime needs to encode the tensor map of one tensor-core matmul operand:
-// a [batch, rows, k] tensor of 16-bit elements, unit stride along k ("K-major") or
-// along rows ("MN-major").
+// What the runtime needs to encode one TMA tensor map over 16-bit elements: a tensor of
+// rank 3 or 4 whose innermost dimension has unit stride, read in boxes with the 128-byte
+// swizzle. Matmul operands: {inner = k or rows, outer, batch}; flash-attention operands:
+// {inner, rows, h0, h1}.
 struct TmapSpec {
   BufRef base;            // operand buffer (absolute address, or an I/O port)
   int64_t off;            // elements
   uint32_t dtype;         // kBF16 / kF16
-  bool mn_major;
-  int64_t rows, k, batch;
-  int64_t ld, gs;         // elements
-  uint32_t desc_word;     // where the owning DMma sits in the descriptor pool (to clear DMma::tmap on failure)
+  uint32_t rank;          // 3 or 4
+  uint64_t dims[4];       // innermost first
+  int64_t strides[3];     // elements, of dims[1..]; must be positive multiples of 8
+  uint32_t box[4];
+  uint32_t desc_word;     // where the owning DMma / DFlash sits in the descriptor pool (to clear its tmap on failure)
+  uint32_t owner_is_flash;
+  bool valid;             // false: known at load to be indescribable (e.g. a batch-broadcast operand)
 };
 
 struct DeviceTables {
@@ -47,7 +51,10 @@ struct DeviceTables {
   uint32_t n_mma_tc = 0;                // ... of which the tensor-core path takes
   uint64_t mma_flops = 0;               // sum over matmul tasks of 2 G M N K
   uint32_t n_flash = 0, n_flash_tc = 0; // flash-attention tasks / ... on the tensor-core path
-  uint32_t n_spread = 0;                // strided-reduction phases spread over all lanes
+  uint32_t n_spread = 0;                // reduction phases re-cut over all lanes
+  uint32_t n_fused_reduce = 0;          // ... of which full reductions (RED_PART + RED_COMB in one phase)
+  bool needs_scratch = false;           // a re-cut full reduction leaves lane totals in the program's scratch
+  uint32_t families = kFamEw;           // tile-op families the program's tasks use (picks the megakernel build)
 };
 
 // `arena_base` is the device address of the arena (only its value is used).

@@ -254,7 +254,7 @@ constexpr int kEwU = 4;  // groups in flight per thread
 
 // One pass of a chain of k ops over elements [lo, hi); lo % 4 == 0, all pointers
 // 16-byte aligned, every dtype 1/2/4 bytes wide.
-__device__ __noinline__ void ew_chain_run(const Lane &L, const EwOp *ops, uint32_t k, uint32_t lo, uint32_t hi) {
+static __device__ __noinline__ void ew_chain_run(const Lane &L, const EwOp *ops, uint32_t k, uint32_t lo, uint32_t hi) {
   const uint32_t ngroups = (hi - lo + 3u) >> 2;
   for (uint32_t g0 = L.tid; g0 < ngroups; g0 += L.nthr * kEwU) {
     uint32_t X[kEwU][4], Y[kEwU][4];
@@ -577,7 +577,7 @@ __device__ __forceinline__ double ld_f64any(const uint8_t *p, uint32_t dt, int64
   return static_cast<double>(ld_i64any(p, dt, i));
 }
 
-__device__ __noinline__ void ew_scalar_run(const Lane &L, const EwOp &o, uint32_t lo, uint32_t hi) {
+static __device__ __noinline__ void ew_scalar_run(const Lane &L, const EwOp &o, uint32_t lo, uint32_t hi) {
   const uint32_t sub = o.sub, dt = o.dt, adt = o.adt;
   const bool wide = dt == kI64 || dt == kF64 || adt == kI64 || adt == kF64;
   for (uint32_t i = lo + L.tid; i < hi; i += L.nthr) {

@@ -283,7 +283,7 @@ __device__ __forceinline__ void ew_stage_rows(const Lane &L, const EwFlat *fl) {
 // multiple of nthr * kEwU), so no access is predicated. TIER: which step bodies are
 // compiled in (ew_tier_has).
 template <bool FULL, int TIER>
-__device__ __noinline__ void ew_steps_run(uint32_t tid, uint32_t nthr, uint32_t lo, uint32_t gb, uint32_t ge) {
+static __device__ __noinline__ void ew_steps_run(uint32_t tid, uint32_t nthr, uint32_t lo, uint32_t gb, uint32_t ge) {
   B2_DYN_SMEM(sm);
   const EwFlat &fl = *reinterpret_cast<const EwFlat *>(sm + kSmemEwFlat);
   const uint32_t nsteps = fl.n;

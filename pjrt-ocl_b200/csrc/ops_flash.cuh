@@ -22,7 +22,7 @@ namespace b2 {
 
 constexpr int kFlashMaxHd = 256;
 
-__device__ __noinline__ void flash_simt_tiles(const Lane &L, const DTask &t, uint32_t tile_lo, uint32_t tile_hi) {
+static __device__ __noinline__ void flash_simt_tiles(const Lane &L, const DTask &t, uint32_t tile_lo, uint32_t tile_hi) {
   const KParams &P = *L.P;
   const int32_t *x = P.aux + t.p[3];
   const int64_t H = x[0], T = x[1], C = x[2], hd = x[3];

@@ -4,24 +4,30 @@
 // Same contract as the CUDA-core path (ops_flash.cuh; pjrt_plugin/kernels/ops/
 // attention.cl:49-159; python/pjrt_ocl/ops/attention.py:52-66): tile = one query row
 // (head g, position m) of out[H,T,hd]; Q [H,T,hd], K given as the QK^T matmul's B
-// operand [H,hd,C], V [H,C,hd]; with `causal` key c is masked when c > m + C - T.
-// Taken for bf16 / f16 operands without views and head_dim 64 (DFlash::tc_mode).
+// operand [H,hd,C], V [H,C,hd], each possibly through a view; with `causal` key c is
+// masked when c > m + C - T. Taken for bf16 / f16 operands with head_dim 64 whose
+// (viewed) layouts three rank-4 TMA tensor maps can describe (DFlash::tc_mode; the
+// loader decides), so a [batch, seq, heads, hd] projection is attended in place.
 //
-// A lane's range of query rows is covered by 128-row blocks aligned inside a head
-// (rows outside the lane's range are computed and dropped: a block that straddles
-// two lanes' ranges is computed by both). Per block, over 128-key blocks:
-//   warps 0-3   producers: Q once, then K^T / V blocks through a 3-stage ring,
-//               16-byte asynchronous copies into the swizzled operand layouts;
-//   warp 4      lane 0 issues S(j) = Q K(j)^T  (M 128, N 128, K 64) into one of two
-//               S buffers, and O(j) = P(j) V(j) (M 128, N 64, K 128) into one of two O
-//               buffers, S(j+1) being issued ahead of O(j);
-//   warps 8-15  softmax: two threads per query row (row = tensor-memory lane, the pair
-//               splits the 128 key columns and the 64 output columns): read S(j), mask,
-//               exchange the half-row maxima through shared memory, write P(j) as
-//               16-bit values into shared memory for the second matmul, then fold
-//               O(j-1) into the register accumulator with the rescale factor; finally
-//               out = acc / (sum of the two half-row sums).
-// Scores are handled in the log2 domain (one ex2 per score). Every wait is bounded.
+// Work unit: 256 consecutive query rows of one head = two 128-row tiles ("slots" A and
+// B) that share one stream of 128-key K / V blocks. Units are handed out heaviest first
+// from a counter in the program's scratch when the loader allowed it (causal units
+// differ 10 x in cost), else a lane takes the units that start inside its row range.
+// Per unit, over the key blocks j:
+//   warp 0   one thread drives TMA: Q tiles once, then K(j) / V(j) through a 3-stage ring
+//            (operands land in the 128-byte-swizzled layouts the tensor core reads);
+//   warp 1   one thread issues the MMAs: S_s(j) = Q_s K(j)^T (128 x 128 x 64) into the
+//            slot's score columns, O_s (+)= P_s(j) V(j) (128 x 64 x 128) into the slot's
+//            output columns, ordered PV_A(j), S_A(j+1), PV_B(j), S_B(j+1) so one slot's
+//            matmuls run under the other slot's softmax;
+//   warps 4-7 / 8-11   softmax of slot A / B, one thread per query row: pass 1 reads the
+//            row's 128 scores from tensor memory for the maximum, pass 2 reads them again,
+//            exponentiates (log2 domain, one ex2 each), and writes P as 16-bit values into
+//            shared memory for the second matmul. O stays in tensor memory for the whole
+//            unit; it is rescaled in place (tcgen05.ld / st) only when a row's maximum grew
+//            by more than 2^8 since the maximum in use was set - P then stays below 256 and
+//            the result is mathematically unchanged. Finally out = O / (row sum).
+// Every wait is bounded; a wait that runs out ends the task with a status.
 #ifndef B2VM_OPS_FLASH_TC_CUH_
 #define B2VM_OPS_FLASH_TC_CUH_
 
@@ -33,66 +39,61 @@ namespace b2 {
 #if B2_HAS_TC
 
 constexpr int kFaStages = 3;
-constexpr int kFaQBytes = 128 * 128;          // Q block: 128 rows x 64 d
-constexpr int kFaKvBytes = 2 * 128 * 128;     // K^T block (64 d x 128 keys) + V block (128 keys x 64 d)
-constexpr int kFaPBytes = 2 * 128 * 128;      // P block: 128 rows x 128 keys = two 64-key sub-tiles
-constexpr uint32_t kFaCols = 512;             // S0 S1 at columns 0 / 128, O0 O1 at 256 / 320
+constexpr uint32_t kFaTile = 128 * 128;        // bytes of a Q tile, a K block or a V block (128 x 64 x 2)
+constexpr uint32_t kFaPBytes = 2 * 128 * 128;  // P of one slot: 128 rows x 128 keys = two 64-key sub-tiles
+constexpr uint32_t kFaCols = 512;              // S_A 0, S_B 128, O_A 256, O_B 320
+constexpr float kFaRescale = 8.0f;             // log2 of the growth of a row maximum that forces a rescale
 
 struct FaShared {
   uint64_t q_full;
   uint64_t kv_full[kFaStages];
   uint64_t kv_empty[kFaStages];
-  uint64_t s_full[2];
-  uint64_t p_full[2];
-  uint64_t o_full[2];
-  uint64_t mx_full[2];      // both halves of every row have published their block maximum
-  uint64_t l_full;          // ... their final row sums
+  uint64_t s_full[2];       // MMA -> softmax: the slot's scores are in tensor memory
+  uint64_t s_free[2];       // softmax -> MMA: the scores have been read (4 warp arrivals)
+  uint64_t p_full[2];       // softmax -> MMA: P is in shared memory, O is rescaled (4 warp arrivals)
+  uint64_t pv_done[2];      // MMA -> softmax: O_s holds block j, P's buffer is free
   uint32_t tmem_base;
   uint32_t failed;
+  uint32_t unit;            // the unit all roles work on next, or 0xffffffff
+  uint32_t pad;
 };
 static_assert(sizeof(FaShared) <= 512, "fits the scratch slot");
 
-__device__ __noinline__ bool flash_tc_tiles(const Lane &L, const DTask &t, uint32_t tile_lo, uint32_t tile_hi) {
+static __device__ __noinline__ bool flash_tc_tiles(const Lane &L, const DTask &t, uint32_t tile_lo, uint32_t tile_hi) {
   const KParams &P = *L.P;
+  const DFlash &df = *reinterpret_cast<const DFlash *>(P.desc + t.desc);
   const int32_t *x = P.aux + t.p[3];
   const int64_t H = x[0], T = x[1], C = x[2];
   constexpr int64_t hd = 64;
   const float sl2 = __int_as_float(x[4]) * 1.4426950408889634f;   // scores in the log2 domain
   const bool causal = x[5] != 0;
   uint8_t *out = resolve(P, t.ptr[0]);
-  const uint8_t *Qb = resolve(P, t.ptr[1]);
-  const uint8_t *Kb = resolve(P, t.ptr[2]);
-  const uint8_t *Vb = resolve(P, t.ptr[3]);
-  if ((reinterpret_cast<uintptr_t>(Qb) | reinterpret_cast<uintptr_t>(Kb) | reinterpret_cast<uintptr_t>(Vb) |
-       reinterpret_cast<uintptr_t>(out)) & 15u)
-    return false;
-  const uint16_t *Q = reinterpret_cast<const uint16_t *>(Qb);
-  const uint16_t *KT = reinterpret_cast<const uint16_t *>(Kb);
-  const uint16_t *V = reinterpret_cast<const uint16_t *>(Vb);
+  if (df.tmap < 0 || (reinterpret_cast<uintptr_t>(out) & 15u)) return false;
+  const DTmap *tm_q = P.tmaps + df.tmap, *tm_k = tm_q + 1, *tm_v = tm_q + 2;
   const uint32_t adt = t.adt, dt = t.dt;
   const int64_t rows_end = min(static_cast<int64_t>(tile_hi), H * T);
-  if (static_cast<int64_t>(tile_lo) >= rows_end) return true;
+  if (static_cast<int64_t>(tile_lo) >= rows_end && df.work_slot == kNoWorkSlot) return true;
 
   B2_DYN_SMEM(sm);
   FaShared *S = reinterpret_cast<FaShared *>(sm + kSmemRed);
   volatile uint32_t *failed = &S->failed;
   const uint32_t base0 = (smem_addr(sm + kSmemSys) + 1023u) & ~1023u;
-  const uint32_t q_s = base0, kv_s = q_s + kFaQBytes, p_s = kv_s + kFaStages * kFaKvBytes;
+  const uint32_t q_s = base0, kv_s = q_s + 2u * kFaTile, p_s = kv_s + kFaStages * 2u * kFaTile;
   const uint32_t w = L.tid / kWarp, lane = L.tid % kWarp;
   const unsigned long long budget = P.wait_budget_ns;
+  const bool k_mn = df.k_mn != 0;
 
   __syncthreads();   // the scratch slot and the workspace are free
   if (L.tid == 0) {
-    mbar_init(&S->q_full, 128);
-    for (int s = 0; s < kFaStages; ++s) { mbar_init(&S->kv_full[s], 128); mbar_init(&S->kv_empty[s], 1); }
+    mbar_init(&S->q_full, 1);
+    for (int s = 0; s < kFaStages; ++s) { mbar_init(&S->kv_full[s], 1); mbar_init(&S->kv_empty[s], 1); }
     for (int b = 0; b < 2; ++b) {
-      mbar_init(&S->s_full[b], 1); mbar_init(&S->p_full[b], 256); mbar_init(&S->o_full[b], 1); mbar_init(&S->mx_full[b], 256);
+      mbar_init(&S->s_full[b], 1); mbar_init(&S->s_free[b], 4); mbar_init(&S->p_full[b], 4); mbar_init(&S->pv_done[b], 1);
     }
-    mbar_init(&S->l_full, 256);
     S->failed = 0u;
     fence_mbar_init();
   }
-  if (w == 4) {
+  if (w == 1) {
     __syncwarp();
     tmem_alloc(&S->tmem_base, kFaCols);
   }
@@ -101,243 +102,299 @@ __device__ __noinline__ bool flash_tc_tiles(const Lane &L, const DTask &t, uint3
   tc_fence_after_sync();
   const uint32_t tmem = S->tmem_base;
 
-  // blocks of 128 query rows, aligned inside a head, that intersect [tile_lo, rows_end)
-  const int64_t nblk = (T + 127) / 128;
-  const int64_t first = static_cast<int64_t>(tile_lo), last = rows_end - 1;
-  const int64_t b_lo = (first / T) * nblk + (first % T) / 128, b_hi = (last / T) * nblk + (last % T) / 128;
-  uint32_t kvit = 0, jt = 0, qn = 0;     // ring positions, carried across blocks by every role
+  // ---- units: 256-row blocks aligned inside a head ----
+  const int64_t upm = (T + 255) / 256;                 // units per head
+  const int64_t n_units = H * upm;
+  const bool dynamic = df.work_slot != kNoWorkSlot;
+  uint32_t *work = dynamic ? reinterpret_cast<RedScratch *>(P.scratch)->work + 2u * df.work_slot : nullptr;
+  // static mode: the units whose first row lies in [tile_lo, rows_end)
+  int64_t u_next = 0, u_stop = 0;
+  if (!dynamic) {
+    const int64_t first = static_cast<int64_t>(tile_lo);
+    auto unit_at_or_after = [&](int64_t row) {       // index of the first unit starting at a row >= `row`
+      const int64_t g = row / T, m = row % T;
+      return g * upm + (m + 255) / 256;
+    };
+    u_next = unit_at_or_after(first);
+    u_stop = unit_at_or_after(rows_end);
+  }
+  // ring / phase positions, carried across units by every role that uses them
+  uint32_t kvpos = 0, qn = 0, cnt[2] = {0u, 0u};
 
-  for (int64_t blk = b_lo; blk <= b_hi; ++blk) {
-    const int64_t g = blk / nblk, m0 = (blk % nblk) * 128;
-    const int64_t rows_q = min(static_cast<int64_t>(128), T - m0);
-    // keys any row of the block may see
-    const int64_t c_max = causal ? min(C, m0 + rows_q - 1 + (C - T) + 1) : C;
-    const int64_t nkb = (c_max + 127) / 128;
+  for (;;) {
+    // ---- next unit (one thread decides, everybody reads it after the barrier) ----
+    if (L.tid == 0) {
+      uint32_t u = 0xffffffffu;
+      if (dynamic) {
+        const uint32_t tk = atomicAdd(&work[0], 1u);
+        if (static_cast<int64_t>(tk) < n_units) {
+          // heaviest first: with a causal mask the last 256 rows of a head see the most keys
+          const int64_t lvl = tk / H, g = tk % H;
+          u = static_cast<uint32_t>(g * upm + (causal ? upm - 1 - lvl : lvl));
+        }
+      } else if (u_next < u_stop) {
+        u = static_cast<uint32_t>(u_next++);
+      }
+      S->unit = u;
+    }
+    tc_fence_before_sync();
+    __syncthreads();       // also: every role is done with the previous unit (Q, P, the rings, tensor memory)
+    tc_fence_after_sync();
+    const uint32_t unit = S->unit;
+    if (unit == 0xffffffffu || S->failed) break;
+    const int64_t g = unit / upm, m0 = (unit % upm) * 256;
+    const int32_t h0c = static_cast<int32_t>(g % df.h0_size), h1c = static_cast<int32_t>(g / df.h0_size);
+    // key blocks each slot needs
+    int64_t nkb[2];
+#pragma unroll
+    for (int s = 0; s < 2; ++s) {
+      const int64_t ms = m0 + 128 * s, rows_q = min(static_cast<int64_t>(128), T - ms);
+      const int64_t c_max = rows_q <= 0 ? 0 : (causal ? min(C, ms + rows_q + (C - T)) : C);
+      nkb[s] = c_max <= 0 ? 0 : (c_max + 127) / 128;
+    }
+    const int64_t nmax = max(nkb[0], nkb[1]);
 
-    if (w < 4) {
-      // ---------------- producers (128 threads) ----------------
-      const uint32_t ptid = L.tid;
-      {   // Q block, K-major: row (query) at 128 B pitch, chunks XORed with row % 8
-        const uint32_t c = ptid & 7u, r = ptid >> 3;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const int64_t row = r + 16 * i;
-          const bool okr = row < rows_q;
-          cp_async_16_zfill(q_s + static_cast<uint32_t>(row) * 128u + ((c ^ (static_cast<uint32_t>(row) & 7u)) << 4),
-                            okr ? Q + ((g * T + m0 + row) * hd + 8 * c) : Q, okr ? 16u : 0u);
-        }
-        cp_async_mbar_arrive(&S->q_full);
-      }
-      for (int64_t j = 0; j < nkb; ++j) {
-        const uint32_t kvpos = kvit + static_cast<uint32_t>(j), s = kvpos % kFaStages;
-        if (!tc_wait_warp(&S->kv_empty[s], ((kvpos / kFaStages) & 1u) ^ 1u, failed, budget, 64u)) break;
-        const uint32_t ks = kv_s + s * kFaKvBytes, vs = ks + 128 * 128;
-        const int64_t n0 = j * 128;
-        {   // K^T block: element (d, key) at KT[(g*hd + d)*C + key]: keys are the unit-stride ("MN") dimension
-          const uint32_t cm = ptid & 15u, dr = ptid >> 4;            // 16 key chunks x 8 d lines per pass
-          const int64_t key = n0 + 8 * cm;
-          const uint32_t kbytes = key < C ? static_cast<uint32_t>(min(static_cast<int64_t>(16), 2 * (C - key))) : 0u;
-#pragma unroll
-          for (uint32_t i = 0; i < 8; ++i) {
-            const uint32_t d = dr + 8u * i;
-            const uint32_t dst = ks + (cm >> 3) * 8192u + (d >> 3) * 1024u + (d & 7u) * 128u + (((cm & 7u) ^ (d & 7u)) << 4);
-            cp_async_16_zfill(dst, kbytes ? KT + ((g * hd + d) * C + key) : KT, kbytes);
-          }
-        }
-        {   // V block: element (key, d) at V[(g*C + key)*hd + d]: d is the unit-stride ("MN") dimension, keys are k
-          const uint32_t cd = ptid & 7u, kr = ptid >> 3;             // 8 d chunks x 16 keys per pass
-#pragma unroll
-          for (uint32_t i = 0; i < 8; ++i) {
-            const uint32_t kk = kr + 16u * i;
-            const int64_t key = n0 + kk;
-            const uint32_t dst = vs + (kk >> 3) * 1024u + (kk & 7u) * 128u + ((cd ^ (kk & 7u)) << 4);
-            cp_async_16_zfill(dst, key < C ? V + ((g * C + key) * hd + 8 * cd) : V, key < C ? 16u : 0u);
-          }
-        }
-        cp_async_mbar_arrive(&S->kv_full[s]);
-      }
-      cp_async_wait_all();
-    } else if (w == 4) {
-      // ---------------- MMA issue ----------------
+    if (w == 0) {
+      // ---------------- producer: one thread drives TMA ----------------
       if (lane == 0) {
-        const uint32_t fmt = adt == kBF16 ? 1u : 0u;
-        // S: A = Q K-major, B = K^T MN-major, N = 128.  O: A = P K-major, B = V MN-major, N = 64.
-        const uint32_t idesc_s = (1u << 4) | (fmt << 7) | (fmt << 10) | (1u << 16) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
-        const uint32_t idesc_o = (1u << 4) | (fmt << 7) | (fmt << 10) | (1u << 16) | ((64u >> 3) << 17) | ((128u >> 4) << 24);
-        bool ok = tc_wait(&S->q_full, qn & 1u, failed, budget);
-        auto issue_s = [&](uint32_t jj, uint32_t kvpos) {   // S(jj) into buffer jj % 2 from ring stage kvpos
-          const uint32_t s = kvpos % kFaStages;
-          if (!tc_wait(&S->kv_full[s], (kvpos / kFaStages) & 1u, failed, budget)) { ok = false; return; }
-          fence_proxy_async_smem();
-          tc_fence_after_sync();
-          const uint64_t da = tc_desc(q_s, 16u, 1024u);
-          const uint64_t db = tc_desc(kv_s + s * kFaKvBytes, 8192u, 1024u);
-#pragma unroll
-          for (uint32_t kk = 0; kk < 4; ++kk)
-            tc_mma_f16(tmem + (jj & 1u) * 128u, da + kk * (32u >> 4), db + kk * (2048u >> 4), idesc_s, kk ? 1u : 0u);
-          tc_commit(&S->s_full[jj & 1u]);
-        };
-        if (ok && nkb > 0) issue_s(jt, kvit);
-        for (int64_t j = 0; ok && j < nkb; ++j) {
-          const uint32_t jj = jt + static_cast<uint32_t>(j), kvpos = kvit + static_cast<uint32_t>(j);
-          if (j + 1 < nkb) issue_s(jj + 1, kvpos + 1);
-          if (!ok) break;
-          if (!tc_wait(&S->p_full[jj & 1u], (jj >> 1) & 1u, failed, budget)) { ok = false; break; }
-          tc_fence_after_sync();
-          const uint32_t s = kvpos % kFaStages;
-          const uint32_t pb = p_s + (jj & 1u) * kFaPBytes;
-          const uint64_t dv = tc_desc(kv_s + s * kFaKvBytes + 128 * 128, 16384u, 1024u);
-#pragma unroll
-          for (uint32_t kk = 0; kk < 8; ++kk) {
-            const uint64_t dp = tc_desc(pb + (kk >> 2) * 16384u + (kk & 3u) * 32u, 16u, 1024u);
-            tc_mma_f16(tmem + 256u + (jj & 1u) * 64u, dp, dv + kk * (2048u >> 4), idesc_o, kk ? 1u : 0u);
+        tma_load_4d(q_s, tm_q, 0, static_cast<int32_t>(m0), h0c, h1c, &S->q_full);        // rows past T arrive as zeros
+        tma_load_4d(q_s + kFaTile, tm_q, 0, static_cast<int32_t>(m0 + 128), h0c, h1c, &S->q_full);
+        mbar_arrive_tx(&S->q_full, 2u * kFaTile);
+        for (int64_t j = 0; j < nmax; ++j) {
+          const uint32_t pos = kvpos + static_cast<uint32_t>(j), st = pos % kFaStages;
+          if (!tc_wait(&S->kv_empty[st], ((pos / kFaStages) & 1u) ^ 1u, failed, budget, 32u)) break;
+          const uint32_t ks = kv_s + st * 2u * kFaTile, vs = ks + kFaTile;
+          const int32_t c0 = static_cast<int32_t>(j * 128);
+          if (k_mn) {       // K as [d][keys]: two boxes of 64 keys x 64 d
+            tma_load_4d(ks, tm_k, c0, 0, h0c, h1c, &S->kv_full[st]);
+            tma_load_4d(ks + 8192u, tm_k, c0 + 64, 0, h0c, h1c, &S->kv_full[st]);
+          } else {          // K as [keys][d]: one box of 128 keys x 64 d
+            tma_load_4d(ks, tm_k, 0, c0, h0c, h1c, &S->kv_full[st]);
           }
-          tc_commit(&S->kv_empty[s]);
-          tc_commit(&S->o_full[jj & 1u]);
+          tma_load_4d(vs, tm_v, 0, c0, h0c, h1c, &S->kv_full[st]);
+          mbar_arrive_tx(&S->kv_full[st], 2u * kFaTile);
         }
       }
       __syncwarp();
-    } else if (w >= 8) {
-      // ---------------- softmax + output: two threads per query row ----------------
-      const uint32_t q4 = w & 3u, hf = (w - 8u) >> 2, r = 32u * q4 + lane;
-      float *xch = reinterpret_cast<float *>(sm + kSmemChain);          // [2 parities][2 halves][128 rows], then [2][128] sums
-      const int64_t m = m0 + r, grow = g * T + m;
-      const bool row_ok = m < T && grow >= first && grow < rows_end;
-      const int64_t c_end = causal ? min(C, m + (C - T) + 1) : C;   // keys this row may see
-      float m_run = -INFINITY, l_run = 0.0f;
-      float acc[32];                                                  // output columns 32 hf .. 32 hf + 31
-#pragma unroll
-      for (int d = 0; d < 32; ++d) acc[d] = 0.0f;
-      bool ok = true;
-      for (int64_t j = 0; ok && j <= nkb; ++j) {
-        const uint32_t jj = jt + static_cast<uint32_t>(j);
-        float alpha = 1.0f;
-        if (j < nkb) {
-          if (!tc_wait_warp(&S->s_full[jj & 1u], (jj >> 1) & 1u, failed, budget)) { ok = false; break; }
+    } else if (w == 1) {
+      // ---------------- MMA issue ----------------
+      if (lane == 0) {
+        const uint32_t fmt = adt == kBF16 ? 1u : 0u;
+        // S: A = Q (K-major), B = K block; O: A = P (K-major), B = V (d is the unit-stride "MN" dimension)
+        const uint32_t idesc_s = (1u << 4) | (fmt << 7) | (fmt << 10) | ((k_mn ? 1u : 0u) << 16) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
+        const uint32_t idesc_o = (1u << 4) | (fmt << 7) | (fmt << 10) | (1u << 16) | ((64u >> 3) << 17) | ((128u >> 4) << 24);
+        bool ok = tc_wait(&S->q_full, qn & 1u, failed, budget);
+        uint32_t kv_seen = 0;     // key blocks of this unit whose arrival has been waited for
+        auto need_kv = [&](int64_t j) {
+          while (ok && static_cast<int64_t>(kv_seen) <= j) {
+            const uint32_t pos = kvpos + kv_seen, st = pos % kFaStages;
+            if (!tc_wait(&S->kv_full[st], (pos / kFaStages) & 1u, failed, budget)) { ok = false; break; }
+            ++kv_seen;
+          }
           tc_fence_after_sync();
-          // valid columns of this thread's half (keys n0 + 64 hf .. + lim - 1)
-          const int lim = static_cast<int>(max(static_cast<int64_t>(0), min(static_cast<int64_t>(64), c_end - j * 128 - 64 * hf)));
-          const uint32_t s_addr = tmem + ((32u * q4) << 16) + (jj & 1u) * 128u + 64u * hf;
-          // pass 1: the half row's maximum over this block, then the row's through shared memory
-          float mx = -INFINITY;
+        };
+        auto issue_s = [&](int s, int64_t j) {
+          need_kv(j);
+          if (!ok) return;
+          const uint32_t use = cnt[s] + static_cast<uint32_t>(j);
+          if (j > 0 && !tc_wait(&S->s_free[s], (use - 1u) & 1u, failed, budget)) { ok = false; return; }
+          tc_fence_after_sync();
+          const uint32_t st = (kvpos + static_cast<uint32_t>(j)) % kFaStages;
+          const uint64_t da = tc_desc(q_s + static_cast<uint32_t>(s) * kFaTile, 16u, 1024u);
+          const uint64_t db = k_mn ? tc_desc(kv_s + st * 2u * kFaTile, 8192u, 1024u) : tc_desc(kv_s + st * 2u * kFaTile, 16u, 1024u);
+          const uint64_t adv_b = k_mn ? (2048u >> 4) : (32u >> 4);
+#pragma unroll
+          for (uint32_t kk = 0; kk < 4; ++kk)
+            tc_mma_f16(tmem + static_cast<uint32_t>(s) * 128u, da + kk * (32u >> 4), db + kk * adv_b, idesc_s, kk ? 1u : 0u);
+          tc_commit(&S->s_full[s]);
+        };
+        auto issue_pv = [&](int s, int64_t j) {
+          const uint32_t use = cnt[s] + static_cast<uint32_t>(j);
+          if (!tc_wait(&S->p_full[s], use & 1u, failed, budget)) { ok = false; return; }
+          tc_fence_after_sync();
+          const uint32_t st = (kvpos + static_cast<uint32_t>(j)) % kFaStages;
+          const uint32_t pb = p_s + static_cast<uint32_t>(s) * kFaPBytes;
+          const uint64_t dv = tc_desc(kv_s + st * 2u * kFaTile + kFaTile, 16384u, 1024u);
+#pragma unroll
+          for (uint32_t kk = 0; kk < 8; ++kk) {
+            const uint64_t dp = tc_desc(pb + (kk >> 2) * 16384u + (kk & 3u) * 32u, 16u, 1024u);
+            tc_mma_f16(tmem + 256u + static_cast<uint32_t>(s) * 64u, dp, dv + kk * (2048u >> 4), idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+          }
+          tc_commit(&S->pv_done[s]);
+        };
+        for (int s = 0; ok && s < 2; ++s)
+          if (nkb[s] > 0) issue_s(s, 0);
+        for (int64_t j = 0; ok && j < nmax; ++j) {
+          for (int s = 0; ok && s < 2; ++s) {
+            if (j < nkb[s]) issue_pv(s, j);
+            if (ok && j + 1 < nkb[s]) issue_s(s, j + 1);
+          }
+          // both slots' matmuls on stage j are issued: free it when they have read it
+          if (ok) tc_commit(&S->kv_empty[(kvpos + static_cast<uint32_t>(j)) % kFaStages]);
+        }
+      }
+      __syncwarp();
+    } else if (w >= 4 && w < 12) {
+      // ---------------- softmax + output: one thread per query row ----------------
+      const int s = w >= 8 ? 1 : 0;
+      const uint32_t q4 = w & 3u, r = 32u * q4 + lane;
+      const int64_t m = m0 + 128 * s + r, grow = g * T + m;
+      const bool row_ok = m < T;
+      const int64_t c_end = causal ? min(C, m + (C - T) + 1) : C;    // keys this row may see
+      const uint32_t s_addr = tmem + ((32u * q4) << 16) + static_cast<uint32_t>(s) * 128u;
+      const uint32_t o_addr = tmem + ((32u * q4) << 16) + 256u + static_cast<uint32_t>(s) * 64u;
+      const uint32_t prow = p_s + static_cast<uint32_t>(s) * kFaPBytes + r * 128u;
+      const bool bf = adt == kBF16;
+      float m_used = -INFINITY, l_run = 0.0f;
+      bool ok = true;
+      const int64_t nb = nkb[s];
+      for (int64_t j = 0; ok && j < nb; ++j) {
+        const uint32_t use = cnt[s] + static_cast<uint32_t>(j);
+        if (!tc_wait_warp(&S->s_full[s], use & 1u, failed, budget)) { ok = false; break; }
+        tc_fence_after_sync();
+        const int lim = static_cast<int>(max(static_cast<int64_t>(0), min(static_cast<int64_t>(128), c_end - j * 128)));
+        // pass 1: the row's maximum over this block
+        float mx = -INFINITY;
+#pragma unroll 1
+        for (int cb = 0; cb < 128; cb += 32) {
+          uint32_t raw[32];
+          __syncwarp();
+          tc_ld32(s_addr + cb, raw);
+          tc_wait_ld();
+          if (cb + 32 <= lim) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(raw[i]));
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (cb + i < lim) mx = fmaxf(mx, __uint_as_float(raw[i]));
+          }
+        }
+        mx *= sl2;     // sl2 > 0 for every softmax scale in use; a non-positive scale takes the CUDA-core path
+        // the maximum in use moves only when the row's true maximum outgrew it by 2^8
+        const bool grow_m = mx > m_used + kFaRescale;
+        const float alpha = !grow_m ? 1.0f : (m_used == -INFINITY ? 0.0f : fast_ex2(m_used - mx));
+        // O(j-1) complete, P's buffer free
+        if (j > 0 && !tc_wait_warp(&S->pv_done[s], (use - 1u) & 1u, failed, budget)) { ok = false; break; }
+        tc_fence_after_sync();
+        if (j > 0 && __any_sync(0xffffffffu, grow_m)) {
 #pragma unroll 1
           for (int cb = 0; cb < 64; cb += 32) {
             uint32_t raw[32];
             __syncwarp();
-            tc_ld32(s_addr + cb, raw);
+            tc_ld32(o_addr + cb, raw);
             tc_wait_ld();
-            if (cb + 32 <= lim) {
 #pragma unroll
-              for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(raw[i]) * sl2);
-            } else {
-#pragma unroll
-              for (int i = 0; i < 32; ++i)
-                if (cb + i < lim) mx = fmaxf(mx, __uint_as_float(raw[i]) * sl2);
-            }
+            for (int i = 0; i < 32; ++i) raw[i] = __float_as_uint(__uint_as_float(raw[i]) * alpha);
+            tc_st32(o_addr + cb, raw);
           }
-          xch[((jj & 1u) * 2u + hf) * 128u + r] = mx;
-          mbar_arrive(&S->mx_full[jj & 1u]);
-          if (!tc_wait_warp(&S->mx_full[jj & 1u], (jj >> 1) & 1u, failed, budget)) { ok = false; break; }
-          mx = fmaxf(mx, xch[((jj & 1u) * 2u + (hf ^ 1u)) * 128u + r]);
-          const float m_new = fmaxf(m_run, mx);
-          alpha = m_run == -INFINITY ? (m_new == -INFINITY ? 1.0f : 0.0f) : fast_ex2(m_run - m_new);
-          const float neg_m = m_new == -INFINITY ? 0.0f : -m_new;
-          // pass 2: p = 2^(s - m_new), written as the 16-bit A operand of the second matmul
-          float psum = 0.0f;
-          const uint32_t prow = p_s + (jj & 1u) * kFaPBytes + hf * 16384u + r * 128u;   // 64 keys = one sub-tile
-          const bool bf = adt == kBF16;
-#pragma unroll 1
-          for (int cb = 0; cb < 64; cb += 16) {
-            uint32_t raw[16];
-            __syncwarp();
-            tc_ld16(s_addr + cb, raw);
-            tc_wait_ld();
-            float pv[16];
-            if (cb + 16 <= lim) {
-#pragma unroll
-              for (int i = 0; i < 16; ++i) pv[i] = fast_ex2(fmaf(__uint_as_float(raw[i]), sl2, neg_m));
-            } else {
-#pragma unroll
-              for (int i = 0; i < 16; ++i) pv[i] = cb + i < lim ? fast_ex2(fmaf(__uint_as_float(raw[i]), sl2, neg_m)) : 0.0f;
-            }
-            uint32_t pk[8];
-            if (bf) {
-#pragma unroll
-              for (int i = 0; i < 8; ++i) pk[i] = cvt_bf16x2(pv[2 * i + 1], pv[2 * i]);
-            } else {
-#pragma unroll
-              for (int i = 0; i < 8; ++i) pk[i] = f32_to_f16_bits(pv[2 * i]) | (f32_to_f16_bits(pv[2 * i + 1]) << 16);
-            }
-#pragma unroll
-            for (int i = 0; i < 16; ++i) psum += pv[i];
-#pragma unroll
-            for (uint32_t q = 0; q < 2; ++q) {                      // 16 keys = 2 chunks of 8
-              const uint32_t ch = (static_cast<uint32_t>(cb) >> 3) + q;
-              uint4 *dstp = reinterpret_cast<uint4 *>(sm + (prow + ((ch ^ (r & 7u)) << 4) - smem_addr(sm)));
-              *dstp = make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
-            }
-          }
-          l_run = l_run * alpha + psum;
-          m_run = m_new;
-          tc_fence_before_sync();
-          fence_proxy_async_smem();               // P (generic-proxy stores) -> the MMA's reads
-          mbar_arrive(&S->p_full[jj & 1u]);
+          tc_wait_st();
         }
-        if (j > 0) {
-          // fold O(j-1) in: acc = (acc + O(j-1)) * alpha(j)
-          const uint32_t pj = jj - 1u;
-          if (!tc_wait_warp(&S->o_full[pj & 1u], (pj >> 1) & 1u, failed, budget)) { ok = false; break; }
-          tc_fence_after_sync();
+        if (grow_m) { l_run *= alpha; m_used = mx; }
+        const float neg_m = m_used == -INFINITY ? 0.0f : -m_used;
+        // pass 2: p = 2^(s - m_used), written as the 16-bit A operand of the second matmul
+        float psum = 0.0f;
+#pragma unroll 1
+        for (int cb = 0; cb < 128; cb += 32) {
           uint32_t raw[32];
           __syncwarp();
-          tc_ld32(tmem + ((32u * q4) << 16) + 256u + (pj & 1u) * 64u + 32u * hf, raw);
+          tc_ld32(s_addr + cb, raw);
           tc_wait_ld();
+          if (cb == 96) {            // the scores are in registers: the slot's next S may be written
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&S->s_free[s]);
+          }
+          float pv[32];
+          if (cb + 32 <= lim) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) acc[i] = (acc[i] + __uint_as_float(raw[i])) * alpha;
-        } else {
+            for (int i = 0; i < 32; ++i) pv[i] = fast_ex2(fmaf(__uint_as_float(raw[i]), sl2, neg_m));
+          } else {
 #pragma unroll
-          for (int d = 0; d < 32; ++d) acc[d] *= alpha;
+            for (int i = 0; i < 32; ++i) pv[i] = cb + i < lim ? fast_ex2(fmaf(__uint_as_float(raw[i]), sl2, neg_m)) : 0.0f;
+          }
+          uint32_t pk[16];
+          if (bf) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) pk[i] = cvt_bf16x2(pv[2 * i + 1], pv[2 * i]);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) pk[i] = f32_to_f16_bits(pv[2 * i]) | (f32_to_f16_bits(pv[2 * i + 1]) << 16);
+          }
+#pragma unroll
+          for (int i = 0; i < 32; ++i) psum += pv[i];
+          // 32 keys = 4 chunks of 8 in the row's 128-byte line of sub-tile cb / 64
+          const uint32_t sub = prow + (static_cast<uint32_t>(cb) >> 6) * 16384u;
+#pragma unroll
+          for (uint32_t q = 0; q < 4; ++q) {
+            const uint32_t ch = ((static_cast<uint32_t>(cb) & 63u) >> 3) + q;
+            uint4 *dstp = reinterpret_cast<uint4 *>(sm + (sub + ((ch ^ (r & 7u)) << 4) - smem_addr(sm)));
+            *dstp = make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
+          }
+        }
+        l_run += psum;
+        tc_fence_before_sync();
+        fence_proxy_async_smem();               // P (generic-proxy stores) -> the MMA's reads
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&S->p_full[s]);
+      }
+      // ---- output: O / l ----
+      if (ok && nb > 0) {
+        const uint32_t use = cnt[s] + static_cast<uint32_t>(nb) - 1u;
+        if (!tc_wait_warp(&S->pv_done[s], use & 1u, failed, budget)) ok = false;
+        tc_fence_after_sync();
+        if (ok) {
+          const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
+#pragma unroll 1
+          for (int cb = 0; cb < 64; cb += 32) {
+            uint32_t raw[32];
+            __syncwarp();
+            tc_ld32(o_addr + cb, raw);
+            tc_wait_ld();
+            if (row_ok) {
+              float v[32];
+#pragma unroll
+              for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(raw[i]) * inv;
+              tc_store_row32(out, dt, grow * hd + cb, v, 32, true);
+            }
+          }
         }
       }
-      // the row's sum is the two halves' (they share the running maximum)
-      float *lx = xch + 512;
-      lx[hf * 128u + r] = l_run;
-      mbar_arrive(&S->l_full);
-      if (ok && !tc_wait_warp(&S->l_full, qn & 1u, failed, budget)) ok = false;
-      if (ok && row_ok) {
-        const float inv = 1.0f / (l_run + lx[(hf ^ 1u) * 128u + r]);
-        float v[32];
-#pragma unroll
-        for (int i = 0; i < 32; ++i) v[i] = acc[i] * inv;
-        tc_store_row32(out, dt, grow * hd + 32 * hf, v, 32, true);
-      }
     }
-    kvit += static_cast<uint32_t>(nkb);
-    jt += static_cast<uint32_t>(nkb);
+    kvpos += static_cast<uint32_t>(nmax);
+    cnt[0] += static_cast<uint32_t>(nkb[0]);
+    cnt[1] += static_cast<uint32_t>(nkb[1]);
     ++qn;
-    // Every role is done with the block: Q, the rings and tensor memory are free again.
-    tc_fence_before_sync();
-    __syncthreads();
-    tc_fence_after_sync();
-    if (S->failed) break;
   }
 
   // ---------------- teardown ----------------
   tc_fence_before_sync();
   __syncthreads();
-  if (w == 4) {
+  const bool gave_up = S->failed != 0u;
+  if (gave_up) {     // copies / matmuls of other roles may still be landing: give them time (see ops_mma_tc.cuh)
+    const unsigned long long t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 50000ull) nanosleep_ns(1000);
+  }
+  if (w == 1) {
     __syncwarp();
     tc_fence_after_sync();
     tmem_dealloc(tmem, kFaCols);
   }
   if (L.tid == 0) {
-    if (S->failed) set_status(P, kStTensorTimeout, L.lane, tile_lo, kTopFlashAttn);
-    mbar_inval(&S->q_full);
-    for (int s = 0; s < kFaStages; ++s) { mbar_inval(&S->kv_full[s]); mbar_inval(&S->kv_empty[s]); }
-    for (int b = 0; b < 2; ++b) {
-      mbar_inval(&S->s_full[b]); mbar_inval(&S->p_full[b]); mbar_inval(&S->o_full[b]); mbar_inval(&S->mx_full[b]);
+    if (gave_up) {
+      set_status(P, kStTensorTimeout, L.lane, tile_lo, kTopFlashAttn);
+    } else {
+      mbar_inval(&S->q_full);
+      for (int s = 0; s < kFaStages; ++s) { mbar_inval(&S->kv_full[s]); mbar_inval(&S->kv_empty[s]); }
+      for (int b = 0; b < 2; ++b) {
+        mbar_inval(&S->s_full[b]); mbar_inval(&S->s_free[b]); mbar_inval(&S->p_full[b]); mbar_inval(&S->pv_done[b]);
+      }
     }
-    mbar_inval(&S->l_full);
+    if (dynamic) {
+      // the last lane to finish puts the counters back to rest for the task's next run
+      __threadfence();
+      if (atomicAdd(&work[1], 1u) == df.n_owner_lanes - 1u) { st_relaxed_gpu(&work[0], 0u); st_relaxed_gpu(&work[1], 0u); }
+    }
   }
   __syncthreads();
   return true;

@@ -39,7 +39,7 @@ __device__ __forceinline__ float mma_epilogue(const KParams &P, const DTask &t, 
 }
 
 template <int NT>
-__device__ __noinline__ void mma_simt_tiles(const Lane &L, const DTask &t, uint32_t tile_lo, uint32_t tile_hi) {
+static __device__ __noinline__ void mma_simt_tiles(const Lane &L, const DTask &t, uint32_t tile_lo, uint32_t tile_hi) {
   constexpr int TC = NT / 32;          // thread columns
   constexpr int TN = kMmaT / TC;       // output columns per thread
   constexpr int TM = 4;                // output rows per thread (32 thread rows x 4 = 128)

@@ -184,7 +184,7 @@ __device__ __forceinline__ void tc_store_row32(uint8_t *dst, uint32_t dt, int64_
 
 // Returns false (nothing done) when this launch cannot use the path (misaligned
 // operand base); the caller then runs the CUDA-core path.
-__device__ __noinline__ bool mma_tc_tiles(const Lane &L, const DTask &t, uint32_t tile_lo, uint32_t tile_hi) {
+static __device__ __noinline__ bool mma_tc_tiles(const Lane &L, const DTask &t, uint32_t tile_lo, uint32_t tile_hi) {
   const KParams &P = *L.P;
   const DMma &dm = *reinterpret_cast<const DMma *>(P.desc + t.desc);
   const int64_t M = t.p[0], N = t.p[1], K = t.p[2], G = t.p[3] ? t.p[3] : 1;

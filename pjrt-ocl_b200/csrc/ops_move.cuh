@@ -93,7 +93,7 @@ __device__ __forceinline__ void transpose_rows(const Lane &L, const DMove &m, E 
 }
 
 // gather: dst[i] = a[base + view(i)];  scatter: dst[base + view(i)] = a[i]
-__device__ __noinline__ void move_tiles(const Lane &L, const DTask &t, uint32_t tile_lo, uint32_t tile_hi, bool scatter) {
+static __device__ __noinline__ void move_tiles(const Lane &L, const DTask &t, uint32_t tile_lo, uint32_t tile_hi, bool scatter) {
   const KParams &P = *L.P;
   const DMove &m = *reinterpret_cast<const DMove *>(P.desc + t.desc);
   uint8_t *dst = resolve(P, t.ptr[0]);
@@ -162,7 +162,7 @@ __device__ __noinline__ void move_tiles(const Lane &L, const DTask &t, uint32_t 
 
 // iota: dst[i] = coordinate of i along `dim` (aux {rank, dims[rank], dim}); the
 // loader stores {dim_size, inner} = sizes such that coord = (i / inner) % dim_size.
-__device__ __noinline__ void iota_tiles(const Lane &L, const DTask &t, uint32_t tile_lo, uint32_t tile_hi) {
+static __device__ __noinline__ void iota_tiles(const Lane &L, const DTask &t, uint32_t tile_lo, uint32_t tile_hi) {
   const KParams &P = *L.P;
   const uint32_t *d = reinterpret_cast<const uint32_t *>(P.desc + t.desc);
   const uint32_t dim_size = d[0], inner = d[1];

@@ -338,9 +338,154 @@ __device__ __forceinline__ bool red_part_stream(const Lane &L, const DTask &t, u
   return true;
 }
 
-// RED_PART: tile t reduces in[t*chunk, min((t+1)*chunk, n)) into partials[t].
-__device__ __noinline__ void red_part_tiles(const Lane &L, const DTask &t, uint32_t tile_lo, uint32_t tile_hi) {
+// One contiguous run of 16-byte words [w_lo, w_hi) of a 4-byte-element array, streamed
+// through the ring of bulk copies (as red_part_stream) and folded by the whole lane;
+// every thread returns the lane's total. Short runs are read directly.
+template <typename C>
+__device__ __forceinline__ uint32_t red_words_lane(const Lane &L, const uint8_t *a, uint64_t w_lo, uint64_t w_hi,
+                                                   uint32_t kind, uint32_t dt, uint32_t ident) {
   const KParams &P = *L.P;
+  uint32_t acc = ident;
+  const uint8_t *src = a + w_lo * 16u;
+  const uint64_t total = (w_hi - w_lo) * 16u;
+  const bool stream = total >= 4u * kStreamChunk && (reinterpret_cast<uintptr_t>(a) & 15u) == 0 &&
+                      L.smem_bytes >= kSmemSys + 1024u + kStreamBufs * kStreamChunk;
+  if (stream) {
+    // Ring of kStreamBufs buffers; per buffer a "full" barrier (the copy's bytes have landed) and an
+    // "empty" barrier (every warp has read its share). Thread 0 issues the copies; nothing else in the
+    // loop is lane-wide, so warps drift up to a ring's length apart instead of meeting at every buffer.
+    const uint32_t nchunks = static_cast<uint32_t>((total + kStreamChunk - 1) / kStreamChunk);
+    const uint32_t nwarps = L.nthr / kWarp, lane_id = L.tid % kWarp;
+    uint64_t *full = reinterpret_cast<uint64_t *>(L.smem + kSmemSys);
+    uint64_t *empty = full + kStreamBufs;
+    uint8_t *bufs = L.smem + kSmemSys + 1024;
+    auto bytes_of = [&](uint32_t c) {
+      const uint64_t left = total - static_cast<uint64_t>(c) * kStreamChunk;
+      return left < kStreamChunk ? static_cast<uint32_t>(left) : kStreamChunk;
+    };
+    auto refill = [&](uint32_t c) {
+      const uint32_t bb = c % kStreamBufs;
+      mbar_arrive_expect_tx(&full[bb], bytes_of(c));
+      bulk_g2s(bufs + bb * kStreamChunk, src + static_cast<size_t>(c) * kStreamChunk, bytes_of(c), &full[bb]);
+    };
+    __syncthreads();
+    if (L.tid == 0) {
+      for (uint32_t i = 0; i < kStreamBufs; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], nwarps); }
+      fence_mbar_init();
+      for (uint32_t c = 0; c < kStreamBufs && c < nchunks; ++c) refill(c);
+    }
+    __syncthreads();
+    uint32_t acc2 = ident;   // two chains per thread: the 16-byte words alternate between them
+    bool ok = true;
+    for (uint32_t c = 0; c < nchunks && ok; ++c) {
+      const uint32_t b = c % kStreamBufs, par = (c / kStreamBufs) & 1u;
+      if (L.tid == 0 && c >= 1u && c - 1u + kStreamBufs < nchunks) {
+        // the buffer of chunk c - 1 goes to chunk c - 1 + kStreamBufs once every warp has left it
+        const uint32_t pb = (c - 1u) % kStreamBufs;
+        if (mbar_wait_bounded(&empty[pb], ((c - 1u) / kStreamBufs) & 1u, P.wait_budget_ns)) {
+          fence_proxy_async_smem();
+          refill(c - 1u + kStreamBufs);
+        } else {
+          set_status(P, kStTensorTimeout, L.lane, c, kTopRedPart);
+        }
+      }
+      if (!mbar_wait_bounded(&full[b], par, P.wait_budget_ns)) {
+        set_status(P, kStTensorTimeout, L.lane, c, kTopRedPart);
+        ok = false;
+      }
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      const uint32_t nw = bytes_of(c) / 16u;
+      const uint4 *q = reinterpret_cast<const uint4 *>(bufs + b * kStreamChunk);
+      uint32_t o = L.tid;
+      for (; o + L.nthr < nw; o += 2u * L.nthr) {
+        const uint4 v = q[o], u = q[o + L.nthr];
+        acc = C::f(C::f(acc, v.x), C::f(v.y, C::f(v.z, v.w)));
+        acc2 = C::f(C::f(acc2, u.x), C::f(u.y, C::f(u.z, u.w)));
+      }
+      if (o < nw) {
+        const uint4 v = q[o];
+        acc = C::f(C::f(acc, v.x), C::f(v.y, C::f(v.z, v.w)));
+      }
+      __syncwarp();
+      if (lane_id == 0) mbar_arrive(&empty[b]);
+    }
+    acc = C::f(acc, acc2);
+    __syncthreads();
+    if (L.tid == 0 && ok)
+      for (uint32_t i = 0; i < kStreamBufs; ++i) { mbar_inval(&full[i]); mbar_inval(&empty[i]); }
+    __syncthreads();
+  } else if (w_hi > w_lo) {
+    acc = static_cast<uint32_t>(reduce_run(a, dt, kind, static_cast<int64_t>(w_lo) * 4, static_cast<int64_t>(w_hi) * 4, L.tid, L.nthr, nullptr, 0).bits);
+  }
+  Acc r;
+  r.bits = acc;
+  return static_cast<uint32_t>(acc_block_reduce(L, kind, dt, r).bits);
+}
+
+// A full reduction re-cut over all lanes by the loader (kRedFused): this lane folds the
+// 16-byte words [w_lo, w_hi) of the input (the last lane also the ragged tail), leaves
+// its total in the program's scratch and counts itself in; the lane that arrives last
+// folds all lanes' totals in lane order and stores the result the RED_COMB would have.
+template <typename C>
+__device__ __forceinline__ void red_full_lane(const Lane &L, const DTask &t, uint32_t w_lo, uint32_t w_hi, uint32_t kind,
+                                              uint32_t dt) {
+  const KParams &P = *L.P;
+  const uint8_t *a = resolve(P, t.ptr[1]);
+  uint8_t *out = resolve(P, t.ptr[3]);
+  const uint64_t n = t.p[0];
+  RedScratch *sc = reinterpret_cast<RedScratch *>(P.scratch);
+  const uint32_t ident = static_cast<uint32_t>(acc_identity(kind, dt).bits);
+  uint32_t total = red_words_lane<C>(L, a, w_lo, w_hi, kind, dt, ident);
+  uint32_t *flag = reinterpret_cast<uint32_t *>(L.smem + kSmemFlag);
+  if (L.tid == 0) {
+    if (L.lane == P.n_lanes - 1u)
+      for (uint64_t i = (n / 4u) * 4u; i < n; ++i) total = C::f(total, reinterpret_cast<const uint32_t *>(a)[i]);
+    sc->total[L.lane] = total;
+    __threadfence();
+    *flag = atom_add_acq_rel_gpu(&sc->arrived, 1u) == P.n_lanes - 1u ? 1u : 0u;
+  }
+  __syncthreads();
+  const bool last = *flag != 0u;
+  __syncthreads();   // the flag word is the grid barrier's too
+  if (!last) return;
+  __threadfence();
+  Acc acc;
+  acc.bits = ident;
+  for (uint32_t l = L.tid; l < P.n_lanes; l += L.nthr) {
+    const unsigned long long v = *reinterpret_cast<volatile unsigned long long *>(&sc->total[l]);
+    acc.bits = C::f(static_cast<uint32_t>(acc.bits), static_cast<uint32_t>(v));
+  }
+  acc = acc_block_reduce(L, kind, dt, acc);
+  if (L.tid == 0) {
+    acc_store(out, dt, 0, acc);
+    st_relaxed_gpu(&sc->arrived, 0u);   // rest state for the next reduction of this program
+  }
+}
+
+// RED_PART: tile t reduces in[t*chunk, min((t+1)*chunk, n)) into partials[t]. With
+// kRedFused the entry names the 16-byte words [w_lo, w_hi) instead (see red_full_lane).
+static __device__ __noinline__ void red_part_tiles(const Lane &L, const DTask &t, uint32_t tile_lo, uint32_t tile_hi,
+                                                   uint32_t w_lo, uint32_t w_hi) {
+  const KParams &P = *L.P;
+  if (t.flags & kRedFused) {
+    const uint32_t kind = t.p[2], dt = t.dt;
+    const bool fl = dt == kF32;
+    if (fl && kind == kSum) red_full_lane<RFSum>(L, t, w_lo, w_hi, kind, dt);
+    else if (fl && kind == kRMax) red_full_lane<RFMax>(L, t, w_lo, w_hi, kind, dt);
+    else if (fl && kind == kRMin) red_full_lane<RFMin>(L, t, w_lo, w_hi, kind, dt);
+    else if (fl) red_full_lane<RFProd>(L, t, w_lo, w_hi, kind, dt);
+    else if (kind == kSum) red_full_lane<RISum>(L, t, w_lo, w_hi, kind, dt);
+    else if (kind == kProd) red_full_lane<RIProd>(L, t, w_lo, w_hi, kind, dt);
+    else if (kind == kRAnd) red_full_lane<RIAnd>(L, t, w_lo, w_hi, kind, dt);
+    else if (kind == kROr) red_full_lane<RIOr>(L, t, w_lo, w_hi, kind, dt);
+    else if (kind == kRXor) red_full_lane<RIXor>(L, t, w_lo, w_hi, kind, dt);
+    else if (kind == kRMax && dt == kI32) red_full_lane<RIMaxS>(L, t, w_lo, w_hi, kind, dt);
+    else if (kind == kRMax) red_full_lane<RIMaxU>(L, t, w_lo, w_hi, kind, dt);
+    else if (dt == kI32) red_full_lane<RIMinS>(L, t, w_lo, w_hi, kind, dt);
+    else red_full_lane<RIMinU>(L, t, w_lo, w_hi, kind, dt);
+    return;
+  }
   uint8_t *dst = resolve(P, t.ptr[0]);
   const uint8_t *a = resolve(P, t.ptr[1]);
   const int64_t n = t.p[0], chunk = t.p[1];
@@ -367,7 +512,7 @@ __device__ __noinline__ void red_part_tiles(const Lane &L, const DTask &t, uint3
 }
 
 // RED_COMB: fold n_parts partials into dst[0] (single tile).
-__device__ __noinline__ void red_comb_tiles(const Lane &L, const DTask &t, uint32_t tile_lo, uint32_t tile_hi) {
+static __device__ __noinline__ void red_comb_tiles(const Lane &L, const DTask &t, uint32_t tile_lo, uint32_t tile_hi) {
   if (!(tile_lo == 0 && tile_hi > 0)) return;
   const KParams &P = *L.P;
   uint8_t *dst = resolve(P, t.ptr[0]);
@@ -381,7 +526,7 @@ __device__ __noinline__ void red_comb_tiles(const Lane &L, const DTask &t, uint3
 
 // RED_SEG: out[o] = reduce(in[o*seg, (o+1)*seg)), one segment per tile index;
 // p3 = 1: dot mode, out[o] = sum_j in[o*seg+j] * b[j].
-__device__ __noinline__ void red_seg_tiles(const Lane &L, const DTask &t, uint32_t tile_lo, uint32_t tile_hi) {
+static __device__ __noinline__ void red_seg_tiles(const Lane &L, const DTask &t, uint32_t tile_lo, uint32_t tile_hi) {
   const KParams &P = *L.P;
   uint8_t *dst = resolve(P, t.ptr[0]);
   const uint8_t *a = resolve(P, t.ptr[1]);
@@ -508,7 +653,7 @@ __device__ __forceinline__ void red_strided_rows_kind(const Lane &L, float *dst,
 // [row_lo, row_hi) (row_hi > row_lo; a row = the `inner` outputs of one o).
 // General path: consecutive threads own consecutive outputs (coalesced along
 // `inner`), each keeps kQ independent outputs in flight.
-__device__ __noinline__ void red_strided_tiles(const Lane &L, const DTask &t, uint32_t tile_lo, uint32_t tile_hi,
+static __device__ __noinline__ void red_strided_tiles(const Lane &L, const DTask &t, uint32_t tile_lo, uint32_t tile_hi,
                                                uint32_t row_lo, uint32_t row_hi) {
   const KParams &P = *L.P;
   uint8_t *dst = resolve(P, t.ptr[0]);

@@ -23,7 +23,7 @@ constexpr uint32_t kRegionMaxMicro = 96;
 constexpr int kRegionU = 2;
 
 
-__device__ __noinline__ void region_tiles(const Lane &L, const DTask &t, uint32_t tile_lo, uint32_t tile_hi) {
+static __device__ __noinline__ void region_tiles(const Lane &L, const DTask &t, uint32_t tile_lo, uint32_t tile_hi) {
   const KParams &P = *L.P;
   const int32_t *x = P.aux + t.p[0];
   const uint32_t n_in = static_cast<uint32_t>(x[0]), out_slot = static_cast<uint32_t>(x[1]) & 7u,

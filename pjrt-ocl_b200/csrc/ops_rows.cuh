@@ -331,7 +331,7 @@ __device__ __forceinline__ void rows_generic(const Lane &L, const DTask &t, uint
   }
 }
 
-__device__ __noinline__ void rows_tiles(const Lane &L, const DTask &t, uint32_t tile_lo, uint32_t tile_hi, bool softmax) {
+static __device__ __noinline__ void rows_tiles(const Lane &L, const DTask &t, uint32_t tile_lo, uint32_t tile_hi, bool softmax) {
   const KParams &P = *L.P;
   const uint32_t n_out = t.p[0], seg = t.p[1];
   const uint32_t hi = min(tile_hi, n_out);

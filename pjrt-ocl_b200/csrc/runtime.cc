@@ -23,11 +23,28 @@
 #include "../../include/b2vm.h"
 #include "format.h"
 #include "loader.h"
+#include "variants.h"
 #include "vmprog.h"
 
 namespace b2 {
-cudaError_t LaunchVm(const KParams &params, uint32_t n_lanes, int threads, uint32_t smem_bytes, cudaStream_t stream);
-cudaError_t VmResidency(int device, int threads, uint32_t smem_bytes, int *max_lanes);
+// One pair of launch glue per build of the megakernel (vm_kernel.cu, variants.h).
+#define B2_DECLARE_VARIANT(name, fams)                                                                              \
+  cudaError_t LaunchVm_##name(const KParams &params, uint32_t n_lanes, int threads, uint32_t smem_bytes,           \
+                              cudaStream_t stream);                                                                 \
+  cudaError_t VmResidency_##name(int device, int threads, uint32_t smem_bytes, int *max_lanes);
+B2_VARIANT_LIST(B2_DECLARE_VARIANT)
+#undef B2_DECLARE_VARIANT
+
+struct VmVariant {
+  const char *name;
+  uint32_t families;
+  cudaError_t (*launch)(const KParams &, uint32_t, int, uint32_t, cudaStream_t);
+  cudaError_t (*residency)(int, int, uint32_t, int *);
+};
+#define B2_VARIANT_ROW(name, fams) {#name, static_cast<uint32_t>(fams), &LaunchVm_##name, &VmResidency_##name},
+const VmVariant kVariants[] = {B2_VARIANT_LIST(B2_VARIANT_ROW)};
+#undef B2_VARIANT_ROW
+constexpr int kNumVariants = static_cast<int>(sizeof(kVariants) / sizeof(kVariants[0]));
 }  // namespace b2
 
 namespace {
@@ -43,21 +60,20 @@ std::string CudaMsg(const char *what, cudaError_t e) {
 
 constexpr size_t kPoolPerSize = 4;  // runtime.h:304
 
-// Encode the TMA tensor map of one tensor-core matmul operand: a rank-3 tensor
-// {inner, outer, batch} of 16-bit elements whose inner dimension is the unit-stride
-// one (k for a K-major operand, the row / column index for an MN-major one), read
-// in boxes of 64 inner elements (128 bytes: one swizzle line) x 128 or 64 outer
-// rows with the 128-byte swizzle the tensor core expects. Elements beyond the
-// tensor's edge read as zero. Returns false when the tensor cannot be described
-// (the matmul then loads with per-thread asynchronous copies instead).
+// Encode one TMA tensor map (loader.h: TmapSpec) at operand address `base`: 16-bit
+// elements, 128-byte swizzle, elements beyond the tensor's edge read as zero. Returns
+// false when the tensor cannot be described (the task then loads with per-thread
+// copies, or falls back to its CUDA-core path).
 bool EncodeTmap(const b2::TmapSpec &s, const void *base, b2::DTmap *out) {
-  if (s.batch > 1 && s.gs <= 0) return false;               // a batch-broadcast operand
-  if (reinterpret_cast<uintptr_t>(base) % 16) return false;
-  const uint64_t inner = static_cast<uint64_t>(s.mn_major ? s.rows : s.k);
-  const uint64_t outer = static_cast<uint64_t>(s.mn_major ? s.k : s.rows);
-  const uint64_t stride1 = static_cast<uint64_t>(s.ld) * 2;
-  const uint64_t stride2 = s.batch > 1 ? static_cast<uint64_t>(s.gs) * 2 : stride1 * outer;
-  if (stride1 % 16 || stride2 % 16 || stride1 >= (1ull << 40) || stride2 >= (1ull << 40)) return false;
+  if (!s.valid || reinterpret_cast<uintptr_t>(base) % 16) return false;
+  cuuint64_t dims[4], strides[3];
+  cuuint32_t box[4], estr[4] = {1u, 1u, 1u, 1u};
+  for (uint32_t k = 0; k < s.rank; ++k) { dims[k] = s.dims[k]; box[k] = s.box[k]; }
+  for (uint32_t k = 0; k + 1 < s.rank; ++k) {
+    if (s.strides[k] <= 0) return false;
+    strides[k] = static_cast<cuuint64_t>(s.strides[k]) * 2;
+    if (strides[k] % 16 || strides[k] >= (1ull << 40)) return false;
+  }
   typedef CUresult (*EncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
                                CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -71,12 +87,8 @@ bool EncodeTmap(const b2::TmapSpec &s, const void *base, b2::DTmap *out) {
   }();
   if (!encode) return false;
   static_assert(sizeof(CUtensorMap) == sizeof(b2::DTmap), "tensor map size");
-  const cuuint64_t dims[3] = {inner, outer, static_cast<cuuint64_t>(s.batch)};
-  const cuuint64_t strides[2] = {stride1, stride2};
-  const cuuint32_t box[3] = {64u, s.mn_major ? 64u : 128u, 1u};
-  const cuuint32_t estr[3] = {1u, 1u, 1u};
   const CUresult r = encode(reinterpret_cast<CUtensorMap *>(out),
-                            s.dtype == b2::kBF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
+                            s.dtype == b2::kBF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, s.rank,
                             const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -153,6 +165,10 @@ struct b2_loaded {
   std::vector<char> tmap_off;            // the owning matmul could not be described at load: per-thread copies instead
   b2::DSync *d_sync = nullptr;
   b2::DSync *h_sync = nullptr;  // pinned mirror
+  unsigned long long *d_lane_ts = nullptr;   // per-lane timing buffer (b2_loaded_lane_timing), else null
+  uint8_t *d_scratch = nullptr; // lane totals of re-cut full reductions (RedScratch), when the program has one
+  size_t scratch_bytes = 0;
+  int variant = b2::kNumVariants - 1;   // which build of the megakernel runs this program
   uint64_t launches = 0;
   bool sync_dirty = true;       // the device sync block must be cleared before the next launch
   uint64_t wait_budget_ns = 2000000000ull;
@@ -161,7 +177,7 @@ struct b2_loaded {
   ~b2_loaded() {
     if (rt) rt->Bind();
     cudaFree(arena); cudaFree(d_tasks); cudaFree(d_entries); cudaFree(d_lanes);
-    cudaFree(d_aux); cudaFree(d_desc); cudaFree(d_sync); cudaFree(d_tmaps);
+    cudaFree(d_aux); cudaFree(d_desc); cudaFree(d_sync); cudaFree(d_tmaps); cudaFree(d_scratch); cudaFree(d_lane_ts);
     if (h_sync) cudaFreeHost(h_sync);
   }
 };
@@ -185,6 +201,7 @@ b2_status Enqueue(b2_loaded *lp, const b2::IoTable &io, cudaStream_t stream, std
   // at first use and after a failed run.
   cudaError_t e = cudaSuccess;
   if (lp->sync_dirty) {
+    if (lp->d_scratch) cudaMemsetAsync(lp->d_scratch, 0, lp->scratch_bytes, stream);   // an aborted run may leave arrivals
     e = cudaMemsetAsync(lp->d_sync, 0, sizeof(b2::DSync), stream);
     if (e != cudaSuccess) { *err = CudaMsg("sync reset", e); return B2_INTERNAL; }
     lp->sync_dirty = false;
@@ -213,11 +230,12 @@ b2_status Enqueue(b2_loaded *lp, const b2::IoTable &io, cudaStream_t stream, std
   kp.aux = lp->d_aux;
   kp.desc = lp->d_desc;
   kp.sync = lp->d_sync;
-  kp.scratch = nullptr;
+  kp.scratch = lp->d_scratch;
+  kp.lane_ts = lp->d_lane_ts;
   kp.n_lanes = lp->prog.n_lanes;
   kp.wait_budget_ns = lp->wait_budget_ns;
   kp.io = io;
-  e = b2::LaunchVm(kp, lp->prog.n_lanes, lp->rt->threads, lp->rt->smem_bytes, stream);
+  e = b2::kVariants[lp->variant].launch(kp, lp->prog.n_lanes, lp->rt->threads, lp->rt->smem_bytes, stream);
   if (e != cudaSuccess) { *err = CudaMsg("megakernel launch", e); cudaGetLastError(); return B2_INTERNAL; }
   lp->launches++;
   lp->last_stream = stream;
@@ -288,10 +306,16 @@ b2_status b2_runtime_create(int device_ordinal, b2_runtime **out, char *err, siz
   // runtime's own reservation.
   size_t optin = rt->prop.sharedMemPerBlockOptin;
   rt->smem_bytes = static_cast<uint32_t>(std::min<size_t>(optin, 227 * 1024) - 1024);
-  if ((e = b2::VmResidency(device_ordinal, rt->threads, rt->smem_bytes, &rt->max_lanes)) != cudaSuccess) {
-    SetErr(err, err_cap, CudaMsg("megakernel occupancy query", e));
-    cudaGetLastError();
-    return B2_INTERNAL;
+  // every build of the megakernel must be launchable with the same lane count
+  rt->max_lanes = 1 << 30;
+  for (const b2::VmVariant &v : b2::kVariants) {
+    int lanes = 0;
+    if ((e = v.residency(device_ordinal, rt->threads, rt->smem_bytes, &lanes)) != cudaSuccess) {
+      SetErr(err, err_cap, CudaMsg("megakernel occupancy query", e) + " (build '" + v.name + "')");
+      cudaGetLastError();
+      return B2_INTERNAL;
+    }
+    rt->max_lanes = std::min(rt->max_lanes, lanes);
   }
   if ((e = cudaStreamCreateWithFlags(&rt->stream, cudaStreamNonBlocking)) != cudaSuccess) {
     SetErr(err, err_cap, CudaMsg("stream create", e));
@@ -428,15 +452,23 @@ b2_status b2_program_load(b2_runtime *rt, b2_program *prog, b2_loaded **out, cha
     SetErr(err, err_cap, "load: " + m);
     return unimpl ? B2_UNIMPLEMENTED : B2_INVALID_ARGUMENT;
   }
+  // The smallest build of the megakernel that holds every tile-op family the program uses.
+  for (int v = 0; v < b2::kNumVariants; ++v)
+    if ((lp->tab.families & ~b2::kVariants[v].families) == 0u) { lp->variant = v; break; }
+  if (const char *force = std::getenv("B2VM_VARIANT")) {   // measurement aid: run on a named (larger) build
+    for (int v = 0; v < b2::kNumVariants; ++v)
+      if (!std::strcmp(force, b2::kVariants[v].name) && (lp->tab.families & ~b2::kVariants[v].families) == 0u) lp->variant = v;
+  }
   // Tensor maps of the tensor-core matmul operands. Arena operands are final here;
   // port operands get a placeholder (the arena) and are re-encoded at bind. A task
   // whose operand cannot be described keeps the per-thread copy path.
   lp->h_tmaps.resize(lp->tab.tmaps.size());
   lp->tmap_base.assign(lp->tab.tmaps.size(), nullptr);
   lp->tmap_off.assign(lp->tab.tmaps.size(), 0);
-  for (size_t i = 0; i + 1 < lp->tab.tmaps.size(); i += 2) {
-    bool ok = true;
-    for (size_t j = i; j < i + 2; ++j) {
+  for (size_t i = 0; i < lp->tab.tmaps.size();) {
+    const size_t group = lp->tab.tmaps[i].owner_is_flash ? 3 : 2;   // Q K V, or A B
+    bool ok = i + group <= lp->tab.tmaps.size();
+    for (size_t j = i; ok && j < i + group; ++j) {
       const b2::TmapSpec &sp = lp->tab.tmaps[j];
       const bool port = (sp.base & b2::kPortBit) != 0;
       const uint8_t *base = port ? lp->arena : reinterpret_cast<const uint8_t *>(static_cast<uintptr_t>(sp.base)) + sp.off * 2;
@@ -444,10 +476,18 @@ b2_status b2_program_load(b2_runtime *rt, b2_program *prog, b2_loaded **out, cha
       lp->tmap_base[j] = port ? nullptr : base;
     }
     if (!ok) {
-      b2::DMma *m = reinterpret_cast<b2::DMma *>(&lp->tab.desc[lp->tab.tmaps[i].desc_word]);
-      m->tmap = -1;
-      lp->tmap_off[i] = lp->tmap_off[i + 1] = 1;
+      // the task keeps its other path: per-thread copies (matmul) or the CUDA-core kernel (attention)
+      uint64_t *dw = &lp->tab.desc[lp->tab.tmaps[i].desc_word];
+      if (lp->tab.tmaps[i].owner_is_flash) {
+        b2::DFlash *f = reinterpret_cast<b2::DFlash *>(dw);
+        f->tmap = -1;
+        f->tc_mode = 0;
+      } else {
+        reinterpret_cast<b2::DMma *>(dw)->tmap = -1;
+      }
+      for (size_t j = i; j < std::min(i + group, lp->tab.tmaps.size()); ++j) lp->tmap_off[j] = 1;
     }
+    i += group;
   }
   std::vector<int32_t> aux = p.aux;
   if ((e = Upload(&lp->d_tmaps, lp->h_tmaps)) != cudaSuccess || (e = Upload(&lp->d_tasks, lp->tab.tasks)) != cudaSuccess || (e = Upload(&lp->d_entries, lp->tab.entries)) != cudaSuccess ||
@@ -460,6 +500,15 @@ b2_status b2_program_load(b2_runtime *rt, b2_program *prog, b2_loaded **out, cha
     return B2_RESOURCE_EXHAUSTED;
   }
   std::memset(lp->h_sync, 0, sizeof(b2::DSync));
+  if (lp->tab.needs_scratch) {
+    lp->scratch_bytes = sizeof(b2::RedScratch) + sizeof(unsigned long long) * p.n_lanes;   // zero = rest state of every counter
+    if ((e = cudaMalloc(reinterpret_cast<void **>(&lp->d_scratch), lp->scratch_bytes)) != cudaSuccess ||
+        (e = cudaMemset(lp->d_scratch, 0, lp->scratch_bytes)) != cudaSuccess) {
+      SetErr(err, err_cap, CudaMsg("reduction scratch allocation", e));
+      cudaGetLastError();
+      return B2_RESOURCE_EXHAUSTED;
+    }
+  }
   for (const auto &k : p.consts) {  // constants are uploaded once (runtime.cc:1064-1072)
     if (k.data.empty()) continue;
     e = cudaMemcpy(lp->arena + p.buffers[k.buffer].offset, k.data.data(), k.data.size(), cudaMemcpyHostToDevice);
@@ -492,6 +541,9 @@ uint64_t b2_loaded_stat(const b2_loaded *lp, int which) {
     case 6: return lp->tab.n_flash;
     case 7: return lp->tab.n_flash_tc;
     case 8: return lp->tab.n_spread;
+    case 9: return static_cast<uint64_t>(lp->variant);
+    case 11: return lp->tab.n_fused_reduce;
+    case 10: return lp->tab.families;
     default: return 0;
   }
 }
@@ -501,6 +553,42 @@ size_t b2_loaded_phase_ns(const b2_loaded *lp, uint64_t *out, size_t cap) {
   std::lock_guard<std::mutex> g(lp->rt->mu);
   size_t n = std::min<size_t>(std::min<size_t>(lp->h_sync->barriers, b2::kPhaseSlots), cap);
   for (size_t i = 0; i < n; ++i) out[i] = lp->h_sync->phase_ns[i];
+  return n;
+}
+
+b2_status b2_loaded_lane_timing(b2_loaded *lp, int on, char *err, size_t err_cap) {
+  if (!lp) return B2_INVALID_ARGUMENT;
+  std::lock_guard<std::mutex> g(lp->rt->mu);
+  lp->rt->Bind();
+  if (!on) {
+    if (lp->last_stream) cudaStreamSynchronize(lp->last_stream);
+    cudaFree(lp->d_lane_ts);
+    lp->d_lane_ts = nullptr;
+    return B2_OK;
+  }
+  if (lp->d_lane_ts) return B2_OK;
+  const size_t bytes = sizeof(unsigned long long) * b2::kLaneTsSlots * lp->prog.n_lanes;
+  cudaError_t e = cudaMalloc(reinterpret_cast<void **>(&lp->d_lane_ts), bytes);
+  if (e == cudaSuccess) e = cudaMemset(lp->d_lane_ts, 0, bytes);
+  if (e != cudaSuccess) {
+    SetErr(err, err_cap, CudaMsg("lane timing buffer", e));
+    cudaGetLastError();
+    return B2_RESOURCE_EXHAUSTED;
+  }
+  return B2_OK;
+}
+
+size_t b2_loaded_lane_times(b2_loaded *lp, uint64_t *out, size_t cap) {
+  if (!lp || !out || !lp->d_lane_ts) return 0;
+  std::lock_guard<std::mutex> g(lp->rt->mu);
+  lp->rt->Bind();
+  const size_t n = std::min<size_t>(cap, static_cast<size_t>(b2::kLaneTsSlots) * lp->prog.n_lanes);
+  cudaStream_t stream = lp->last_stream ? lp->last_stream : lp->rt->stream;
+  if (cudaStreamSynchronize(stream) != cudaSuccess ||
+      cudaMemcpy(out, lp->d_lane_ts, n * sizeof(uint64_t), cudaMemcpyDeviceToHost) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
   return n;
 }
 

@@ -13,19 +13,48 @@
 //  - frame-stack overflow and unknown tile ops set a status instead of corrupting state.
 #include <cuda_runtime.h>
 
+// This file is compiled once per entry of variants.h, with
+//   -DB2_VARIANT=<name> -DB2_FAMILIES=<mask>
+// and then holds only the tile-op families in the mask. The kernel and its launch
+// glue carry the variant's name; the runtime picks the build per program.
+#ifndef B2_FAMILIES
+#define B2_FAMILIES 0xFFFFFFFFu
+#define B2_VARIANT all
+#endif
+#define B2_HAS(fam) (((B2_FAMILIES) & (fam)) != 0u)
+#define B2_PASTE2(a, b) a##b
+#define B2_PASTE(a, b) B2_PASTE2(a, b)
+
 #include "dev_common.cuh"
 #include "ops_ew.cuh"
 #include "ops_ew_steps.cuh"
+#if B2_HAS(0x20u)   // kFamMma
+#include "ops_mma.cuh"
 #include "ops_mma_tc.cuh"
+#endif
+#if B2_HAS(0x40u)   // kFamFlash
 #include "ops_flash_tc.cuh"
 #include "ops_flash.cuh"
-#include "ops_mma.cuh"
+#endif
+#if B2_HAS(0x02u)   // kFamMove
 #include "ops_move.cuh"
+#endif
+#if B2_HAS(0x04u)   // kFamRed
 #include "ops_reduce.cuh"
+#endif
+#if B2_HAS(0x10u)   // kFamRegion
 #include "ops_region.cuh"
+#endif
+#if B2_HAS(0x08u)   // kFamRows
 #include "ops_rows.cuh"
+#endif
+#if B2_HAS(0x80u)   // kFamIndex
+#include "ops_index.cuh"
+#endif
 
 namespace b2 {
+static_assert(kFamMove == 0x02u && kFamRed == 0x04u && kFamRows == 0x08u && kFamRegion == 0x10u && kFamMma == 0x20u &&
+              kFamFlash == 0x40u && kFamIndex == 0x80u, "the literals in the #if lines above");
 
 constexpr int kVmThreads = 512;   // threads per lane: the one instantiation the library carries
 struct Frame { uint32_t pc, end, widx, phase; };  // phase: 0 while-cond, 1 while-body, 2 if, FOR: trips left
@@ -40,6 +69,7 @@ __device__ __forceinline__ bool grid_barrier(const Lane &L, uint32_t barrier_ind
   if (L.tid == 0) {
     bool ok = true;
     DSync *s = P.sync;
+    if (P.lane_ts && barrier_index < kPhaseSlots) P.lane_ts[L.lane * kLaneTsSlots + 2u + barrier_index] = globaltimer_ns();
     const uint32_t gen = ld_relaxed_gpu(&s->gen);
     __threadfence();  // release this lane's stores (made visible to thread 0 by the CTA barrier above)
     const uint32_t prev = atom_add_acq_rel_gpu(&s->arrive, 1u);
@@ -79,36 +109,55 @@ __device__ __forceinline__ void exec_entry(const Lane &L, const DEntry &en) {
   const KParams &P = *L.P;
   const DTask &t = P.tasks[en.task];
   switch (t.op) {
+#if B2_HAS(0x20u)
     case kTopMma: {
       const DMma &dm = *reinterpret_cast<const DMma *>(P.desc + t.desc);
       const bool tc = NT == 512 && B2_HAS_TC && (dm.tc_mode & kTcOk) && mma_tc_tiles(L, t, en.tile_lo, en.tile_hi);
       if (!tc) mma_simt_tiles<NT>(L, t, en.tile_lo, en.tile_hi);
       break;
     }
+#endif
+#if B2_HAS(0x02u)
     case kTopGather: case kTopDynGather: move_tiles(L, t, en.tile_lo, en.tile_hi, false); break;
     case kTopScatter: case kTopDynScatter: move_tiles(L, t, en.tile_lo, en.tile_hi, true); break;
-    case kTopRedPart: red_part_tiles(L, t, en.tile_lo, en.tile_hi); break;
-    case kTopRedComb: red_comb_tiles(L, t, en.tile_lo, en.tile_hi); break;
     case kTopIotaDim: iota_tiles(L, t, en.tile_lo, en.tile_hi); break;
+#endif
+#if B2_HAS(0x04u)
+    case kTopRedPart: red_part_tiles(L, t, en.tile_lo, en.tile_hi, en.a, en.b); break;
+    case kTopRedComb: red_comb_tiles(L, t, en.tile_lo, en.tile_hi); break;
     case kTopRedSeg: red_seg_tiles(L, t, en.tile_lo, en.tile_hi); break;
+    case kTopRedStrided: red_strided_tiles(L, t, en.tile_lo, en.tile_hi, en.a, en.b); break;
+#endif
+#if B2_HAS(0x08u)
     case kTopSoftmaxSeg: rows_tiles(L, t, en.tile_lo, en.tile_hi, true); break;
     case kTopLayernormSeg: rows_tiles(L, t, en.tile_lo, en.tile_hi, false); break;
+#endif
+#if B2_HAS(0x10u)
     case kTopMapRegion: region_tiles(L, t, en.tile_lo, en.tile_hi); break;
+#endif
+#if B2_HAS(0x40u)
     case kTopFlashAttn: {
       const DFlash &df = *reinterpret_cast<const DFlash *>(P.desc + t.desc);
       const bool tc = NT == 512 && B2_HAS_TC && df.tc_mode && flash_tc_tiles(L, t, en.tile_lo, en.tile_hi);
       if (!tc) flash_simt_tiles(L, t, en.tile_lo, en.tile_hi);
       break;
     }
-    case kTopRedStrided: red_strided_tiles(L, t, en.tile_lo, en.tile_hi, en.a, en.b); break;
-    default:
+#endif
+#if B2_HAS(0x80u)
+    case kTopRedWindow: red_window_tiles(L, t, en.tile_lo, en.tile_hi); break;
+    case kTopGatherIndex: indexed_tiles(L, t, en.tile_lo, en.tile_hi, false); break;
+    case kTopScatterIndex: indexed_tiles(L, t, en.tile_lo, en.tile_hi, true); break;
+    case kTopConv: conv_tiles(L, t, en.tile_lo, en.tile_hi); break;
+#endif
+    default:   // a tile op this build does not hold (the host picks the build, so: a host bug) or an unknown one
       if (L.tid == 0) set_status(P, kStBadOp, L.lane, en.task, t.op);
       break;
   }
 }
 
+#define B2_VM_KERNEL B2_PASTE(b2_vm_, B2_VARIANT)
 template <int NT>
-__global__ void __launch_bounds__(NT, 1) b2_vm(const __grid_constant__ KParams P, const uint32_t smem_bytes) {
+__global__ void __launch_bounds__(NT, 1) B2_VM_KERNEL(const __grid_constant__ KParams P, const uint32_t smem_bytes) {
   B2_DYN_SMEM(smem);
   Lane L;
   L.P = &P;
@@ -120,6 +169,7 @@ __global__ void __launch_bounds__(NT, 1) b2_vm(const __grid_constant__ KParams P
   const VmLane span = P.lanes[L.lane];
   const DEntry *stream = P.entries + span.off;
   const unsigned long long t_start = globaltimer_ns();
+  if (P.lane_ts && L.tid == 0) P.lane_ts[L.lane * kLaneTsSlots] = t_start;
 
   Frame st[kMaxDepth + 1];
   int sp = 0;
@@ -198,25 +248,26 @@ __global__ void __launch_bounds__(NT, 1) b2_vm(const __grid_constant__ KParams P
     }
     f.pc++;
   }
+  if (P.lane_ts && L.tid == 0) P.lane_ts[L.lane * kLaneTsSlots + 1u] = globaltimer_ns();
   if (L.lane == 0 && L.tid == 0) {
     P.sync->barriers = barrier_i;
     P.sync->device_ns = globaltimer_ns() - t_start;
   }
 }
 
-// ---- host-side launch glue (called from runtime.cc) ----------------------------------
-cudaError_t LaunchVm(const KParams &params, uint32_t n_lanes, int threads, uint32_t smem_bytes,
-                     cudaStream_t stream) {
+// ---- host-side launch glue (called from runtime.cc through the table in variants.h) ----
+cudaError_t B2_PASTE(LaunchVm_, B2_VARIANT)(const KParams &params, uint32_t n_lanes, int threads, uint32_t smem_bytes,
+                                            cudaStream_t stream) {
   void *args[2] = {const_cast<KParams *>(&params), &smem_bytes};
   if (threads != kVmThreads) return cudaErrorInvalidValue;
-  const void *fn = reinterpret_cast<const void *>(&b2_vm<kVmThreads>);
+  const void *fn = reinterpret_cast<const void *>(&B2_VM_KERNEL<kVmThreads>);
   return cudaLaunchCooperativeKernel(fn, dim3(n_lanes), dim3(threads), args, smem_bytes, stream);
 }
 
-// Co-resident CTAs of the megakernel at `threads` per lane and `smem_bytes` of dynamic shared memory.
-cudaError_t VmResidency(int device, int threads, uint32_t smem_bytes, int *max_lanes) {
+// Co-resident CTAs of this build at `threads` per lane and `smem_bytes` of dynamic shared memory.
+cudaError_t B2_PASTE(VmResidency_, B2_VARIANT)(int device, int threads, uint32_t smem_bytes, int *max_lanes) {
   if (threads != kVmThreads) return cudaErrorInvalidValue;
-  const void *fn = reinterpret_cast<const void *>(&b2_vm<kVmThreads>);
+  const void *fn = reinterpret_cast<const void *>(&B2_VM_KERNEL<kVmThreads>);
   cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_bytes));
   if (e != cudaSuccess) return e;
   int per_sm = 0, sms = 0;

@@ -301,9 +301,12 @@ def _rmsnorm(a, x, gain, eps):
 
 
 def c5_block(batch=8, seq=2048, d_model=1024, heads=16, d_ff=4096,
-             nlanes=NLANES, dtype=BF16, eps=1e-6):
+             nlanes=NLANES, dtype=BF16, eps=1e-6, attend_in_place=True):
     """Prefill: x (batch*seq, d_model) -> decoder block output, causal fused
-    flash-attention over (batch*heads) heads."""
+    flash-attention over (batch*heads) heads. `attend_in_place`: the head split of the
+    q / k / v projections reaches the attention op as operand views (the way the
+    reference folds reshapes and transposes into matmul operands, lowering.py:2381-2452)
+    instead of three materialised transposes."""
     hd = d_model // heads
     n = batch * seq
     a = Asm()
@@ -328,9 +331,14 @@ def c5_block(batch=8, seq=2048, d_model=1024, heads=16, d_ff=4096,
     q4 = a.reshape(q, (batch, seq, heads, hd))
     k4 = a.reshape(k, (batch, seq, heads, hd))
     v4 = a.reshape(v, (batch, seq, heads, hd))
-    qh = a.reshape(a.transpose(q4, [0, 2, 1, 3]), (batch * heads, seq, hd))
-    kt = a.reshape(a.transpose(k4, [0, 2, 3, 1]), (batch * heads, hd, seq))
-    vh = a.reshape(a.transpose(v4, [0, 2, 1, 3]), (batch * heads, seq, hd))
+    if attend_in_place:
+        qh = a.transpose_view(q4, [0, 2, 1, 3], (batch * heads, seq, hd))
+        kt = a.transpose_view(k4, [0, 2, 3, 1], (batch * heads, hd, seq))
+        vh = a.transpose_view(v4, [0, 2, 1, 3], (batch * heads, seq, hd))
+    else:
+        qh = a.reshape(a.transpose(q4, [0, 2, 1, 3]), (batch * heads, seq, hd))
+        kt = a.reshape(a.transpose(k4, [0, 2, 3, 1]), (batch * heads, hd, seq))
+        vh = a.reshape(a.transpose(v4, [0, 2, 1, 3]), (batch * heads, seq, hd))
     o = a.flash_attn(qh, kt, vh, 1.0 / math.sqrt(hd), causal=True)
     o2 = a.reshape(a.transpose(a.reshape(o, (batch, heads, seq, hd)),
                                [0, 2, 1, 3]), (n, d_model))

@@ -36,6 +36,9 @@ def gen_item(rng, item):
     if kind == "int":             # params: lo, hi (hi exclusive)
         return rng.integers(int(p[0]), int(p[1]), size=shape,
                             dtype=np.int64).astype(npdt)
+    if kind == "perm":            # params: n; the first prod(shape) entries of a permutation of range(n)
+        count = int(np.prod(shape)) if shape else 1
+        return rng.permutation(int(p[0]))[:count].reshape(shape).astype(npdt)
     if kind == "ones":
         return np.ones(shape, np.float32).astype(npdt)
     if kind == "value":           # params: the scalar value

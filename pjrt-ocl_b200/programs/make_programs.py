@@ -52,6 +52,8 @@ for stage in ("layernorm", "affine_gelu", "softmax", "sum"):
 PROGRAMS["c2_chain_f32_cpu_sample"] = lambda: cases.c2_chain(rows=512, dtype=F32)
 PROGRAMS["c2_chain_bf16_cpu_sample"] = lambda: cases.c2_chain(rows=512, dtype=BF16)
 PROGRAMS["c2_int_chain_cpu_sample"] = lambda: cases.c2_int_chain(rows=512)
+# bounded sample of config 5 for the timed CPU arm: one sequence of 512 tokens through the same block
+PROGRAMS["c5_block_bf16_cpu_sample"] = lambda: cases.c5_block(batch=1, seq=512, nlanes=16)
 PROGRAMS["c3_sgd_apply_bf16"] = lambda: cases.sgd_apply(
     [(1024, 4096), (4096, 4096), (4096, 1024)])
 

@@ -64,6 +64,15 @@ class T:
         return math.prod(self.shape) if self.shape else 1
 
 
+@dataclasses.dataclass(eq=False)
+class ViewT(T):
+    """A strided view of another tensor's buffer that has not been materialised:
+    `buf` is the SOURCE buffer, `view` the descriptor [rank, dims, strides, offset]
+    mapping the flat index of `shape` into it (the GATHER aux layout, ops/shape.py:
+    57-84). Only ops that take operand views accept one (flash_attn)."""
+    view: tuple = ()
+
+
 class Asm:
     def __init__(self):
         self.ctx = L._Ctx()
@@ -143,6 +152,19 @@ class Asm:
         ins = _strides(x.shape)
         out_shape = [x.shape[p] for p in perm]
         return self._gather(x, out_shape, [ins[p] for p in perm])
+
+    def transpose_view(self, x: T, perm, reshape_to=None) -> ViewT:
+        """The transpose as an operand view instead of a gather: nothing is emitted;
+        the consumer reads `x`'s buffer through the strides. `reshape_to` regroups the
+        transposed axes (same element order)."""
+        ins = _strides(x.shape)
+        dims = [x.shape[p] for p in perm]
+        strides = [ins[p] for p in perm]
+        shape = tuple(reshape_to) if reshape_to is not None else tuple(dims)
+        assert math.prod(shape) == x.n
+        t = ViewT(x.buf, shape, x.dtype, tuple([len(dims)] + dims + strides + [0]))
+        self._keep.append(t)
+        return t
 
     def slice(self, x: T, starts, limits, strides=None) -> T:
         """ops/shape.py:131-153."""
@@ -293,6 +315,94 @@ class Asm:
                                   imm2=inner))
         return out
 
+    def reduce_window(self, x: T, window, strides=None, pad_low=None, pad_high=None, kind=SUM) -> T:
+        """stablehlo.reduce_window without dilations (ops/reduce_window.py:104-145):
+        OP_REDUCE_WINDOW with aux [kind, rank, out, win, stride, pad_low, in dims,
+        in strides]; padding elements are the reduction's identity."""
+        rank = len(x.shape)
+        strides = list(strides or [1] * rank)
+        pad_low = list(pad_low or [0] * rank)
+        pad_high = list(pad_high or [0] * rank)
+        out_shape = [(x.shape[d] + pad_low[d] + pad_high[d] - window[d]) // strides[d] + 1
+                     for d in range(rank)]
+        aux = ([kind, rank] + out_shape + list(window) + strides + pad_low
+               + list(x.shape) + _strides(x.shape))
+        d = self._new(out_shape, x.dtype)
+        self.ctx.emit(L.Instr(L.OP_REDUCE_WINDOW, dst=d.buf, a=x.buf, n=d.n,
+                              aux=self.ctx.add_aux(aux)))
+        return d
+
+    def gather_index(self, operand: T, indices: T, out_shape, op_stride, si_stride,
+                     idx_op_stride, clamp_max, si_vec_stride=0) -> T:
+        """stablehlo.gather as the reference plans it (ops/gather_index.py:128-143):
+        OP_GATHER_INDEX with aux [out_rank, nidx, si_vec_stride, is64, 0, idx buffer,
+        out dims, operand stride per out dim, indices stride per out dim, operand
+        stride per index component, clamp per component]."""
+        is64 = 1 if indices.dtype == I64 else 0
+        aux = ([len(out_shape), len(idx_op_stride), si_vec_stride, is64, 0, indices.buf]
+               + list(out_shape) + list(op_stride) + list(si_stride)
+               + list(idx_op_stride) + list(clamp_max))
+        d = self._new(out_shape, operand.dtype)
+        self.ctx.emit(L.Instr(L.OP_GATHER_INDEX, dst=d.buf, a=operand.buf, n=d.n,
+                              aux=self.ctx.add_aux(aux), reads_hint=(indices.buf,)))
+        return d
+
+    def take_rows(self, table: T, idx: T) -> T:
+        """table[idx] for a 2-D table and a 1-D index vector (an embedding lookup):
+        offset dim 1 walks a row, index component 0 picks it."""
+        v, dcols = table.shape
+        return self.gather_index(table, idx, (idx.shape[0], dcols), [0, 1], [1, 0],
+                                 [dcols], [v - 1])
+
+    def take_points(self, x: T, idx: T) -> T:
+        """x[idx[:, 0], idx[:, 1]] for a 2-D x and an (n, 2) index matrix."""
+        r, c = x.shape
+        return self.gather_index(x, idx, (idx.shape[0],), [0], [2], [c, 1],
+                                 [r - 1, c - 1], si_vec_stride=1)
+
+    def scatter_index(self, operand: T, indices: T, updates: T, kind: int, op_stride,
+                      si_stride, idx_op_stride, clamp_max, si_vec_stride=0) -> T:
+        """stablehlo.scatter (ops/scatter_index.py:196-216): an identity-gather copy
+        of the operand, then OP_SCATTER_INDEX combining the updates into it.
+        kind: 0 set, 1 add, 2 max, 3 min."""
+        is64 = 1 if indices.dtype == I64 else 0
+        out = self._new(operand.shape, operand.dtype)
+        caux = self.ctx.add_aux([len(operand.shape)] + list(operand.shape)
+                                + _strides(operand.shape) + [0])
+        self.ctx.emit(L.Instr(L.OP_GATHER_STRIDED, dst=out.buf, a=operand.buf,
+                              n=operand.n, aux=caux))
+        aux = ([len(updates.shape), len(idx_op_stride), si_vec_stride, is64, 0, indices.buf, kind]
+               + list(updates.shape) + list(op_stride) + list(si_stride)
+               + list(idx_op_stride) + list(clamp_max))
+        self.ctx.emit(L.Instr(L.OP_SCATTER_INDEX, dst=out.buf, a=updates.buf,
+                              n=updates.n, aux=self.ctx.add_aux(aux),
+                              reads_hint=(indices.buf,)))
+        return out
+
+    def scatter_rows(self, table: T, idx: T, upd: T, kind: int) -> T:
+        """table.at[idx].{set,add,max,min}(upd): 2-D table, 1-D indices, (n, cols) updates."""
+        v, dcols = table.shape
+        return self.scatter_index(table, idx, upd, kind, [0, 1], [1, 0], [dcols], [v - 1])
+
+    def conv(self, x: T, w: T, strides=None, pad_low=None, pad_high=None, dilation=None) -> T:
+        """stablehlo.convolution in the canonical layout (ops/conv.py:131-143):
+        x [B, S..., Cin], w [W..., Cin, Cout] -> [B, O..., Cout], f32."""
+        sdim = len(x.shape) - 2
+        strides = list(strides or [1] * sdim)
+        pad_low = list(pad_low or [0] * sdim)
+        pad_high = list(pad_high or [0] * sdim)
+        dilation = list(dilation or [1] * sdim)
+        spatial, win = list(x.shape[1:1 + sdim]), list(w.shape[:sdim])
+        cin, cout = x.shape[-1], w.shape[-1]
+        assert w.shape[sdim] == cin
+        out_sp = [(spatial[d] + pad_low[d] + pad_high[d] - (win[d] - 1) * dilation[d] - 1)
+                  // strides[d] + 1 for d in range(sdim)]
+        aux = [sdim, cin, cout] + out_sp + win + strides + pad_low + dilation + spatial
+        d = self._new([x.shape[0]] + out_sp + [cout], F32)
+        self.ctx.emit(L.Instr(L.OP_CONV, dst=d.buf, a=x.buf, b=w.buf, n=d.n,
+                              aux=self.ctx.add_aux(aux)))
+        return d
+
     def softmax_fused(self, x: T) -> T:
         """OP_SOFTMAX over the last axis (ops/reduce.py:478-491; emitted by
         `_fuse_norm`, lowering.py:1561-1730, for seg <= 1024 - here for any seg)."""
@@ -358,8 +468,11 @@ class Asm:
         H, Tq, hd = q.shape
         C = kT.shape[2]
         assert kT.shape == (H, hd, C) and v.shape == (H, C, hd)
+        # operands given as views are read in place: descriptor words 6..8 hold 1 + the
+        # aux offset of each operand's view (0 = contiguous), ops/attention.py:16-19
+        views = [self.ctx.add_aux(list(o.view)) + 1 if isinstance(o, ViewT) else 0 for o in (q, kT, v)]
         aux = self.ctx.add_aux([H, Tq, C, hd, L._f32_bits(scale),
-                                1 if causal else 0, 0, 0, 0])
+                                1 if causal else 0] + views)
         d = self._new((H, Tq, hd), q.dtype if out_dtype is None else out_dtype)
         self.ctx.emit(L.Instr(L.OP_FLASH_ATTN, dst=d.buf, a=q.buf, b=kT.buf,
                               n=H, imm=Tq, aux=aux, imm2=v.buf))

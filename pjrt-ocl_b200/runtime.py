@@ -97,6 +97,7 @@ EXPORTS = [
     "b2_loaded_program", "b2_execute_host", "b2_execute_device", "b2_execute_device_async",
     "b2_loaded_status", "b2_loaded_launch_count", "b2_loaded_set_wait_budget_ns",
     "b2_loaded_phase_ns", "b2_loaded_stat", "b2_sum_f32_static", "b2_sum_f32_static_max_elems",
+    "b2_loaded_lane_timing", "b2_loaded_lane_times",
 ]
 
 
@@ -142,6 +143,8 @@ def lib():
         "b2_loaded_set_wait_budget_ns": (None, [vp, ctypes.c_uint64]),
         "b2_loaded_phase_ns": (sz, [vp, ctypes.POINTER(ctypes.c_uint64), sz]),
         "b2_loaded_stat": (ctypes.c_uint64, [vp, ctypes.c_int]),
+        "b2_loaded_lane_timing": (ctypes.c_int, [vp, ctypes.c_int, cp, sz]),
+        "b2_loaded_lane_times": (sz, [vp, ctypes.POINTER(ctypes.c_uint64), sz]),
         "b2_sum_f32_static": (ctypes.c_int, [ctypes.c_int, vp, ctypes.c_uint64, vp, vp, cp, sz]),
         "b2_sum_f32_static_max_elems": (ctypes.c_uint64, []),
     }
@@ -360,8 +363,43 @@ class LoadedProgram:
         n = lib().b2_loaded_phase_ns(self._h, buf, 64)
         return [int(buf[i]) for i in range(n)]
 
+    def LaneTiming(self, on: bool = True) -> None:
+        """Switch per-lane timestamps on or off for the next executes."""
+        err = _errbuf()
+        _check(lib().b2_loaded_lane_timing(self._h, 1 if on else 0, err, _ERRCAP), err)
+
+    def LaneReport(self) -> dict:
+        """Per-phase wall time, arrival skew and mean idle of the last execute, and
+        the mean lane utilisation over the launch - the figures the reference prints
+        under PJRT_OCL_PHASE_TS (runtime.cc:2196-2240), from every lane's arrival
+        time at every grid barrier. Empty when lane timing is off."""
+        slots = 66
+        n = self.prog.n_lanes * slots
+        buf = (ctypes.c_uint64 * n)()
+        got = lib().b2_loaded_lane_times(self._h, buf, n)
+        if got != n:
+            return {}
+        t = np.frombuffer(buf, dtype=np.uint64).reshape(self.prog.n_lanes, slots).astype(np.int64)
+        start = int(t[:, 0].min())
+        phases, prev = [], start
+        for b in range(64):
+            arr = t[:, 2 + b]
+            if not arr.all():
+                break
+            release = int(arr.max())
+            phases.append({"wall_ns": release - prev, "skew_ns": release - int(arr.min()),
+                           "idle_ns": float(release - arr.mean())})
+            prev = release
+        end = int(t[:, 1].max())
+        tail = {"wall_ns": end - prev, "skew_ns": end - int(t[:, 1].min()), "idle_ns": float(end - t[:, 1].mean())}
+        wall = sum(p["wall_ns"] for p in phases) + tail["wall_ns"]
+        idle = sum(p["idle_ns"] for p in phases) + tail["idle_ns"]
+        return {"phases": phases, "tail": tail, "total_ns": end - start,
+                "mean_lane_util": 1.0 - idle / wall if wall else 0.0}
+
     _STATS = {"chains": 0, "forwarded": 0 + 1, "dead_stores": 2, "matmuls": 3, "tensor_core_matmuls": 4,
-              "matmul_flops": 5, "flash": 6, "tensor_core_flash": 7, "spread_reductions": 8}
+              "matmul_flops": 5, "flash": 6, "tensor_core_flash": 7, "spread_reductions": 8,
+              "kernel_build": 9, "families": 10, "fused_full_reductions": 11}
 
     def stat(self, name: str) -> int:
         """Load-time mapping facts, by name (see `_STATS`)."""

@@ -444,6 +444,113 @@ def _():
     return blob, prog, (18, [N((RAG,)), N((RAG,)), N((RAG,))])
 
 
+# ---------------------------------------------------------------- windows, indexed moves, convolution
+@case("reduce_window_f32", rtol=1e-5, atol=1e-5)
+def _():
+    """Pooling shapes: channel-last 2x2/2 max and 3x3/2 padded sum (NHWC), a
+    window over the innermost axes (NCHW) with padding, and a 1-D running min."""
+    a = Asm()
+    x = a.input((2, 17, 19, 8), F32)
+    y = a.input((3, 4, 21, 22), F32)
+    z = a.input((5003,), F32)
+    outs = [a.reduce_window(x, (1, 2, 2, 1), (1, 2, 2, 1), kind=MAX),
+            a.reduce_window(x, (1, 3, 3, 1), (1, 2, 2, 1), (0, 1, 1, 0), (0, 1, 1, 0), kind=SUM),
+            a.reduce_window(y, (1, 1, 3, 3), (1, 1, 1, 2), (0, 0, 1, 2), (0, 0, 1, 0), kind=MAX),
+            a.reduce_window(z, (7,), (3,), (2,), (4,), kind=MIN)]
+    blob, prog = a.finish(outs, nlanes=5)
+    return blob, prog, (40, [N((2, 17, 19, 8)), N((3, 4, 21, 22)), N((5003,))])
+
+
+@case("reduce_window_int", exact=True)
+def _():
+    a = Asm()
+    x = a.input((3, 33, 12), I32)
+    u = a.input((40, 36), U32)
+    outs = [a.reduce_window(x, (1, 4, 1), (1, 3, 1), (0, 2, 0), (0, 1, 0), kind=SUM),
+            a.reduce_window(x, (2, 2, 2), (1, 1, 2), kind=MAX),
+            a.reduce_window(u, (3, 3), (2, 1), (1, 1), (1, 1), kind=MAX),
+            a.reduce_window(u, (2, 5), (2, 3), kind=MIN)]
+    blob, prog = a.finish(outs, nlanes=3)
+    return blob, prog, (41, [I((3, 33, 12), -2 ** 30, 2 ** 30), I((40, 36), 0, 2 ** 32, "u32")])
+
+
+@case("gather_index", exact=True)
+def _():
+    """Embedding-style row lookups (f32 rows of 64, bf16 rows of 40, i64 rows of 3,
+    i64 indices, out-of-range indices clamped) and a two-component point gather."""
+    a = Asm()
+    tab = a.input((300, 64), F32)
+    tb = a.input((129, 40), BF16)
+    tl = a.input((50, 3), I64)
+    grid = a.input((37, 53), I32)
+    i1 = a.input((1200,), I32)
+    i2 = a.input((700,), I64)
+    i3 = a.input((900, 2), I32)
+    outs = [a.take_rows(tab, i1), a.take_rows(tb, i2), a.take_rows(tl, i2), a.take_points(grid, i3)]
+    blob, prog = a.finish(outs, nlanes=6)
+    return blob, prog, (42, [N((300, 64)), N((129, 40), "bf16"), I((50, 3), -2 ** 40, 2 ** 40, "i64"),
+                             I((37, 53), -1000, 1000), I((1200,), -5, 305), I((700,), -3, 140, "i64"),
+                             I((900, 2), -2, 56)])
+
+
+@case("scatter_index_exact", exact=True)
+def _():
+    """Overwrite with unique indices (any order gives the same bytes) and the
+    integer combiners with heavily duplicated indices (order-free, bit-exact)."""
+    a = Asm()
+    tab = a.input((400, 16), F32)
+    ti = a.input((64, 8), I32)
+    tu = a.input((64, 8), U32)
+    uniq = a.input((250,), I32)
+    dup = a.input((3000,), I32)
+    uf = a.input((250, 16), F32)
+    ui = a.input((3000, 8), I32)
+    uu = a.input((3000, 8), U32)
+    outs = [a.scatter_rows(tab, uniq, uf, 0), a.scatter_rows(ti, dup, ui, 1), a.scatter_rows(ti, dup, ui, 2),
+            a.scatter_rows(ti, dup, ui, 3), a.scatter_rows(tu, dup, uu, 1), a.scatter_rows(tu, dup, uu, 2),
+            a.scatter_rows(tu, dup, uu, 3)]
+    blob, prog = a.finish(outs, nlanes=4)
+    return blob, prog, (43, [N((400, 16)), I((64, 8), -10 ** 6, 10 ** 6), I((64, 8), 0, 2 ** 32, "u32"),
+                             ("perm", (250,), "i32", 400), I((3000,), -4, 70),
+                             N((250, 16)), I((3000, 8), -10 ** 6, 10 ** 6), I((3000, 8), 0, 2 ** 32, "u32")])
+
+
+@case("scatter_index_f32", exact=True)
+def _():
+    """f32 combiners with duplicate indices. max / min are order-free; add sums ~47
+    updates per row in whatever order the lanes reach them, so the values are small
+    integers: every partial sum is exact and the result is the same in any order
+    (the reference's lane simulator refuses a phase whose result depends on lane order)."""
+    a = Asm()
+    tab = a.input((64, 32), F32)
+    dup = a.input((3000,), I32)
+    upd = a.input((3000, 32), F32)
+    outs = [a.scatter_rows(tab, dup, upd, 1), a.scatter_rows(tab, dup, upd, 2), a.scatter_rows(tab, dup, upd, 3)]
+    blob, prog = a.finish(outs, nlanes=4)
+    return blob, prog, (44, [I((64, 32), -50, 50, "f32"), I((3000,), -4, 70), I((3000, 32), -64, 64, "f32")])
+
+
+@case("conv_f32", rtol=1e-5, atol=2e-5)
+def _():
+    """1-D, 2-D (stride, padding, dilation; Cout not a multiple of 4) and 3-D convolutions."""
+    a = Asm()
+    x1 = a.input((3, 50, 5), F32)
+    w1 = a.input((4, 5, 7), F32)
+    x2 = a.input((2, 15, 14, 6), F32)
+    w2 = a.input((3, 3, 6, 16), F32)
+    w2b = a.input((2, 3, 6, 5), F32)
+    x3 = a.input((1, 6, 7, 5, 3), F32)
+    w3 = a.input((2, 2, 2, 3, 8), F32)
+    outs = [a.conv(x1, w1, (2,), (1,), (2,)),
+            a.conv(x2, w2, (1, 1), (1, 1), (1, 1)),
+            a.conv(x2, w2b, (2, 1), (0, 2), (1, 0), (2, 1)),
+            a.conv(x3, w3, (1, 2, 1))]
+    blob, prog = a.finish(outs, nlanes=4)
+    return blob, prog, (45, [N((3, 50, 5)), N((4, 5, 7), "f32", 0.3), N((2, 15, 14, 6)),
+                             N((3, 3, 6, 16), "f32", 0.2), N((2, 3, 6, 5), "f32", 0.2),
+                             N((1, 6, 7, 5, 3)), N((2, 2, 2, 3, 8), "f32", 0.3)])
+
+
 # ---------------------------------------------------------------- control flow
 @case("golden_layout_kat", exact=True)
 def _():

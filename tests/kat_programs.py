@@ -191,7 +191,60 @@ def kat_strided_reduce_in_control_ranges():
     return b.serialize(), [x, z0], out
 
 
+def kat_full_reduce_recut():
+    """Three full reductions (RED_PART + RED_COMB) a loader can re-cut over all lanes:
+    an i32 sum with a ragged tail (70003 elements, wraps exactly), an f32 max, and a u32
+    xor inside a FOR body of 3 trips whose result is accumulated each trip - the lanes'
+    arrival counter must return to rest between the trips."""
+    RED_PART, RED_COMB = 3, 4
+    n, chunk, lanes = 70003, 16384, 4
+    parts = -(-n // chunk)
+    b = Builder(lanes)
+    bi, bf, bu = b.buf(n, 1), b.buf(n, 0), b.buf(n, 2)
+    pi, pf, pu = b.buf(parts, 1), b.buf(parts, 0), b.buf(parts, 2)
+    oi, of, ou, acc = b.buf(1, 1), b.buf(1, 0), b.buf(1, 2), b.buf(1, 2)
+    b.inputs, b.outputs = [bi, bf, bu, acc], [oi, of, acc]
+    b.in_dims, b.out_dims = [[n], [n], [n], []], [[], [], []]
+    t_pi = b.task(RED_PART, pi, bi, bi, n, chunk, 0, dtype=1, adtype=1)
+    t_ci = b.task(RED_COMB, oi, pi, pi, parts, 0, dtype=1, adtype=1)
+    t_pf = b.task(RED_PART, pf, bf, bf, n, chunk, 1)
+    t_cf = b.task(RED_COMB, of, pf, pf, parts, 1)
+    t_pu = b.task(RED_PART, pu, bu, bu, n, chunk, 6, dtype=2, adtype=2)
+    t_cu = b.task(RED_COMB, ou, pu, pu, parts, 6, dtype=2, adtype=2)
+    t_acc = b.task(EW, acc, acc, ou, 0, 1, dtype=2, adtype=2)          # acc += xor(bu)
+    split = [(parts * l // lanes, parts * (l + 1) // lanes) for l in range(lanes)]
+    # root: i32 parts | barrier | i32 comb + f32 parts | barrier | f32 comb | barrier | FOR 3 x {parts | comb | acc}
+    for l, (lo, hi) in enumerate(split):
+        b.ent(l, t_pi, lo, hi)
+        b.ent(l, BARRIER)
+        if l == 0:
+            b.ent(l, t_ci, 0, 1)
+        else:
+            b.ent(l, NOP)
+        b.ent(l, BARRIER)
+        b.ent(l, t_pf, lo, hi)
+        b.ent(l, BARRIER)
+        b.ent(l, t_cf, 0, 1) if l == 1 else b.ent(l, NOP)
+        b.ent(l, BARRIER)
+        b.ent(l, FOR, 9, 5, 3)                      # entry 8: body [9, 14)
+        b.ent(l, t_pu, lo, hi)                      # 9
+        b.ent(l, BARRIER)                           # 10
+        b.ent(l, t_cu, 0, 1) if l == 2 else b.ent(l, NOP)   # 11
+        b.ent(l, BARRIER)                           # 12
+        b.ent(l, t_acc, 0, 1) if l == 2 else b.ent(l, NOP)  # 13
+    b.root_lens = [9] * lanes
+    rng = np.random.default_rng(11)
+    xi = rng.integers(-2 ** 31, 2 ** 31, size=n, dtype=np.int64).astype(np.int32)
+    xf = rng.standard_normal(n).astype(np.float32)
+    xu = rng.integers(0, 2 ** 32, size=n, dtype=np.int64).astype(np.uint32)
+    a0 = np.uint32(12345)
+    want_i = np.int32((int(np.sum(xi.astype(np.int64))) + 2 ** 31) % 2 ** 32 - 2 ** 31)   # two's-complement wrap
+    want_u = np.uint32((int(a0) + 3 * int(np.bitwise_xor.reduce(xu))) % 2 ** 32)
+    return b.serialize(), [xi, xf, xu, a0], [want_i, np.max(xf), want_u]
+
+
 ALL = {
     "A_two_level": kat_a_two_level, "B_while": kat_b_while, "C_region_gelu": kat_c_region_gelu,
     "while_counter": kat_while_counter, "int_div_zero": kat_int_div_zero,
+    "full_reduce_recut": kat_full_reduce_recut,
 }

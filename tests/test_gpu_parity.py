@@ -103,6 +103,31 @@ def test_strided_reduce_spread_over_lanes_in_control_ranges(rt, flag):
         np.testing.assert_array_equal(np.asarray(o).view(np.float32).reshape(e.shape), e)
 
 
+def test_full_reductions_are_recut_over_all_lanes(rt):
+    """RED_PART + RED_COMB pairs whose partials nothing else reads run as one phase:
+    every lane reduces an equal share and the last lane to arrive stores the result."""
+    vm = package()
+    blob, args, expected = K.kat_full_reduce_recut()
+    lp = vm.LoadedProgram.Load(rt, vm.VmProgram.Parse(blob))
+    assert lp.stat("fused_full_reductions") == 3
+    for _ in range(2):                     # twice: the arrival counter is back at rest after a run
+        out = lp.Execute(args)
+        np.testing.assert_array_equal(out[0], expected[0])
+        np.testing.assert_array_equal(out[1], expected[1])
+        np.testing.assert_array_equal(out[2], expected[2])
+        args[3] = np.uint32(out[2])
+        expected[2] = np.uint32((int(out[2]) + 3 * int(np.bitwise_xor.reduce(args[2]))) % 2 ** 32)
+
+
+@pytest.mark.parametrize("name,build", [("c2_chain_f32_small", "stream"), ("dot_tc_bf16", "matmul"),
+                                         ("flash_tc_bf16", "attn"), ("reduce_window_f32", "all")])
+def test_program_runs_on_the_smallest_kernel_build_that_has_its_families(rt, name, build):
+    vm = package()
+    from conftest import Golden
+    lp = vm.LoadedProgram.Load(rt, vm.VmProgram.Parse(Golden(name).blob))
+    assert ["stream", "matmul", "attn", "all"][lp.stat("kernel_build")] == build
+
+
 def test_config4_reductions_are_spread_over_lanes(rt):
     vm = package()
     from conftest import Golden
