@@ -59,6 +59,7 @@ struct FaShared {
 };
 static_assert(sizeof(FaShared) <= 512, "fits the scratch slot");
 
+template <typename Lane>
 static __device__ __noinline__ bool flash_tc_tiles(const Lane &L, const DTask &t, uint32_t tile_lo, uint32_t tile_hi) {
   const KParams &P = *L.P;
   const DFlash &df = *reinterpret_cast<const DFlash *>(P.desc + t.desc);
@@ -184,53 +185,78 @@ static __device__ __noinline__ bool flash_tc_tiles(const Lane &L, const DTask &t
         const uint32_t idesc_s = (1u << 4) | (fmt << 7) | (fmt << 10) | ((k_mn ? 1u : 0u) << 16) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
         const uint32_t idesc_o = (1u << 4) | (fmt << 7) | (fmt << 10) | (1u << 16) | ((64u >> 3) << 17) | ((128u >> 4) << 24);
         bool ok = tc_wait(&S->q_full, qn & 1u, failed, budget);
-        uint32_t kv_seen = 0;     // key blocks of this unit whose arrival has been waited for
-        auto need_kv = [&](int64_t j) {
-          while (ok && static_cast<int64_t>(kv_seen) <= j) {
-            const uint32_t pos = kvpos + kv_seen, st = pos % kFaStages;
-            if (!tc_wait(&S->kv_full[st], (pos / kFaStages) & 1u, failed, budget)) { ok = false; break; }
-            ++kv_seen;
-          }
-          tc_fence_after_sync();
-        };
-        auto issue_s = [&](int s, int64_t j) {
-          need_kv(j);
-          if (!ok) return;
-          const uint32_t use = cnt[s] + static_cast<uint32_t>(j);
-          if (j > 0 && !tc_wait(&S->s_free[s], (use - 1u) & 1u, failed, budget)) { ok = false; return; }
-          tc_fence_after_sync();
-          const uint32_t st = (kvpos + static_cast<uint32_t>(j)) % kFaStages;
-          const uint64_t da = tc_desc(q_s + static_cast<uint32_t>(s) * kFaTile, 16u, 1024u);
-          const uint64_t db = k_mn ? tc_desc(kv_s + st * 2u * kFaTile, 8192u, 1024u) : tc_desc(kv_s + st * 2u * kFaTile, 16u, 1024u);
-          const uint64_t adv_b = k_mn ? (2048u >> 4) : (32u >> 4);
+        tc_fence_after_sync();
+        // Descriptors of stage 0 / slot 0; the others differ in the 16-byte-unit address field only.
+        const uint64_t dq0 = tc_desc(q_s, 16u, 1024u), dp0 = tc_desc(p_s, 16u, 1024u);
+        const uint64_t dk0 = k_mn ? tc_desc(kv_s, 8192u, 1024u) : tc_desc(kv_s, 16u, 1024u);
+        const uint64_t dv0 = tc_desc(kv_s + kFaTile, 16384u, 1024u);
+        const uint64_t adv_b = k_mn ? (2048u >> 4) : (32u >> 4);
+        // The issuer is an event loop over both slots: S(j+1) of a slot goes out as soon as the slot's
+        // scores are in registers (s_free) and the keys have landed; P.V(j) when the slot's P is written.
+        // S is tried first, so the next scores are ready when the softmax warps finish a block.
+        int64_t ns[2] = {0, 0}, npv[2] = {0, 0}, released = 0;
+        uint32_t kv_seen = 0, idle = 0;
+        unsigned long long t_idle = 0;
+        while (ok) {
+          bool progressed = false, done = true;
 #pragma unroll
-          for (uint32_t kk = 0; kk < 4; ++kk)
-            tc_mma_f16(tmem + static_cast<uint32_t>(s) * 128u, da + kk * (32u >> 4), db + kk * adv_b, idesc_s, kk ? 1u : 0u);
-          tc_commit(&S->s_full[s]);
-        };
-        auto issue_pv = [&](int s, int64_t j) {
-          const uint32_t use = cnt[s] + static_cast<uint32_t>(j);
-          if (!tc_wait(&S->p_full[s], use & 1u, failed, budget)) { ok = false; return; }
-          tc_fence_after_sync();
-          const uint32_t st = (kvpos + static_cast<uint32_t>(j)) % kFaStages;
-          const uint32_t pb = p_s + static_cast<uint32_t>(s) * kFaPBytes;
-          const uint64_t dv = tc_desc(kv_s + st * 2u * kFaTile + kFaTile, 16384u, 1024u);
+          for (int s = 0; s < 2; ++s) {
+            if (ns[s] < nkb[s]) {
+              done = false;
+              const int64_t j = ns[s];
+              if (static_cast<int64_t>(kv_seen) <= j) {
+                const uint32_t pos = kvpos + kv_seen;
+                if (mbar_test_wait_parity(&S->kv_full[pos % kFaStages], (pos / kFaStages) & 1u)) ++kv_seen;
+              }
+              if (static_cast<int64_t>(kv_seen) > j &&
+                  (j == 0 || mbar_test_wait_parity(&S->s_free[s], (cnt[s] + static_cast<uint32_t>(j) - 1u) & 1u))) {
+                tc_fence_after_sync();
+                const uint32_t st = (kvpos + static_cast<uint32_t>(j)) % kFaStages;
+                const uint64_t da = dq0 + static_cast<uint32_t>(s) * (kFaTile >> 4);
+                const uint64_t db = dk0 + st * ((2u * kFaTile) >> 4);
 #pragma unroll
-          for (uint32_t kk = 0; kk < 8; ++kk) {
-            const uint64_t dp = tc_desc(pb + (kk >> 2) * 16384u + (kk & 3u) * 32u, 16u, 1024u);
-            tc_mma_f16(tmem + 256u + static_cast<uint32_t>(s) * 64u, dp, dv + kk * (2048u >> 4), idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+                for (uint32_t kk = 0; kk < 4; ++kk)
+                  tc_mma_f16(tmem + static_cast<uint32_t>(s) * 128u, da + kk * (32u >> 4), db + kk * adv_b, idesc_s, kk ? 1u : 0u);
+                tc_commit(&S->s_full[s]);
+                ++ns[s];
+                progressed = true;
+              }
+            }
+            if (npv[s] < nkb[s]) {
+              done = false;
+              const int64_t j = npv[s];
+              if (ns[s] > j && mbar_test_wait_parity(&S->p_full[s], (cnt[s] + static_cast<uint32_t>(j)) & 1u)) {
+                tc_fence_after_sync();
+                const uint32_t st = (kvpos + static_cast<uint32_t>(j)) % kFaStages;
+                const uint64_t dp = dp0 + static_cast<uint32_t>(s) * (kFaPBytes >> 4);
+                const uint64_t dv = dv0 + st * ((2u * kFaTile) >> 4);
+#pragma unroll
+                for (uint32_t kk = 0; kk < 8; ++kk)
+                  tc_mma_f16(tmem + 256u + static_cast<uint32_t>(s) * 64u, dp + ((kk >> 2) * 16384u + (kk & 3u) * 32u) / 16u,
+                             dv + kk * (2048u >> 4), idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+                tc_commit(&S->pv_done[s]);
+                ++npv[s];
+                progressed = true;
+              }
+            }
           }
-          tc_commit(&S->pv_done[s]);
-        };
-        for (int s = 0; ok && s < 2; ++s)
-          if (nkb[s] > 0) issue_s(s, 0);
-        for (int64_t j = 0; ok && j < nmax; ++j) {
-          for (int s = 0; ok && s < 2; ++s) {
-            if (j < nkb[s]) issue_pv(s, j);
-            if (ok && j + 1 < nkb[s]) issue_s(s, j + 1);
+          // a stage is free when the matmuls of both slots that read it have completed
+          while (released < nmax && (released >= nkb[0] || npv[0] > released) && (released >= nkb[1] || npv[1] > released)) {
+            tc_commit(&S->kv_empty[(kvpos + static_cast<uint32_t>(released)) % kFaStages]);
+            ++released;
           }
-          // both slots' matmuls on stage j are issued: free it when they have read it
-          if (ok) tc_commit(&S->kv_empty[(kvpos + static_cast<uint32_t>(j)) % kFaStages]);
+          if (done) break;
+          if (progressed) {
+            idle = 0;
+            continue;
+          }
+          nanosleep_ns(32);      // leave the issue slots to the softmax warps of this scheduler
+          if ((++idle & 1023u) == 0u) {
+            if (*failed) { ok = false; break; }
+            const unsigned long long now = globaltimer_ns();
+            if (idle == 1024u) t_idle = now;
+            else if (now - t_idle > budget) { *failed = 1u; ok = false; break; }
+          }
         }
       }
       __syncwarp();
@@ -254,7 +280,7 @@ static __device__ __noinline__ bool flash_tc_tiles(const Lane &L, const DTask &t
         tc_fence_after_sync();
         const int lim = static_cast<int>(max(static_cast<int64_t>(0), min(static_cast<int64_t>(128), c_end - j * 128)));
         // pass 1: the row's maximum over this block
-        float mx = -INFINITY;
+        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};     // four independent chains
 #pragma unroll 1
         for (int cb = 0; cb < 128; cb += 32) {
           uint32_t raw[32];
@@ -263,13 +289,14 @@ static __device__ __noinline__ bool flash_tc_tiles(const Lane &L, const DTask &t
           tc_wait_ld();
           if (cb + 32 <= lim) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(raw[i]));
+            for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(raw[i]));
           } else {
 #pragma unroll
             for (int i = 0; i < 32; ++i)
-              if (cb + i < lim) mx = fmaxf(mx, __uint_as_float(raw[i]));
+              if (cb + i < lim) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(raw[i]));
           }
         }
+        float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
         mx *= sl2;     // sl2 > 0 for every softmax scale in use; a non-positive scale takes the CUDA-core path
         // the maximum in use moves only when the row's true maximum outgrew it by 2^8
         const bool grow_m = mx > m_used + kFaRescale;
@@ -293,7 +320,7 @@ static __device__ __noinline__ bool flash_tc_tiles(const Lane &L, const DTask &t
         if (grow_m) { l_run *= alpha; m_used = mx; }
         const float neg_m = m_used == -INFINITY ? 0.0f : -m_used;
         // pass 2: p = 2^(s - m_used), written as the 16-bit A operand of the second matmul
-        float psum = 0.0f;
+        float ps4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll 1
         for (int cb = 0; cb < 128; cb += 32) {
           uint32_t raw[32];
@@ -322,7 +349,7 @@ static __device__ __noinline__ bool flash_tc_tiles(const Lane &L, const DTask &t
             for (int i = 0; i < 16; ++i) pk[i] = f32_to_f16_bits(pv[2 * i]) | (f32_to_f16_bits(pv[2 * i + 1]) << 16);
           }
 #pragma unroll
-          for (int i = 0; i < 32; ++i) psum += pv[i];
+          for (int i = 0; i < 32; ++i) ps4[i & 3] += pv[i];
           // 32 keys = 4 chunks of 8 in the row's 128-byte line of sub-tile cb / 64
           const uint32_t sub = prow + (static_cast<uint32_t>(cb) >> 6) * 16384u;
 #pragma unroll
@@ -332,7 +359,7 @@ static __device__ __noinline__ bool flash_tc_tiles(const Lane &L, const DTask &t
             *dstp = make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
           }
         }
-        l_run += psum;
+        l_run += (ps4[0] + ps4[1]) + (ps4[2] + ps4[3]);
         tc_fence_before_sync();
         fence_proxy_async_smem();               // P (generic-proxy stores) -> the MMA's reads
         __syncwarp();

@@ -249,6 +249,18 @@ __device__ __forceinline__ bool mbar_try_wait_parity(uint64_t *bar, uint32_t par
       : "memory");
   return ok != 0;
 }
+// The non-blocking form: one look at the phase (try_wait may suspend the thread for a while).
+__device__ __forceinline__ bool mbar_test_wait_parity(uint64_t *bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_addr(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
 // Bounded wait: returns false when `budget_ns` ran out (the caller records a
 // status and abandons the tile; nothing spins forever).
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity, unsigned long long budget_ns) {

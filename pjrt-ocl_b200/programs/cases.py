@@ -156,7 +156,7 @@ def c2_int_chain(rows=8192, cols=4096, nlanes=NLANES):
 # config 3: 3-layer MLP forward + grad of MSE + one SGD step
 # --------------------------------------------------------------------------
 def c3_mlp_step(batch=8192, widths=(1024, 4096, 4096, 1024), nlanes=NLANES,
-                dtype=BF16, lr=1e-3, global_batch=None, apply_sgd=True):
+                dtype=BF16, lr=1e-3, global_batch=None, apply_sgd=True, fold_transposes=True):
     """Storage `dtype`, f32 accumulate in every contraction.  Outputs: loss
     (f32 scalar) and either the three updated weights (`apply_sgd`) or the three
     weight gradients (for the data-parallel path, where the all-reduce sits
@@ -213,7 +213,10 @@ def c3_mlp_step(batch=8192, widths=(1024, 4096, 4096, 1024), nlanes=NLANES,
             outs.append(a_.convert(upd, dtype))
     else:
         outs = [loss, dw1, dw2, dw3]
-    blob, prog = a_.finish(outs, nlanes=nlanes, costs=B200_COSTS)
+    # `fold_transposes`: the transposed operands of the backward contractions reach the matmul
+    # tasks as operand views (what the reference's _fuse_matmul_views does for f32,
+    # lowering.py:2381-2452) instead of materialised 2-byte transposes
+    blob, prog = a_.finish(outs, nlanes=nlanes, costs=B200_COSTS, fold_2byte_matmul_views=fold_transposes)
 
     # x, y are drawn at the GLOBAL batch size; a data-parallel shard takes its
     # rows of them (the caller slices), weights are replicated.
@@ -396,6 +399,56 @@ def c5_decode(batch=32, cache=2048, d_model=1024, heads=16, d_ff=4096,
     d = DN[dtype]
     items = [("ones", (d_model,), d), ("normal", (batch, d_model), d),
              ("normal", (H, cache, hd), d), ("normal", (H, cache, hd), d)]
+    items += [("normal", (d_model, d_model), d, 0.02)] * 4
+    items += [("ones", (d_model,), d), ("normal", (d_model, d_ff), d, 0.02),
+              ("normal", (d_ff, d_model), d, 0.02)]
+    return blob, prog, (0, items)
+
+
+def c5_decode_in_place(batch=32, cache=2048, d_model=1024, heads=16, d_ff=4096,
+                       nlanes=NLANES, dtype=BF16, eps=1e-6):
+    """The decode step of `c5_decode` with the caches as in/out buffers of
+    `cache + 1` positions: the new K/V rows are written at position `pos` by the
+    scatter half of dynamic_update_slice alone (the reference's in-place DUS into a
+    loop carry), K is read through a transposed view instead of being transposed,
+    and the caches come back as results 1 and 2 (the same buffers)."""
+    hd = d_model // heads
+    H = batch * heads
+    C = cache + 1
+    a = Asm()
+    g1 = a.input((d_model,), dtype)
+    x = a.input((batch, d_model), dtype)
+    kc = a.input((H, C, hd), dtype)
+    vc = a.input((H, C, hd), dtype)
+    pos = a.input((), I32)
+    wq = a.input((d_model, d_model), dtype)
+    wk = a.input((d_model, d_model), dtype)
+    wv = a.input((d_model, d_model), dtype)
+    wo = a.input((d_model, d_model), dtype)
+    g2 = a.input((d_model,), dtype)
+    w1 = a.input((d_model, d_ff), dtype)
+    w2 = a.input((d_ff, d_model), dtype)
+    zero = a.const(0, I32)
+
+    h = _rmsnorm(a, x, g1, eps)
+    q = a.reshape(a.matmul(h, wq, out_dtype=dtype), (H, 1, hd))
+    k = a.reshape(a.matmul(h, wk, out_dtype=dtype), (H, 1, hd))
+    v = a.reshape(a.matmul(h, wv, out_dtype=dtype), (H, 1, hd))
+    kc = a.dynamic_update_in_place(kc, k, [zero, pos, zero])
+    vc = a.dynamic_update_in_place(vc, v, [zero, pos, zero])
+    kt = a.transpose_view(kc, [0, 2, 1])              # (H, hd, C) read in place
+    o = a.flash_attn(q, kt, vc, 1.0 / math.sqrt(hd), causal=True)
+    o2 = a.reshape(o, (batch, d_model))
+    x1 = a.add(x, a.matmul(o2, wo, out_dtype=dtype))
+    h2 = _rmsnorm(a, x1, g2, eps)
+    f = a.gelu_tanh(a.matmul(h2, w1, out_dtype=dtype))
+    y = a.add(x1, a.matmul(f, w2, out_dtype=dtype))
+    blob, prog = a.finish([y, kc, vc], nlanes=nlanes, costs=B200_COSTS)
+
+    d = DN[dtype]
+    items = [("ones", (d_model,), d), ("normal", (batch, d_model), d),
+             ("normal", (H, C, hd), d), ("normal", (H, C, hd), d),
+             ("value", (), "i32", cache)]
     items += [("normal", (d_model, d_model), d, 0.02)] * 4
     items += [("ones", (d_model,), d), ("normal", (d_model, d_ff), d, 0.02),
               ("normal", (d_ff, d_model), d, 0.02)]

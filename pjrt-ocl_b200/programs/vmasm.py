@@ -507,6 +507,21 @@ class Asm:
                   upd.buf, upd.n)
         return d
 
+    def dynamic_update_in_place(self, x: T, upd: T, starts: list) -> T:
+        """The scatter half of dynamic_update_slice alone, writing into `x`'s own
+        buffer: what the reference's loop-carry fold leaves of a DUS whose operand
+        is the carry (lowering.py:1126-1150, ops/dynslice.py:107-129 without the
+        identity gather). Returns `x` (same buffer, now updated)."""
+        from pjrt_ocl.ops.dynslice import _emit_dyn
+        rank = len(x.shape)
+        outs = _strides(x.shape)
+        cmax = [x.shape[d] - upd.shape[d] for d in range(rank)]
+        is64 = 1 if starts[0].dtype == I64 else 0
+        _emit_dyn(self.ctx, L.OP_DYNAMIC_UPDATE_SLICE, list(upd.shape), outs,
+                  cmax, [s.buf for s in starts], [0] * rank, is64, x.buf,
+                  upd.buf, upd.n)
+        return x
+
     def concatenate(self, xs: list, axis: int) -> T:
         """ops/concat.py: one OP_SCATTER per operand into a shared output,
         all tagged with the same `disjoint` group."""
