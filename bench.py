@@ -97,6 +97,14 @@ WORKLOADS = {
                     "B = 67 MB (N,N) tensors: 28 A + 16 B",
                     roof_alg=(28 * 4096 * 4096 * 3 * 4 + 16 * 4096 * 4096 * 4) * 200, secondary=True, plan="c4",
                     max_steps=3),
+    "flash_decode_bf16": _wl("flash_decode_bf16_c5", "decode-attention GB/s", "GB/s", 2 * 512 * 2049 * 64 * 2, 1e9, "hbm", "bf16",
+                             "config 5's decode attention alone: 512 heads x 1 query x 2049 keys, head_dim 64; "
+                             "bytes = K and V read once", secondary=True),
+    "c5_decode_in_place": _wl("c5_decode_in_place_bf16", "transformer-block tokens/s per B200", "tokens/s", 32, 1.0, "hbm", "bf16",
+                              "config 5 decode step, batch 32, KV cache 2048 + the new position: K/V written in place "
+                              "(in/out buffers), K read through its view; bytes = weights + KV cache read once",
+                              roof_alg=2 * (4 * 1024 * 1024 + 2 * 1024 * 4096) + 2 * 32 * 16 * 2049 * 64 * 2,
+                              plan="c5_decode_in_place"),
     "c5_decode": _wl("c5_decode_bf16", "transformer-block tokens/s per B200", "tokens/s", 32, 1.0, "hbm", "bf16",
                      "config 5 decode step: batch 32, KV cache 2048; bytes = weights + KV cache read once",
                      roof_alg=2 * (4 * 1024 * 1024 + 2 * 1024 * 4096) + 2 * 32 * 16 * 2048 * 64 * 2, plan="c5_decode"),
@@ -291,6 +299,9 @@ def main():
         dev_out = [bucket[bucket_slots[i]:bucket_slots[i] + max(s["bytes"], 16)] if i in bucket_slots
                    else torch.empty(max(s["bytes"], 16), dtype=torch.uint8, device="cuda")
                    for i, s in enumerate(lp.prog.outputs)]
+        # in/out buffers (a KV cache updated in place): the result is the argument's own memory
+        for i_arg, i_res in lp.InOutResults().items():
+            dev_out[i_res] = dev_in[i_arg]
         pin_out = [torch.empty(max(s["bytes"], 1), dtype=torch.uint8, pin_memory=True) for s in lp.prog.outputs]
         torch.cuda.synchronize()
         ins = [t.data_ptr() for t in dev_in]

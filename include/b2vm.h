@@ -125,11 +125,19 @@ b2_status b2_execute_device(b2_loaded *lp, void *const *dev_inputs, size_t n_inp
  * if one of them fails on the device (a wait ran out), the launches queued
  * behind it find the abort flag set, return at their first barrier without
  * writing results, and b2_loaded_status reports the first failure - so fetch
- * the status before trusting the results of a pipelined batch. */
+ * the status before trusting the results of a pipelined batch.
+ * In/out buffers: a program buffer that is one argument and one result and that
+ * the program writes (a cache updated in place; the reference copies such donated
+ * buffers through its arena, runtime.cc:799-801) is updated in the RESULT's memory.
+ * Pass the same address as that argument and that result and nothing is copied;
+ * pass different ones and the argument is first copied into the result. */
 b2_status b2_execute_device_async(b2_loaded *lp, void *const *dev_inputs, size_t n_inputs,
                                   void *const *dev_outputs, size_t n_outputs,
                                   void *cuda_stream, char *err, size_t err_cap);
 b2_status b2_loaded_status(b2_loaded *lp, b2_exec_status *out, char *err, size_t err_cap);
+/* The result that argument `input` shares its buffer with when that buffer is an
+ * in/out buffer (see b2_execute_device_async), else -1. */
+int b2_loaded_in_out_result(const b2_loaded *lp, uint32_t input);
 /* Number of kernels launched by this loaded program so far. */
 uint64_t b2_loaded_launch_count(const b2_loaded *lp);
 /* Load-time facts about how the program was mapped to the device, for tests and
@@ -144,7 +152,8 @@ uint64_t b2_loaded_launch_count(const b2_loaded *lp);
  * families, and a program runs on the smallest one that has all it uses),
  * 10 bit mask of the tile-op families the program uses, 11 full reductions
  * (RED_PART + RED_COMB) re-cut evenly over all lanes with the combine folded into
- * the same phase. Unknown `which` returns 0. */
+ * the same phase, 12 flash-attention tasks on the decode path (few query rows; K and
+ * V rows read with 16-byte loads), 13 in/out ports. Unknown `which` returns 0. */
 uint64_t b2_loaded_stat(const b2_loaded *lp, int which);
 /* Per-wait budget of device-side bounded waits, in nanoseconds (default 2e9). */
 void b2_loaded_set_wait_budget_ns(b2_loaded *lp, uint64_t ns);

@@ -175,10 +175,11 @@ enum StatusCode : uint32_t { kStOk = 0, kStBarrierTimeout = 1, kStStackOverflow 
 // Barrier + status block in device memory (one per loaded program).
 struct DSync {
   uint32_t arrive;       // arrival counter
-  uint32_t gen;          // barrier generation
-  uint32_t abort;        // set by the first lane whose wait ran out; polled by all
-  uint32_t status[4];    // code, lane, where, detail (first writer wins)
   uint32_t pad;
+  uint32_t gen;          // barrier generation   } one aligned 8-byte word: a waiting lane polls
+  uint32_t abort;        // set by the first lane } both with a single load
+                         // whose wait ran out
+  uint32_t status[4];    // code, lane, where, detail (first writer wins)
   unsigned long long barriers;   // lane 0
   unsigned long long device_ns;  // lane 0
   // lane 0's arrival time (ns since kernel entry) at each of its first
@@ -187,6 +188,7 @@ struct DSync {
   unsigned long long phase_ns[64];
 };
 constexpr uint32_t kPhaseSlots = 64;
+static_assert(offsetof(DSync, gen) % 8 == 0 && offsetof(DSync, abort) == offsetof(DSync, gen) + 4, "gen and abort are polled as one 8-byte word");
 
 // ---- per-op descriptors the loader writes into the descriptor pool -------------
 // Descriptor the loader writes for GATHER / SCATTER / DYN_* tasks.
@@ -242,7 +244,11 @@ struct DFlash {        // loader-built
   // program's scratch (heaviest first) instead of keeping their static ranges.
   uint32_t work_slot;             // index of the {next, done} pair in the scratch, or kNoWorkSlot
   uint32_t n_owner_lanes;
-  uint32_t pad;
+  // Few query rows per head (a decode step) with 16-bit K and V whose head_dim axis is the
+  // unit-stride one: element (g, key, d) of K at dk_off + g * dk_g + key * dk_c + d (V alike),
+  // every term a multiple of 8 elements, so a key's row is read with 16-byte loads.
+  uint32_t dec_mode;
+  int64_t dk_g, dk_c, dk_off, dv_g, dv_c, dv_off;
 };
 constexpr uint32_t kNoWorkSlot = 0xFFFFFFFFu;
 

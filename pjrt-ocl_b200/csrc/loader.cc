@@ -396,26 +396,39 @@ bool BuildDeviceTables(const VmProgram &p, uint64_t arena_base, DeviceTables *ou
 
   // ---- zero-copy I/O ports (runtime.cc:798-821): a buffer that is only an input
   // or only an output, is not a constant, and is among the first kMaxIoPorts such.
+  // Beyond the reference (whose donated buffers fall back to the arena): a buffer that
+  // is one argument AND one result and that some task writes - a cache updated in
+  // place - is an in/out port: the kernel works on the result's memory, which the
+  // argument is copied into first unless the caller passed the same address for both.
   std::set<uint32_t> in_ids(p.args.ids.begin(), p.args.ids.end()), out_ids(p.results.ids.begin(), p.results.ids.end());
   std::set<uint32_t> const_ids;
   for (const auto &k : p.consts) const_ids.insert(k.buffer);
+  // A result buffer that no task ever writes (a pass-through of arena-resident
+  // data) has to come out of the arena.
+  std::set<uint32_t> written;
+  for (const VmTask &t : p.tasks) written.insert(t.dst);
+  auto times_in = [](const std::vector<uint32_t> &v, uint32_t id) { return std::count(v.begin(), v.end(), id); };
   auto assign_port = [&](uint32_t id) -> int {
-    if (in_ids.count(id) && out_ids.count(id)) return -1;
+    if (in_ids.count(id) && out_ids.count(id) &&
+        !(written.count(id) && times_in(p.args.ids, id) == 1 && times_in(p.results.ids, id) == 1))
+      return -1;
     if (const_ids.count(id)) return -1;
     auto it = c.port_of.find(id);
     if (it != c.port_of.end()) return it->second;
     if (out->n_ports >= static_cast<int>(kMaxIoPorts)) return -1;
     return c.port_of[id] = out->n_ports++;
   };
-  // A result buffer that no task ever writes (a pass-through of arena-resident
-  // data) has to come out of the arena.
-  std::set<uint32_t> written;
-  for (const VmTask &t : p.tasks) written.insert(t.dst);
   out->input_port.assign(p.args.ids.size(), -1);
   out->output_port.assign(p.results.ids.size(), -1);
+  out->inout_result.assign(p.args.ids.size(), -1);
   for (size_t i = 0; i < p.args.ids.size(); ++i) out->input_port[i] = assign_port(p.args.ids[i]);
   for (size_t o = 0; o < p.results.ids.size(); ++o)
     out->output_port[o] = written.count(p.results.ids[o]) ? assign_port(p.results.ids[o]) : -1;
+  for (size_t i = 0; i < p.args.ids.size(); ++i) {
+    if (out->input_port[i] < 0 || !out_ids.count(p.args.ids[i])) continue;
+    for (size_t o = 0; o < p.results.ids.size(); ++o)
+      if (p.results.ids[o] == p.args.ids[i]) out->inout_result[i] = static_cast<int>(o);
+  }
 
   // ---- tasks ----
   out->tasks.resize(p.tasks.size());
@@ -659,6 +672,26 @@ bool BuildDeviceTables(const VmProgram &p, uint64_t arena_base, DeviceTables *ou
             else out->tmaps.push_back(fa_spec(d.ptr[2], ok_, static_cast<uint64_t>(C), 64, sk[2], sk[1], sk[0], 64u));
             out->tmaps.push_back(fa_spec(d.ptr[3], ov, 64, static_cast<uint64_t>(C), sv[2], sv[1], sv[0], 128u));
             ++out->n_flash_tc;
+          }
+        }
+        // Decode-shaped tasks (few query rows, CUDA-core path): K and V rows by 16-byte loads when
+        // head_dim is their unit-stride axis. K arrives as [H, hd, C] (a view of a [H, C, hd] cache).
+        if (!f.tc_mode && (d.adt == kBF16 || d.adt == kF16) && !qv && (x[3] == 64 || x[3] == 128) && x[1] <= 8 &&
+            x[0] > 0 && x[2] > 0 && c.Aligned16(t.a) && c.Aligned16(t.b) && c.Aligned16(t.p0)) {
+          const int64_t H = x[0], C = x[2], hd = x[3];
+          const int64_t nk[3] = {H, hd, C}, nv[3] = {H, C, hd};
+          int64_t sk[3] = {hd * C, C, 1}, sv[3] = {C * hd, hd, 1}, ko = 0, vo = 0;
+          bool ok = true;
+          if (kv) ok = ok && AffineOverAxesN(f.vk, nk, 3, sk, &ko);
+          if (vv) ok = ok && AffineOverAxesN(f.vv, nv, 3, sv, &vo);
+          if (H == 1) sk[0] = sv[0] = 8;
+          auto good = [](int64_t st) { return st >= 0 && st % 8 == 0; };
+          if (ok && sk[1] == 1 && sv[2] == 1 && good(sk[0]) && good(sk[2]) && sk[2] > 0 && good(sv[0]) && good(sv[1]) && sv[1] > 0 &&
+              good(ko) && good(vo)) {
+            f.dec_mode = 1;
+            f.dk_g = sk[0]; f.dk_c = sk[2]; f.dk_off = ko;
+            f.dv_g = sv[0]; f.dv_c = sv[1]; f.dv_off = vo;
+            ++out->n_flash_decode;
           }
         }
         ++out->n_flash;

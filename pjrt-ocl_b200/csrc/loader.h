@@ -41,6 +41,7 @@ struct DeviceTables {
   std::vector<uint64_t> desc;           // descriptor pool (word 0 reserved: offset 0 = none)
   std::vector<int> input_port;          // per program input: port index or -1 (goes through the arena)
   std::vector<int> output_port;         // per program output
+  std::vector<int> inout_result;        // per program input: the result that is the same buffer (an in/out port), or -1
   int n_ports = 0;
   std::vector<TmapSpec> tmaps;          // two per tensor-core matmul task (A, B), in DMma::tmap order
   // statistics for tests / logging
@@ -51,6 +52,7 @@ struct DeviceTables {
   uint32_t n_mma_tc = 0;                // ... of which the tensor-core path takes
   uint64_t mma_flops = 0;               // sum over matmul tasks of 2 G M N K
   uint32_t n_flash = 0, n_flash_tc = 0; // flash-attention tasks / ... on the tensor-core path
+  uint32_t n_flash_decode = 0;          // ... on the 16-byte-load decode path
   uint32_t n_spread = 0;                // reduction phases re-cut over all lanes
   uint32_t n_fused_reduce = 0;          // ... of which full reductions (RED_PART + RED_COMB in one phase)
   bool needs_scratch = false;           // a re-cut full reduction leaves lane totals in the program's scratch

@@ -22,6 +22,127 @@ namespace b2 {
 
 constexpr int kFlashMaxHd = 256;
 
+// Decode-shaped tasks (DFlash::dec_mode): every (head, query row) tile is worked on by the whole
+// lane. LPK = hd / 8 threads share one key: each holds 8 consecutive d of q (pre-scaled by
+// scale * log2 e) and reads the same 8 d of the key's K row and V row as one 16-byte load
+// each. A warp covers 32 / LPK keys per load and 8 loads per operand and trip (16 loads in
+// flight per thread); the lane's warps take trips round-robin, keep their own running (max, sum,
+// accumulator) in the base-2 domain, and are merged through shared memory.
+template <int HD, bool BF>
+static __device__ __noinline__ void flash_decode_tiles(const Lane &L, const DTask &t, const DFlash &df, uint32_t tile_lo,
+                                                          int64_t hi, int64_t T, int64_t C, float scale, bool causal) {
+  constexpr int LPK = HD / 8;              // threads per key
+  constexpr int KPL = 32 / LPK;            // keys per warp-wide load
+  constexpr int U = 8;                     // loads in flight per operand
+  constexpr int KPT = KPL * U;             // keys per warp trip
+  const KParams &P = *L.P;
+  uint8_t *out = resolve(P, t.ptr[0]);
+  const uint16_t *Q = reinterpret_cast<const uint16_t *>(resolve(P, t.ptr[1]));
+  const uint16_t *K = reinterpret_cast<const uint16_t *>(resolve(P, t.ptr[2])) + df.dk_off;
+  const uint16_t *V = reinterpret_cast<const uint16_t *>(resolve(P, t.ptr[3])) + df.dv_off;
+  constexpr bool bf = BF;
+  const uint32_t w = L.tid / kWarp, l = L.tid % kWarp, nw = L.nthr / kWarp;
+  const uint32_t part = l % LPK, sub = l / LPK;
+  float *ml = reinterpret_cast<float *>(L.smem + kSmemSys);                          // [nw][2]
+  float *os = ml + 2 * 32;                                                           // [nw][HD]
+  auto unpack8 = [&](const uint4 &v, float (&f)[8]) {
+    const uint32_t wd[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      f[2 * i] = bf ? __uint_as_float(wd[i] << 16) : f16_bits_to_f32(wd[i] & 0xffffu);
+      f[2 * i + 1] = bf ? __uint_as_float(wd[i] & 0xffff0000u) : f16_bits_to_f32(wd[i] >> 16);
+    }
+  };
+  const float sl2 = scale * 1.4426950408889634f;
+  for (int64_t tile = tile_lo; tile < hi; ++tile) {
+    const int64_t g = tile / T, m = tile % T;
+    const int64_t c_end = causal ? min(C, m + (C - T) + 1) : C;
+    float q[8];
+    unpack8(ldg_v4(Q + (g * T + m) * HD + part * 8), q);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) q[i] *= sl2;
+    const uint16_t *Kg = K + g * df.dk_g + part * 8, *Vg = V + g * df.dv_g + part * 8;
+    float m_run = -INFINITY, l_run = 0.0f, o[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o[i] = 0.0f;
+    auto load = [&](uint4 (&kk)[U], uint4 (&vv)[U], int64_t c0) {
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int64_t key = c0 + u * KPL + sub;
+        kk[u] = key < c_end ? ldg_v4(Kg + key * df.dk_c) : make_uint4(0u, 0u, 0u, 0u);
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int64_t key = c0 + u * KPL + sub;
+        vv[u] = key < c_end ? ldg_v4(Vg + key * df.dv_c) : make_uint4(0u, 0u, 0u, 0u);
+      }
+    };
+    auto compute = [&](const uint4 (&kk)[U], const uint4 (&vv)[U], int64_t c0) {
+      float sc[U], cmax = -INFINITY;
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        float kf[8];
+        unpack8(kk[u], kf);
+        float a = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) a = fmaf(q[i], kf[i], a);
+#pragma unroll
+        for (int d = 1; d < LPK; d <<= 1) a += __shfl_xor_sync(0xffffffffu, a, d);
+        sc[u] = (c0 + u * KPL + sub) < c_end ? a : -INFINITY;
+        cmax = fmaxf(cmax, sc[u]);
+      }
+#pragma unroll
+      for (int d = LPK; d < 32; d <<= 1) cmax = fmaxf(cmax, __shfl_xor_sync(0xffffffffu, cmax, d));
+      const float m_new = fmaxf(m_run, cmax);       // finite: the trip's first key exists
+      const float alpha = m_run == -INFINITY ? 0.0f : fast_ex2(m_run - m_new);
+      m_run = m_new;
+      l_run *= alpha;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) o[i] *= alpha;
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const float pr = sc[u] == -INFINITY ? 0.0f : fast_ex2(sc[u] - m_new);
+        l_run += pr;
+        float vf[8];
+        unpack8(vv[u], vf);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] = fmaf(pr, vf[i], o[i]);
+      }
+    };
+    for (int64_t c0 = static_cast<int64_t>(KPT) * w; c0 < c_end; c0 += static_cast<int64_t>(KPT) * nw) {
+      uint4 kk[U], vv[U];
+      load(kk, vv, c0);
+      compute(kk, vv, c0);
+    }
+    // the warp's threads hold partial sums over their own keys: add across the key groups
+#pragma unroll
+    for (int d = LPK; d < 32; d <<= 1) {
+      l_run += __shfl_xor_sync(0xffffffffu, l_run, d);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) o[i] += __shfl_xor_sync(0xffffffffu, o[i], d);
+    }
+    __syncthreads();            // the previous tile's merge has read the workspace
+    if (l == 0) { ml[2 * w] = m_run; ml[2 * w + 1] = l_run; }
+    if (sub == 0) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) os[w * HD + part * 8 + i] = o[i];
+    }
+    __syncthreads();
+    for (int64_t d = L.tid; d < HD; d += L.nthr) {
+      float M = -INFINITY;
+      for (uint32_t ww = 0; ww < nw; ++ww) M = fmaxf(M, ml[2 * ww]);
+      float num = 0.0f, den = 0.0f;
+      for (uint32_t ww = 0; ww < nw; ++ww) {
+        const float e = ml[2 * ww] == -INFINITY ? 0.0f : fast_ex2(ml[2 * ww] - M);
+        num = fmaf(os[ww * HD + d], e, num);
+        den = fmaf(ml[2 * ww + 1], e, den);
+      }
+      storef(out, t.dt, (g * T + m) * HD + d, __fdiv_rn(num, den));
+    }
+  }
+  __syncthreads();
+}
+
 static __device__ __noinline__ void flash_simt_tiles(const Lane &L, const DTask &t, uint32_t tile_lo, uint32_t tile_hi) {
   const KParams &P = *L.P;
   const int32_t *x = P.aux + t.p[3];
@@ -38,6 +159,13 @@ static __device__ __noinline__ void flash_simt_tiles(const Lane &L, const DTask 
   float *qs = reinterpret_cast<float *>(L.smem + kSmemSys) + static_cast<size_t>(w) * kFlashMaxHd;
   const int64_t hi = min(static_cast<int64_t>(tile_hi), H * T);
   __syncthreads();  // workspace handover from the previous op
+  if (df.dec_mode) {
+    if (hd == 64 && adt == kBF16) flash_decode_tiles<64, true>(L, t, df, tile_lo, hi, T, C, scale, causal);
+    else if (hd == 64) flash_decode_tiles<64, false>(L, t, df, tile_lo, hi, T, C, scale, causal);
+    else if (adt == kBF16) flash_decode_tiles<128, true>(L, t, df, tile_lo, hi, T, C, scale, causal);
+    else flash_decode_tiles<128, false>(L, t, df, tile_lo, hi, T, C, scale, causal);
+    return;
+  }
   if ((hi - static_cast<int64_t>(tile_lo)) * 2 <= static_cast<int64_t>(nw) && hd <= 128) {
     // Few query rows for this lane (a decode step): a warp per row would leave most
     // warps idle and each row's keys in one warp's serial loop. Instead the lane's

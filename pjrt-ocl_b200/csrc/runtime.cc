@@ -13,6 +13,7 @@
 #include <cstddef>
 #include <cstdio>
 #include <cstdlib>
+#include <algorithm>
 #include <cstring>
 #include <memory>
 #include <mutex>
@@ -529,6 +530,9 @@ const b2_program *b2_loaded_program(const b2_loaded *lp) {
 }
 
 uint64_t b2_loaded_launch_count(const b2_loaded *lp) { return lp->launches; }
+int b2_loaded_in_out_result(const b2_loaded *lp, uint32_t input) {
+  return lp && input < lp->tab.inout_result.size() ? lp->tab.inout_result[input] : -1;
+}
 uint64_t b2_loaded_stat(const b2_loaded *lp, int which) {
   if (!lp) return 0;
   switch (which) {
@@ -544,6 +548,8 @@ uint64_t b2_loaded_stat(const b2_loaded *lp, int which) {
     case 9: return static_cast<uint64_t>(lp->variant);
     case 11: return lp->tab.n_fused_reduce;
     case 10: return lp->tab.families;
+    case 12: return lp->tab.n_flash_decode;
+    case 13: return static_cast<uint64_t>(std::count_if(lp->tab.inout_result.begin(), lp->tab.inout_result.end(), [](int o) { return o >= 0; }));
     default: return 0;
   }
 }
@@ -628,6 +634,13 @@ static b2_status BindAndRun(b2_loaded *lp, void *const *dev_in, void *const *dev
     if (lp->tab.input_port[i] >= 0) {
       if (reinterpret_cast<uintptr_t>(dev_in[i]) % 16) { *err = "argument " + std::to_string(i) + " is not 16-byte aligned"; return B2_INVALID_ARGUMENT; }
       io.p[lp->tab.input_port[i]] = dev_in[i];
+      // an in/out buffer: the kernel updates the result's memory (bound below), which starts as the argument
+      const int o = lp->tab.inout_result[i];
+      if (o >= 0 && dev_out[o] != dev_in[i] &&
+          (e = cudaMemcpyAsync(dev_out[o], dev_in[i], b.bytes, cudaMemcpyDeviceToDevice, stream)) != cudaSuccess) {
+        *err = CudaMsg("in/out argument copy into its result", e);
+        return B2_INTERNAL;
+      }
     } else if ((e = cudaMemcpyAsync(lp->arena + b.offset, dev_in[i], b.bytes, cudaMemcpyDeviceToDevice, stream)) != cudaSuccess) {
       *err = CudaMsg("argument copy into the arena", e);
       return B2_INTERNAL;

@@ -62,7 +62,13 @@ constexpr uint32_t kRoot = 0xFFFFFFFFu;
 
 // Grid-wide barrier over the n_lanes co-resident CTAs. Returns false when the
 // wait was abandoned (budget exhausted here or abort raised by another lane).
-__device__ __forceinline__ bool grid_barrier(const Lane &L, uint32_t barrier_index, unsigned long long t_start) {
+// `gen` is the generation this lane expects (thread 0's copy, read once at kernel
+// entry: every lane passes every barrier, so it advances by one per call).
+// Ordering: the CTA barrier makes the lane's stores visible to thread 0, whose
+// acq_rel arrival publishes them (release is cumulative); the last arriver's release
+// on `gen` and the waiters' acquire loads of it carry them to every other lane, and
+// the closing CTA barrier to that lane's other threads.
+__device__ __forceinline__ bool grid_barrier(const Lane &L, uint32_t barrier_index, unsigned long long t_start, uint32_t &gen) {
   const KParams &P = *L.P;
   volatile uint32_t &ok_flag = *reinterpret_cast<volatile uint32_t *>(L.smem + kSmemFlag);
   __syncthreads();
@@ -70,34 +76,31 @@ __device__ __forceinline__ bool grid_barrier(const Lane &L, uint32_t barrier_ind
     bool ok = true;
     DSync *s = P.sync;
     if (P.lane_ts && barrier_index < kPhaseSlots) P.lane_ts[L.lane * kLaneTsSlots + 2u + barrier_index] = globaltimer_ns();
-    const uint32_t gen = ld_relaxed_gpu(&s->gen);
-    __threadfence();  // release this lane's stores (made visible to thread 0 by the CTA barrier above)
     const uint32_t prev = atom_add_acq_rel_gpu(&s->arrive, 1u);
     if (prev == P.n_lanes - 1u) {
       st_relaxed_gpu(&s->arrive, 0u);
-      __threadfence();
       red_release_gpu_add(&s->gen, 1u);
+      if (ld_relaxed_gpu(&s->abort)) ok = false;
     } else {
       const unsigned long long t0 = globaltimer_ns();
       uint32_t spins = 0;
-      while (ld_acquire_gpu(&s->gen) == gen) {
+      for (;;) {
+        const unsigned long long v = ld_acquire_gpu_u64(&s->gen);      // {gen, abort}
+        if (static_cast<uint32_t>(v >> 32)) { ok = false; break; }
+        if (static_cast<uint32_t>(v) != gen) break;
         if (++spins > 32u) {
           nanosleep_ns(64);
-          if ((spins & 255u) == 0u) {
-            if (ld_relaxed_gpu(&s->abort)) { ok = false; break; }
-            if (globaltimer_ns() - t0 > P.wait_budget_ns) {
-              set_status(P, kStBarrierTimeout, L.lane, barrier_index, 0u);
-              ok = false;
-              break;
-            }
+          if ((spins & 255u) == 0u && globaltimer_ns() - t0 > P.wait_budget_ns) {
+            set_status(P, kStBarrierTimeout, L.lane, barrier_index, 0u);
+            ok = false;
+            break;
           }
         }
       }
     }
+    ++gen;
     // when the phase ended for everybody: the barrier's release as lane 0 sees it
     if (L.lane == 0 && barrier_index < kPhaseSlots) s->phase_ns[barrier_index] = globaltimer_ns() - t_start;
-    __threadfence();  // acquire: later plain loads of this CTA see every lane's stores
-    if (ok && ld_relaxed_gpu(&s->abort)) ok = false;
     ok_flag = ok ? 1u : 0u;
   }
   __syncthreads();
@@ -175,6 +178,7 @@ __global__ void __launch_bounds__(NT, 1) B2_VM_KERNEL(const __grid_constant__ KP
   int sp = 0;
   st[0].pc = 0; st[0].end = span.root_len; st[0].widx = kRoot; st[0].phase = 0;
   uint32_t barrier_i = 0;
+  uint32_t gen = L.tid == 0 ? ld_relaxed_gpu(&P.sync->gen) : 0u;   // thread 0's copy of the barrier generation
   bool pub = false;   // a tile entry ran since the last barrier (vm_main.cl:82-100)
   bool alive = true;
 
@@ -188,7 +192,7 @@ __global__ void __launch_bounds__(NT, 1) B2_VM_KERNEL(const __grid_constant__ KP
         st[sp].pc++;
         continue;
       }
-      alive = grid_barrier(L, barrier_i++, t_start);
+      alive = grid_barrier(L, barrier_i++, t_start, gen);
       pub = false;
       if (!alive) break;
       if (w.task == kEntFor) {                   // one iteration done
@@ -206,7 +210,7 @@ __global__ void __launch_bounds__(NT, 1) B2_VM_KERNEL(const __grid_constant__ KP
     const uint32_t epc = f.pc;
     const DEntry en = stream[epc];
     if (en.task == kEntBarrier) {
-      alive = grid_barrier(L, barrier_i++, t_start);
+      alive = grid_barrier(L, barrier_i++, t_start, gen);
       pub = false;
       f.pc++;
       continue;

@@ -68,6 +68,7 @@ PLANS = {
     # config 5: batch shards, no exchange
     "c5_block": DpPlan("c5_block_bf16", "c5_block_bf16_dp{n}", scaling="strong"),
     "c5_decode": DpPlan("c5_decode_bf16", "c5_decode_bf16_dp{n}", scaling="strong"),
+    "c5_decode_in_place": DpPlan("c5_decode_in_place_bf16", "c5_decode_in_place_bf16_dp{n}", scaling="strong"),
 }
 
 

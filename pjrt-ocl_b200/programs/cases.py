@@ -70,6 +70,19 @@ def flash_only(H=128, T=2048, hd=64, causal=True, nlanes=NLANES, dtype=BF16):
                             ("normal", (H, T, hd), DN[dtype])])
 
 
+def flash_decode_only(H=512, C=2049, hd=64, nlanes=NLANES, dtype=BF16):
+    """The attention of config 5's decode step on its own: one query row per head against
+    a cache of C positions, K [H,C,hd] read through its transposed view, V [H,C,hd]."""
+    a_ = Asm()
+    q = a_.input((H, 1, hd), dtype)
+    kc = a_.input((H, C, hd), dtype)
+    vc = a_.input((H, C, hd), dtype)
+    o = a_.flash_attn(q, a_.transpose_view(kc, [0, 2, 1]), vc, 1.0 / math.sqrt(hd), True)
+    blob, prog = a_.finish([o], nlanes=nlanes, costs=B200_COSTS)
+    return blob, prog, (6, [("normal", (H, 1, hd), DN[dtype]), ("normal", (H, C, hd), DN[dtype]),
+                            ("normal", (H, C, hd), DN[dtype])])
+
+
 # --------------------------------------------------------------------------
 # config 2: LayerNorm -> tanh-GELU -> softmax -> full sum ; i32 add/xor/max
 # --------------------------------------------------------------------------

@@ -37,6 +37,7 @@ PROGRAMS = {
     "c4_nbody": lambda: cases.c4_nbody(),
     "c5_block_bf16": lambda: cases.c5_block(nlanes=MULTI_UNIT_LANES),
     "c5_decode_bf16": lambda: cases.c5_decode(nlanes=MULTI_UNIT_LANES),
+    "c5_decode_in_place_bf16": lambda: cases.c5_decode_in_place(nlanes=MULTI_UNIT_LANES),
 }
 # data-parallel shards of config 3 / 5 (batch split over 2, 4, 8 GPUs)
 for g in (2, 4, 8):
@@ -44,6 +45,8 @@ for g in (2, 4, 8):
         lambda g=g: cases.c3_mlp_step(batch=8192 // g, global_batch=8192, apply_sgd=False, nlanes=MULTI_UNIT_LANES))
     PROGRAMS[f"c5_block_bf16_dp{g}"] = lambda g=g: cases.c5_block(batch=8 // g, nlanes=MULTI_UNIT_LANES)
     PROGRAMS[f"c5_decode_bf16_dp{g}"] = lambda g=g: cases.c5_decode(batch=32 // g, nlanes=MULTI_UNIT_LANES)
+    PROGRAMS[f"c5_decode_in_place_bf16_dp{g}"] = (
+        lambda g=g: cases.c5_decode_in_place(batch=32 // g, nlanes=MULTI_UNIT_LANES))
 # the four stages of config 2 as programs of their own (one tile-op family each),
 # for per-family roofline numbers and ncu captures
 for stage in ("layernorm", "affine_gelu", "softmax", "sum"):
@@ -65,6 +68,7 @@ PROGRAMS["c4_nbody_2steps"] = lambda: cases.c4_nbody(steps=2)
 PROGRAMS["dot_bf16_8192"] = lambda: cases.dot_general_square(8192)
 PROGRAMS["dot_bf16_4096"] = lambda: cases.dot_general_square(4096)
 PROGRAMS["flash_bf16_c5"] = lambda: cases.flash_only()
+PROGRAMS["flash_decode_bf16_c5"] = lambda: cases.flash_decode_only()
 
 
 def main():

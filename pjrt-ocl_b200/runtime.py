@@ -97,7 +97,7 @@ EXPORTS = [
     "b2_loaded_program", "b2_execute_host", "b2_execute_device", "b2_execute_device_async",
     "b2_loaded_status", "b2_loaded_launch_count", "b2_loaded_set_wait_budget_ns",
     "b2_loaded_phase_ns", "b2_loaded_stat", "b2_sum_f32_static", "b2_sum_f32_static_max_elems",
-    "b2_loaded_lane_timing", "b2_loaded_lane_times",
+    "b2_loaded_lane_timing", "b2_loaded_lane_times", "b2_loaded_in_out_result",
 ]
 
 
@@ -145,6 +145,7 @@ def lib():
         "b2_loaded_stat": (ctypes.c_uint64, [vp, ctypes.c_int]),
         "b2_loaded_lane_timing": (ctypes.c_int, [vp, ctypes.c_int, cp, sz]),
         "b2_loaded_lane_times": (sz, [vp, ctypes.POINTER(ctypes.c_uint64), sz]),
+        "b2_loaded_in_out_result": (ctypes.c_int, [vp, ctypes.c_uint32]),
         "b2_sum_f32_static": (ctypes.c_int, [ctypes.c_int, vp, ctypes.c_uint64, vp, vp, cp, sz]),
         "b2_sum_f32_static_max_elems": (ctypes.c_uint64, []),
     }
@@ -349,6 +350,16 @@ class LoadedProgram:
         _check(lib().b2_execute_device_async(self._h, ins, len(dev_inputs), outs, len(dev_outputs),
                                              ctypes.c_void_p(stream), err, _ERRCAP), err)
 
+    def InOutResults(self) -> dict:
+        """{argument index: result index} of the program's in/out buffers: pass the
+        same device address for both and the buffer is updated in place."""
+        pairs = {}
+        for i in range(self.prog.n_inputs):
+            o = lib().b2_loaded_in_out_result(self._h, i)
+            if o >= 0:
+                pairs[i] = int(o)
+        return pairs
+
     def Status(self) -> dict:
         st = _ExecStatus()
         err = _errbuf()
@@ -399,7 +410,8 @@ class LoadedProgram:
 
     _STATS = {"chains": 0, "forwarded": 0 + 1, "dead_stores": 2, "matmuls": 3, "tensor_core_matmuls": 4,
               "matmul_flops": 5, "flash": 6, "tensor_core_flash": 7, "spread_reductions": 8,
-              "kernel_build": 9, "families": 10, "fused_full_reductions": 11}
+              "kernel_build": 9, "families": 10, "fused_full_reductions": 11, "decode_flash": 12,
+              "in_out_ports": 13}
 
     def stat(self, name: str) -> int:
         """Load-time mapping facts, by name (see `_STATS`)."""

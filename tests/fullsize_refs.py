@@ -175,6 +175,17 @@ def verify_workload(program: str, args, outs, oracle_rows=None) -> str:
         want = c5_block_sequence(x.reshape(nseq, seq, d)[b], g1, wq, wk, wv, wo, g2, w1, w2, heads=16)
         assert_close(got[b], want, 2e-2, f"sequence {b}")
         return f"sequence {b} of {nseq} against the numpy restatement (rel 2e-2)"
+    if program.startswith("c5_decode_in_place"):
+        g1, x, kc, vc, pos, wq, wk, wv, wo, g2, w1, w2 = args
+        p_ = int(np.asarray(pos).reshape(-1)[0])
+        assert p_ == kc.shape[1] - 1, "the restatement appends at the last position"
+        want_y, k, v = c5_decode_step(x, kc[:, :p_], vc[:, :p_], g1, wq, wk, wv, wo, g2, w1, w2, heads=16)
+        assert_close(_as(outs[0], BF16, x.shape).astype(np.float32), want_y, 2e-2, "decode y")
+        for o, cache, row, what in ((outs[1], kc, k, "K"), (outs[2], vc, v, "V")):
+            got = _as(o, BF16, cache.shape)
+            assert np.array_equal(got[:, :p_].view(np.uint16), cache[:, :p_].view(np.uint16)), f"{what} cache rows below pos changed"
+            assert_close(got[:, p_].astype(np.float32), row, 2e-2, f"{what} row written at pos")
+        return "y, the K and V rows written in place at pos, and the untouched cache rows against the numpy restatement"
     if program.startswith("c5_decode"):
         g1, x, kc, vc, wq, wk, wv, wo, g2, w1, w2 = args
         want_y, k, v = c5_decode_step(x, kc, vc, g1, wq, wk, wv, wo, g2, w1, w2, heads=16)
@@ -202,6 +213,16 @@ def verify_workload(program: str, args, outs, oracle_rows=None) -> str:
         want = x[rows].astype(np.float64) @ w.astype(np.float64)
         assert_close(got[rows], want, 2e-2, "sampled rows")
         return "16 sampled rows against a float64 dot"
+    if program.startswith("flash_decode_bf16"):
+        q, kc, vc = args
+        H, C, hd = kc.shape
+        got = _as(outs[0], BF16, (H, hd)).astype(np.float32)
+        heads = np.sort(np.random.default_rng(9).choice(H, 32, replace=False))
+        s = np.einsum("hd,hcd->hc", f32(q)[heads, 0].astype(np.float64), f32(kc)[heads].astype(np.float64)) / math.sqrt(hd)
+        pm = np.exp(s - s.max(axis=1, keepdims=True))
+        want = np.einsum("hc,hcd->hd", pm / pm.sum(axis=1, keepdims=True), f32(vc)[heads].astype(np.float64))
+        assert_close(got[heads], want.astype(np.float32), 2e-2, "decode attention")
+        return "32 sampled heads against float64 softmax(qK^T)V"
     if program.startswith("flash_bf16"):
         q, kt, v = args
         H, T, hd = q.shape

@@ -890,6 +890,20 @@ def _():
                            nlanes=8, dtype=BF16)
 
 
+@case("c5_decode_in_place_f32_small", rtol=1e-4, atol=1e-4)
+def _():
+    return cases.c5_decode_in_place(batch=3, cache=70, d_model=128, heads=2, d_ff=256,
+                                    nlanes=8, dtype=F32)
+
+
+@case("c5_decode_in_place_bf16_small", rtol=2e-2, atol=3e-2,
+      twin=lambda: cases.c5_decode_in_place(batch=3, cache=70, d_model=128, heads=2,
+                                            d_ff=256, nlanes=8, dtype=F32))
+def _():
+    return cases.c5_decode_in_place(batch=3, cache=70, d_model=128, heads=2, d_ff=256,
+                                    nlanes=8, dtype=BF16)
+
+
 # ---------------------------------------------------------------- driver
 def build(name):
     fn, meta = CASES[name]

@@ -147,6 +147,15 @@ def test_config5_decode_values_at_full_size(rt):
     F.assert_close(np.asarray(y).view(ml_dtypes.bfloat16).reshape(32, 1024).astype(np.float32), want_y, 2e-2, "decode y")
 
 
+def test_config5_decode_in_place_values_at_full_size(rt):
+    """The in-place decode step through the allocating entry point (argument and result
+    differ: the caches are copied into the results, then updated there)."""
+    import fullsize_refs as F
+    args, outs = _run(rt, "c5_decode_in_place_bf16")
+    what = F.verify_workload("c5_decode_in_place_bf16", args, [np.asarray(o).view(np.uint8).reshape(-1) for o in outs])
+    assert "in place" in what
+
+
 def test_config2_f32_chain_properties_at_full_size(rt):
     _, outs = _run(rt, "c2_chain_f32")
     sm = np.asarray(outs[0]).view(np.float32).reshape(8192, 4096)

@@ -42,7 +42,7 @@ def test_execute_matches_reference_validators(rt, name):
 
 @pytest.mark.parametrize("name", ["c2_int_chain_small", "c2_chain_f32_small", "c3_mlp_bf16_small",
                                   "c4_nbody_small", "c5_block_bf16_small", "dynslice",
-                                  "while_loop_data_dependent"])
+                                  "while_loop_data_dependent", "c5_decode_in_place_bf16_small"])
 def test_execute_device_matches_oracle(rt, name):
     """ExecuteDevice (device pointers in, pooled device buffers out) against the
     C oracle run on the same inputs."""
@@ -66,6 +66,42 @@ def test_execute_device_matches_oracle(rt, name):
     for i, (a, b, e) in enumerate(zip(got, want, g.expected)):
         if g.meta.get("exact") or e.dtype.kind in "iub":
             np.testing.assert_array_equal(a, b, err_msg=f"{name} out {i} vs oracle")
+
+
+@pytest.mark.parametrize("name", ["c5_decode_in_place_f32_small", "c5_decode_in_place_bf16_small"])
+def test_in_out_buffers_are_updated_in_place(rt, name):
+    """A KV cache that is argument and result of the program: with the same device address
+    passed for both nothing is copied and the cache is updated where it lies; two steps in
+    a row give the same answer (the step overwrites one position with the same values)."""
+    vm = package()
+    g = Golden(name)
+    lp = vm.LoadedProgram.Load(rt, vm.VmProgram.Parse(g.blob))
+    pairs = lp.InOutResults()
+    assert pairs == {2: 1, 3: 2} and lp.stat("in_out_ports") == 2
+    if name.endswith("bf16_small"):
+        assert lp.stat("decode_flash") == 1
+    dins = []
+    for a in g.args:
+        a = np.ascontiguousarray(a)
+        p = rt.AllocDevice(max(a.nbytes, 16))
+        rt.WriteToDevice(p, a)
+        dins.append((p, max(a.nbytes, 16)))
+    douts = []
+    for o, s in enumerate(lp.prog.outputs):
+        src = [i for i, r in pairs.items() if r == o]
+        douts.append(dins[src[0]][0] if src else rt.AllocDevice(max(s["bytes"], 16)))
+    for _ in range(2):
+        lp.ExecuteDeviceAsync([p for p, _ in dins], douts)
+        assert lp.Status()["code"] == 0
+    got = [rt.ReadFromDevice(p, s["bytes"]) for p, s in zip(douts, lp.prog.outputs)]
+    check_outputs(g, got, "cuda-in-place")
+    # the cache argument itself now holds the updated cache
+    np.testing.assert_array_equal(rt.ReadFromDevice(dins[2][0], lp.prog.outputs[1]["bytes"]), got[1])
+    for o, (p, s) in enumerate(zip(douts, lp.prog.outputs)):
+        if o not in pairs.values():
+            rt.PoolFree(p, max(s["bytes"], 16))
+    for p, n in dins:
+        rt.PoolFree(p, n)
 
 
 @pytest.mark.parametrize("name", sorted(K.ALL))
