@@ -234,4 +234,14 @@ def verify_workload(program: str, args, outs, oracle_rows=None) -> str:
             want = (pm / pm.sum()) @ v[h, : m + 1].astype(np.float64)
             assert np.max(np.abs(got[h, m] - want) / (np.abs(want) + 2e-2)) < 2e-2, (h, m)
         return "12 sampled query rows against float64 softmax(QK^T)V"
+    if program.startswith("c4_nbody"):
+        pos0, vel0, mass = args
+        pos = _as(outs[0], np.float32, pos0.shape).astype(np.float64)
+        vel = _as(outs[1], np.float32, vel0.shape).astype(np.float64)
+        assert np.isfinite(pos).all() and np.isfinite(vel).all()
+        m = mass.astype(np.float64).reshape(-1, 1)
+        p0, p1 = (m * vel0).sum(axis=0), (m * vel).sum(axis=0)
+        assert np.all(np.abs(p1 - p0) <= 1e-3 * np.abs(m * vel).sum(axis=0)), "total momentum drifted"
+        assert np.abs(pos - pos0).max() > 1e-3, "the system did not move"
+        return "finite state, total momentum conserved over the 200 steps (1e-3 of the summed magnitudes), bodies moved"
     return ""
