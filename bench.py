@@ -416,7 +416,13 @@ def main():
             try:
                 if lp2 is None:
                     host_out = [d.cpu().numpy()[:s["bytes"]] for d, s in zip(dev_out, lp.prog.outputs)]
+                    if world > 1 and plan and plan.reduce_outputs and not plan.batch_inputs and not plan.seed_per_rank:
+                        # replicas of one input: an all-reduced result is `world` times the single-GPU value
+                        for i in plan.reduce_outputs:
+                            host_out[i] = (host_out[i].view(np.float32) / np.float32(world)).view(np.uint8)
                     verified_what = fullsize_refs.verify_workload(name, host_in, host_out, oracle_rows)
+                    if world > 1 and verified_what and plan and plan.reduce_outputs and not plan.batch_inputs:
+                        verified_what += f"; the all-reduced scalar is {world} x the single-GPU one"
                 else:
                     # config 3 on N GPUs: every rank must hold the same updated weights, and they must be
                     # what the single-GPU step gives on the global batch (checked on rank 0)

@@ -821,7 +821,17 @@ bool BuildDeviceTables(const VmProgram &p, uint64_t arena_base, DeviceTables *ou
     std::memset(&d, 0, sizeof(d));
     d.task = e.task; d.tile_lo = e.tile_lo; d.tile_hi = e.tile_hi;
     const bool control = e.task == kEntWhile || e.task == kEntIf || e.task == kEntFor;
-    if (control) { d.a = e.wait_flag; d.b = e.wait_count; }   // tile entries: the reserved words stay 0
+    if (control) { d.a = e.wait_flag; d.b = e.wait_count; }   // tile entries: the device words stay 0
+    // Point-to-point dependencies (scheduler.py:201-209 reserves wait_flag / wait_count / signal_flag of tile and
+    // barrier entries for them; the reference emits "no flag" and a zero count): this backend orders phases by grid
+    // barriers only, so an entry that names a flag is refused rather than run without its ordering.
+    constexpr uint32_t kFlagNone = 0xFFFFFFFFu;
+    if (!control && ((e.wait_flag != kFlagNone && e.wait_flag != 0u) || e.wait_count ||
+                     (e.signal_flag != kFlagNone && e.signal_flag != 0u))) {
+      *unimplemented = true;
+      *err = "entry " + std::to_string(i) + " carries point-to-point wait / signal fields: not implemented by this backend";
+      return false;
+    }
     if (e.task == kEntWhile || e.task == kEntIf) d.cond = c.Ref(e.signal_flag);
   }
 

@@ -237,7 +237,12 @@ b2_status Enqueue(b2_loaded *lp, const b2::IoTable &io, cudaStream_t stream, std
   kp.wait_budget_ns = lp->wait_budget_ns;
   kp.io = io;
   e = b2::kVariants[lp->variant].launch(kp, lp->prog.n_lanes, lp->rt->threads, lp->rt->smem_bytes, stream);
-  if (e != cudaSuccess) { *err = CudaMsg("megakernel launch", e); cudaGetLastError(); return B2_INTERNAL; }
+  if (e != cudaSuccess) {          // whatever was queued before the failure may have run: start clean next time
+    *err = CudaMsg("megakernel launch", e);
+    cudaGetLastError();
+    lp->sync_dirty = true;
+    return B2_INTERNAL;
+  }
   lp->launches++;
   lp->last_stream = stream;
   return B2_OK;
@@ -652,20 +657,22 @@ static b2_status BindAndRun(b2_loaded *lp, void *const *dev_in, void *const *dev
     io.p[lp->tab.output_port[o]] = dev_out[o];
   }
   const b2_status st = Enqueue(lp, io, stream, err);
-  if (st != B2_OK) return st;
+  if (st != B2_OK) { lp->sync_dirty = true; return st; }
   for (size_t o = 0; o < p.results.ids.size(); ++o) {
     const auto &b = p.buffers[p.results.ids[o]];
     if (lp->tab.output_port[o] >= 0 || !b.bytes) continue;
     if ((e = cudaMemcpyAsync(dev_out[o], lp->arena + b.offset, b.bytes, cudaMemcpyDeviceToDevice, stream)) != cudaSuccess) {
       *err = CudaMsg("result copy out of the arena", e);
+      lp->sync_dirty = true;
       return B2_INTERNAL;
     }
   }
   if (!synchronous) return B2_OK;
-  if (FetchStatus(lp, stream, err) != B2_OK) return B2_INTERNAL;
+  if (FetchStatus(lp, stream, err) != B2_OK) { lp->sync_dirty = true; return B2_INTERNAL; }
   if ((e = cudaStreamSynchronize(stream)) != cudaSuccess) {
     *err = CudaMsg("execute", e);
     cudaGetLastError();
+    lp->sync_dirty = true;
     return B2_INTERNAL;
   }
   return CheckDeviceStatus(lp, err);

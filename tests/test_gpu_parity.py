@@ -104,6 +104,23 @@ def test_in_out_buffers_are_updated_in_place(rt, name):
         rt.PoolFree(p, n)
 
 
+def test_point_to_point_entry_fields_are_refused(rt):
+    """Tile entries whose reserved wait / signal words are set (scheduler.py:201-209 keeps them
+    for point-to-point dependencies and emits "no flag") are refused at load, not ignored."""
+    from blobs import Builder
+    vm = package()
+    b = Builder(2)
+    ba, bb, bc = (b.buf(2 * 4096) for _ in range(3))
+    b.inputs, b.outputs = [ba, bb], [bc]
+    b.in_dims, b.out_dims = [[2 * 4096], [2 * 4096]], [[2 * 4096]]
+    t0 = b.task(0, bc, ba, bb, 0, 2 * 4096)
+    b.ent(0, t0, 0, 1, 3, 1)             # waits once on flag 3
+    b.ent(1, t0, 1, 2)
+    b.barrier_all()
+    with pytest.raises(vm.Unimplemented, match="point-to-point"):
+        vm.LoadedProgram.Load(rt, vm.VmProgram.Parse(b.serialize()))
+
+
 @pytest.mark.parametrize("name", sorted(K.ALL))
 def test_known_answer_programs(rt, name):
     vm = package()
