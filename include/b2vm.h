@@ -153,7 +153,9 @@ uint64_t b2_loaded_launch_count(const b2_loaded *lp);
  * 10 bit mask of the tile-op families the program uses, 11 full reductions
  * (RED_PART + RED_COMB) re-cut evenly over all lanes with the combine folded into
  * the same phase, 12 flash-attention tasks on the decode path (few query rows; K and
- * V rows read with 16-byte loads), 13 in/out ports. Unknown `which` returns 0. */
+ * V rows read with 16-byte loads), 13 in/out ports, 14 phases whose units (matmuls of
+ * different depth, regions, elementwise chains) were re-cut evenly over all lanes.
+ * Unknown `which` returns 0. */
 uint64_t b2_loaded_stat(const b2_loaded *lp, int which);
 /* Per-wait budget of device-side bounded waits, in nanoseconds (default 2e9). */
 void b2_loaded_set_wait_budget_ns(b2_loaded *lp, uint64_t ns);

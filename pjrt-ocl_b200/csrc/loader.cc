@@ -2,6 +2,7 @@
 #include "loader.h"
 
 #include <algorithm>
+#include <cstdlib>
 #include <cstring>
 #include <map>
 #include <set>
@@ -106,6 +107,28 @@ bool ViewFromAux(const VmProgram &p, uint32_t aux_off, DView *v, std::string *er
     return false;
   }
   return true;
+}
+
+// Does every index an access map can produce fall inside a buffer of `n_elems` elements?
+// `slack` is the largest dynamic start offset (dynamic slices: sum of clamp_max x index stride).
+// A malformed blob must fail on the host, not fault on the device.
+bool AccessInside(const int32_t *dims, const int32_t *strides, int rank, int64_t off, int64_t slack, uint64_t n_elems) {
+  int64_t lo = off, hi = off + slack;
+  for (int k = 0; k < rank; ++k) {
+    if (dims[k] <= 0) return true;                       // an empty index space touches nothing
+    const int64_t span = static_cast<int64_t>(dims[k] - 1) * strides[k];
+    if (span < 0) lo += span; else hi += span;
+  }
+  return lo >= 0 && static_cast<uint64_t>(hi) < n_elems;
+}
+
+// The view at aux[aux_off] (rank, dims, strides, offset), read from buffer `buf` as elements of `dtype`.
+bool ViewInsideBuffer(const VmProgram &p, uint32_t aux_off, uint32_t buf, uint32_t dtype, std::string *err) {
+  const int32_t rank = p.aux[aux_off];
+  const uint64_t n = buf < p.buffers.size() ? p.buffers[buf].bytes / std::max<uint64_t>(1, DtypeSize(dtype)) : 0;
+  if (AccessInside(&p.aux[aux_off + 1], &p.aux[aux_off + 1 + rank], rank, p.aux[aux_off + 1 + 2 * rank], 0, n)) return true;
+  *err = "operand view reaches outside buffer " + std::to_string(buf) + " (" + std::to_string(n) + " elements)";
+  return false;
 }
 
 // Is the view, read over the row-major flat index of a [n0, n1, n2] tensor, affine
@@ -388,8 +411,150 @@ bool CollapseView(const int32_t *dims, const int32_t *strides, int rank, int64_t
   return true;
 }
 
+// ---- re-cutting phases whose units differ in cost per tile ----
+//
+// The scheduler packs a phase's units onto lanes by a cost per tile that is one constant per
+// tile-op class (scheduler.py:115-156, 396-432): a matmul tile with K = 8192 counts like one
+// with K = 1024, a GELU-gradient region like a cast. In a phase that mixes such units the
+// lanes holding the dear ones finish last by factors (config 3: a weight-gradient matmul
+// with K = 8192 on 14 lanes beside a forward matmul with K = 1024 on 109 lanes: 708 us of
+// wall time against a median lane at 129 us). Units of one phase are independent of each
+// other (entries of different lanes in a phase never depend on one another; entries of one
+// lane may, but only as a chain over the SAME tile range), so the loader may hand every lane
+// an equal share of every unit instead: no cost model, every lane does a little of each.
+// Applied to straight-line programs (no control entries), to phases of elementwise /
+// region / matmul units whose cost classes differ; everything else keeps the scheduler's cut.
+namespace {
+struct RebUnit {
+  std::vector<uint32_t> tasks;                        // the chain, in lane order
+  std::vector<std::pair<uint32_t, uint32_t>> ranges;  // tile ranges held by the lanes
+  VmEntry proto[8];                                   // one original entry per chain task
+  uint64_t tiles = 0;
+};
+}  // namespace
+
+bool RebalancePhases(const VmProgram &p, VmProgram *q, uint32_t *n_done) {
+  const uint32_t L = static_cast<uint32_t>(p.lane_tab.size());
+  *n_done = 0;
+  if (L < 4) return false;
+  for (const VmEntry &e : p.entries)
+    if (e.task == kEntWhile || e.task == kEntIf || e.task == kEntFor) return false;
+  std::vector<std::vector<std::vector<VmEntry>>> ph(L);   // lane -> phase -> tile entries
+  for (uint32_t l = 0; l < L; ++l) {
+    const VmLane &ln = p.lane_tab[l];
+    if (ln.root_len != ln.count) return false;
+    ph[l].emplace_back();
+    for (uint32_t i = 0; i < ln.count; ++i) {
+      const VmEntry &e = p.entries[ln.off + i];
+      if (e.task == kEntBarrier) { ph[l].emplace_back(); continue; }
+      if (e.task == kEntNop) continue;
+      if (e.task >= p.tasks.size()) return false;
+      ph[l].back().push_back(e);
+    }
+    if (ph[l].size() != ph[0].size()) return false;
+  }
+  const size_t n_ph = ph[0].size();
+  auto cost_class = [&](const RebUnit &u) {
+    const VmTask &t = p.tasks[u.tasks[0]];
+    const uint32_t op = t.tile_op & 0xFFu;
+    // matmuls: by K (p2) and batch; regions: by program length (p0 is the aux offset: use the task id, regions differ);
+    // elementwise: by chain length
+    if (op == kTopMma) return (static_cast<uint64_t>(1) << 60) | (static_cast<uint64_t>(t.p2) << 8) | (t.p3 & 0xFFu);
+    if (op == kTopMapRegion) return (static_cast<uint64_t>(2) << 60) | u.tasks[0];
+    return (static_cast<uint64_t>(3) << 60) | u.tasks.size();
+  };
+  for (size_t k = 0; k < n_ph; ++k) {
+    std::vector<RebUnit> units;
+    std::map<uint32_t, size_t> unit_of;     // task -> unit
+    bool ok = true;
+    for (uint32_t l = 0; l < L && ok; ++l) {
+      const auto &es = ph[l][k];
+      for (size_t i = 0; i < es.size() && ok;) {
+        size_t j = i + 1;
+        while (j < es.size() && es[j].tile_lo == es[i].tile_lo && es[j].tile_hi == es[i].tile_hi && es[j].task != es[i].task) ++j;
+        if (j - i > 8) { ok = false; break; }
+        std::vector<uint32_t> key;
+        for (size_t x = i; x < j; ++x) key.push_back(es[x].task);
+        auto it = unit_of.find(key[0]);
+        size_t ui;
+        if (it == unit_of.end()) {
+          for (uint32_t t : key) if (unit_of.count(t)) ok = false;
+          if (!ok) break;
+          ui = units.size();
+          units.emplace_back();
+          units[ui].tasks = key;
+          for (size_t x = i; x < j; ++x) { units[ui].proto[x - i] = es[x]; unit_of[es[x].task] = ui; }
+        } else {
+          ui = it->second;
+          if (units[ui].tasks != key) { ok = false; break; }
+        }
+        if (es[i].tile_hi > es[i].tile_lo) units[ui].ranges.push_back({es[i].tile_lo, es[i].tile_hi});
+        i = j;
+      }
+    }
+    if (!ok || units.size() < 2) continue;
+    bool differ = false;
+    for (RebUnit &u : units) {
+      for (uint32_t t : u.tasks) {
+        const uint32_t op = p.tasks[t].tile_op & 0xFFu;
+        if (!(op == kTopEw || op == kTopMapRegion || op == kTopMma)) ok = false;
+      }
+      std::sort(u.ranges.begin(), u.ranges.end());
+      uint32_t at = 0;
+      for (const auto &r : u.ranges) { if (r.first != at) ok = false; at = r.second; }   // an exact partition of [0, tiles)
+      u.tiles = at;
+      if (!u.tiles) ok = false;
+      if (cost_class(u) != cost_class(units[0])) differ = true;
+    }
+    if (!ok || !differ) continue;
+    for (uint32_t l = 0; l < L; ++l) {
+      auto &es = ph[l][k];
+      es.clear();
+      for (const RebUnit &u : units) {
+        const uint32_t lo = static_cast<uint32_t>(u.tiles * l / L), hi = static_cast<uint32_t>(u.tiles * (l + 1) / L);
+        if (hi <= lo) continue;
+        for (size_t x = 0; x < u.tasks.size(); ++x) {
+          VmEntry e = u.proto[x];
+          e.tile_lo = lo; e.tile_hi = hi;
+          es.push_back(e);
+        }
+      }
+    }
+    ++*n_done;
+  }
+  if (!*n_done) return false;
+  *q = p;
+  q->entries.clear();
+  VmEntry bar;
+  std::memset(&bar, 0, sizeof(bar));
+  bar.task = kEntBarrier; bar.wait_flag = 0xFFFFFFFFu; bar.signal_flag = 0xFFFFFFFFu;
+  for (uint32_t l = 0; l < L; ++l) {
+    const uint32_t off = static_cast<uint32_t>(q->entries.size());
+    for (size_t k = 0; k < n_ph; ++k) {
+      if (k) q->entries.push_back(bar);
+      for (const VmEntry &e : ph[l][k]) q->entries.push_back(e);
+    }
+    const uint32_t cnt = static_cast<uint32_t>(q->entries.size()) - off;
+    q->lane_tab[l] = VmLane{off, cnt, cnt, 0u};
+  }
+  return true;
+}
+
+static bool BuildDeviceTablesFor(const VmProgram &p, uint64_t arena_base, DeviceTables *out, std::string *err,
+                                 bool *unimplemented);
+
 bool BuildDeviceTables(const VmProgram &p, uint64_t arena_base, DeviceTables *out, std::string *err,
                        bool *unimplemented) {
+  VmProgram q;
+  uint32_t n_reb = 0;
+  const bool recut = std::getenv("B2VM_NO_REBALANCE") == nullptr && RebalancePhases(p, &q, &n_reb);
+  const bool ok = BuildDeviceTablesFor(recut ? q : p, arena_base, out, err, unimplemented);
+  out->n_rebalanced = n_reb;
+  return ok;
+}
+
+static bool BuildDeviceTablesFor(const VmProgram &p, uint64_t arena_base, DeviceTables *out, std::string *err,
+                                 bool *unimplemented) {
   *unimplemented = false;
   Ctx c{p, arena_base, {}, out};
   out->desc.assign(1, 0);
@@ -460,10 +625,12 @@ bool BuildDeviceTables(const VmProgram &p, uint64_t arena_base, DeviceTables *ou
         std::memset(views, 0, sizeof(views));
         if (viewable && t.p2) {
           if (!ViewFromAux(p, t.p2 - 1, &views[0], err)) return fail_unimpl(*err);
+          if (!ViewInsideBuffer(p, t.p2 - 1, t.a, d.adt, err)) return false;
           d.flags |= kViewA;
         }
         if (viewable && IsBin(sub) && t.p3) {
           if (!ViewFromAux(p, t.p3 - 1, &views[1], err)) return fail_unimpl(*err);
+          if (!ViewInsideBuffer(p, t.p3 - 1, t.b, d.adt, err)) return false;
           d.flags |= kViewB;
         }
         if (d.flags & (kViewA | kViewB)) d.desc = c.PushDesc(views);
@@ -485,6 +652,18 @@ bool BuildDeviceTables(const VmProgram &p, uint64_t arena_base, DeviceTables *ou
         if (!CollapseView(&p.aux[x + 1], &p.aux[x + 1 + rank], rank, dyn ? 0 : p.aux[x + 1 + 2 * rank], &m.view))
           return fail_unimpl("access map does not collapse");
         m.esz = static_cast<uint32_t>(DtypeSize(d.dt));
+        {
+          // the strided side: the source of a gather, the destination of a scatter
+          const uint32_t side = (d.op == kTopGather || d.op == kTopDynGather) ? t.a : t.dst;
+          int64_t slack = 0;
+          if (dyn) for (int32_t k = 0; k < rank; ++k) slack += static_cast<int64_t>(p.aux[x + 1 + 2 * rank + k]) * p.aux[x + 1 + rank + k];
+          const uint64_t n_side = p.buffers[side].bytes / std::max<uint64_t>(1, m.esz);
+          const int32_t *mv_strides = &p.aux[x + 1 + rank];
+          if (!AccessInside(&p.aux[x + 1], mv_strides, rank, dyn ? 0 : p.aux[x + 1 + 2 * rank], slack, n_side)) {
+            *err = "task " + std::to_string(ti) + ": access map reaches outside buffer " + std::to_string(side);
+            return false;
+          }
+        }
         if (dyn) {
           if (rank > 8) return fail_unimpl("dynamic slice of rank > 8");
           m.n_idx = static_cast<uint32_t>(rank);
@@ -550,10 +729,12 @@ bool BuildDeviceTables(const VmProgram &p, uint64_t arena_base, DeviceTables *ou
         std::memset(&m, 0, sizeof(m));
         if (t.p4) {
           if (!ViewFromAux(p, t.p4 - 1, &m.va, err)) return fail_unimpl(*err);
+          if (!ViewInsideBuffer(p, t.p4 - 1, t.a, d.adt, err)) return false;
           d.flags |= kViewA;
         }
         if (t.p5) {
           if (!ViewFromAux(p, t.p5 - 1, &m.vb, err)) return fail_unimpl(*err);
+          if (!ViewInsideBuffer(p, t.p5 - 1, t.b, d.adt, err)) return false;
           d.flags |= kViewB;
         }
         if (t.p6) {
@@ -620,9 +801,9 @@ bool BuildDeviceTables(const VmProgram &p, uint64_t arena_base, DeviceTables *ou
         const int32_t *x = &p.aux[t.p3];
         if (x[3] > 256) return fail_unimpl("flash-attention head_dim > 256");
         const uint32_t qv = static_cast<uint32_t>(x[6]), kv = static_cast<uint32_t>(x[7]), vv = static_cast<uint32_t>(x[8]);
-        if (qv) { if (!ViewFromAux(p, qv - 1, &f.vq, err)) return fail_unimpl(*err); f.has_q = 1; }
-        if (kv) { if (!ViewFromAux(p, kv - 1, &f.vk, err)) return fail_unimpl(*err); f.has_k = 1; }
-        if (vv) { if (!ViewFromAux(p, vv - 1, &f.vv, err)) return fail_unimpl(*err); f.has_v = 1; }
+        if (qv) { if (!ViewFromAux(p, qv - 1, &f.vq, err)) return fail_unimpl(*err); if (!ViewInsideBuffer(p, qv - 1, t.a, d.adt, err)) return false; f.has_q = 1; }
+        if (kv) { if (!ViewFromAux(p, kv - 1, &f.vk, err)) return fail_unimpl(*err); if (!ViewInsideBuffer(p, kv - 1, t.b, d.adt, err)) return false; f.has_k = 1; }
+        if (vv) { if (!ViewFromAux(p, vv - 1, &f.vv, err)) return fail_unimpl(*err); if (!ViewInsideBuffer(p, vv - 1, t.p0, d.adt, err)) return false; f.has_v = 1; }
         float scale_f;
         std::memcpy(&scale_f, &x[4], 4);
         const bool scale_positive = scale_f > 0.0f && scale_f < 1e30f;   // the row maximum is taken before scaling

@@ -714,6 +714,24 @@ def _():
     return _dot_tc_case(BF16, BF16, fold_views=True)
 
 
+@case("dot_tc_broadcast_bf16", rtol=2e-2, atol=3e-2)
+def _():
+    """A batched 16-bit dot_general whose right operand is the broadcast of one program
+    input over the batch: `_fuse_matmul_views` folds the broadcast into the matmul's operand
+    view (batch stride 0), and the operand is an I/O port. Both results must come out the
+    same whichever path (tensor maps or per-thread copies) the backend takes."""
+    a = Asm()
+    x = a.input((4, 200, 136), BF16)
+    w = a.input((136, 152), BF16)
+    wb = a.broadcast_in_dim(w, (4, 136, 152), [1, 2])
+    o = a.dot_general(x, wb, lb=[0], lc=2, rb=[0], rc=1, out_dtype=BF16)           # [4,200,152]
+    xb = a.broadcast_in_dim(a.input((200, 136), BF16), (4, 200, 136), [1, 2])
+    o2 = a.dot_general(xb, a.input((4, 136, 88), BF16), lb=[0], lc=2, rb=[0], rc=1, out_dtype=F32)
+    blob, prog = a.finish([o, o2], nlanes=6, fold_2byte_matmul_views=True)
+    return blob, prog, (31, [N((4, 200, 136), "bf16", 0.5), N((136, 152), "bf16", 0.2),
+                             N((200, 136), "bf16", 0.5), N((4, 136, 88), "bf16", 0.2)])
+
+
 @case("dot_kat_2x2", exact=True)
 def _():
     """tests/test_ops_dot.py:56-63 known answer: [[1,2],[3,4]] @ [[5,6],[7,8]]

@@ -104,6 +104,20 @@ def test_in_out_buffers_are_updated_in_place(rt, name):
         rt.PoolFree(p, n)
 
 
+def test_phases_mixing_unit_costs_are_recut_over_all_lanes(rt):
+    """Config 3's backward phases hold matmuls of different depth, regions and casts side by
+    side; the scheduler's cost per tile is one constant per op class, so the loader re-cuts
+    such phases evenly over all lanes. Values are those of the scheduler's own cut."""
+    vm = package()
+    g = Golden("c3_mlp_bf16_small")
+    lp = vm.LoadedProgram.Load(rt, vm.VmProgram.Parse(g.blob))
+    assert lp.stat("rebalanced_phases") >= 1
+    check_outputs(g, [np.ascontiguousarray(o).view(np.uint8).reshape(-1) for o in lp.Execute(g.args)], "cuda-recut")
+    # a phase of equal units keeps the scheduler's cut
+    g2 = Golden("c2_chain_f32_small")
+    assert vm.LoadedProgram.Load(rt, vm.VmProgram.Parse(g2.blob)).stat("rebalanced_phases") == 0
+
+
 def test_point_to_point_entry_fields_are_refused(rt):
     """Tile entries whose reserved wait / signal words are set (scheduler.py:201-209 keeps them
     for point-to-point dependencies and emits "no flag") are refused at load, not ignored."""
@@ -118,6 +132,24 @@ def test_point_to_point_entry_fields_are_refused(rt):
     b.ent(1, t0, 1, 2)
     b.barrier_all()
     with pytest.raises(vm.Unimplemented, match="point-to-point"):
+        vm.LoadedProgram.Load(rt, vm.VmProgram.Parse(b.serialize()))
+
+
+def test_operand_view_outside_its_buffer_is_refused(rt):
+    """A view whose largest index lies beyond its buffer is a malformed program: refused on
+    the host at load (INVALID_ARGUMENT), never run."""
+    from blobs import Builder
+    vm = package()
+    n = 4096
+    b = Builder(1)
+    ba, bb, bc = (b.buf(n) for _ in range(3))
+    b.inputs, b.outputs = [ba, bb], [bc]
+    b.in_dims, b.out_dims = [[n], [n]], [[n]]
+    b.aux = [0, 1, n, 2, 0]              # word 1..: rank 1, dims [n], strides [2], offset 0 -> indices up to 2n - 2
+    t0 = b.task(0, bc, ba, bb, 0, n, 2)  # add, operand a through the view at aux[1]
+    b.ent(0, t0, 0, 1)
+    b.barrier_all()
+    with pytest.raises(vm.InvalidArgument, match="outside buffer"):
         vm.LoadedProgram.Load(rt, vm.VmProgram.Parse(b.serialize()))
 
 
