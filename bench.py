@@ -101,6 +101,9 @@ WORKLOADS = {
                            "f32", "config 4 cut to 2 RK4 steps (46 grid barriers): the same phases as the 200-step launch, "
                            "short enough to profile", roof_alg=(28 * 4096 * 4096 * 3 * 4 + 16 * 4096 * 4096 * 4) * 2,
                            secondary=True),
+    "c3_stage_gelu_grad": _wl("c3_stage_gelu_grad_f32", "eltwise HBM GB/s", "GB/s", 2 * N_C2 * 4, 1e9, "hbm", "f32",
+                              "config 3 stage: the GELU-derivative MAP_REGION (14 micro-ops) over 8192 x 4096 f32",
+                              secondary=True),
     "flash_decode_bf16": _wl("flash_decode_bf16_c5", "decode-attention GB/s", "GB/s", 2 * 512 * 2049 * 64 * 2, 1e9, "hbm", "bf16",
                              "config 5's decode attention alone: 512 heads x 1 query x 2049 keys, head_dim 64; "
                              "bytes = K and V read once", secondary=True, traffic=297.1e6),

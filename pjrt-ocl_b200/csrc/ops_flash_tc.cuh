@@ -80,7 +80,7 @@ static __device__ __noinline__ bool flash_tc_tiles(const Lane &L, const DTask &t
   volatile uint32_t *failed = &S->failed;
   const uint32_t base0 = (smem_addr(sm + kSmemSys) + 1023u) & ~1023u;
   const uint32_t q_s = base0, kv_s = q_s + 2u * kFaTile, p_s = kv_s + kFaStages * 2u * kFaTile;
-  const uint32_t w = L.tid / kWarp, lane = L.tid % kWarp;
+  const uint32_t w = __shfl_sync(0xffffffffu, L.tid / kWarp, 0), lane = L.tid % kWarp;   // the warp index, provably uniform
   const unsigned long long budget = P.wait_budget_ns;
   const bool k_mn = df.k_mn != 0;
 
@@ -141,7 +141,7 @@ static __device__ __noinline__ bool flash_tc_tiles(const Lane &L, const DTask &t
     tc_fence_before_sync();
     __syncthreads();       // also: every role is done with the previous unit (Q, P, the rings, tensor memory)
     tc_fence_after_sync();
-    const uint32_t unit = S->unit;
+    const uint32_t unit = __shfl_sync(0xffffffffu, S->unit, 0);
     if (unit == 0xffffffffu || S->failed) break;
     const int64_t g = unit / upm, m0 = (unit % upm) * 256;
     const int32_t h0c = static_cast<int32_t>(g % df.h0_size), h1c = static_cast<int32_t>(g / df.h0_size);
@@ -179,70 +179,83 @@ static __device__ __noinline__ bool flash_tc_tiles(const Lane &L, const DTask &t
       __syncwarp();
     } else if (w == 1) {
       // ---------------- MMA issue ----------------
-      if (lane == 0) {
+      // The whole warp walks the loop with warp-uniform control (votes, shuffles from lane 0) and one
+      // elected lane issues: operands that the compiler can prove uniform stay in uniform registers,
+      // which is what makes a tcgen05.mma cheap to issue (measured: ~95 cycles each from a thread inside
+      // a lane == 0 branch, where every operand has to be moved over first).
+      {
         const uint32_t fmt = adt == kBF16 ? 1u : 0u;
         // S: A = Q (K-major), B = K block; O: A = P (K-major), B = V (d is the unit-stride "MN" dimension)
         const uint32_t idesc_s = (1u << 4) | (fmt << 7) | (fmt << 10) | ((k_mn ? 1u : 0u) << 16) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
         const uint32_t idesc_o = (1u << 4) | (fmt << 7) | (fmt << 10) | (1u << 16) | ((64u >> 3) << 17) | ((128u >> 4) << 24);
-        bool ok = tc_wait(&S->q_full, qn & 1u, failed, budget);
+        bool ok = tc_wait_warp(&S->q_full, qn & 1u, failed, budget);
         tc_fence_after_sync();
         // Descriptors of stage 0 / slot 0; the others differ in the 16-byte-unit address field only.
         const uint64_t dq0 = tc_desc(q_s, 16u, 1024u), dp0 = tc_desc(p_s, 16u, 1024u);
         const uint64_t dk0 = k_mn ? tc_desc(kv_s, 8192u, 1024u) : tc_desc(kv_s, 16u, 1024u);
         const uint64_t dv0 = tc_desc(kv_s + kFaTile, 16384u, 1024u);
         const uint64_t adv_b = k_mn ? (2048u >> 4) : (32u >> 4);
+        const bool issuer = elect_one_sync();
         // The issuer is an event loop over both slots: S(j+1) of a slot goes out as soon as the slot's
         // scores are in registers (s_free) and the keys have landed; P.V(j) when the slot's P is written.
         // S is tried first, so the next scores are ready when the softmax warps finish a block.
-        int64_t ns[2] = {0, 0}, npv[2] = {0, 0}, released = 0;
+        uint32_t ns[2] = {0u, 0u}, npv[2] = {0u, 0u}, released = 0u;
+        const uint32_t nk0 = static_cast<uint32_t>(nkb[0]), nk1 = static_cast<uint32_t>(nkb[1]), nmx = static_cast<uint32_t>(nmax);
         uint32_t kv_seen = 0, idle = 0;
         unsigned long long t_idle = 0;
         while (ok) {
           bool progressed = false, done = true;
 #pragma unroll
           for (int s = 0; s < 2; ++s) {
-            if (ns[s] < nkb[s]) {
+            const uint32_t nk = s ? nk1 : nk0;
+            if (ns[s] < nk) {
               done = false;
-              const int64_t j = ns[s];
-              if (static_cast<int64_t>(kv_seen) <= j) {
+              const uint32_t j = ns[s];
+              if (kv_seen <= j) {
                 const uint32_t pos = kvpos + kv_seen;
-                if (mbar_test_wait_parity(&S->kv_full[pos % kFaStages], (pos / kFaStages) & 1u)) ++kv_seen;
+                if (__all_sync(0xffffffffu, mbar_test_wait_parity(&S->kv_full[pos % kFaStages], (pos / kFaStages) & 1u))) ++kv_seen;
               }
-              if (static_cast<int64_t>(kv_seen) > j &&
-                  (j == 0 || mbar_test_wait_parity(&S->s_free[s], (cnt[s] + static_cast<uint32_t>(j) - 1u) & 1u))) {
+              if (kv_seen > j && (j == 0u || __all_sync(0xffffffffu, mbar_test_wait_parity(&S->s_free[s], (cnt[s] + j - 1u) & 1u)))) {
                 tc_fence_after_sync();
-                const uint32_t st = (kvpos + static_cast<uint32_t>(j)) % kFaStages;
+                const uint32_t st = (kvpos + j) % kFaStages;
                 const uint64_t da = dq0 + static_cast<uint32_t>(s) * (kFaTile >> 4);
                 const uint64_t db = dk0 + st * ((2u * kFaTile) >> 4);
+                if (issuer) {
 #pragma unroll
-                for (uint32_t kk = 0; kk < 4; ++kk)
-                  tc_mma_f16(tmem + static_cast<uint32_t>(s) * 128u, da + kk * (32u >> 4), db + kk * adv_b, idesc_s, kk ? 1u : 0u);
-                tc_commit(&S->s_full[s]);
+                  for (uint32_t kk = 0; kk < 4; ++kk)
+                    tc_mma_f16(tmem + static_cast<uint32_t>(s) * 128u, da + kk * (32u >> 4), db + kk * adv_b, idesc_s, kk ? 1u : 0u);
+                  tc_commit(&S->s_full[s]);
+                }
+                __syncwarp();
                 ++ns[s];
                 progressed = true;
               }
             }
-            if (npv[s] < nkb[s]) {
+            if (npv[s] < nk) {
               done = false;
-              const int64_t j = npv[s];
-              if (ns[s] > j && mbar_test_wait_parity(&S->p_full[s], (cnt[s] + static_cast<uint32_t>(j)) & 1u)) {
+              const uint32_t j = npv[s];
+              if (ns[s] > j && __all_sync(0xffffffffu, mbar_test_wait_parity(&S->p_full[s], (cnt[s] + j) & 1u))) {
                 tc_fence_after_sync();
-                const uint32_t st = (kvpos + static_cast<uint32_t>(j)) % kFaStages;
+                const uint32_t st = (kvpos + j) % kFaStages;
                 const uint64_t dp = dp0 + static_cast<uint32_t>(s) * (kFaPBytes >> 4);
                 const uint64_t dv = dv0 + st * ((2u * kFaTile) >> 4);
+                if (issuer) {
 #pragma unroll
-                for (uint32_t kk = 0; kk < 8; ++kk)
-                  tc_mma_f16(tmem + 256u + static_cast<uint32_t>(s) * 64u, dp + ((kk >> 2) * 16384u + (kk & 3u) * 32u) / 16u,
-                             dv + kk * (2048u >> 4), idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
-                tc_commit(&S->pv_done[s]);
+                  for (uint32_t kk = 0; kk < 8; ++kk)
+                    tc_mma_f16(tmem + 256u + static_cast<uint32_t>(s) * 64u, dp + ((kk >> 2) * 16384u + (kk & 3u) * 32u) / 16u,
+                               dv + kk * (2048u >> 4), idesc_o, (j > 0u || kk > 0u) ? 1u : 0u);
+                  tc_commit(&S->pv_done[s]);
+                }
+                __syncwarp();
                 ++npv[s];
                 progressed = true;
               }
             }
           }
           // a stage is free when the matmuls of both slots that read it have completed
-          while (released < nmax && (released >= nkb[0] || npv[0] > released) && (released >= nkb[1] || npv[1] > released)) {
-            tc_commit(&S->kv_empty[(kvpos + static_cast<uint32_t>(released)) % kFaStages]);
+          while (released < nmx && (released >= nk0 || npv[0] > released) && (released >= nk1 || npv[1] > released)) {
+            if (issuer) tc_commit(&S->kv_empty[(kvpos + released) % kFaStages]);
+            __syncwarp();
             ++released;
           }
           if (done) break;
@@ -252,10 +265,14 @@ static __device__ __noinline__ bool flash_tc_tiles(const Lane &L, const DTask &t
           }
           nanosleep_ns(32);      // leave the issue slots to the softmax warps of this scheduler
           if ((++idle & 1023u) == 0u) {
-            if (*failed) { ok = false; break; }
-            const unsigned long long now = globaltimer_ns();
-            if (idle == 1024u) t_idle = now;
-            else if (now - t_idle > budget) { *failed = 1u; ok = false; break; }
+            uint32_t give_up = 0u;
+            if (lane == 0) {
+              if (*failed) give_up = 1u;
+              const unsigned long long now = globaltimer_ns();
+              if (idle == 1024u) t_idle = now;
+              else if (now - t_idle > budget) { *failed = 1u; give_up = 1u; }
+            }
+            if (__shfl_sync(0xffffffffu, give_up, 0)) { ok = false; break; }
           }
         }
       }

@@ -70,6 +70,23 @@ def flash_only(H=128, T=2048, hd=64, causal=True, nlanes=NLANES, dtype=BF16):
                             ("normal", (H, T, hd), DN[dtype])])
 
 
+def region_only(n=8192 * 4096, nlanes=NLANES):
+    """One MAP_REGION over n f32 elements: the GELU derivative of config 3's backward pass
+    (14 micro-ops, one input), for per-family numbers."""
+    a_ = Asm()
+    zf = a_.input((n,), F32)
+    c, k = 0.7978845608, 0.044715
+    z2 = a_.mul(zf, zf)
+    u = a_.mul(a_.scalar(c, zf), a_.add(zf, a_.mul(a_.scalar(k, zf), a_.mul(z2, zf))))
+    t = a_.tanh(u)
+    sech2 = a_.sub(a_.scalar(1.0, t), a_.mul(t, t))
+    du = a_.mul(a_.scalar(c, zf), a_.add(a_.scalar(1.0, zf), a_.mul(a_.scalar(3 * k, zf), z2)))
+    g = a_.add(a_.mul(a_.scalar(0.5, t), a_.add(a_.scalar(1.0, t), t)),
+               a_.mul(a_.mul(a_.scalar(0.5, zf), zf), a_.mul(sech2, du)))
+    blob, prog = a_.finish([g], nlanes=nlanes, costs=B200_COSTS)
+    return blob, prog, (7, [("normal", (n,), "f32")])
+
+
 def flash_decode_only(H=512, C=2049, hd=64, nlanes=NLANES, dtype=BF16):
     """The attention of config 5's decode step on its own: one query row per head against
     a cache of C positions, K [H,C,hd] read through its transposed view, V [H,C,hd]."""

@@ -69,6 +69,7 @@ PROGRAMS["dot_bf16_8192"] = lambda: cases.dot_general_square(8192)
 PROGRAMS["dot_bf16_4096"] = lambda: cases.dot_general_square(4096)
 PROGRAMS["flash_bf16_c5"] = lambda: cases.flash_only()
 PROGRAMS["flash_decode_bf16_c5"] = lambda: cases.flash_decode_only()
+PROGRAMS["c3_stage_gelu_grad_f32"] = lambda: cases.region_only()
 
 
 def main():
