@@ -80,7 +80,7 @@ WORKLOADS = {
                          "one dot_general bf16 4096 x 4096 x 4096", secondary=True, traffic=163.1e6),
     "flash_bf16": _wl("flash_bf16_c5", "flash-attention TFLOP/s", "TFLOP/s", _C5_ATT_FLOPS, 1e12, "tensor", "bf16",
                       "config 5's attention alone: 128 heads x 2048 x 2048, head_dim 64, causal (flops count the "
-                      "causal half)", secondary=True, traffic=148.1e6),
+                      "causal half)", secondary=True, traffic=150.6e6),
     "c3_mlp": _wl("c3_mlp_step_bf16", "dot_general TFLOP/s", "TFLOP/s", _C3_FLOPS, 1e12, "tensor", "bf16",
                   "config 3: 3-layer MLP forward + grad of MSE + SGD step, batch 8192, 1024-4096-4096-1024, bf16; "
                   "on N GPUs: local-batch gradients, NCCL all-reduce, SGD program", plan="c3"),

@@ -11,6 +11,12 @@
 #include "format.h"
 #include "ptx.cuh"
 
+// Short-run paths (segments of 2..8 elements, views whose source runs are shorter than 16 bytes, pow with
+// constant exponents): compiled only into the builds that carry that family (vm_kernel.cu sets B2_SHORT).
+#ifndef B2_SHORT
+#define B2_SHORT 1
+#endif
+
 namespace b2 {
 
 // Shared-memory map of one lane (CTA). The first kSmemSys bytes are reserved for
@@ -151,6 +157,56 @@ __device__ __forceinline__ int64_t view_index(const DView &v, uint32_t i) {
   if (v.rank > 0) idx += static_cast<int64_t>(rem) * v.stride[0];
   return idx;
 }
+// Walking a view of rank 1..3 element by element: the coordinates of the first
+// element cost the divisions, every following one an increment with carry. The
+// fields live in registers, so a run of consecutive consumer elements whose source
+// elements are not adjacent (an innermost axis of 3, a strided slice) costs a few
+// instructions per element instead of a descriptor walk each.
+struct ViewWalk {
+  uint32_t dA, dB;          // innermost / middle dimension (0xFFFFFFFF where that level never wraps)
+  uint32_t mgA, shA, mgB, shB;
+  int64_t stA, stB, stO, off;
+  int rank;
+};
+__device__ __forceinline__ ViewWalk view_walk(const DView &v) {
+  ViewWalk w;
+  const int r = v.rank;
+  w.rank = r;
+  w.dA = r >= 2 ? v.dim[r - 1] : 0xFFFFFFFFu;
+  w.dB = r >= 3 ? v.dim[1] : 0xFFFFFFFFu;
+  w.mgA = v.magic[r - 1]; w.shA = v.shift[r - 1];
+  w.mgB = v.magic[1]; w.shB = v.shift[1];
+  w.stA = v.stride[r - 1];
+  w.stB = r >= 3 ? v.stride[1] : (r == 2 ? v.stride[0] : 0);
+  w.stO = r >= 3 ? v.stride[0] : 0;
+  w.off = v.off;
+  return w;
+}
+__device__ __forceinline__ void view_walk_seek(const ViewWalk &w, uint32_t i, uint32_t &cA, uint32_t &cB, uint32_t &cO) {
+  cA = i; cB = 0u; cO = 0u;
+  if (w.rank >= 2) {
+    const uint32_t mh = __umulhi(i, w.mgA);
+    const uint32_t q = (((i - mh) >> 1) + mh) >> w.shA;
+    cA = i - q * w.dA;
+    cB = q;
+  }
+  if (w.rank >= 3) {
+    const uint32_t mh = __umulhi(cB, w.mgB);
+    const uint32_t q = (((cB - mh) >> 1) + mh) >> w.shB;
+    cB -= q * w.dB;
+    cO = q;
+  }
+}
+__device__ __forceinline__ int64_t view_walk_index(const ViewWalk &w, uint32_t cA, uint32_t cB, uint32_t cO) {
+  return w.off + static_cast<int64_t>(cA) * w.stA + static_cast<int64_t>(cB) * w.stB + static_cast<int64_t>(cO) * w.stO;
+}
+__device__ __forceinline__ void view_walk_next(const ViewWalk &w, uint32_t &cA, uint32_t &cB, uint32_t &cO) {
+  if (++cA == w.dA) {
+    cA = 0u;
+    if (++cB == w.dB) { cB = 0u; ++cO; }
+  }
+}
+
 // Uncollapsed aux-pool descriptor {rank, dims[rank], strides[rank], src_off}
 // (pjrt_plugin/kernels/ops/ew.cl:174-185): used where a view exceeds 4 dims.
 __device__ __forceinline__ int64_t aux_view_index(const int32_t *x, uint32_t i) {

@@ -45,6 +45,8 @@ enum Family : uint32_t {
   kFamMma = 1u << 5,     // TILE_MMA
   kFamFlash = 1u << 6,   // FLASH_ATTN
   kFamIndex = 1u << 7,   // RED_WINDOW, GATHER_INDEX, SCATTER_INDEX, CONV
+  kFamShort = 1u << 8,   // short-run paths of the families above: RED_SEG over segments of 2..8 elements, elementwise
+                         // views and gathers whose source runs are shorter than 16 bytes, pow with constant exponents
   kFamAll = 0xFFFFFFFFu
 };
 B2_HOST_DEVICE inline uint32_t family_of(uint32_t tile_op) {

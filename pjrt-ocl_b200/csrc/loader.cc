@@ -605,6 +605,9 @@ static bool BuildDeviceTablesFor(const VmProgram &p, uint64_t arena_base, Device
     d.dt = (t.tile_op >> 8) & 0xFFu;
     d.adt = (t.tile_op >> 16) & 0xFFu;
     out->families |= family_of(d.op);
+    // the short-run paths (a build of their own, so that programs without such work do not carry them)
+    if (d.op == kTopRedSeg && !t.p3 && d.dt == kF32 && d.adt == kF32 && t.p1 >= 2 && t.p1 <= 8) out->families |= kFamShort;
+    if (d.op == kTopEw && t.p0 == kPow && d.dt == kF32) out->families |= kFamShort;
     const uint32_t raw[8] = {t.p0, t.p1, t.p2, t.p3, t.p4, t.p5, t.p6, t.p7};
     std::memcpy(d.p, raw, sizeof(raw));
     d.ptr[0] = c.Ref(t.dst);
@@ -626,11 +629,13 @@ static bool BuildDeviceTablesFor(const VmProgram &p, uint64_t arena_base, Device
         if (viewable && t.p2) {
           if (!ViewFromAux(p, t.p2 - 1, &views[0], err)) return fail_unimpl(*err);
           if (!ViewInsideBuffer(p, t.p2 - 1, t.a, d.adt, err)) return false;
+          if (!views[0].vec_ok && views[0].rank >= 1 && views[0].rank <= 3) out->families |= kFamShort;
           d.flags |= kViewA;
         }
         if (viewable && IsBin(sub) && t.p3) {
           if (!ViewFromAux(p, t.p3 - 1, &views[1], err)) return fail_unimpl(*err);
           if (!ViewInsideBuffer(p, t.p3 - 1, t.b, d.adt, err)) return false;
+          if (!views[1].vec_ok && views[1].rank >= 1 && views[1].rank <= 3) out->families |= kFamShort;
           d.flags |= kViewB;
         }
         if (d.flags & (kViewA | kViewB)) d.desc = c.PushDesc(views);
@@ -684,6 +689,7 @@ static bool BuildDeviceTablesFor(const VmProgram &p, uint64_t arena_base, Device
                   v.dim[v.rank - 1] % chunk == 0 && v.off % chunk == 0;
         for (int k = 0; ok && k < v.rank - 1; ++k) ok = v.stride[k] % static_cast<int32_t>(chunk) == 0;
         m.chunk = ok ? chunk : 0u;
+        if (d.op == kTopGather && !m.chunk && m.esz == 4 && m.view.rank >= 1 && m.view.rank <= 3) out->families |= kFamShort;
         // a transpose: dst[..., r, c] = src[... + r + c * ld], 2- or 4-byte elements
         m.transposed = (d.op == kTopGather && !m.chunk && (m.esz == 2 || m.esz == 4) && v.rank >= 2 &&
                         v.stride[v.rank - 2] == 1 && v.stride[v.rank - 1] > 1 && v.dim[v.rank - 1] >= 32 &&

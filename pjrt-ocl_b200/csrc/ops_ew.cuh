@@ -85,6 +85,21 @@ __device__ __forceinline__ float fast_tanh(float x) {
 // a*s + t with two roundings, as the validator computes it (no contraction)
 __device__ __forceinline__ float affine2(float a, float s, float t) { return __fadd_rn(__fmul_rn(a, s), t); }
 
+// x ** y. The exponents a lowered graph actually carries are a handful of constants
+// (inverse-square laws: -1.5; norms: 2, 0.5, -0.5); for positive x those are a few
+// correctly rounded operations instead of the general routine. Everything else,
+// and every x <= 0 / NaN, takes powf, so the special values keep its semantics.
+__device__ __forceinline__ float pow_f32(float x, float y) {
+  if (x > 0.0f && x < INFINITY) {
+    if (y == -1.5f) { const float r = __frsqrt_rn(x); return __fmul_rn(__fmul_rn(r, r), r); }
+    if (y == 2.0f) return __fmul_rn(x, x);
+    if (y == 0.5f) return __fsqrt_rn(x);
+    if (y == -0.5f) return __frsqrt_rn(x);
+    if (y == -1.0f) return __frcp_rn(x);
+  }
+  return powf(x, y);
+}
+
 __device__ __forceinline__ float alu_f(uint32_t sub, float x, float y) {
   switch (sub) {
     case kAdd: return __fadd_rn(x, y);
@@ -93,7 +108,11 @@ __device__ __forceinline__ float alu_f(uint32_t sub, float x, float y) {
     case kDiv: return __fdiv_rn(x, y);
     case kMax: return np_max(x, y);
     case kMin: return np_min(x, y);
+#if B2_SHORT
+    case kPow: return pow_f32(x, y);
+#else
     case kPow: return powf(x, y);
+#endif
     case kAtan2: return atan2f(x, y);
     case kRemainder: return fmodf(x, y);
     case kCopy: return x;
@@ -428,7 +447,11 @@ static __device__ __noinline__ void ew_chain_run(const Lane &L, const EwOp *ops,
             B2_EW_F(kDiv, __fdiv_rn(x, y))
             B2_EW_F(kMax, np_max(x, y))
             B2_EW_F(kMin, np_min(x, y))
+#if B2_SHORT
+            B2_EW_F(kPow, pow_f32(x, y))
+#else
             B2_EW_F(kPow, powf(x, y))
+#endif
             B2_EW_F(kAtan2, atan2f(x, y))
             B2_EW_F(kRemainder, fmodf(x, y))
             B2_EW_F(kCopy, x)

@@ -27,7 +27,7 @@ enum EwStepCode : uint32_t {
   kSLdXB1, kSLdYB1,          // contiguous bool
   kSLdXRowW4, kSLdYRowW4,    // a row vector broadcast over rows: index = off + i mod d
   kSLdXRowBf, kSLdYRowBf,
-  kSLdXViewW4, kSLdYViewW4,  // any vector-friendly view
+  kSLdXViewW4, kSLdYViewW4,  // any view of up to 4 (vector-friendly) or 3 (element-wise walk) collapsed dims
   kSLdXViewBf, kSLdYViewBf,
   kSLdXColW4, kSLdYColW4,    // a column vector broadcast along rows: index = off + (i / d) * stride
   kSLdXColBf, kSLdYColBf,
@@ -40,12 +40,12 @@ enum EwStepCode : uint32_t {
   kSCmpI = kSCmpF + 6,
   kSCmpU = kSCmpI + 6,
   kSFlt = kSCmpU + 6,        // + ew_fcode(Sub) (float arithmetic)
-  kSInt = kSFlt + 17,        // + ew_icode(Sub) (i32 / u32 / bool arithmetic)
+  kSInt = kSFlt + 18,        // + ew_icode(Sub) (i32 / u32 / bool arithmetic)
   kSEnd = kSInt + 14,
 };
 // The codes are dense on purpose: the dispatch switch compiles to one jump table.
-__host__ __device__ constexpr uint32_t ew_fcode(uint32_t sub) {   // kAdd..kMin, kNeg..kSign, kGelu
-  return sub <= kMin ? sub : sub <= kSign ? sub - 2u : 16u;
+__host__ __device__ constexpr uint32_t ew_fcode(uint32_t sub) {   // kAdd..kMin, kNeg..kSign, kGelu, kPow
+  return sub <= kMin ? sub : sub == kPow ? 17u : sub <= kSign ? sub - 2u : 16u;
 }
 __host__ __device__ constexpr uint32_t ew_icode(uint32_t sub) {
   return sub <= kSubt ? sub : sub == kMax ? 3u : sub == kMin ? 4u : sub == kNeg ? 5u : sub == kAbs ? 6u
@@ -82,7 +82,18 @@ __device__ inline void ew_build_steps(EwOp *o, uint32_t smem_off_of_op) {
       else ok = false;
       return;
     }
-    if (!(w4 || bf) || !v.vec_ok) { ok = false; return; }
+    if (!(w4 || bf)) { ok = false; return; }
+    if (!v.vec_ok) {
+#if B2_SHORT
+      // the 4 elements of a group are not adjacent in the source (an innermost axis of 3,
+      // a strided slice): the general view load walks the coordinates element by element
+      if (v.rank < 1 || v.rank > 3) { ok = false; return; }
+      emit((w4 ? kSLdXViewW4 : kSLdXViewBf) + is_y, p, voff, 0, 0);
+#else
+      ok = false;
+#endif
+      return;
+    }
     if (v.rank == 1 && v.inner_stride == 1 && v.aligned4) {      // an offset slice: contiguous
       emit((w4 ? kSLdXW4 : kSLdXBf) + is_y, p + v.off * static_cast<int64_t>(esz), 0, 0, 0);
     } else if (v.rank == 2 && v.stride[0] == 0 && v.inner_stride == 1 && v.aligned4) {
@@ -136,7 +147,7 @@ __device__ inline void ew_build_steps(EwOp *o, uint32_t smem_off_of_op) {
         else if (sub == kFill) emit(kSFill, nullptr, 0, o->p2, 0);
         else if (sub == kIotaFlat) emit(kSIotaF, nullptr, 0, 0, 0);
         else if (sub == kCopy) quant = quant && adt != kBF16;
-        else if (sub <= kMin || (sub >= kNeg && sub <= kSign) || sub == kGelu) {
+        else if (sub <= (B2_SHORT ? kPow : kMin) || (sub >= kNeg && sub <= kSign) || sub == kGelu) {
           emit(kSFlt + ew_fcode(sub), nullptr, 0, 0, 0);
           if ((sub == kNeg || sub == kAbs || sub == kMax || sub == kMin) && adt == kBF16) quant = false;
         } else ok = false;
@@ -375,6 +386,22 @@ static __device__ __noinline__ void ew_steps_run(uint32_t tid, uint32_t nthr, ui
     };
     auto ld_view = [&](uint32_t (&R)[kEwU][4], const EwStep &st, bool bf) {
       const DView &v = *reinterpret_cast<const DView *>(sm + st.voff);
+#if B2_SHORT
+      if (!v.vec_ok) {
+        const ViewWalk w = view_walk(v);
+        B2_GROUPS {
+          uint32_t cA, cB, cO;
+          view_walk_seek(w, eb + u * estep, cA, cB, cO);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int64_t idx = view_walk_index(w, cA, cB, cO);
+            R[u][e] = bf ? (ldg_u16(st.ptr + idx * 2) << 16) : ldg_u32(st.ptr + idx * 4);
+            view_walk_next(w, cA, cB, cO);
+          }
+        }
+        return;
+      }
+#endif
       const bool bcast = v.inner_stride == 0, al4 = v.aligned4 != 0;
       B2_GROUPS B2_SET(R, ld_at(st.ptr, view_index(v, eb + u * estep), bf, bcast, al4))
     };
@@ -510,6 +537,9 @@ static __device__ __noinline__ void ew_steps_run(uint32_t tid, uint32_t nthr, ui
           B2_SFC(kCeil, ceilf(x))
           B2_SFC(kSign, (x > 0.0f ? 1.0f : (x < 0.0f ? -1.0f : x)))
           B2_SF(kGelu, gelu_tanh(x))
+#if B2_SHORT
+          B2_SF(kPow, pow_f32(x, y))
+#endif
           B2_SI(kAdd, x + y)
           B2_SI(kMul, x * y)
           B2_SI(kSubt, x - y)

@@ -154,7 +154,43 @@ static __device__ __noinline__ void move_tiles(const Lane &L, const DTask &t, ui
     }
     return;
   }
-  for (uint32_t i = lo + L.tid; i < hi; i += L.nthr) {
+  uint32_t i = lo + L.tid;
+#if B2_SHORT
+  if (!scatter && esz == 4 && m.view.rank >= 1 && m.view.rank <= 3 && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+    // A gather whose source runs are shorter than 16 bytes (an (N, 3) table repeated
+    // along a middle axis): a thread owns whole 16-byte chunks of dst, finds the source
+    // coordinates of a chunk's first element once and walks to the next three; two
+    // chunks (8 loads) are in flight per trip. lo is a multiple of the 4096-element tile.
+    const ViewWalk w = view_walk(m.view);
+    const uint32_t *s32 = reinterpret_cast<const uint32_t *>(src);
+    constexpr uint32_t U = 2;
+    const uint32_t c_hi = hi / 4u;
+    uint32_t k = lo / 4u + L.tid;
+    for (; k < c_hi; k += U * L.nthr) {
+      uint32_t v[U][4];
+#pragma unroll
+      for (uint32_t u = 0; u < U; ++u) {
+        const uint32_t kk = k + u * L.nthr;
+        if (kk < c_hi) {
+          uint32_t cA, cB, cO;
+          view_walk_seek(w, kk * 4u, cA, cB, cO);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            v[u][e] = s32[base + view_walk_index(w, cA, cB, cO)];
+            view_walk_next(w, cA, cB, cO);
+          }
+        }
+      }
+#pragma unroll
+      for (uint32_t u = 0; u < U; ++u) {
+        const uint32_t kk = k + u * L.nthr;
+        if (kk < c_hi) *reinterpret_cast<uint4 *>(dst + static_cast<size_t>(kk) * 16) = make_uint4(v[u][0], v[u][1], v[u][2], v[u][3]);
+      }
+    }
+    i = c_hi * 4u + L.tid;      // the ragged end of the range, below
+  }
+#endif
+  for (; i < hi; i += L.nthr) {
     const int64_t s = base + view_index(m.view, i);
     if (scatter) copy_elem(dst, s, src, i, esz); else copy_elem(dst, i, src, s, esz);
   }

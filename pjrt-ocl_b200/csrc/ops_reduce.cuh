@@ -524,6 +524,61 @@ static __device__ __noinline__ void red_comb_tiles(const Lane &L, const DTask &t
 }
 
 
+#if B2_SHORT
+// RED_SEG on f32 with segments of 2..8 elements (a trailing axis of 3 in an
+// (N, N, 3) tensor): a thread per segment reads 4 bytes at a stride of `seg`
+// words and the load pipeline never fills. Here a warp takes 128 consecutive
+// segments (128 * seg contiguous floats) with `seg` coalesced 16-byte loads per
+// thread, parks them in its shared-memory slab, and each thread folds segments
+// l, l+32, l+64, l+96 from there; results leave as 128-byte rows. Elements of a
+// segment are folded in index order, like the per-thread loop.
+// SEG > 0: the segment length as a constant (its loads sit in exactly SEG registers);
+// SEG == 0: any length up to 8.
+template <uint32_t KIND, uint32_t SEG>
+__device__ __forceinline__ void red_seg_small_f32(const Lane &L, float *dst, const float *a, uint32_t lo, uint32_t hi,
+                                                  uint32_t seg_rt) {
+  constexpr uint32_t kSpan = 128, kMaxSeg = SEG ? SEG : 8;
+  const uint32_t seg = SEG ? SEG : seg_rt;
+  const uint32_t w = L.tid / kWarp, l = L.tid % kWarp, nw = L.nthr / kWarp;
+  float *stage = reinterpret_cast<float *>(L.smem + kSmemSys) + static_cast<size_t>(w) * kSpan * kMaxSeg;
+  auto one = [&](uint32_t o) {
+    const float *p = a + static_cast<int64_t>(o) * seg;
+    float r = p[0];
+    for (uint32_t i = 1; i < seg; ++i) r = red_f(KIND, r, p[i]);
+    dst[o] = r;
+  };
+  const uint32_t o_al = min(hi, (lo + 3u) & ~3u);          // 16-byte alignment of the first full span
+  for (uint32_t o = lo + L.tid; o < o_al; o += L.nthr) one(o);
+  const uint32_t nsteps = (hi - o_al) / kSpan;
+  const uint32_t span_lines = (kSpan * seg * 4u + 127u) / 128u;
+  for (uint32_t s = w; s < nsteps; s += nw) {
+    const uint32_t o0 = o_al + s * kSpan;
+    const float *p = a + static_cast<int64_t>(o0) * seg;
+    uint4 v[kMaxSeg];
+#pragma unroll
+    for (uint32_t j = 0; j < kMaxSeg; ++j)
+      if (j < seg) v[j] = ldg_v4(p + (j * kWarp + l) * 4u);
+    if (s + nw < nsteps && l < span_lines)                   // the warp's next span, into L2
+      prefetch_l2(reinterpret_cast<const uint8_t *>(p + static_cast<int64_t>(nw) * kSpan * seg) + l * 128u);
+#pragma unroll
+    for (uint32_t j = 0; j < kMaxSeg; ++j)
+      if (j < seg) *reinterpret_cast<uint4 *>(stage + (j * kWarp + l) * 4u) = v[j];
+    __syncwarp();
+#pragma unroll
+    for (uint32_t q = 0; q < kSpan / kWarp; ++q) {
+      const uint32_t si = l + q * kWarp;
+      const float *sp = stage + si * seg;
+      float r = sp[0];
+      for (uint32_t i = 1; i < seg; ++i) r = red_f(KIND, r, sp[i]);
+      dst[o0 + si] = r;
+    }
+    __syncwarp();
+  }
+  for (uint32_t o = o_al + nsteps * kSpan + L.tid; o < hi; o += L.nthr) one(o);
+}
+
+#endif
+
 // RED_SEG: out[o] = reduce(in[o*seg, (o+1)*seg)), one segment per tile index;
 // p3 = 1: dot mode, out[o] = sum_j in[o*seg+j] * b[j].
 static __device__ __noinline__ void red_seg_tiles(const Lane &L, const DTask &t, uint32_t tile_lo, uint32_t tile_hi) {
@@ -535,6 +590,21 @@ static __device__ __noinline__ void red_seg_tiles(const Lane &L, const DTask &t,
   const uint32_t dt = t.p[3] ? t.adt : t.dt;  // reduce keeps the input dtype; dot mode reads adt
   const uint8_t *vecb = t.p[3] ? resolve(P, t.ptr[2]) : nullptr;
   const uint32_t hi = min(tile_hi, n_out);
+#if B2_SHORT
+  if (!t.p[3] && dt == kF32 && t.dt == kF32 && seg >= 2 && seg <= 8 && hi > tile_lo &&
+      (reinterpret_cast<uintptr_t>(a) & 15u) == 0 && (kind == kSum || kind == kRMax || kind == kRMin)) {
+    float *d = reinterpret_cast<float *>(dst);
+    const float *s = reinterpret_cast<const float *>(a);
+    const uint32_t sg = static_cast<uint32_t>(seg);
+    if (kind == kSum && sg == 3) red_seg_small_f32<kSum, 3>(L, d, s, tile_lo, hi, sg);
+    else if (kind == kSum && sg == 2) red_seg_small_f32<kSum, 2>(L, d, s, tile_lo, hi, sg);
+    else if (kind == kSum && sg == 4) red_seg_small_f32<kSum, 4>(L, d, s, tile_lo, hi, sg);
+    else if (kind == kSum) red_seg_small_f32<kSum, 0>(L, d, s, tile_lo, hi, sg);
+    else if (kind == kRMax) red_seg_small_f32<kRMax, 0>(L, d, s, tile_lo, hi, sg);
+    else red_seg_small_f32<kRMin, 0>(L, d, s, tile_lo, hi, sg);
+    return;
+  }
+#endif
   if (seg <= 16) {  // thread per segment
     for (uint32_t o = tile_lo + L.tid; o < hi; o += L.nthr) {
       Acc acc = reduce_run(a, dt, kind, o * seg, (o + 1) * seg, 0, 1, vecb, 0);

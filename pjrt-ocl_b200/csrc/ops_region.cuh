@@ -147,16 +147,7 @@ static __device__ __noinline__ void region_tiles(const Lane &L, const DTask &t, 
   uint4 *slots = reinterpret_cast<uint4 *>(L.smem + kSmemSys + prog_words * 4u);
   const uint8_t **in_ptr = reinterpret_cast<const uint8_t **>(L.smem + kSmemPtrs);
   const bool vec = (t.flags & kVecPath) != 0;
-  // slots in use: 1 + the highest slot any input, micro-op or the output names
-  uint32_t n_slots = out_slot + 1u;
-  for (uint32_t k = 0; k < n_in; ++k) n_slots = max(n_slots, (static_cast<uint32_t>(x[3 + k]) & 7u) + 1u);
-  for (uint32_t m = 0; m < n_micro; ++m) {
-    const int32_t *q = x + 3 + n_in + 6 * m;
-    n_slots = max(n_slots, max(static_cast<uint32_t>(q[1]) & 7u, max(static_cast<uint32_t>(q[2]) & 7u, static_cast<uint32_t>(q[3]) & 7u)) + 1u);
-  }
   const uint32_t pitch = L.nthr;
-  const uint32_t room = (L.smem_bytes - kSmemSys - prog_words * 4u) / (16u * pitch);     // slot columns that fit
-  const bool wide = n_slots * 4u <= room;
   __syncthreads();
   for (uint32_t k = L.tid; k < n_in; k += L.nthr) prog[k] = static_cast<uint32_t>(x[3 + k]);
   for (uint32_t m = L.tid; m < n_micro; m += L.nthr) {
@@ -172,6 +163,15 @@ static __device__ __noinline__ void region_tiles(const Lane &L, const DTask &t, 
   }
   if (L.tid < 8) in_ptr[L.tid] = L.tid < n_in ? resolve(P, dr.in[L.tid]) : nullptr;
   __syncthreads();
+  // slots in use: 1 + the highest slot any input, micro-op or the output names (read back from the decoded copy)
+  uint32_t n_slots = out_slot + 1u;
+  for (uint32_t k = 0; k < n_in; ++k) n_slots = max(n_slots, (prog[k] & 7u) + 1u);
+  for (uint32_t m = 0; m < n_micro; ++m) {
+    const uint4 q = *reinterpret_cast<const uint4 *>(prog + in_words + 8u * m);
+    n_slots = max(n_slots, max(q.y, max(q.z, q.w)) / pitch + 1u);
+  }
+  const uint32_t room = (L.smem_bytes - kSmemSys - prog_words * 4u) / (16u * pitch);     // slot columns that fit
+  const bool wide = n_slots * 4u <= room;
   uint8_t *dst = resolve(P, t.ptr[0]);
   const uint32_t n = t.p[1], adt = t.adt, dt = t.dt;
   const uint64_t lo64 = static_cast<uint64_t>(tile_lo) * kEwTs;
@@ -179,7 +179,8 @@ static __device__ __noinline__ void region_tiles(const Lane &L, const DTask &t, 
   if (hi64 > n) hi64 = n;
   if (lo64 >= hi64) return;
   const uint32_t lo = static_cast<uint32_t>(lo64), hi = static_cast<uint32_t>(hi64);
-  if (wide) region_trips<4>(L, prog, prog + in_words, slots, in_ptr, dst, n_in, n_micro, out_slot, n_slots, lo, hi, adt, dt, vec);
+  // 16 elements per dispatch pay when every thread gets them; a short range is spread thinner instead
+  if (wide && hi - lo >= 16u * L.nthr) region_trips<4>(L, prog, prog + in_words, slots, in_ptr, dst, n_in, n_micro, out_slot, n_slots, lo, hi, adt, dt, vec);
   else region_trips<2>(L, prog, prog + in_words, slots, in_ptr, dst, n_in, n_micro, out_slot, kRegionSlots, lo, hi, adt, dt, vec);
 }
 

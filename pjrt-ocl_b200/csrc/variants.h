@@ -17,6 +17,7 @@
 #define B2_FAMS_STREAM (b2::kFamEw | b2::kFamMove | b2::kFamRed | b2::kFamRows | b2::kFamRegion)
 #define B2_VARIANT_LIST(X)                               \
   X(stream, B2_FAMS_STREAM)                              \
+  X(shortrun, B2_FAMS_STREAM | b2::kFamShort)            \
   X(matmul, B2_FAMS_STREAM | b2::kFamMma)                \
   X(attn, B2_FAMS_STREAM | b2::kFamMma | b2::kFamFlash)  \
   X(all, b2::kFamAll)

@@ -25,6 +25,7 @@
 #define B2_PASTE2(a, b) a##b
 #define B2_PASTE(a, b) B2_PASTE2(a, b)
 
+#define B2_SHORT B2_HAS(0x100u)   // kFamShort
 #include "dev_common.cuh"
 #include "ops_ew.cuh"
 #include "ops_ew_steps.cuh"
@@ -54,7 +55,7 @@
 
 namespace b2 {
 static_assert(kFamMove == 0x02u && kFamRed == 0x04u && kFamRows == 0x08u && kFamRegion == 0x10u && kFamMma == 0x20u &&
-              kFamFlash == 0x40u && kFamIndex == 0x80u, "the literals in the #if lines above");
+              kFamFlash == 0x40u && kFamIndex == 0x80u && kFamShort == 0x100u, "the literals in the #if lines above");
 
 constexpr int kVmThreads = 512;   // threads per lane: the one instantiation the library carries
 struct Frame { uint32_t pc, end, widx, phase; };  // phase: 0 while-cond, 1 while-body, 2 if, FOR: trips left

@@ -136,6 +136,24 @@ def _():
     return _ew_int(I32, 3)
 
 
+@case("ew_u32_high", exact=True)
+def _():
+    """u32 operands at and above 2^31, where signed and unsigned arithmetic part ways:
+    division, maximum / minimum, right shifts, comparison and the conversion to f32."""
+    a = Asm()
+    x = a.input((RAG,), U32)
+    y = a.input((RAG,), U32)
+    s = a.input((RAG,), U32)
+    outs = [a.binop(op, x, y) for op in (L.OP_ADD_F32, L.OP_SUB_F32, L.OP_DIV_F32, L.OP_MAX_F32, L.OP_MIN_F32,
+                                         L.OP_AND, L.OP_OR, L.OP_XOR)]
+    outs += [a.binop(op, x, s) for op in (L.OP_SHR_L, L.OP_SHL)]
+    outs += [a.compare(x, y, d) for d in ("LT", "GE")]
+    outs.append(a.convert(x, F32))
+    blob, prog = a.finish(outs, nlanes=3)
+    return blob, prog, (21, [I((RAG,), 2 ** 31 - 5000, 2 ** 32 - 1, "u32"), I((RAG,), 2 ** 31 - 100, 2 ** 32 - 7, "u32"),
+                             I((RAG,), 0, 32, "u32")])
+
+
 @case("ew_i64_all", exact=True)
 def _():
     return _ew_int(I64, 2)

@@ -204,13 +204,14 @@ def test_full_reductions_are_recut_over_all_lanes(rt):
         expected[2] = np.uint32((int(out[2]) + 3 * int(np.bitwise_xor.reduce(args[2]))) % 2 ** 32)
 
 
-@pytest.mark.parametrize("name,build", [("c2_chain_f32_small", "stream"), ("dot_tc_bf16", "matmul"),
-                                         ("flash_tc_bf16", "attn"), ("reduce_window_f32", "all")])
+@pytest.mark.parametrize("name,build", [("c2_chain_f32_small", "stream"), ("c4_nbody_small", "shortrun"),
+                                         ("dot_tc_bf16", "matmul"), ("flash_tc_bf16", "attn"),
+                                         ("reduce_window_f32", "all")])
 def test_program_runs_on_the_smallest_kernel_build_that_has_its_families(rt, name, build):
     vm = package()
     from conftest import Golden
     lp = vm.LoadedProgram.Load(rt, vm.VmProgram.Parse(Golden(name).blob))
-    assert ["stream", "matmul", "attn", "all"][lp.stat("kernel_build")] == build
+    assert ["stream", "shortrun", "matmul", "attn", "all"][lp.stat("kernel_build")] == build
 
 
 def test_config4_reductions_are_spread_over_lanes(rt):
