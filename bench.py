@@ -419,12 +419,15 @@ def main():
             try:
                 if lp2 is None:
                     host_out = [d.cpu().numpy()[:s["bytes"]] for d, s in zip(dev_out, lp.prog.outputs)]
+                    replica_sums = []       # replicas of one input: an all-reduced result is `world` times the single-GPU value
                     if world > 1 and plan and plan.reduce_outputs and not plan.batch_inputs and not plan.seed_per_rank:
-                        # replicas of one input: an all-reduced result is `world` times the single-GPU value
-                        for i in plan.reduce_outputs:
-                            host_out[i] = (host_out[i].view(np.float32) / np.float32(world)).view(np.uint8)
+                        replica_sums = list(plan.reduce_outputs)
+                    elif world > 1 and not plan and wl["program"].startswith("c2_chain"):
+                        replica_sums = [len(host_out) - 1]
+                    for i in replica_sums:
+                        host_out[i] = (host_out[i].view(np.float32) / np.float32(world)).view(np.uint8)
                     verified_what = fullsize_refs.verify_workload(name, host_in, host_out, oracle_rows)
-                    if world > 1 and verified_what and plan and plan.reduce_outputs and not plan.batch_inputs:
+                    if replica_sums and verified_what:
                         verified_what += f"; the all-reduced scalar is {world} x the single-GPU one"
                 else:
                     # config 3 on N GPUs: every rank must hold the same updated weights, and they must be
@@ -443,7 +446,7 @@ def main():
                     verified_what = (verified_what or "as rank 0") + "; all ranks hold identical weights"
                 verified = True if verified_what else None     # None: no value check exists for this workload
             except AssertionError as e:
-                verified, verified_what = False, str(e)[:300]
+                verified, verified_what = False, (str(e)[:300] or "a value check failed (bare assertion in tests/fullsize_refs.py)")
         e2e = None
         if want_e2e:
             n_e2e = max(3, min(steps, 10))
