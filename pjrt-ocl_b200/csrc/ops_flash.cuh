@@ -143,6 +143,173 @@ static __device__ __noinline__ void flash_decode_tiles(const Lane &L, const DTas
   __syncthreads();
 }
 
+// The same decode-shaped task when the K and V rows of a head are contiguous (key pitch == head_dim: a plain
+// [H, C, hd] cache): K and V stream through a ring of shared-memory stages filled by bulk asynchronous copies
+// (one thread issues them; 256 keys = 32 KB of K + 32 KB of V per stage at head_dim 64, three stages), so that
+// two stages are in flight while one is worked on, at no cost in registers. A warp takes 16 keys of every
+// stage (4 per load position, as in flash_decode_tiles); the ring runs on across the lane's tiles, so the next
+// head's first stages arrive during this head's merge.
+template <int HD, bool BF>
+static __device__ __noinline__ void flash_decode_ring(const Lane &L, const DTask &t, const DFlash &df, uint32_t tile_lo,
+                                                      int64_t hi, int64_t T, int64_t C, float scale, bool causal) {
+  constexpr int LPK = HD / 8;              // threads per key
+  constexpr int KPL = 32 / LPK;            // keys per warp-wide load
+  constexpr uint32_t kDepth = 3;
+  constexpr uint32_t kRowB = HD * 2u;      // bytes of one key's row
+  const KParams &P = *L.P;
+  uint8_t *out = resolve(P, t.ptr[0]);
+  const uint16_t *Q = reinterpret_cast<const uint16_t *>(resolve(P, t.ptr[1]));
+  const uint8_t *K = reinterpret_cast<const uint8_t *>(reinterpret_cast<const uint16_t *>(resolve(P, t.ptr[2])) + df.dk_off);
+  const uint8_t *V = reinterpret_cast<const uint8_t *>(reinterpret_cast<const uint16_t *>(resolve(P, t.ptr[3])) + df.dv_off);
+  constexpr bool bf = BF;
+  const uint32_t w = L.tid / kWarp, l = L.tid % kWarp, nw = L.nthr / kWarp;
+  const uint32_t part = l % LPK, sub = l / LPK;
+  const uint32_t kps = nw * 4u * KPL;      // keys per stage: every warp gets 4 load positions of KPL keys
+  const uint32_t stage_b = kps * kRowB;    // bytes of K (and of V) per stage
+  float *ml = reinterpret_cast<float *>(L.smem + kSmemSys);                          // [nw][2]
+  float *os = ml + 2 * 32;                                                           // [nw][HD]
+  uint64_t *full = reinterpret_cast<uint64_t *>(L.smem + kSmemSys + 256 + 4u * 32u * HD);   // after ml / os
+  uint64_t *empty = full + 2u * kDepth;           // full[2 b] : K of buffer b has landed, full[2 b + 1] : V
+  uint8_t *ring = L.smem + ((kSmemSys + 256 + 4u * 32u * HD + 96 + 127) & ~127u);
+  auto unpack8 = [&](const uint4 &v, float (&f)[8]) {
+    const uint32_t wd[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      f[2 * i] = bf ? __uint_as_float(wd[i] << 16) : f16_bits_to_f32(wd[i] & 0xffffu);
+      f[2 * i + 1] = bf ? __uint_as_float(wd[i] & 0xffff0000u) : f16_bits_to_f32(wd[i] >> 16);
+    }
+  };
+  // the lane's stages, in order: tile by tile, kps keys each (the last of a tile ragged)
+  auto c_end_of = [&](int64_t tile) { const int64_t m = tile % T; return causal ? min(C, m + (C - T) + 1) : C; };
+  auto stages_of = [&](int64_t tile) { return static_cast<uint32_t>((c_end_of(tile) + kps - 1) / kps); };
+  // producer state (thread 0): the next stage to request
+  int64_t p_tile = tile_lo;
+  uint32_t p_stage = 0, p_seq = 0;
+  auto request = [&]() {          // thread 0: issue the copies of the next stage, if any is left
+    while (p_tile < hi && p_stage >= stages_of(p_tile)) { ++p_tile; p_stage = 0; }
+    if (p_tile >= hi) return;
+    const int64_t g = p_tile / T, c_end = c_end_of(p_tile);
+    const int64_t k0 = static_cast<int64_t>(p_stage) * kps;
+    const uint32_t bytes = static_cast<uint32_t>(min(static_cast<int64_t>(kps), c_end - k0)) * kRowB;
+    const uint32_t b = p_seq % kDepth;
+    mbar_arrive_expect_tx(&full[2u * b], bytes);
+    bulk_g2s(ring + b * 2u * stage_b, K + (g * df.dk_g + k0 * HD) * 2, bytes, &full[2u * b]);
+    mbar_arrive_expect_tx(&full[2u * b + 1u], bytes);
+    bulk_g2s(ring + b * 2u * stage_b + stage_b, V + (g * df.dv_g + k0 * HD) * 2, bytes, &full[2u * b + 1u]);
+    ++p_stage; ++p_seq;
+  };
+  __syncthreads();
+  if (L.tid == 0) {
+    for (uint32_t i = 0; i < kDepth; ++i) { mbar_init(&full[2u * i], 1); mbar_init(&full[2u * i + 1u], 1); mbar_init(&empty[i], nw); }
+    fence_mbar_init();
+    for (uint32_t i = 0; i < kDepth; ++i) request();
+  }
+  __syncthreads();
+  const float sl2 = scale * 1.4426950408889634f;
+  uint32_t seq = 0;                // stages consumed so far by this lane (all threads count alike)
+  bool ok = true;
+  for (int64_t tile = tile_lo; tile < hi && ok; ++tile) {
+    const int64_t g = tile / T, m = tile % T;
+    const int64_t c_end = c_end_of(tile);
+    float q[8];
+    unpack8(ldg_v4(Q + (g * T + m) * HD + part * 8), q);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) q[i] *= sl2;
+    float m_run = -INFINITY, l_run = 0.0f, o[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o[i] = 0.0f;
+    const uint32_t ns = stages_of(tile);
+    for (uint32_t sg = 0; sg < ns && ok; ++sg, ++seq) {
+      const uint32_t b = seq % kDepth, par = (seq / kDepth) & 1u;
+      if (L.tid == 0 && seq >= 1u) {
+        // the buffer of the previous stage goes to the stage kDepth - 1 ahead once every warp has left it
+        if (mbar_wait_bounded(&empty[(seq - 1u) % kDepth], ((seq - 1u) / kDepth) & 1u, P.wait_budget_ns)) {
+          fence_proxy_async_smem();
+          request();
+        } else {
+          set_status(P, kStTensorTimeout, L.lane, static_cast<uint32_t>(tile), kTopFlashAttn);
+        }
+      }
+      if (!mbar_wait_bounded(&full[2u * b], par, P.wait_budget_ns) || !mbar_wait_bounded(&full[2u * b + 1u], par, P.wait_budget_ns)) {
+        set_status(P, kStTensorTimeout, L.lane, static_cast<uint32_t>(tile), kTopFlashAttn);
+        ok = false;
+      }
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      const int64_t k0 = static_cast<int64_t>(sg) * kps + w * 4u * KPL;      // this warp's first key of the stage
+      if (k0 < c_end) {
+        const uint8_t *ks = ring + b * 2u * stage_b + (w * 4u * KPL + sub) * kRowB + part * 16u, *vs = ks + stage_b;
+        float sc[4], cmax = -INFINITY;
+        uint4 vv[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const bool valid = k0 + u * KPL + sub < c_end;
+          const uint4 kk = valid ? *reinterpret_cast<const uint4 *>(ks + u * KPL * kRowB) : make_uint4(0u, 0u, 0u, 0u);
+          vv[u] = valid ? *reinterpret_cast<const uint4 *>(vs + u * KPL * kRowB) : make_uint4(0u, 0u, 0u, 0u);
+          float kf[8];
+          unpack8(kk, kf);
+          float a = 0.0f;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) a = fmaf(q[i], kf[i], a);
+#pragma unroll
+          for (int d = 1; d < LPK; d <<= 1) a += __shfl_xor_sync(0xffffffffu, a, d);
+          sc[u] = valid ? a : -INFINITY;
+          cmax = fmaxf(cmax, sc[u]);
+        }
+#pragma unroll
+        for (int d = LPK; d < 32; d <<= 1) cmax = fmaxf(cmax, __shfl_xor_sync(0xffffffffu, cmax, d));
+        const float m_new = fmaxf(m_run, cmax);       // finite: the warp's first key of the stage exists
+        const float alpha = m_run == -INFINITY ? 0.0f : fast_ex2(m_run - m_new);
+        m_run = m_new;
+        l_run *= alpha;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] *= alpha;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const float pr = sc[u] == -INFINITY ? 0.0f : fast_ex2(sc[u] - m_new);
+          l_run += pr;
+          float vf[8];
+          unpack8(vv[u], vf);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) o[i] = fmaf(pr, vf[i], o[i]);
+        }
+      }
+      __syncwarp();
+      if (l == 0) mbar_arrive(&empty[b]);
+    }
+    if (!ok) break;
+    // the warp's threads hold partial sums over their own keys: add across the key groups
+#pragma unroll
+    for (int d = LPK; d < 32; d <<= 1) {
+      l_run += __shfl_xor_sync(0xffffffffu, l_run, d);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) o[i] += __shfl_xor_sync(0xffffffffu, o[i], d);
+    }
+    __syncthreads();            // the previous tile's merge has read the workspace
+    if (l == 0) { ml[2 * w] = m_run; ml[2 * w + 1] = l_run; }
+    if (sub == 0) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) os[w * HD + part * 8 + i] = o[i];
+    }
+    __syncthreads();
+    for (int64_t d = L.tid; d < HD; d += L.nthr) {
+      float M = -INFINITY;
+      for (uint32_t ww = 0; ww < nw; ++ww) M = fmaxf(M, ml[2 * ww]);
+      float num = 0.0f, den = 0.0f;
+      for (uint32_t ww = 0; ww < nw; ++ww) {
+        const float e = ml[2 * ww] == -INFINITY ? 0.0f : fast_ex2(ml[2 * ww] - M);
+        num = fmaf(os[ww * HD + d], e, num);
+        den = fmaf(ml[2 * ww + 1], e, den);
+      }
+      storef(out, t.dt, (g * T + m) * HD + d, __fdiv_rn(num, den));
+    }
+  }
+  __syncthreads();
+  if (L.tid == 0 && ok)
+    for (uint32_t i = 0; i < kDepth; ++i) { mbar_inval(&full[2u * i]); mbar_inval(&full[2u * i + 1u]); mbar_inval(&empty[i]); }
+  __syncthreads();
+}
+
 static __device__ __noinline__ void flash_simt_tiles(const Lane &L, const DTask &t, uint32_t tile_lo, uint32_t tile_hi) {
   const KParams &P = *L.P;
   const int32_t *x = P.aux + t.p[3];
@@ -159,6 +326,15 @@ static __device__ __noinline__ void flash_simt_tiles(const Lane &L, const DTask 
   float *qs = reinterpret_cast<float *>(L.smem + kSmemSys) + static_cast<size_t>(w) * kFlashMaxHd;
   const int64_t hi = min(static_cast<int64_t>(tile_hi), H * T);
   __syncthreads();  // workspace handover from the previous op
+  if (df.dec_mode && df.dk_c == hd && df.dv_c == hd && L.nthr == 512u &&
+      L.smem_bytes >= kSmemSys + 256u + 4u * 32u * static_cast<uint32_t>(hd) + 192u + 3u * 2u * (L.nthr / kWarp) * 4u * (256u / static_cast<uint32_t>(hd)) * static_cast<uint32_t>(hd) * 2u) {
+    // contiguous K / V rows: the ring of bulk copies
+    if (hd == 64 && adt == kBF16) flash_decode_ring<64, true>(L, t, df, tile_lo, hi, T, C, scale, causal);
+    else if (hd == 64) flash_decode_ring<64, false>(L, t, df, tile_lo, hi, T, C, scale, causal);
+    else if (adt == kBF16) flash_decode_ring<128, true>(L, t, df, tile_lo, hi, T, C, scale, causal);
+    else flash_decode_ring<128, false>(L, t, df, tile_lo, hi, T, C, scale, causal);
+    return;
+  }
   if (df.dec_mode) {
     if (hd == 64 && adt == kBF16) flash_decode_tiles<64, true>(L, t, df, tile_lo, hi, T, C, scale, causal);
     else if (hd == 64) flash_decode_tiles<64, false>(L, t, df, tile_lo, hi, T, C, scale, causal);
