@@ -154,7 +154,9 @@ uint64_t b2_loaded_launch_count(const b2_loaded *lp);
  * (RED_PART + RED_COMB) re-cut evenly over all lanes with the combine folded into
  * the same phase, 12 flash-attention tasks on the decode path (few query rows; K and
  * V rows read with 16-byte loads), 13 in/out ports, 14 phases whose units (matmuls of
- * different depth, regions, elementwise chains) were re-cut evenly over all lanes.
+ * different depth, regions, elementwise chains) were re-cut evenly over all lanes,
+ * 15 groups of neighbouring row-local phases (row norms and elementwise chains over
+ * the same rows) run as one pipeline per lane with the barriers between them removed.
  * Unknown `which` returns 0. */
 uint64_t b2_loaded_stat(const b2_loaded *lp, int which);
 /* Per-wait budget of device-side bounded waits, in nanoseconds (default 2e9). */

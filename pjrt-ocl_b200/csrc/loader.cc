@@ -433,9 +433,10 @@ struct RebUnit {
 };
 }  // namespace
 
-bool RebalancePhases(const VmProgram &p, VmProgram *q, uint32_t *n_done) {
+bool RebalancePhases(const VmProgram &p, VmProgram *q, uint32_t *n_done, uint32_t *n_piped_out) {
   const uint32_t L = static_cast<uint32_t>(p.lane_tab.size());
   *n_done = 0;
+  *n_piped_out = 0;
   if (L < 4) return false;
   for (const VmEntry &e : p.entries)
     if (e.task == kEntWhile || e.task == kEntIf || e.task == kEntFor) return false;
@@ -452,6 +453,119 @@ bool RebalancePhases(const VmProgram &p, VmProgram *q, uint32_t *n_done) {
       ph[l].back().push_back(e);
     }
     if (ph[l].size() != ph[0].size()) return false;
+  }
+  // ---- row pipelines ----
+  // Neighbouring phases that each hold ONE unit working row by row on rows of exactly one elementwise tile
+  // (LAYERNORM_SEG / SOFTMAX_SEG with a segment of kEwTs elements, elementwise chains over rows x kEwTs
+  // elements), cut the same way over the lanes, each reading its predecessor's result at the same index: row r
+  // of a later unit needs row r of the earlier one and nothing else that the group writes. The grid barriers
+  // between them order nothing the lane's own program order does not, so they go; optionally (B2VM_ROW_BLOCK)
+  // the lane walks its rows in blocks - unit 1, unit 2, unit 3 on block 0, then block 1, ... - so that a block's
+  // intermediates are read back from L2 instead of HBM. Refused whenever a result's memory overlaps anything a unit of the group
+  // reads through a view or under another buffer id (arena slots are reused).
+  uint32_t n_piped = 0;
+  {
+    struct One { std::vector<uint32_t> tasks; bool ok; };
+    auto unit_of_phase = [&](size_t k) {
+      One u{{}, true};
+      bool any = false;
+      for (uint32_t l = 0; l < L && u.ok; ++l) {
+        const auto &es = ph[l][k];
+        if (es.empty()) continue;
+        std::vector<uint32_t> key;
+        for (const VmEntry &e : es) {
+          const VmTask &t = p.tasks[e.task];
+          const uint32_t op = t.tile_op & 0xFFu;
+          if (e.tile_lo != es[0].tile_lo || e.tile_hi != es[0].tile_hi) u.ok = false;
+          if (op == kTopEw) {
+            if (t.p0 == kSelect || t.p1 % kEwTs != 0u) u.ok = false;
+          } else if (op == kTopSoftmaxSeg || op == kTopLayernormSeg) {
+            if (t.p1 != kEwTs || es.size() != 1u) u.ok = false;
+          } else {
+            u.ok = false;
+          }
+          key.push_back(e.task);
+        }
+        if (!any) { u.tasks = key; any = true; }
+        else if (u.tasks != key) u.ok = false;
+      }
+      if (!any) u.ok = false;
+      return u;
+    };
+    auto n_tiles = [&](uint32_t ti) {
+      const VmTask &t = p.tasks[ti];
+      return (t.tile_op & 0xFFu) == kTopEw ? t.p1 / kEwTs : t.p0;
+    };
+    auto overlap = [&](uint32_t x, uint32_t y) {
+      const BufferSlot &bx = p.buffers[x], &by = p.buffers[y];
+      return bx.bytes && by.bytes && bx.offset < by.offset + by.bytes && by.offset < bx.offset + bx.bytes;
+    };
+    struct Read { uint32_t buf; bool viewed; };
+    auto reads_of = [&](uint32_t ti, std::vector<Read> *r) {
+      const VmTask &t = p.tasks[ti];
+      if ((t.tile_op & 0xFFu) != kTopEw) { r->push_back({t.a, false}); return; }
+      if (EwReadsA(t.p0)) r->push_back({t.a, t.p2 != 0u});
+      if (EwReadsB(t.p0)) r->push_back({t.b, t.p3 != 0u});
+    };
+    const char *rb_env = std::getenv("B2VM_ROW_BLOCK");
+    // Rows per block. Measured on config 2 (55 rows of 16 KB per lane): every extra block costs ~9 us per unit in
+    // fill, drain and entry set-up, more than the L2 hits return (one block 224 us, two 252 us, four 279 us against
+    // 235 us with the barriers in place), so by default a lane's whole range is one block and only the barriers go.
+    const uint32_t row_block = rb_env ? static_cast<uint32_t>(std::max(1, std::atoi(rb_env))) : 0x7fffffffu;
+    size_t k = 0;
+    while (k + 1 < ph[0].size()) {
+      // the longest run of phases k, k + 1, ... that form one pipeline
+      std::vector<One> grp;
+      grp.push_back(unit_of_phase(k));
+      size_t n = 1;
+      while (grp[0].ok && k + n < ph[0].size()) {
+        One nx = unit_of_phase(k + n);
+        bool ok = nx.ok && n_tiles(nx.tasks[0]) == n_tiles(grp[0].tasks[0]);
+        for (uint32_t l = 0; l < L && ok; ++l) {          // the same cut on every lane
+          const auto &ea = ph[l][k], &eb = ph[l][k + n];
+          if (ea.empty() != eb.empty()) ok = false;
+          else if (!ea.empty() && (ea[0].tile_lo != eb[0].tile_lo || ea[0].tile_hi != eb[0].tile_hi)) ok = false;
+        }
+        if (ok) {
+          std::vector<uint32_t> all;
+          for (const One &g : grp) all.insert(all.end(), g.tasks.begin(), g.tasks.end());
+          all.insert(all.end(), nx.tasks.begin(), nx.tasks.end());
+          std::vector<Read> rd;
+          for (uint32_t ti : all) reads_of(ti, &rd);
+          // two ids on exactly the same bytes (a reused arena slot) and the same element size behave like one
+          // buffer here: every access in the group is row-local
+          auto same_bytes = [&](uint32_t x, uint32_t y) {
+            return x == y || (p.buffers[x].offset == p.buffers[y].offset && p.buffers[x].bytes == p.buffers[y].bytes &&
+                              DtypeSize(p.buffers[x].dtype) == DtypeSize(p.buffers[y].dtype));
+          };
+          for (size_t i = 0; i < all.size() && ok; ++i) {
+            const uint32_t d = p.tasks[all[i]].dst;
+            for (const Read &r : rd)
+              if (overlap(d, r.buf) && (!same_bytes(r.buf, d) || r.viewed)) ok = false;
+            for (size_t j = 0; j < all.size(); ++j)
+              if (j != i && overlap(d, p.tasks[all[j]].dst) && !same_bytes(d, p.tasks[all[j]].dst)) ok = false;
+          }
+        }
+        if (!ok) break;
+        grp.push_back(nx);
+        ++n;
+      }
+      if (n < 2) { ++k; continue; }
+      for (uint32_t l = 0; l < L; ++l) {
+        if (ph[l][k].empty()) { for (size_t i = 1; i < n; ++i) ph[l].erase(ph[l].begin() + static_cast<long>(k) + 1); continue; }
+        const uint32_t lo = ph[l][k][0].tile_lo, hi = ph[l][k][0].tile_hi;
+        std::vector<VmEntry> merged;
+        for (uint64_t b0 = lo; b0 < hi; b0 += row_block) {
+          const uint32_t b1 = static_cast<uint32_t>(std::min<uint64_t>(hi, b0 + row_block));
+          for (size_t i = 0; i < n; ++i)
+            for (VmEntry e : ph[l][k + i]) { e.tile_lo = static_cast<uint32_t>(b0); e.tile_hi = b1; merged.push_back(e); }
+        }
+        ph[l][k] = merged;
+        for (size_t i = 1; i < n; ++i) ph[l].erase(ph[l].begin() + static_cast<long>(k) + 1);
+      }
+      ++n_piped;
+      ++k;
+    }
   }
   const size_t n_ph = ph[0].size();
   auto cost_class = [&](const RebUnit &u) {
@@ -522,7 +636,8 @@ bool RebalancePhases(const VmProgram &p, VmProgram *q, uint32_t *n_done) {
     }
     ++*n_done;
   }
-  if (!*n_done) return false;
+  if (!*n_done && !n_piped) return false;
+  *n_piped_out = n_piped;
   *q = p;
   q->entries.clear();
   VmEntry bar;
@@ -546,10 +661,11 @@ static bool BuildDeviceTablesFor(const VmProgram &p, uint64_t arena_base, Device
 bool BuildDeviceTables(const VmProgram &p, uint64_t arena_base, DeviceTables *out, std::string *err,
                        bool *unimplemented) {
   VmProgram q;
-  uint32_t n_reb = 0;
-  const bool recut = std::getenv("B2VM_NO_REBALANCE") == nullptr && RebalancePhases(p, &q, &n_reb);
+  uint32_t n_reb = 0, n_piped = 0;
+  const bool recut = std::getenv("B2VM_NO_REBALANCE") == nullptr && RebalancePhases(p, &q, &n_reb, &n_piped);
   const bool ok = BuildDeviceTablesFor(recut ? q : p, arena_base, out, err, unimplemented);
   out->n_rebalanced = n_reb;
+  out->n_row_pipelines = n_piped;
   return ok;
 }
 

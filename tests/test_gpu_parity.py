@@ -118,6 +118,21 @@ def test_phases_mixing_unit_costs_are_recut_over_all_lanes(rt):
     assert vm.LoadedProgram.Load(rt, vm.VmProgram.Parse(g2.blob)).stat("rebalanced_phases") == 0
 
 
+def test_row_local_phases_run_as_one_pipeline(rt, monkeypatch):
+    """LayerNorm rows -> elementwise chain -> softmax rows over the same rows of one elementwise tile each:
+    the loader removes the two grid barriers between them (every row depends only on the same row of its
+    predecessor); with a block size the lane also interleaves the three units block by block. Same values."""
+    vm = package()
+    g = Golden("c2_chain_f32_small")
+    for block in (None, "2"):
+        if block:
+            monkeypatch.setenv("B2VM_ROW_BLOCK", block)
+        lp = vm.LoadedProgram.Load(rt, vm.VmProgram.Parse(g.blob))
+        assert lp.stat("row_pipelines") == 1
+        check_outputs(g, [np.ascontiguousarray(o).view(np.uint8).reshape(-1) for o in lp.Execute(g.args)], "cuda-rows")
+        assert lp.Status()["barriers"] == 2       # 4 phases -> the pipeline, the sum (its combine folded in)
+
+
 def test_point_to_point_entry_fields_are_refused(rt):
     """Tile entries whose reserved wait / signal words are set (scheduler.py:201-209 keeps them
     for point-to-point dependencies and emits "no flag") are refused at load, not ignored."""
