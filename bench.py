@@ -66,7 +66,7 @@ WORKLOADS = {
     "c2_f32": _wl("c2_chain_f32", "eltwise HBM GB/s", "GB/s", 7 * N_C2 * 4 + 2 * 4096 * 4, 1e9, "hbm", "f32",
                   "config 2: LayerNorm -> tanh-GELU -> softmax -> full sum on f32 (8192,4096); "
                   "bytes = LayerNorm r+w, GELU r+w, softmax r+w, sum r, + gamma/beta",
-                  sample="c2_chain_f32_cpu_sample", sample_frac=512 / 8192, traffic=942.6e6,
+                  sample="c2_chain_f32_cpu_sample", sample_frac=512 / 8192, traffic=940.7e6,
                   sample_what="512 of the 8192 rows"),
     "c2_bf16": _wl("c2_chain_bf16", "eltwise HBM GB/s", "GB/s", 7 * N_C2 * 2 + 2 * 4096 * 2, 1e9, "hbm", "bf16",
                    "config 2 on bf16-storage copies of the same values",
@@ -106,12 +106,12 @@ WORKLOADS = {
                               secondary=True),
     "flash_decode_bf16": _wl("flash_decode_bf16_c5", "decode-attention GB/s", "GB/s", 2 * 512 * 2049 * 64 * 2, 1e9, "hbm", "bf16",
                              "config 5's decode attention alone: 512 heads x 1 query x 2049 keys, head_dim 64; "
-                             "bytes = K and V read once", secondary=True, traffic=297.1e6),
+                             "bytes = K and V read once", secondary=True, traffic=283.2e6),
     "c5_decode_in_place": _wl("c5_decode_in_place_bf16", "transformer-block tokens/s per B200", "tokens/s", 32, 1.0, "hbm", "bf16",
                               "config 5 decode step, batch 32, KV cache 2048 + the new position: K/V written in place "
                               "(in/out buffers), K read through its view; bytes = weights + KV cache read once",
                               roof_alg=2 * (4 * 1024 * 1024 + 2 * 1024 * 4096) + 2 * 32 * 16 * 2049 * 64 * 2,
-                              plan="c5_decode_in_place", traffic=324.7e6),
+                              plan="c5_decode_in_place", traffic=312.0e6),
     "c5_decode": _wl("c5_decode_bf16", "transformer-block tokens/s per B200", "tokens/s", 32, 1.0, "hbm", "bf16",
                      "config 5 decode step: batch 32, KV cache 2048; bytes = weights + KV cache read once",
                      roof_alg=2 * (4 * 1024 * 1024 + 2 * 1024 * 4096) + 2 * 32 * 16 * 2048 * 64 * 2, plan="c5_decode"),
