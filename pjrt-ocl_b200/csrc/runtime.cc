@@ -31,7 +31,7 @@ namespace b2 {
 // One pair of launch glue per build of the megakernel (vm_kernel.cu, variants.h).
 #define B2_DECLARE_VARIANT(name, fams)                                                                              \
   cudaError_t LaunchVm_##name(const KParams &params, uint32_t n_lanes, int threads, uint32_t smem_bytes,           \
-                              cudaStream_t stream);                                                                 \
+                              cudaStream_t stream, const void *keep_base, size_t keep_bytes);                     \
   cudaError_t VmResidency_##name(int device, int threads, uint32_t smem_bytes, int *max_lanes);
 B2_VARIANT_LIST(B2_DECLARE_VARIANT)
 #undef B2_DECLARE_VARIANT
@@ -39,7 +39,7 @@ B2_VARIANT_LIST(B2_DECLARE_VARIANT)
 struct VmVariant {
   const char *name;
   uint32_t families;
-  cudaError_t (*launch)(const KParams &, uint32_t, int, uint32_t, cudaStream_t);
+  cudaError_t (*launch)(const KParams &, uint32_t, int, uint32_t, cudaStream_t, const void *, size_t);
   cudaError_t (*residency)(int, int, uint32_t, int *);
 };
 #define B2_VARIANT_ROW(name, fams) {#name, static_cast<uint32_t>(fams), &LaunchVm_##name, &VmResidency_##name},
@@ -109,6 +109,7 @@ struct b2_runtime {
   int threads = 512;
   uint32_t smem_bytes = 0;
   int max_lanes = 0;
+  size_t l2_keep_bytes = 0;   // L2 set aside for persisting lines (the loaded programs' tables), 0 = unavailable
   std::mutex mu;        // serialises execute and host<->device copies (runtime.h:301)
   std::mutex pool_mu;   // runtime.h:302
   std::unordered_map<size_t, std::vector<void *>> pool;
@@ -155,6 +156,8 @@ struct b2_loaded {
   b2::VmProgram prog;
   b2::DeviceTables tab;
   uint8_t *arena = nullptr;
+  uint8_t *d_tables = nullptr;   // one allocation holding the tensor maps, tasks, entries, lane table, aux and descriptor pools
+  size_t tables_bytes = 0;
   b2::DTask *d_tasks = nullptr;
   b2::DEntry *d_entries = nullptr;
   b2::VmLane *d_lanes = nullptr;
@@ -177,21 +180,24 @@ struct b2_loaded {
 
   ~b2_loaded() {
     if (rt) rt->Bind();
-    cudaFree(arena); cudaFree(d_tasks); cudaFree(d_entries); cudaFree(d_lanes);
-    cudaFree(d_aux); cudaFree(d_desc); cudaFree(d_sync); cudaFree(d_tmaps); cudaFree(d_scratch); cudaFree(d_lane_ts);
+    cudaFree(arena); cudaFree(d_tables);      // the tables are carved out of d_tables
+    cudaFree(d_sync); cudaFree(d_scratch); cudaFree(d_lane_ts);
     if (h_sync) cudaFreeHost(h_sync);
   }
 };
 
 namespace {
 
+// The device tables of a loaded program live in ONE allocation, each table at a 256-byte boundary: every
+// launch names that range as an L2 persistence window, so that the few KB a lane reads at the start of each
+// phase (entry, task, descriptors: a chain of dependent loads) are not evicted by the gigabytes the phases
+// stream through the cache in between.
+size_t TableBytes(size_t n) { return (std::max<size_t>(n, 16) + 255) & ~static_cast<size_t>(255); }
 template <typename T>
-cudaError_t Upload(T **dptr, const std::vector<T> &v) {
-  const size_t bytes = std::max<size_t>(v.size() * sizeof(T), 16);
-  cudaError_t e = cudaMalloc(reinterpret_cast<void **>(dptr), bytes);
-  if (e != cudaSuccess) return e;
-  if (!v.empty()) e = cudaMemcpy(*dptr, v.data(), v.size() * sizeof(T), cudaMemcpyHostToDevice);
-  return e;
+cudaError_t Carve(uint8_t *pool, size_t *off, T **dptr, const std::vector<T> &v) {
+  *dptr = reinterpret_cast<T *>(pool + *off);
+  *off += TableBytes(v.size() * sizeof(T));
+  return v.empty() ? cudaSuccess : cudaMemcpy(*dptr, v.data(), v.size() * sizeof(T), cudaMemcpyHostToDevice);
 }
 
 // Enqueue one execution on `stream`: reset the sync block, launch the megakernel,
@@ -236,7 +242,8 @@ b2_status Enqueue(b2_loaded *lp, const b2::IoTable &io, cudaStream_t stream, std
   kp.n_lanes = lp->prog.n_lanes;
   kp.wait_budget_ns = lp->wait_budget_ns;
   kp.io = io;
-  e = b2::kVariants[lp->variant].launch(kp, lp->prog.n_lanes, lp->rt->threads, lp->rt->smem_bytes, stream);
+  e = b2::kVariants[lp->variant].launch(kp, lp->prog.n_lanes, lp->rt->threads, lp->rt->smem_bytes, stream, lp->d_tables,
+                                        std::min(lp->tables_bytes, lp->rt->l2_keep_bytes));
   if (e != cudaSuccess) {          // whatever was queued before the failure may have run: start clean next time
     *err = CudaMsg("megakernel launch", e);
     cudaGetLastError();
@@ -322,6 +329,14 @@ b2_status b2_runtime_create(int device_ordinal, b2_runtime **out, char *err, siz
       return B2_INTERNAL;
     }
     rt->max_lanes = std::min(rt->max_lanes, lanes);
+  }
+  // A few MB of L2 for lines marked persisting (context-scoped; released with the context). Failure only means
+  // the tables compete for L2 like everything else.
+  {
+    const size_t want = std::min<size_t>(static_cast<size_t>(std::max(rt->prop.persistingL2CacheMaxSize, 0)), 4u << 20);
+    if (want && !std::getenv("B2VM_NO_L2_KEEP") && cudaDeviceSetLimit(cudaLimitPersistingL2CacheSize, want) == cudaSuccess)
+      rt->l2_keep_bytes = std::min<size_t>(want, static_cast<size_t>(std::max(rt->prop.accessPolicyMaxWindowSize, 0)));
+    cudaGetLastError();
   }
   if ((e = cudaStreamCreateWithFlags(&rt->stream, cudaStreamNonBlocking)) != cudaSuccess) {
     SetErr(err, err_cap, CudaMsg("stream create", e));
@@ -496,9 +511,15 @@ b2_status b2_program_load(b2_runtime *rt, b2_program *prog, b2_loaded **out, cha
     i += group;
   }
   std::vector<int32_t> aux = p.aux;
-  if ((e = Upload(&lp->d_tmaps, lp->h_tmaps)) != cudaSuccess || (e = Upload(&lp->d_tasks, lp->tab.tasks)) != cudaSuccess || (e = Upload(&lp->d_entries, lp->tab.entries)) != cudaSuccess ||
-      (e = Upload(&lp->d_lanes, lp->tab.lanes)) != cudaSuccess || (e = Upload(&lp->d_aux, aux)) != cudaSuccess ||
-      (e = Upload(&lp->d_desc, lp->tab.desc)) != cudaSuccess ||
+  lp->tables_bytes = TableBytes(lp->h_tmaps.size() * sizeof(lp->h_tmaps[0])) + TableBytes(lp->tab.tasks.size() * sizeof(lp->tab.tasks[0])) +
+                     TableBytes(lp->tab.entries.size() * sizeof(lp->tab.entries[0])) + TableBytes(lp->tab.lanes.size() * sizeof(lp->tab.lanes[0])) +
+                     TableBytes(aux.size() * sizeof(aux[0])) + TableBytes(lp->tab.desc.size() * sizeof(lp->tab.desc[0]));
+  size_t toff = 0;
+  if ((e = cudaMalloc(reinterpret_cast<void **>(&lp->d_tables), lp->tables_bytes)) != cudaSuccess ||
+      (e = Carve(lp->d_tables, &toff, &lp->d_tmaps, lp->h_tmaps)) != cudaSuccess || (e = Carve(lp->d_tables, &toff, &lp->d_tasks, lp->tab.tasks)) != cudaSuccess ||
+      (e = Carve(lp->d_tables, &toff, &lp->d_entries, lp->tab.entries)) != cudaSuccess ||
+      (e = Carve(lp->d_tables, &toff, &lp->d_lanes, lp->tab.lanes)) != cudaSuccess || (e = Carve(lp->d_tables, &toff, &lp->d_aux, aux)) != cudaSuccess ||
+      (e = Carve(lp->d_tables, &toff, &lp->d_desc, lp->tab.desc)) != cudaSuccess ||
       (e = cudaMalloc(reinterpret_cast<void **>(&lp->d_sync), sizeof(b2::DSync))) != cudaSuccess ||
       (e = cudaMallocHost(reinterpret_cast<void **>(&lp->h_sync), sizeof(b2::DSync))) != cudaSuccess) {
     SetErr(err, err_cap, CudaMsg("device table upload", e));

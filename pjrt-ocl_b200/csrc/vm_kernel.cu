@@ -25,6 +25,7 @@
 #define B2_PASTE2(a, b) a##b
 #define B2_PASTE(a, b) B2_PASTE2(a, b)
 
+#include <cstring>
 #define B2_SHORT B2_HAS(0x100u)   // kFamShort
 #include "dev_common.cuh"
 #include "ops_ew.cuh"
@@ -262,11 +263,27 @@ __global__ void __launch_bounds__(NT, 1) B2_VM_KERNEL(const __grid_constant__ KP
 
 // ---- host-side launch glue (called from runtime.cc through the table in variants.h) ----
 cudaError_t B2_PASTE(LaunchVm_, B2_VARIANT)(const KParams &params, uint32_t n_lanes, int threads, uint32_t smem_bytes,
-                                            cudaStream_t stream) {
+                                            cudaStream_t stream, const void *keep_base, size_t keep_bytes) {
   void *args[2] = {const_cast<KParams *>(&params), &smem_bytes};
   if (threads != kVmThreads) return cudaErrorInvalidValue;
   const void *fn = reinterpret_cast<const void *>(&B2_VM_KERNEL<kVmThreads>);
-  return cudaLaunchCooperativeKernel(fn, dim3(n_lanes), dim3(threads), args, smem_bytes, stream);
+  cudaLaunchAttribute attr[2];
+  std::memset(attr, 0, sizeof(attr));
+  attr[0].id = cudaLaunchAttributeCooperative;
+  attr[0].val.cooperative = 1;
+  unsigned n_attr = 1;
+  if (keep_base && keep_bytes) {        // the program's tables stay in the L2 set-aside between the phases
+    attr[1].id = cudaLaunchAttributeAccessPolicyWindow;
+    attr[1].val.accessPolicyWindow.base_ptr = const_cast<void *>(keep_base);
+    attr[1].val.accessPolicyWindow.num_bytes = keep_bytes;
+    attr[1].val.accessPolicyWindow.hitRatio = 1.0f;
+    attr[1].val.accessPolicyWindow.hitProp = cudaAccessPropertyPersisting;
+    attr[1].val.accessPolicyWindow.missProp = cudaAccessPropertyNormal;
+    n_attr = 2;
+  }
+  // {grid, block, dynamic shared memory, stream, attributes, their count}
+  cudaLaunchConfig_t cfg = {dim3(n_lanes), dim3(static_cast<unsigned>(threads)), smem_bytes, stream, attr, n_attr};
+  return cudaLaunchKernelExC(&cfg, fn, args);
 }
 
 // Co-resident CTAs of this build at `threads` per lane and `smem_bytes` of dynamic shared memory.
