@@ -140,6 +140,8 @@ enum TaskFlags : uint32_t {
   kFwdC = 1u << 6,      // select predicate forwarded
   kRedFused = 1u << 7,  // RED_PART re-cut over all lanes with the combine folded in: entries carry word
                         // ranges, ptr[3] is the final result, lane totals meet in KParams::scratch
+  kRedSrcBf16 = 1u << 8, // ... and its input is the bf16 (kRedSrcF16: f16) source of the convert that fed it: the
+  kRedSrcF16 = 1u << 9,  // f32 copy is never written, each 32-bit word of the stream holds two elements
 };
 
 // Scratch of a loaded program (KParams::scratch): where the lanes of a re-cut full

@@ -237,7 +237,8 @@ void LaneRuns(const VmProgram &p, const VmLane &l, std::vector<StreamRun> *runs)
 // of 16-byte words (DEntry::a, b), leaves its total in the program's scratch, and
 // the lane that arrives last folds the lanes' totals in lane order into the
 // RED_COMB's result; the RED_COMB entry becomes a NOP.
-void SpreadReductions(const VmProgram &p, const std::vector<int> &fused_comb, DeviceTables *out) {
+void SpreadReductions(const VmProgram &p, const std::vector<int> &fused_comb, const std::vector<int> &half_src, Ctx *cx,
+                      DeviceTables *out) {
   const uint32_t n_lanes = static_cast<uint32_t>(p.lane_tab.size());
   if (n_lanes < 4) return;
   std::vector<std::vector<StreamRun>> runs(n_lanes);
@@ -282,7 +283,7 @@ void SpreadReductions(const VmProgram &p, const std::vector<int> &fused_comb, De
     if (full) {
       const uint64_t nt = (static_cast<uint64_t>(t.p0) + t.p1 - 1) / t.p1;
       if (tiles != nt) continue;
-      rows = t.p0 / 4;
+      rows = half_src[task] >= 0 ? t.p0 / 8 : t.p0 / 4;     // 16-byte words of the stream
     } else {
       const int64_t n_out = t.p0, red = t.p1, inner = t.p2;
       if (!red_strided_rows_ok(dt, red, inner, t.p3) || n_out % inner != 0) continue;
@@ -309,6 +310,31 @@ void SpreadReductions(const VmProgram &p, const std::vector<int> &fused_comb, De
       const int comb = fused_comb[task];
       dp.flags |= kRedFused;
       dp.ptr[3] = out->tasks[comb].ptr[0];        // where the RED_COMB would have put the result
+      if (half_src[task] >= 0) {
+        // the convert that fed this reduction is folded in: stream its 16-bit source, never write the f32 copy
+        const VmTask &cv = p.tasks[half_src[task]];
+        dp.ptr[1] = cx->Ref(cv.a);
+        dp.flags |= ((cv.tile_op >> 16) & 0xFFu) == kBF16 ? kRedSrcBf16 : kRedSrcF16;
+        for (DEntry &e : out->entries)
+          if (e.task == static_cast<uint32_t>(half_src[task])) e.task = kEntNop;
+        // chains the convert sat in close up over the gap: live members first, the count on the new head
+        for (const VmLane &l : out->lanes)
+          for (uint32_t i = l.off; i < l.off + l.count; ++i) {
+            const uint32_t n = out->entries[i].chain;
+            if (n <= 1u) continue;
+            uint32_t live = 0;
+            for (uint32_t k = i; k < i + n; ++k)
+              if (out->entries[k].task != kEntNop) {
+                DEntry m = out->entries[k];
+                out->entries[k].task = kEntNop;
+                out->entries[i + live++] = m;
+              }
+            for (uint32_t k = i; k < i + n; ++k) out->entries[k].chain = 0u;
+            if (live) out->entries[i].chain = live;
+            i += n - 1u;
+          }
+        out->n_folded_converts++;
+      }
       for (DEntry &e : out->entries)
         if (e.task == static_cast<uint32_t>(comb)) e.task = kEntNop;
       out->n_fused_reduce++;
@@ -1276,7 +1302,61 @@ static bool BuildDeviceTablesFor(const VmProgram &p, uint64_t arena_base, Device
     }
     fused_comb[ti] = static_cast<int>(ci);
   }
-  SpreadReductions(p, fused_comb, out);
+  // A full f32 sum whose input is the f32 copy of a 16-bit buffer, made by a plain convert in the phase just
+  // before and read by nothing else: the reduction streams the 16-bit source instead (half the bytes) and the
+  // convert's phase does nothing. Straight-line programs only (phases counted by barriers in the root walk).
+  std::vector<int> half_src(p.tasks.size(), -1);
+  {
+    bool straight = std::getenv("B2VM_NO_CONVERT_FOLD") == nullptr;
+    for (const VmEntry &e : p.entries)
+      if (e.task == kEntWhile || e.task == kEntIf || e.task == kEntFor) straight = false;
+    std::vector<int> phase_lo(p.tasks.size(), 1 << 30), phase_hi(p.tasks.size(), -1);
+    if (straight)
+      for (const VmLane &l : p.lane_tab) {
+        int ph = 0;
+        for (uint32_t i = 0; i < l.count; ++i) {
+          const VmEntry &e = p.entries[l.off + i];
+          if (e.task == kEntBarrier) { ++ph; continue; }
+          if (e.task >= p.tasks.size()) continue;
+          phase_lo[e.task] = std::min(phase_lo[e.task], ph);
+          phase_hi[e.task] = std::max(phase_hi[e.task], ph);
+        }
+      }
+    for (size_t ti = 0; straight && ti < p.tasks.size(); ++ti) {
+      if (fused_comb[ti] < 0) continue;
+      const VmTask &tp = p.tasks[ti];
+      if (((tp.tile_op >> 8) & 0xFFu) != kF32 || tp.p2 != kSum) continue;
+      const uint32_t src = tp.a;
+      if (readers[src].size() != 1 || pinned.count(src) || in_ids.count(src) || out_ids.count(src) || const_ids.count(src)) continue;
+      int conv = -1;
+      uint32_t writers = 0;
+      for (size_t k = 0; k < p.tasks.size(); ++k)
+        if (p.tasks[k].dst == src) { ++writers; conv = static_cast<int>(k); }
+      if (writers != 1) continue;
+      const VmTask &cv = p.tasks[conv];
+      const uint32_t cadt = (cv.tile_op >> 16) & 0xFFu;
+      if ((cv.tile_op & 0xFFu) != kTopEw || cv.p0 != kConvert || ((cv.tile_op >> 8) & 0xFFu) != kF32 || !(cadt == kBF16 || cadt == kF16) ||
+          cv.p2 != 0u || cv.p1 != tp.p0 || !c.Aligned16(cv.a) || tp.p0 % 8u != 0u)
+        continue;
+      if (phase_lo[conv] != phase_hi[conv] || phase_lo[ti] != phase_hi[ti] || phase_hi[conv] + 1 != phase_lo[ti]) continue;
+      // nothing may write the 16-bit source (or bytes it shares) in the convert's or the reduction's phase
+      bool clobbered = false;
+      for (size_t k = 0; k < p.tasks.size() && !clobbered; ++k) {
+        if (static_cast<int>(k) == conv || phase_hi[k] < phase_lo[conv] || phase_lo[k] > phase_lo[ti]) continue;
+        const BufferSlot &wb = p.buffers[p.tasks[k].dst], &sb = p.buffers[cv.a];
+        if (wb.bytes && sb.bytes && wb.offset < sb.offset + sb.bytes && sb.offset < wb.offset + wb.bytes && !c.port_of.count(cv.a)) clobbered = true;
+        if (p.tasks[k].dst == cv.a) clobbered = true;
+      }
+      if (clobbered) continue;
+      // the convert leaves its chain, so it may neither take nor hand over a value in registers
+      bool forwards = (out->tasks[conv].flags & (kFwdA | kFwdB | kDeadStore)) != 0u;
+      for (size_t k = 0; k < p.tasks.size(); ++k)
+        if (pred[k] == conv && (out->tasks[k].flags & (kFwdA | kFwdB))) forwards = true;
+      if (forwards) continue;
+      half_src[ti] = conv;
+    }
+  }
+  SpreadReductions(p, fused_comb, half_src, &c, out);
   // Dynamic work distribution for tensor-core attention tasks: allowed when the task's
   // entries cover all its query rows, no lane holds more than one of them, and they
   // sit outside the sub-ranges of WHILE / IF entries (where lanes may not all arrive).

@@ -141,19 +141,28 @@ __device__ __forceinline__ Acc acc_block_reduce(const Lane &L, uint32_t kind, ui
 }
 
 // Combine functors over the 32-bit register representation.
-struct RFSum { static __device__ __forceinline__ uint32_t f(uint32_t a, uint32_t b) { return __float_as_uint(__uint_as_float(a) + __uint_as_float(b)); } };
-struct RFProd { static __device__ __forceinline__ uint32_t f(uint32_t a, uint32_t b) { return __float_as_uint(__uint_as_float(a) * __uint_as_float(b)); } };
-struct RFMax { static __device__ __forceinline__ uint32_t f(uint32_t a, uint32_t b) { return __float_as_uint(np_max(__uint_as_float(a), __uint_as_float(b))); } };
-struct RFMin { static __device__ __forceinline__ uint32_t f(uint32_t a, uint32_t b) { return __float_as_uint(np_min(__uint_as_float(a), __uint_as_float(b))); } };
-struct RISum { static __device__ __forceinline__ uint32_t f(uint32_t a, uint32_t b) { return a + b; } };
-struct RIProd { static __device__ __forceinline__ uint32_t f(uint32_t a, uint32_t b) { return a * b; } };
-struct RIAnd { static __device__ __forceinline__ uint32_t f(uint32_t a, uint32_t b) { return a & b; } };
-struct RIOr { static __device__ __forceinline__ uint32_t f(uint32_t a, uint32_t b) { return a | b; } };
-struct RIXor { static __device__ __forceinline__ uint32_t f(uint32_t a, uint32_t b) { return a ^ b; } };
-struct RIMaxS { static __device__ __forceinline__ uint32_t f(uint32_t a, uint32_t b) { return static_cast<uint32_t>(max(static_cast<int32_t>(a), static_cast<int32_t>(b))); } };
-struct RIMinS { static __device__ __forceinline__ uint32_t f(uint32_t a, uint32_t b) { return static_cast<uint32_t>(min(static_cast<int32_t>(a), static_cast<int32_t>(b))); } };
-struct RIMaxU { static __device__ __forceinline__ uint32_t f(uint32_t a, uint32_t b) { return max(a, b); } };
-struct RIMinU { static __device__ __forceinline__ uint32_t f(uint32_t a, uint32_t b) { return min(a, b); } };
+struct RFSum { static __device__ __forceinline__ uint32_t pre(uint32_t w) { return w; } static __device__ __forceinline__ uint32_t f(uint32_t a, uint32_t b) { return __float_as_uint(__uint_as_float(a) + __uint_as_float(b)); } };
+struct RFProd { static __device__ __forceinline__ uint32_t pre(uint32_t w) { return w; } static __device__ __forceinline__ uint32_t f(uint32_t a, uint32_t b) { return __float_as_uint(__uint_as_float(a) * __uint_as_float(b)); } };
+struct RFMax { static __device__ __forceinline__ uint32_t pre(uint32_t w) { return w; } static __device__ __forceinline__ uint32_t f(uint32_t a, uint32_t b) { return __float_as_uint(np_max(__uint_as_float(a), __uint_as_float(b))); } };
+struct RFMin { static __device__ __forceinline__ uint32_t pre(uint32_t w) { return w; } static __device__ __forceinline__ uint32_t f(uint32_t a, uint32_t b) { return __float_as_uint(np_min(__uint_as_float(a), __uint_as_float(b))); } };
+// Sums whose stream is the 16-bit source of a convert: a 32-bit word holds two elements, folded on the way in.
+struct RFSumBf {
+  static __device__ __forceinline__ uint32_t pre(uint32_t w) { return __float_as_uint(__uint_as_float(w << 16) + __uint_as_float(w & 0xffff0000u)); }
+  static __device__ __forceinline__ uint32_t f(uint32_t a, uint32_t b) { return __float_as_uint(__uint_as_float(a) + __uint_as_float(b)); }
+};
+struct RFSumF16 {
+  static __device__ __forceinline__ uint32_t pre(uint32_t w) { return __float_as_uint(f16_bits_to_f32(w & 0xffffu) + f16_bits_to_f32(w >> 16)); }
+  static __device__ __forceinline__ uint32_t f(uint32_t a, uint32_t b) { return __float_as_uint(__uint_as_float(a) + __uint_as_float(b)); }
+};
+struct RISum { static __device__ __forceinline__ uint32_t pre(uint32_t w) { return w; } static __device__ __forceinline__ uint32_t f(uint32_t a, uint32_t b) { return a + b; } };
+struct RIProd { static __device__ __forceinline__ uint32_t pre(uint32_t w) { return w; } static __device__ __forceinline__ uint32_t f(uint32_t a, uint32_t b) { return a * b; } };
+struct RIAnd { static __device__ __forceinline__ uint32_t pre(uint32_t w) { return w; } static __device__ __forceinline__ uint32_t f(uint32_t a, uint32_t b) { return a & b; } };
+struct RIOr { static __device__ __forceinline__ uint32_t pre(uint32_t w) { return w; } static __device__ __forceinline__ uint32_t f(uint32_t a, uint32_t b) { return a | b; } };
+struct RIXor { static __device__ __forceinline__ uint32_t pre(uint32_t w) { return w; } static __device__ __forceinline__ uint32_t f(uint32_t a, uint32_t b) { return a ^ b; } };
+struct RIMaxS { static __device__ __forceinline__ uint32_t pre(uint32_t w) { return w; } static __device__ __forceinline__ uint32_t f(uint32_t a, uint32_t b) { return static_cast<uint32_t>(max(static_cast<int32_t>(a), static_cast<int32_t>(b))); } };
+struct RIMinS { static __device__ __forceinline__ uint32_t pre(uint32_t w) { return w; } static __device__ __forceinline__ uint32_t f(uint32_t a, uint32_t b) { return static_cast<uint32_t>(min(static_cast<int32_t>(a), static_cast<int32_t>(b))); } };
+struct RIMaxU { static __device__ __forceinline__ uint32_t pre(uint32_t w) { return w; } static __device__ __forceinline__ uint32_t f(uint32_t a, uint32_t b) { return max(a, b); } };
+struct RIMinU { static __device__ __forceinline__ uint32_t pre(uint32_t w) { return w; } static __device__ __forceinline__ uint32_t f(uint32_t a, uint32_t b) { return min(a, b); } };
 
 // Groups of 4 elements [g_lo, g_hi), strided over `nthreads`; DOT multiplies by
 // the shared vector at element (4g - dbase) first (GEMV mode).
@@ -400,12 +409,12 @@ __device__ __forceinline__ uint32_t red_words_lane(const Lane &L, const uint8_t 
       uint32_t o = L.tid;
       for (; o + L.nthr < nw; o += 2u * L.nthr) {
         const uint4 v = q[o], u = q[o + L.nthr];
-        acc = C::f(C::f(acc, v.x), C::f(v.y, C::f(v.z, v.w)));
-        acc2 = C::f(C::f(acc2, u.x), C::f(u.y, C::f(u.z, u.w)));
+        acc = C::f(C::f(acc, C::pre(v.x)), C::f(C::pre(v.y), C::f(C::pre(v.z), C::pre(v.w))));
+        acc2 = C::f(C::f(acc2, C::pre(u.x)), C::f(C::pre(u.y), C::f(C::pre(u.z), C::pre(u.w))));
       }
       if (o < nw) {
         const uint4 v = q[o];
-        acc = C::f(C::f(acc, v.x), C::f(v.y, C::f(v.z, v.w)));
+        acc = C::f(C::f(acc, C::pre(v.x)), C::f(C::pre(v.y), C::f(C::pre(v.z), C::pre(v.w))));
       }
       __syncwarp();
       if (lane_id == 0) mbar_arrive(&empty[b]);
@@ -416,7 +425,11 @@ __device__ __forceinline__ uint32_t red_words_lane(const Lane &L, const uint8_t 
       for (uint32_t i = 0; i < kStreamBufs; ++i) { mbar_inval(&full[i]); mbar_inval(&empty[i]); }
     __syncthreads();
   } else if (w_hi > w_lo) {
-    acc = static_cast<uint32_t>(reduce_run(a, dt, kind, static_cast<int64_t>(w_lo) * 4, static_cast<int64_t>(w_hi) * 4, L.tid, L.nthr, nullptr, 0).bits);
+    const uint4 *q = reinterpret_cast<const uint4 *>(a);
+    for (uint64_t o = w_lo + L.tid; o < w_hi; o += L.nthr) {
+      const uint4 v = ldg_v4(q + o);
+      acc = C::f(C::f(acc, C::pre(v.x)), C::f(C::pre(v.y), C::f(C::pre(v.z), C::pre(v.w))));
+    }
   }
   Acc r;
   r.bits = acc;
@@ -439,8 +452,16 @@ __device__ __forceinline__ void red_full_lane(const Lane &L, const DTask &t, uin
   uint32_t total = red_words_lane<C>(L, a, w_lo, w_hi, kind, dt, ident);
   uint32_t *flag = reinterpret_cast<uint32_t *>(L.smem + kSmemFlag);
   if (L.tid == 0) {
-    if (L.lane == P.n_lanes - 1u)
-      for (uint64_t i = (n / 4u) * 4u; i < n; ++i) total = C::f(total, reinterpret_cast<const uint32_t *>(a)[i]);
+    if (L.lane == P.n_lanes - 1u) {       // the elements past the last whole 16-byte word
+      if (t.flags & (kRedSrcBf16 | kRedSrcF16)) {
+        for (uint64_t i = (n / 8u) * 8u; i < n; ++i) {
+          const uint32_t h = reinterpret_cast<const uint16_t *>(a)[i];
+          total = C::f(total, __float_as_uint((t.flags & kRedSrcBf16) ? bf16_bits_to_f32(h) : f16_bits_to_f32(h)));
+        }
+      } else {
+        for (uint64_t i = (n / 4u) * 4u; i < n; ++i) total = C::f(total, reinterpret_cast<const uint32_t *>(a)[i]);
+      }
+    }
     sc->total[L.lane] = total;
     __threadfence();
     *flag = atom_add_acq_rel_gpu(&sc->arrived, 1u) == P.n_lanes - 1u ? 1u : 0u;
@@ -471,7 +492,9 @@ static __device__ __noinline__ void red_part_tiles(const Lane &L, const DTask &t
   if (t.flags & kRedFused) {
     const uint32_t kind = t.p[2], dt = t.dt;
     const bool fl = dt == kF32;
-    if (fl && kind == kSum) red_full_lane<RFSum>(L, t, w_lo, w_hi, kind, dt);
+    if (fl && kind == kSum && (t.flags & kRedSrcBf16)) red_full_lane<RFSumBf>(L, t, w_lo, w_hi, kind, dt);
+    else if (fl && kind == kSum && (t.flags & kRedSrcF16)) red_full_lane<RFSumF16>(L, t, w_lo, w_hi, kind, dt);
+    else if (fl && kind == kSum) red_full_lane<RFSum>(L, t, w_lo, w_hi, kind, dt);
     else if (fl && kind == kRMax) red_full_lane<RFMax>(L, t, w_lo, w_hi, kind, dt);
     else if (fl && kind == kRMin) red_full_lane<RFMin>(L, t, w_lo, w_hi, kind, dt);
     else if (fl) red_full_lane<RFProd>(L, t, w_lo, w_hi, kind, dt);

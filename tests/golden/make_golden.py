@@ -356,6 +356,23 @@ def _():
     return blob, prog, (11, [N((5, 4096 * 3 + 11)), N((100,)), U((64,), 0.8, 1.25)])
 
 
+@case("reduce_full_16bit_source", rtol=1e-5, atol=1e-3)
+def _():
+    """Full f32 sums of the f32 copies of a bf16 and an f16 tensor (what an upcasting reduction lowers
+    to): the backend may stream the 16-bit source instead of writing the copy. A third sum reads a copy
+    that is also a program output, which therefore has to be written."""
+    a = Asm()
+    n = 65536 + 8 * 37
+    xb = a.input((n,), BF16)
+    xh = a.input((n,), F16)
+    xk = a.input((n,), BF16)
+    kept = a.convert(xk, F32)
+    outs = [a.reduce(a.convert(xb, F32), [0], SUM), a.reduce(a.convert(xh, F32), [0], SUM),
+            a.reduce(kept, [0], SUM), kept]
+    blob, prog = a.finish(outs, nlanes=5)
+    return blob, prog, (23, [N((n,), "bf16"), N((n,), "f16"), N((n,), "bf16")])
+
+
 @case("reduce_full_int", exact=True)
 def _():
     a = Asm()

@@ -133,6 +133,21 @@ def test_row_local_phases_run_as_one_pipeline(rt, monkeypatch):
         assert lp.Status()["barriers"] == 2       # 4 phases -> the pipeline, the sum (its combine folded in)
 
 
+def test_convert_feeding_a_full_sum_is_folded(rt, monkeypatch):
+    """A full f32 sum over the f32 copy of a bf16 / f16 buffer reads the 16-bit source itself when nothing else
+    wants the copy (two of the fixture's three sums; the third copy is also a program output and stays). Same
+    values either way: convert to f32 per element, accumulate in f32 (vmreader.py convert + reduce)."""
+    vm = package()
+    g = Golden("reduce_full_16bit_source")
+    for off, want in ((None, 2), ("1", 0)):
+        with monkeypatch.context() as m:
+            if off:
+                m.setenv("B2VM_NO_CONVERT_FOLD", off)
+            lp = vm.LoadedProgram.Load(rt, vm.VmProgram.Parse(g.blob))
+            assert lp.stat("folded_converts") == want
+            check_outputs(g, [np.ascontiguousarray(o).view(np.uint8).reshape(-1) for o in lp.Execute(g.args)], "cuda-fold")
+
+
 def test_point_to_point_entry_fields_are_refused(rt):
     """Tile entries whose reserved wait / signal words are set (scheduler.py:201-209 keeps them
     for point-to-point dependencies and emits "no flag") are refused at load, not ignored."""
