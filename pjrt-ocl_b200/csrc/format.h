@@ -142,6 +142,9 @@ enum TaskFlags : uint32_t {
                         // ranges, ptr[3] is the final result, lane totals meet in KParams::scratch
   kRedSrcBf16 = 1u << 8, // ... and its input is the bf16 (kRedSrcF16: f16) source of the convert that fed it: the
   kRedSrcF16 = 1u << 9,  // f32 copy is never written, each 32-bit word of the stream holds two elements
+  kRowCarrySum = 1u << 10, // SOFTMAX_SEG / LAYERNORM_SEG: also add every value stored to this lane's carry word in the
+                           // scratch (as f32, after rounding to the output type): the full sum that follows reads
+  kRedCarried = 1u << 11,  // ... that word instead of the array (on the kRedFused RED_PART)
 };
 
 // Scratch of a loaded program (KParams::scratch): where the lanes of a re-cut full
@@ -151,7 +154,7 @@ struct RedScratch {
   uint32_t arrived;
   uint32_t pad[3];
   uint32_t work[2 * kMaxWorkSlots];   // {next unit, lanes done} per dynamically distributed task; at rest 0
-  unsigned long long total[1];        // [n_lanes]
+  unsigned long long total[1];        // [n_lanes] lane totals, then [n_lanes] carry words (kRowCarrySum; at rest 0)
 };
 
 struct DTask {

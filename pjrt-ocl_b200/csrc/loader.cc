@@ -1306,12 +1306,13 @@ static bool BuildDeviceTablesFor(const VmProgram &p, uint64_t arena_base, Device
   // before and read by nothing else: the reduction streams the 16-bit source instead (half the bytes) and the
   // convert's phase does nothing. Straight-line programs only (phases counted by barriers in the root walk).
   std::vector<int> half_src(p.tasks.size(), -1);
+  bool straight_line = true;
+  for (const VmEntry &e : p.entries)
+    if (e.task == kEntWhile || e.task == kEntIf || e.task == kEntFor) straight_line = false;
+  std::vector<int> phase_lo(p.tasks.size(), 1 << 30), phase_hi(p.tasks.size(), -1);
   {
-    bool straight = std::getenv("B2VM_NO_CONVERT_FOLD") == nullptr;
-    for (const VmEntry &e : p.entries)
-      if (e.task == kEntWhile || e.task == kEntIf || e.task == kEntFor) straight = false;
-    std::vector<int> phase_lo(p.tasks.size(), 1 << 30), phase_hi(p.tasks.size(), -1);
-    if (straight)
+    const bool straight = straight_line && std::getenv("B2VM_NO_CONVERT_FOLD") == nullptr;
+    if (straight_line)
       for (const VmLane &l : p.lane_tab) {
         int ph = 0;
         for (uint32_t i = 0; i < l.count; ++i) {
@@ -1357,6 +1358,48 @@ static bool BuildDeviceTablesFor(const VmProgram &p, uint64_t arena_base, Device
     }
   }
   SpreadReductions(p, fused_comb, half_src, &c, out);
+  // A full f32 sum (already shared by all lanes) over a buffer that one SOFTMAX_SEG / LAYERNORM_SEG task wrote in an
+  // earlier phase: the row op adds what it stores to its lane's carry word, the sum's lanes read those words and
+  // never stream the buffer. One such pair per program (the lanes have one carry word each). Straight-line only.
+  if (straight_line && std::getenv("B2VM_NO_CARRIED_SUM") == nullptr) {
+    for (size_t ti = 0; ti < p.tasks.size(); ++ti) {
+      const VmTask &tp = p.tasks[ti];
+      DTask &dt_ = out->tasks[ti];
+      if ((tp.tile_op & 0xFFu) != kTopRedPart || !(dt_.flags & kRedFused) || ((tp.tile_op >> 8) & 0xFFu) != kF32 || tp.p2 != kSum) continue;
+      const uint32_t src = half_src[ti] >= 0 ? p.tasks[half_src[ti]].a : tp.a;
+      const uint32_t sdt = half_src[ti] >= 0 ? (p.tasks[half_src[ti]].tile_op >> 16) & 0xFFu : static_cast<uint32_t>(kF32);
+      if (half_src[ti] < 0 && tp.p0 % 4u != 0u) continue;
+      int wr = -1;
+      uint32_t writers = 0;
+      for (size_t k = 0; k < p.tasks.size(); ++k)
+        if (p.tasks[k].dst == src) { ++writers; wr = static_cast<int>(k); }
+      if (writers != 1 || in_ids.count(src) || const_ids.count(src)) continue;
+      const VmTask &wt = p.tasks[wr];
+      const uint32_t wop = wt.tile_op & 0xFFu;
+      if (wop != kTopSoftmaxSeg && wop != kTopLayernormSeg) continue;
+      if (((wt.tile_op >> 8) & 0xFFu) != sdt || static_cast<uint64_t>(wt.p0) * wt.p1 != tp.p0) continue;
+      if (phase_lo[wr] != phase_hi[wr] || phase_lo[ti] != phase_hi[ti] || phase_hi[wr] >= phase_lo[ti]) continue;
+      // every row exactly once, and nothing else may write the buffer's bytes from the row op's phase to the sum's
+      uint64_t rows = 0;
+      for (const DEntry &e : out->entries)
+        if (e.task == static_cast<uint32_t>(wr)) rows += std::min(e.tile_hi, wt.p0) > e.tile_lo ? std::min(e.tile_hi, wt.p0) - e.tile_lo : 0u;
+      if (rows != wt.p0) continue;
+      bool clobbered = false;
+      const BufferSlot &sb = p.buffers[src];
+      for (size_t k = 0; k < p.tasks.size() && !clobbered; ++k) {
+        if (static_cast<int>(k) == wr || phase_hi[k] < phase_lo[wr] || phase_lo[k] > phase_lo[ti]) continue;
+        const BufferSlot &wb = p.buffers[p.tasks[k].dst];
+        if (!c.port_of.count(src) && !c.port_of.count(p.tasks[k].dst) && wb.bytes && sb.bytes &&
+            wb.offset < sb.offset + sb.bytes && sb.offset < wb.offset + wb.bytes)
+          clobbered = true;
+      }
+      if (clobbered) continue;
+      out->tasks[wr].flags |= kRowCarrySum;
+      dt_.flags |= kRedCarried;
+      out->n_carried_sums++;
+      break;
+    }
+  }
   // Dynamic work distribution for tensor-core attention tasks: allowed when the task's
   // entries cover all its query rows, no lane holds more than one of them, and they
   // sit outside the sub-ranges of WHILE / IF entries (where lanes may not all arrive).

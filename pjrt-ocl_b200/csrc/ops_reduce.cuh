@@ -449,10 +449,16 @@ __device__ __forceinline__ void red_full_lane(const Lane &L, const DTask &t, uin
   const uint64_t n = t.p[0];
   RedScratch *sc = reinterpret_cast<RedScratch *>(P.scratch);
   const uint32_t ident = static_cast<uint32_t>(acc_identity(kind, dt).bits);
-  uint32_t total = red_words_lane<C>(L, a, w_lo, w_hi, kind, dt, ident);
+  const bool carried = (t.flags & kRedCarried) != 0u;   // the row op that wrote the input summed it on the way
+  uint32_t total = carried ? ident : red_words_lane<C>(L, a, w_lo, w_hi, kind, dt, ident);
   uint32_t *flag = reinterpret_cast<uint32_t *>(L.smem + kSmemFlag);
+  if (carried) __syncthreads();           // the flag word is the grid barrier's too: everybody has read its verdict
   if (L.tid == 0) {
-    if (L.lane == P.n_lanes - 1u) {       // the elements past the last whole 16-byte word
+    if (carried) {
+      uint32_t *w = reinterpret_cast<uint32_t *>(&sc->total[P.n_lanes + L.lane]);
+      total = *w;
+      *w = 0u;                            // rest state for the next execute
+    } else if (L.lane == P.n_lanes - 1u) {       // the elements past the last whole 16-byte word
       if (t.flags & (kRedSrcBf16 | kRedSrcF16)) {
         for (uint64_t i = (n / 8u) * 8u; i < n; ++i) {
           const uint32_t h = reinterpret_cast<const uint16_t *>(a)[i];

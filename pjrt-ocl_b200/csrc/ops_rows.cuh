@@ -39,6 +39,30 @@ __device__ __forceinline__ float group_reduce(float v, F f, float *slot, int bar
   return r;
 }
 
+// kRowCarrySum: the lane's carry word (an f32 in the scratch, after the lane totals) takes the sum of the
+// values this entry stored. Only this lane ever touches its word; all threads call.
+__device__ __forceinline__ void rows_carry_add(const Lane &L, float v) {
+  const KParams &P = *L.P;
+  v = block_reduce(L, v, [](float a, float c) { return a + c; }, 0.0f);
+  if (L.tid == 0) {
+    RedScratch *sc = reinterpret_cast<RedScratch *>(P.scratch);
+    float *w = reinterpret_cast<float *>(&sc->total[P.n_lanes + L.lane]);
+    *w += v;
+  }
+}
+
+// The same for the paths that do not sum as they store: read the rows back (this lane just wrote them).
+__device__ __forceinline__ void rows_carry_reread(const Lane &L, const DTask &t, uint32_t lo, uint32_t hi) {
+  const uint8_t *dst = resolve(*L.P, t.ptr[0]);
+  const uint32_t seg = t.p[1], dt = t.dt;
+  __threadfence_block();
+  __syncthreads();
+  float s = 0.0f;
+  const uint64_t e_lo = static_cast<uint64_t>(lo) * seg, e_hi = static_cast<uint64_t>(hi) * seg;
+  for (uint64_t i = e_lo + L.tid; i < e_hi; i += L.nthr) s += __uint_as_float(load1(dst, dt, i));
+  rows_carry_add(L, s);
+}
+
 // rows [tile_lo, tile_hi) through the staged pipeline. Preconditions (checked by
 // the caller): seg*esz % 16 == 0, both buffers 16-byte aligned, 2 buffers per group fit.
 __device__ __forceinline__ void rows_staged(const Lane &L, const DTask &t, uint32_t lo, uint32_t hi, bool softmax) {
@@ -67,6 +91,8 @@ __device__ __forceinline__ void rows_staged(const Lane &L, const DTask &t, uint3
 
   uint64_t *bar = bars + gi * kRowMaxBufs;
   float *slot = slots + gi * 4;
+  const bool carry = (t.flags & kRowCarrySum) != 0u;
+  float csum = 0.0f;     // this thread's share of the values it stored (kRowCarrySum)
   const int bid = 1 + static_cast<int>(gi);
   const uint32_t first = lo + gi;
   if (gl == 0) {
@@ -139,6 +165,7 @@ __device__ __forceinline__ void rows_staged(const Lane &L, const DTask &t, uint3
           float4 v = r4[g];
           v.x *= rs; v.y *= rs; v.z *= rs; v.w *= rs;
           o4[g] = v;
+          csum += (v.x + v.y) + (v.z + v.w);
         }
       } else {
         float s = 0.0f, s2 = 0.0f;
@@ -157,6 +184,7 @@ __device__ __forceinline__ void rows_staged(const Lane &L, const DTask &t, uint3
           float4 v = r4[g];
           v.x = (v.x - mu) * rden; v.y = (v.y - mu) * rden; v.z = (v.z - mu) * rden; v.w = (v.w - mu) * rden;
           o4[g] = v;
+          csum += (v.x + v.y) + (v.z + v.w);
         }
       }
     } else if (adt == kBF16 && dt == kBF16 && (seg & 7u) == 0u) {
@@ -172,6 +200,11 @@ __device__ __forceinline__ void rows_staged(const Lane &L, const DTask &t, uint3
       };
       auto pack8 = [](const float (&f)[8]) {
         return make_uint4(cvt_bf16x2(f[1], f[0]), cvt_bf16x2(f[3], f[2]), cvt_bf16x2(f[5], f[4]), cvt_bf16x2(f[7], f[6]));
+      };
+      auto sum8 = [&](const uint4 w) {     // the eight values as stored (rounded to bf16)
+        float f[8];
+        unpack8(w, f);
+        return ((f[0] + f[1]) + (f[2] + f[3])) + ((f[4] + f[5]) + (f[6] + f[7]));
       };
       if (softmax) {
         float m = -INFINITY;
@@ -198,7 +231,9 @@ __device__ __forceinline__ void rows_staged(const Lane &L, const DTask &t, uint3
           unpack8(r8[g], f);
 #pragma unroll
           for (int e = 0; e < 8; ++e) f[e] = fast_ex2(fmaf(f[e], kLog2e, -mb)) * rs;
-          o8[g] = pack8(f);
+          const uint4 w = pack8(f);
+          o8[g] = w;
+          if (carry) csum += sum8(w);
         }
       } else {
         float sum = 0.0f, s2 = 0.0f;
@@ -219,7 +254,9 @@ __device__ __forceinline__ void rows_staged(const Lane &L, const DTask &t, uint3
           unpack8(r8[g], f);
 #pragma unroll
           for (int e = 0; e < 8; ++e) f[e] = (f[e] - mu) * rden;
-          o8[g] = pack8(f);
+          const uint4 w = pack8(f);
+          o8[g] = w;
+          if (carry) csum += sum8(w);
         }
       }
     } else if (softmax) {
@@ -291,6 +328,10 @@ __device__ __forceinline__ void rows_staged(const Lane &L, const DTask &t, uint3
   if (L.tid == 0)
     for (uint32_t i = 0; i < ngroups * kRowMaxBufs; ++i) mbar_inval(&bars[i]);
   __syncthreads();
+  if (carry) {
+    if ((adt == kF32 && dt == kF32) || (adt == kBF16 && dt == kBF16 && (seg & 7u) == 0u)) rows_carry_add(L, csum);
+    else rows_carry_reread(L, t, lo, hi);
+  }
 }
 
 // warp per row; re-reads the row (L1/L2) instead of staging it.
@@ -345,8 +386,12 @@ static __device__ __noinline__ void rows_tiles(const Lane &L, const DTask &t, ui
                       seg >= 1024 && seg % 4 == 0 && in_bytes % 16 == 0 && dt_size(t.adt) <= 4 && dt_size(t.dt) <= 4 &&
                       reinterpret_cast<uintptr_t>(src) % 16 == 0 && reinterpret_cast<uintptr_t>(dst) % 16 == 0 &&
                       static_cast<size_t>(kSmemSys) + kRowHdr + static_cast<size_t>(ngroups) * 2 * buf_stride <= L.smem_bytes;
-  if (staged) rows_staged(L, t, tile_lo, hi, softmax);
-  else rows_generic(L, t, tile_lo, hi, softmax);
+  if (staged) {
+    rows_staged(L, t, tile_lo, hi, softmax);
+  } else {
+    rows_generic(L, t, tile_lo, hi, softmax);
+    if (t.flags & kRowCarrySum) rows_carry_reread(L, t, tile_lo, hi);
+  }
 }
 
 }  // namespace b2

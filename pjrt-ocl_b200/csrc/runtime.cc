@@ -528,7 +528,7 @@ b2_status b2_program_load(b2_runtime *rt, b2_program *prog, b2_loaded **out, cha
   }
   std::memset(lp->h_sync, 0, sizeof(b2::DSync));
   if (lp->tab.needs_scratch) {
-    lp->scratch_bytes = sizeof(b2::RedScratch) + sizeof(unsigned long long) * p.n_lanes;   // zero = rest state of every counter
+    lp->scratch_bytes = sizeof(b2::RedScratch) + sizeof(unsigned long long) * 2u * p.n_lanes;   // zero = rest state of every counter
     if ((e = cudaMalloc(reinterpret_cast<void **>(&lp->d_scratch), lp->scratch_bytes)) != cudaSuccess ||
         (e = cudaMemset(lp->d_scratch, 0, lp->scratch_bytes)) != cudaSuccess) {
       SetErr(err, err_cap, CudaMsg("reduction scratch allocation", e));
@@ -578,6 +578,7 @@ uint64_t b2_loaded_stat(const b2_loaded *lp, int which) {
     case 14: return lp->tab.n_rebalanced;
     case 15: return lp->tab.n_row_pipelines;
     case 16: return lp->tab.n_folded_converts;
+    case 17: return lp->tab.n_carried_sums;
     case 13: return static_cast<uint64_t>(std::count_if(lp->tab.inout_result.begin(), lp->tab.inout_result.end(), [](int o) { return o >= 0; }));
     default: return 0;
   }

@@ -373,6 +373,41 @@ def _():
     return blob, prog, (23, [N((n,), "bf16"), N((n,), "f16"), N((n,), "bf16")])
 
 
+@case("rows_then_full_sum_f32", rtol=1e-5, atol=1e-4)
+def _():
+    """Softmax rows, then the sum of everything it wrote; the rows are a program output too. The backend may
+    let the row op carry the sum instead of streaming the rows again."""
+    a = Asm()
+    x = a.input((72, 1024), F32)
+    sm = a.softmax_fused(x)
+    blob, prog = a.finish([sm, a.reduce(sm, [0, 1], SUM)], nlanes=5)
+    return blob, prog, (29, [N((72, 1024), "f32", 2.0, 0.5)])
+
+
+@case("rows_then_full_sum_bf16", rtol=0.3, atol=2e-2)
+def _():
+    """The same through 16-bit storage: layer norm and softmax in bf16, up-cast, full sum; neither the rows nor
+    their f32 copy leave the program. The validators' numpy bodies add a bf16 row up in bf16 (reduce.py:464-475
+    applied to bf16 arrays), so their softmax rows sum to about 1.25 where f32 accumulation gives 1: this fixture
+    pins the total only that loosely, and the GPU tests compare the carried total with the streamed one."""
+    a = Asm()
+    x = a.input((72, 1024), BF16)
+    g = a.input((72, 1024), BF16)
+    ln = a.layernorm_fused(x, 1e-5)
+    total = a.reduce(a.convert(a.softmax_fused(a.add(ln, g)), F32), [0, 1], SUM)
+    blob, prog = a.finish([total], nlanes=5)
+    return blob, prog, (31, [N((72, 1024), "bf16", 2.0, 0.5), N((72, 1024), "bf16")])
+
+
+@case("rows_then_full_sum_ragged", rtol=1e-5, atol=1e-4)
+def _():
+    """Rows too short for the staged path (100 elements), summed afterwards."""
+    a = Asm()
+    x = a.input((700, 100), F32)
+    blob, prog = a.finish([a.reduce(a.softmax_fused(x), [0, 1], SUM)], nlanes=5)
+    return blob, prog, (37, [N((700, 100), "f32", 2.0, 0.5)])
+
+
 @case("reduce_full_int", exact=True)
 def _():
     a = Asm()

@@ -148,6 +148,30 @@ def test_convert_feeding_a_full_sum_is_folded(rt, monkeypatch):
             check_outputs(g, [np.ascontiguousarray(o).view(np.uint8).reshape(-1) for o in lp.Execute(g.args)], "cuda-fold")
 
 
+@pytest.mark.parametrize("name,folds", [("rows_then_full_sum_f32", 0), ("rows_then_full_sum_bf16", 1), ("rows_then_full_sum_ragged", 0)])
+def test_full_sum_carried_by_the_row_op(rt, monkeypatch, name, folds):
+    """A full sum over what one softmax / layer-norm task wrote is taken from that task (each lane adds what it
+    stores to its carry word) instead of streaming the rows again: same total as the streamed sum to f32
+    summation-order accuracy, on the staged f32 and bf16 paths and on the short-row path, and again on a second
+    execute (the carry words return to zero)."""
+    vm = package()
+    g = Golden(name)
+    totals = {}
+    for off in (None, "1"):
+        with monkeypatch.context() as m:
+            if off:
+                m.setenv("B2VM_NO_CARRIED_SUM", off)
+            lp = vm.LoadedProgram.Load(rt, vm.VmProgram.Parse(g.blob))
+            assert lp.stat("carried_sums") == (0 if off else 1)
+            assert lp.stat("folded_converts") == folds
+            first = lp.Execute(g.args)
+            check_outputs(g, [np.ascontiguousarray(o).view(np.uint8).reshape(-1) for o in first], "cuda-carried")
+            second = lp.Execute(g.args)
+            totals[off] = [float(np.asarray(o[-1]).reshape(-1)[0]) for o in (first, second)]
+    assert totals[None][0] == totals[None][1]
+    np.testing.assert_allclose(totals[None][0], totals["1"][0], rtol=1e-5)
+
+
 def test_point_to_point_entry_fields_are_refused(rt):
     """Tile entries whose reserved wait / signal words are set (scheduler.py:201-209 keeps them
     for point-to-point dependencies and emits "no flag") are refused at load, not ignored."""
