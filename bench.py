@@ -66,7 +66,7 @@ WORKLOADS = {
     "c2_f32": _wl("c2_chain_f32", "eltwise HBM GB/s", "GB/s", 7 * N_C2 * 4 + 2 * 4096 * 4, 1e9, "hbm", "f32",
                   "config 2: LayerNorm -> tanh-GELU -> softmax -> full sum on f32 (8192,4096); "
                   "bytes = LayerNorm r+w, GELU r+w, softmax r+w, sum r, + gamma/beta",
-                  sample="c2_chain_f32_cpu_sample", sample_frac=512 / 8192, traffic=940.7e6,
+                  sample="c2_chain_f32_cpu_sample", sample_frac=512 / 8192, traffic=778.3e6,
                   sample_what="512 of the 8192 rows"),
     "c2_bf16": _wl("c2_chain_bf16", "eltwise HBM GB/s", "GB/s", 7 * N_C2 * 2 + 2 * 4096 * 2, 1e9, "hbm", "bf16",
                    "config 2 on bf16-storage copies of the same values",

@@ -158,7 +158,8 @@ uint64_t b2_loaded_launch_count(const b2_loaded *lp);
  * 15 groups of neighbouring row-local phases (row norms and elementwise chains over
  * the same rows) run as one pipeline per lane with the barriers between them removed,
  * 16 converts from a 16-bit dtype to f32 folded into the full sum that follows them,
- * 17 full sums taken from the row op (softmax / layer norm) that wrote their input.
+ * 17 full sums taken from the row op (softmax / layer norm) that wrote their input,
+ * 18 grid barriers between such a row op and its sum that were dropped (they ordered nothing any more).
  * Unknown `which` returns 0. */
 uint64_t b2_loaded_stat(const b2_loaded *lp, int which);
 /* Per-wait budget of device-side bounded waits, in nanoseconds (default 2e9). */

@@ -1397,6 +1397,33 @@ static bool BuildDeviceTablesFor(const VmProgram &p, uint64_t arena_base, Device
       out->tasks[wr].flags |= kRowCarrySum;
       dt_.flags |= kRedCarried;
       out->n_carried_sums++;
+      // A lane's share of the sum is now its own carry word, and the lanes' totals meet through the arrival counter:
+      // when the phases after the row op's up to the sum's hold nothing but the sum, and no other shared reduction
+      // runs beside the row op (one arrival counter), the barriers in between order nothing and go.
+      const int pw = phase_lo[wr], pt = phase_lo[ti];
+      bool alone = true;
+      for (const VmLane &l : out->lanes) {
+        int ph = 0;
+        for (uint32_t i = l.off; i < l.off + l.count && alone; ++i) {
+          const DEntry &e = out->entries[i];
+          if (e.task == kEntBarrier) { ++ph; continue; }
+          if (e.task == kEntNop || e.task >= out->tasks.size() || ph < pw || ph > pt) continue;
+          if (e.task == static_cast<uint32_t>(ti)) continue;
+          if (ph > pw || (out->tasks[e.task].flags & kRedFused && (p.tasks[e.task].tile_op & 0xFFu) == kTopRedPart)) alone = false;
+        }
+      }
+      if (alone) {
+        for (const VmLane &l : out->lanes) {
+          int ph = 0;
+          for (uint32_t i = l.off; i < l.off + l.count; ++i) {
+            DEntry &e = out->entries[i];
+            if (e.task != kEntBarrier) continue;
+            if (ph >= pw && ph < pt) e.task = kEntNop;
+            ++ph;
+          }
+        }
+        out->n_carried_barriers_removed += static_cast<uint32_t>(pt - pw);
+      }
       break;
     }
   }

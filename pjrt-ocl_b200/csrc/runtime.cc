@@ -579,6 +579,7 @@ uint64_t b2_loaded_stat(const b2_loaded *lp, int which) {
     case 15: return lp->tab.n_row_pipelines;
     case 16: return lp->tab.n_folded_converts;
     case 17: return lp->tab.n_carried_sums;
+    case 18: return lp->tab.n_carried_barriers_removed;
     case 13: return static_cast<uint64_t>(std::count_if(lp->tab.inout_result.begin(), lp->tab.inout_result.end(), [](int o) { return o >= 0; }));
     default: return 0;
   }

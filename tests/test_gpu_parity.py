@@ -130,7 +130,9 @@ def test_row_local_phases_run_as_one_pipeline(rt, monkeypatch):
         lp = vm.LoadedProgram.Load(rt, vm.VmProgram.Parse(g.blob))
         assert lp.stat("row_pipelines") == 1
         check_outputs(g, [np.ascontiguousarray(o).view(np.uint8).reshape(-1) for o in lp.Execute(g.args)], "cuda-rows")
-        assert lp.Status()["barriers"] == 2       # 4 phases -> the pipeline, the sum (its combine folded in)
+        # 4 phases -> one: the pipeline, whose softmax also carries the sum (so the barrier before the sum goes too)
+        assert lp.stat("carried_sums") == 1 and lp.stat("carried_barriers_removed") == 1
+        assert lp.Status()["barriers"] == 1
 
 
 def test_convert_feeding_a_full_sum_is_folded(rt, monkeypatch):
@@ -163,6 +165,7 @@ def test_full_sum_carried_by_the_row_op(rt, monkeypatch, name, folds):
                 m.setenv("B2VM_NO_CARRIED_SUM", off)
             lp = vm.LoadedProgram.Load(rt, vm.VmProgram.Parse(g.blob))
             assert lp.stat("carried_sums") == (0 if off else 1)
+            assert lp.stat("carried_barriers_removed") == (0 if off else 1 + folds)   # the folded convert's empty phase goes too
             assert lp.stat("folded_converts") == folds
             first = lp.Execute(g.args)
             check_outputs(g, [np.ascontiguousarray(o).view(np.uint8).reshape(-1) for o in first], "cuda-carried")
