@@ -159,7 +159,9 @@ uint64_t b2_loaded_launch_count(const b2_loaded *lp);
  * the same rows) run as one pipeline per lane with the barriers between them removed,
  * 16 converts from a 16-bit dtype to f32 folded into the full sum that follows them,
  * 17 full sums taken from the row op (softmax / layer norm) that wrote their input,
- * 18 grid barriers between such a row op and its sum that were dropped (they ordered nothing any more).
+ * 18 grid barriers between such a row op and its sum that were dropped (they ordered nothing any more),
+ * 19 decomposed RMS norms over bf16 rows (convert, square, row sum, scalar region, two broadcast multiplies,
+ * convert) run as one row op, 20 barriers dropped because the phase they closed holds nothing after that.
  * Unknown `which` returns 0. */
 uint64_t b2_loaded_stat(const b2_loaded *lp, int which);
 /* Per-wait budget of device-side bounded waits, in nanoseconds (default 2e9). */

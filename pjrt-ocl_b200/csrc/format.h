@@ -31,7 +31,10 @@ enum TileOp : uint32_t {
   kTopEw = 0, kTopMma, kTopGather, kTopRedPart, kTopRedComb, kTopIotaDim, kTopScatter,
   kTopDynGather, kTopDynScatter, kTopRedWindow, kTopRedSeg, kTopSoftmaxSeg, kTopLayernormSeg,
   kTopMapRegion, kTopFlashAttn, kTopRedStrided, kTopGatherIndex, kTopConv, kTopScatterIndex,
-  kTopMax = kTopScatterIndex
+  kTopMax = kTopScatterIndex,
+  // Not on the wire: the loader's own row op for a recognised RMS-norm idiom over bf16 rows (convert, square, row sum,
+  // per-row scalar region, two broadcast multiplies, convert back), see rms_rows_tiles.
+  kTopRmsRows = 32
 };
 
 // Tile-op families: the unit in which code is compiled into a build of the
@@ -54,7 +57,7 @@ B2_HOST_DEVICE inline uint32_t family_of(uint32_t tile_op) {
     case kTopEw: return kFamEw;
     case kTopGather: case kTopScatter: case kTopDynGather: case kTopDynScatter: case kTopIotaDim: return kFamMove;
     case kTopRedPart: case kTopRedComb: case kTopRedSeg: case kTopRedStrided: return kFamRed;
-    case kTopSoftmaxSeg: case kTopLayernormSeg: return kFamRows;
+    case kTopSoftmaxSeg: case kTopLayernormSeg: case kTopRmsRows: return kFamRows;
     case kTopMapRegion: return kFamRegion;
     case kTopMma: return kFamMma;
     case kTopFlashAttn: return kFamFlash;

@@ -237,6 +237,26 @@ void LaneRuns(const VmProgram &p, const VmLane &l, std::vector<StreamRun> *runs)
 // of 16-byte words (DEntry::a, b), leaves its total in the program's scratch, and
 // the lane that arrives last folds the lanes' totals in lane order into the
 // RED_COMB's result; the RED_COMB entry becomes a NOP.
+// After entries of a chain were turned into no-ops: the chain closes up over the gaps, live members first, the
+// count on the new head.
+void CompactChains(DeviceTables *out) {
+  for (const VmLane &l : out->lanes)
+    for (uint32_t i = l.off; i < l.off + l.count; ++i) {
+      const uint32_t n = out->entries[i].chain;
+      if (n <= 1u) continue;
+      uint32_t live = 0;
+      for (uint32_t k = i; k < i + n; ++k)
+        if (out->entries[k].task != kEntNop) {
+          DEntry m = out->entries[k];
+          out->entries[k].task = kEntNop;
+          out->entries[i + live++] = m;
+        }
+      for (uint32_t k = i; k < i + n; ++k) out->entries[k].chain = 0u;
+      if (live) out->entries[i].chain = live;
+      i += n - 1u;
+    }
+}
+
 void SpreadReductions(const VmProgram &p, const std::vector<int> &fused_comb, const std::vector<int> &half_src, Ctx *cx,
                       DeviceTables *out) {
   const uint32_t n_lanes = static_cast<uint32_t>(p.lane_tab.size());
@@ -317,22 +337,7 @@ void SpreadReductions(const VmProgram &p, const std::vector<int> &fused_comb, co
         dp.flags |= ((cv.tile_op >> 16) & 0xFFu) == kBF16 ? kRedSrcBf16 : kRedSrcF16;
         for (DEntry &e : out->entries)
           if (e.task == static_cast<uint32_t>(half_src[task])) e.task = kEntNop;
-        // chains the convert sat in close up over the gap: live members first, the count on the new head
-        for (const VmLane &l : out->lanes)
-          for (uint32_t i = l.off; i < l.off + l.count; ++i) {
-            const uint32_t n = out->entries[i].chain;
-            if (n <= 1u) continue;
-            uint32_t live = 0;
-            for (uint32_t k = i; k < i + n; ++k)
-              if (out->entries[k].task != kEntNop) {
-                DEntry m = out->entries[k];
-                out->entries[k].task = kEntNop;
-                out->entries[i + live++] = m;
-              }
-            for (uint32_t k = i; k < i + n; ++k) out->entries[k].chain = 0u;
-            if (live) out->entries[i].chain = live;
-            i += n - 1u;
-          }
+        CompactChains(out);
         out->n_folded_converts++;
       }
       for (DEntry &e : out->entries)
@@ -1425,6 +1430,144 @@ static bool BuildDeviceTablesFor(const VmProgram &p, uint64_t arena_base, Device
         out->n_carried_barriers_removed += static_cast<uint32_t>(pt - pw);
       }
       break;
+    }
+  }
+  // The decomposed RMS norm over bf16 rows - convert to f32, square, RED_SEG row sums, a MAP_REGION on the row sums,
+  // multiply by the broadcast row scalar, multiply by the broadcast f32 gain, convert to bf16 - becomes one row op
+  // on the last convert's entries (rms_rows_tiles); the six other tasks' entries leave the stream. Every
+  // intermediate must be read by the idiom alone. Straight-line programs only.
+  if (straight_line && std::getenv("B2VM_NO_RMS_FUSION") == nullptr) {
+    auto sole_writer = [&](uint32_t id) {
+      int w = -1;
+      for (size_t k = 0; k < p.tasks.size(); ++k)
+        if (p.tasks[k].dst == id) { if (w >= 0) return -1; w = static_cast<int>(k); }
+      return w;
+    };
+    auto scratch_only = [&](uint32_t id, std::initializer_list<uint32_t> want) {
+      if (pinned.count(id) || in_ids.count(id) || out_ids.count(id) || const_ids.count(id)) return false;
+      return readers[id] == std::set<uint32_t>(want);
+    };
+    auto is_ew = [&](const VmTask &t, uint32_t subop, uint32_t dt, uint32_t adt) {
+      return (t.tile_op & 0xFFu) == kTopEw && t.p0 == subop && ((t.tile_op >> 8) & 0xFFu) == dt && ((t.tile_op >> 16) & 0xFFu) == adt;
+    };
+    // view descriptor (rank, dims, strides, offset) of a [rows, d] broadcast with the given strides
+    auto is_broadcast = [&](uint32_t field, int64_t rows, int64_t d, int64_t s0, int64_t s1) {
+      if (!field) return false;
+      const size_t x = field - 1;
+      if (x + 6 > p.aux.size()) return false;
+      return p.aux[x] == 2 && p.aux[x + 1] == rows && p.aux[x + 2] == d && p.aux[x + 3] == s0 && p.aux[x + 4] == s1 && p.aux[x + 5] == 0;
+    };
+    bool any = false;
+    for (size_t cvi = 0; cvi < p.tasks.size(); ++cvi) {
+      const VmTask &cv = p.tasks[cvi];
+      if (!is_ew(cv, kConvert, kBF16, kF32) || cv.p2 != 0u) continue;
+      const int m2i = sole_writer(cv.a);
+      if (m2i < 0) continue;
+      const VmTask &m2 = p.tasks[m2i];
+      if (!is_ew(m2, kMul, kF32, kF32) || m2.p2 != 0u || m2.p1 != cv.p1) continue;
+      const int m1i = sole_writer(m2.a);
+      if (m1i < 0) continue;
+      const VmTask &m1 = p.tasks[m1i];
+      if (!is_ew(m1, kMul, kF32, kF32) || m1.p2 != 0u || m1.p1 != cv.p1) continue;
+      const int ci = sole_writer(m1.a), gi = sole_writer(m1.b);
+      if (ci < 0 || gi < 0) continue;
+      const VmTask &cx = p.tasks[ci], &gr = p.tasks[gi];
+      if (!is_ew(cx, kConvert, kF32, kBF16) || cx.p2 != 0u || cx.p1 != cv.p1) continue;
+      if ((gr.tile_op & 0xFFu) != kTopMapRegion || ((gr.tile_op >> 8) & 0xFFu) != kF32 || ((gr.tile_op >> 16) & 0xFFu) != kF32) continue;
+      const int64_t rows = gr.p1, d = rows ? static_cast<int64_t>(cv.p1) / rows : 0;
+      if (rows <= 0 || rows * d != static_cast<int64_t>(cv.p1) || d % 256 != 0 || d > 2048 || kEwTs % d != 0) continue;
+      if (!is_broadcast(m1.p3, rows, d, 1, 0) || !is_broadcast(m2.p3, rows, d, 0, 1)) continue;
+      const int ri = sole_writer(gr.a);
+      if (ri < 0) continue;
+      const VmTask &rd = p.tasks[ri];
+      if ((rd.tile_op & 0xFFu) != kTopRedSeg || ((rd.tile_op >> 8) & 0xFFu) != kF32 || rd.p0 != rows || rd.p1 != d || rd.p2 != kSum) continue;
+      // every input of the region is the row sum
+      const size_t gx = gr.p0;
+      if (gx + 3 > p.aux.size() || p.aux[gx] < 1 || p.aux[gx] > 8 || p.aux[gx + 2] < 0 ||
+          gx + 3 + static_cast<size_t>(p.aux[gx]) + 6u * static_cast<size_t>(p.aux[gx + 2]) > p.aux.size())
+        continue;
+      const uint32_t gin[8] = {gr.a, gr.b, gr.p2, gr.p3, gr.p4, gr.p5, gr.p6, gr.p7};
+      bool same = true;
+      for (int k = 0; k < p.aux[gx]; ++k) same = same && gin[k] == rd.dst;
+      if (!same) continue;
+      const int si = sole_writer(rd.a);
+      if (si < 0) continue;
+      const VmTask &sq = p.tasks[si];
+      if (!is_ew(sq, kMul, kF32, kF32) || sq.p2 != 0u || sq.p3 != 0u || sq.a != cx.dst || sq.b != cx.dst || sq.p1 != cv.p1) continue;
+      const uint32_t U = static_cast<uint32_t>(cvi), M2 = static_cast<uint32_t>(m2i), M1 = static_cast<uint32_t>(m1i), C = static_cast<uint32_t>(ci),
+                     G = static_cast<uint32_t>(gi), R = static_cast<uint32_t>(ri), S = static_cast<uint32_t>(si);
+      if (!scratch_only(cv.a, {U}) || !scratch_only(m2.a, {M2}) || !scratch_only(cx.dst, {S, M1}) || !scratch_only(gr.dst, {M1}) ||
+          !scratch_only(rd.dst, {G}) || !scratch_only(sq.dst, {R}))
+        continue;
+      // x and the gain are read in the last convert's phase now: both written before it, x in memory (not a value a
+      // chain only hands on in registers), neither's bytes written from their old readers' phases to that one
+      const uint32_t xid = cx.a, gid = m2.b;
+      const int pu = phase_lo[cvi];
+      if (phase_lo[cvi] != phase_hi[cvi] || !c.Aligned16(xid) || !c.Aligned16(gid) || !c.Aligned16(cv.dst)) continue;
+      bool safe = true;
+      for (uint32_t id : {xid, gid}) {
+        const int first_read = id == xid ? phase_lo[ci] : phase_lo[m2i];
+        for (size_t k = 0; k < p.tasks.size() && safe; ++k) {
+          if (phase_hi[k] < 0) continue;
+          if (p.tasks[k].dst == id) {      // its writer: a whole phase earlier than the row op, and storing
+            if (phase_hi[k] >= pu || (out->tasks[k].flags & kDeadStore)) safe = false;
+            continue;
+          }
+          if (phase_hi[k] < first_read || phase_lo[k] > pu || c.port_of.count(id) || c.port_of.count(p.tasks[k].dst)) continue;
+          const BufferSlot &wb = p.buffers[p.tasks[k].dst], &sb = p.buffers[id];
+          if (wb.bytes && sb.bytes && wb.offset < sb.offset + sb.bytes && sb.offset < wb.offset + wb.bytes) safe = false;
+        }
+      }
+      // the result's bytes may not be anything the idiom still had to read when the convert ran: it is written in
+      // the same phase as before, so that holds as it did.
+      if (!safe) continue;
+      uint64_t covered = 0;
+      for (const DEntry &e : out->entries)
+        if (e.task == U) covered += e.tile_hi > e.tile_lo ? e.tile_hi - e.tile_lo : 0u;
+      if (covered != (static_cast<uint64_t>(cv.p1) + kEwTs - 1) / kEwTs) continue;
+      DTask &du = out->tasks[cvi];
+      du.op = kTopRmsRows;
+      du.flags = 0u;
+      du.desc = 0u;
+      du.ptr[1] = c.Ref(xid);
+      du.ptr[2] = c.Ref(gid);
+      std::memset(du.p, 0, sizeof(du.p));
+      du.p[0] = static_cast<uint32_t>(rows);
+      du.p[1] = static_cast<uint32_t>(d);
+      du.p[2] = gr.p0;
+      du.adt = kBF16;
+      for (DEntry &e : out->entries)
+        if (e.task == M2 || e.task == M1 || e.task == C || e.task == G || e.task == R || e.task == S) e.task = kEntNop;
+      // a task that forwarded into one of these in a chain stores its result again
+      for (size_t k = 0; k < p.tasks.size(); ++k)
+        if (succ[k] == ci || succ[k] == m1i || succ[k] == m2i || succ[k] == si) out->tasks[k].flags &= ~kDeadStore;
+      out->families |= kFamRows;
+      out->n_rms_rows++;
+      any = true;
+    }
+    if (any) {
+      CompactChains(out);
+      // phases that hold nothing any more lose the barrier that closed them
+      const uint32_t n_bar = [&] { uint32_t n = 0; const VmLane &l = out->lanes[0];
+                                   for (uint32_t i = l.off; i < l.off + l.count; ++i) n += out->entries[i].task == kEntBarrier; return n; }();
+      std::vector<char> busy(n_bar + 1, 0);
+      for (const VmLane &l : out->lanes) {
+        uint32_t ph = 0;
+        for (uint32_t i = l.off; i < l.off + l.count; ++i) {
+          const uint32_t tk = out->entries[i].task;
+          if (tk == kEntBarrier) { ++ph; continue; }
+          if (tk != kEntNop && ph <= n_bar) busy[ph] = 1;
+        }
+      }
+      for (const VmLane &l : out->lanes) {
+        uint32_t ph = 0;
+        for (uint32_t i = l.off; i < l.off + l.count; ++i) {
+          if (out->entries[i].task != kEntBarrier) continue;
+          if (ph <= n_bar && !busy[ph]) out->entries[i].task = kEntNop;
+          ++ph;
+        }
+      }
+      for (uint32_t ph = 0; ph < n_bar; ++ph) out->n_empty_phases_dropped += busy[ph] ? 0u : 1u;
     }
   }
   // Dynamic work distribution for tensor-core attention tasks: allowed when the task's

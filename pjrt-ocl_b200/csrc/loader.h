@@ -56,6 +56,8 @@ struct DeviceTables {
   uint32_t n_rebalanced = 0;            // phases whose units were re-cut evenly over all lanes
   uint32_t n_carried_sums = 0;          // full sums whose input the row op that wrote it summed on the way (kRowCarrySum)
   uint32_t n_carried_barriers_removed = 0;   // barriers between such a row op and its sum that ordered nothing any more
+  uint32_t n_rms_rows = 0;              // decomposed RMS norms over bf16 rows run as one row op
+  uint32_t n_empty_phases_dropped = 0;  // barriers closing phases that hold nothing after such a rewrite
   uint32_t n_folded_converts = 0;       // 16-bit -> f32 converts folded into the full reduction that follows them
   uint32_t n_row_pipelines = 0;         // groups of neighbouring row-local phases run as one pipeline per lane, barriers removed
   uint32_t n_spread = 0;                // reduction phases re-cut over all lanes

@@ -435,14 +435,34 @@ static __device__ __noinline__ bool mma_tc_tiles(const Lane &L, const DTask &t, 
         for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[j]);
         if (r < M && c < N) {
           const int64_t ncols = min(static_cast<int64_t>(32), N - c);
+          // v[] and y[] are only ever indexed by constants, so they stay in registers; the rare paths that walk
+          // columns in a rolled loop do it on copies of their own (which live in local memory).
           if (epi_generic) {
+            float tv[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) tv[j] = v[j];
 #pragma unroll 1
             for (int j = 0; j < 32; ++j)
-              if (j < ncols) v[j] = mma_epilogue(P, t, res, v[j], g, r, c + j, M, N);
+              if (j < ncols) tv[j] = mma_epilogue(P, t, res, tv[j], g, r, c + j, M, N);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = tv[j];
           }
 #pragma unroll
           for (int mi = 0; mi < kEpiMax; ++mi) {
             if (mi >= epi_n) break;
+            const float es = epi_s[mi], et = epi_t[mi];
+            const uint32_t kind = epi_kind[mi];
+            // one-operand micro-ops never materialise a second operand (32 more live registers)
+            if (kind == kGelu) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] = gelu_tanh(v[j]);
+              continue;
+            }
+            if (kind == kAffine) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] = affine2(v[j], es, et);
+              continue;
+            }
             float y[32];
             if (epi_src[mi]) {      // 1: the residual's element, 2: the per-column vector's
               const int64_t yi = epi_src[mi] == 1u ? (g * M + r) * N + c : c;
@@ -463,25 +483,31 @@ static __device__ __noinline__ bool mma_tc_tiles(const Lane &L, const DTask &t, 
                   }
                 }
               } else {
+                float ty[32];
 #pragma unroll 1
-                for (int j = 0; j < 32; ++j) y[j] = j < ncols ? loadf(res, cdt, yi + j) : 0.0f;
+                for (int j = 0; j < 32; ++j) ty[j] = j < ncols ? loadf(res, cdt, yi + j) : 0.0f;
+#pragma unroll
+                for (int j = 0; j < 32; ++j) y[j] = ty[j];
               }
             } else {
 #pragma unroll
               for (int j = 0; j < 32; ++j) y[j] = v[j];
             }
-            const float es = epi_s[mi], et = epi_t[mi];
-            switch (epi_kind[mi]) {     // one dispatch, the 32 evaluations inside
+            switch (kind) {     // one dispatch, the 32 evaluations inside
               case kAdd: _Pragma("unroll") for (int j = 0; j < 32; ++j) v[j] = __fadd_rn(v[j], y[j]); break;
               case kMul: _Pragma("unroll") for (int j = 0; j < 32; ++j) v[j] = __fmul_rn(v[j], y[j]); break;
               case kSubt: _Pragma("unroll") for (int j = 0; j < 32; ++j) v[j] = __fsub_rn(v[j], y[j]); break;
               case kMax: _Pragma("unroll") for (int j = 0; j < 32; ++j) v[j] = np_max(v[j], y[j]); break;
-              case kGelu: _Pragma("unroll") for (int j = 0; j < 32; ++j) v[j] = gelu_tanh(v[j]); break;
-              case kAffine: _Pragma("unroll") for (int j = 0; j < 32; ++j) v[j] = affine2(v[j], es, et); break;
-              default:
+              default: {
+                float tv[32], ty[32];
+#pragma unroll
+                for (int j = 0; j < 32; ++j) { tv[j] = v[j]; ty[j] = y[j]; }
 #pragma unroll 1
-                for (int j = 0; j < 32; ++j) v[j] = micro_alu(epi_kind[mi], v[j], y[j], es, et);
+                for (int j = 0; j < 32; ++j) tv[j] = micro_alu(kind, tv[j], ty[j], es, et);
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] = tv[j];
                 break;
+              }
             }
           }
           if (!(coalesce && c + 32 <= N)) tc_store_row32(dst, dt, (g * M + r) * N + c, v, ncols, vec_store);

@@ -580,6 +580,8 @@ uint64_t b2_loaded_stat(const b2_loaded *lp, int which) {
     case 16: return lp->tab.n_folded_converts;
     case 17: return lp->tab.n_carried_sums;
     case 18: return lp->tab.n_carried_barriers_removed;
+    case 19: return lp->tab.n_rms_rows;
+    case 20: return lp->tab.n_empty_phases_dropped;
     case 13: return static_cast<uint64_t>(std::count_if(lp->tab.inout_result.begin(), lp->tab.inout_result.end(), [](int o) { return o >= 0; }));
     default: return 0;
   }

@@ -136,6 +136,7 @@ __device__ __forceinline__ void exec_entry(const Lane &L, const DEntry &en) {
 #if B2_HAS(0x08u)
     case kTopSoftmaxSeg: rows_tiles(L, t, en.tile_lo, en.tile_hi, true); break;
     case kTopLayernormSeg: rows_tiles(L, t, en.tile_lo, en.tile_hi, false); break;
+    case kTopRmsRows: rms_rows_tiles(L, t, en.tile_lo, en.tile_hi); break;
 #endif
 #if B2_HAS(0x10u)
     case kTopMapRegion: region_tiles(L, t, en.tile_lo, en.tile_hi); break;

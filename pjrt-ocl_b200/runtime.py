@@ -411,7 +411,8 @@ class LoadedProgram:
     _STATS = {"chains": 0, "forwarded": 0 + 1, "dead_stores": 2, "matmuls": 3, "tensor_core_matmuls": 4,
               "matmul_flops": 5, "flash": 6, "tensor_core_flash": 7, "spread_reductions": 8,
               "kernel_build": 9, "families": 10, "fused_full_reductions": 11, "decode_flash": 12,
-              "in_out_ports": 13, "rebalanced_phases": 14, "row_pipelines": 15, "folded_converts": 16, "carried_sums": 17, "carried_barriers_removed": 18}
+              "in_out_ports": 13, "rebalanced_phases": 14, "row_pipelines": 15, "folded_converts": 16, "carried_sums": 17, "carried_barriers_removed": 18, "rms_rows": 19,
+              "empty_phases_dropped": 20}
 
     def stat(self, name: str) -> int:
         """Load-time mapping facts, by name (see `_STATS`)."""

@@ -408,6 +408,23 @@ def _():
     return blob, prog, (37, [N((700, 100), "f32", 2.0, 0.5)])
 
 
+@case("rmsnorm_rows_bf16", rtol=2e-2, atol=2e-2)
+def _():
+    """The decomposed RMS norm of the decoder block (cases._rmsnorm: f32 statistics, bf16 in and out) on rows of
+    1024 and of 256 elements, the second one fed by an add the way the block's residual feeds its second norm.
+    The backend may run each as one row op."""
+    a = Asm()
+    x = a.input((96, 1024), BF16)
+    g = a.input((1024,), BF16)
+    r = a.input((100, 256), BF16)
+    s = a.input((100, 256), BF16)
+    g2 = a.input((256,), BF16)
+    x1 = a.add(r, s)
+    blob, prog = a.finish([cases._rmsnorm(a, x, g, 1e-6), cases._rmsnorm(a, x1, g2, 1e-6), x1], nlanes=5)
+    return blob, prog, (41, [N((96, 1024), "bf16", 1.5, 0.3), N((1024,), "bf16", 0.2, 1.0),
+                             N((100, 256), "bf16"), N((100, 256), "bf16"), N((256,), "bf16", 0.2, 1.0)])
+
+
 @case("reduce_full_int", exact=True)
 def _():
     a = Asm()

@@ -175,6 +175,25 @@ def test_full_sum_carried_by_the_row_op(rt, monkeypatch, name, folds):
     np.testing.assert_allclose(totals[None][0], totals["1"][0], rtol=1e-5)
 
 
+def test_decomposed_rms_norm_runs_as_one_row_op(rt, monkeypatch):
+    """The block's RMS norm arrives as seven tile ops in five phases (convert, square, RED_SEG, a region on the row
+    sums, two multiplies through broadcast views, convert); the loader runs it as one row op on the last
+    convert's entries and drops the phases that empty. Same values as the separate ops, rows of 1024 and 256."""
+    vm = package()
+    g = Golden("rmsnorm_rows_bf16")
+    barriers = {}
+    for off, want in ((None, 2), ("1", 0)):
+        with monkeypatch.context() as m:
+            if off:
+                m.setenv("B2VM_NO_RMS_FUSION", off)
+            lp = vm.LoadedProgram.Load(rt, vm.VmProgram.Parse(g.blob))
+            assert lp.stat("rms_rows") == want
+            check_outputs(g, [np.ascontiguousarray(o).view(np.uint8).reshape(-1) for o in lp.Execute(g.args)], "cuda-rms")
+            barriers[off] = (lp.Status()["barriers"], lp.stat("empty_phases_dropped"))
+    assert barriers["1"][1] == 0 and barriers[None][1] > 0
+    assert barriers[None][0] + barriers[None][1] == barriers["1"][0]
+
+
 def test_point_to_point_entry_fields_are_refused(rt):
     """Tile entries whose reserved wait / signal words are set (scheduler.py:201-209 keeps them
     for point-to-point dependencies and emits "no flag") are refused at load, not ignored."""
