@@ -1432,7 +1432,7 @@ static bool BuildDeviceTablesFor(const VmProgram &p, uint64_t arena_base, Device
       break;
     }
   }
-  // The decomposed RMS norm over bf16 rows - convert to f32, square, RED_SEG row sums, a MAP_REGION on the row sums,
+  // The decomposed RMS norm over bf16 rows - convert to f32, square, RED_SEG row sums, a MAP_REGION {affine, rsqrt} on them,
   // multiply by the broadcast row scalar, multiply by the broadcast f32 gain, convert to bf16 - becomes one row op
   // on the last convert's entries (rms_rows_tiles); the six other tasks' entries leave the stream. Every
   // intermediate must be read by the idiom alone. Straight-line programs only.
@@ -1475,21 +1475,20 @@ static bool BuildDeviceTablesFor(const VmProgram &p, uint64_t arena_base, Device
       if (!is_ew(cx, kConvert, kF32, kBF16) || cx.p2 != 0u || cx.p1 != cv.p1) continue;
       if ((gr.tile_op & 0xFFu) != kTopMapRegion || ((gr.tile_op >> 8) & 0xFFu) != kF32 || ((gr.tile_op >> 16) & 0xFFu) != kF32) continue;
       const int64_t rows = gr.p1, d = rows ? static_cast<int64_t>(cv.p1) / rows : 0;
-      if (rows <= 0 || rows * d != static_cast<int64_t>(cv.p1) || d % 256 != 0 || d > 2048 || kEwTs % d != 0) continue;
+      if (rows <= 0 || rows * d != static_cast<int64_t>(cv.p1) || !(d == 256 || d == 512 || d == 1024 || d == 2048)) continue;
       if (!is_broadcast(m1.p3, rows, d, 1, 0) || !is_broadcast(m2.p3, rows, d, 0, 1)) continue;
       const int ri = sole_writer(gr.a);
       if (ri < 0) continue;
       const VmTask &rd = p.tasks[ri];
       if ((rd.tile_op & 0xFFu) != kTopRedSeg || ((rd.tile_op >> 8) & 0xFFu) != kF32 || rd.p0 != rows || rd.p1 != d || rd.p2 != kSum) continue;
-      // every input of the region is the row sum
+      // the region (region.py:19-23: n_in, out_slot, n_micro, in_slot[n_in], n_micro x {kind, dst, a, b, s, t}) is
+      // exactly r = rsqrt(affine(row sum)): one input, two micro-ops
       const size_t gx = gr.p0;
-      if (gx + 3 > p.aux.size() || p.aux[gx] < 1 || p.aux[gx] > 8 || p.aux[gx + 2] < 0 ||
-          gx + 3 + static_cast<size_t>(p.aux[gx]) + 6u * static_cast<size_t>(p.aux[gx + 2]) > p.aux.size())
+      if (gx + 4 + 12 > p.aux.size() || p.aux[gx] != 1 || p.aux[gx + 2] != 2 || gr.a != rd.dst) continue;
+      const int32_t *mo = &p.aux[gx + 4];
+      if (mo[0] != static_cast<int32_t>(kAffine) || mo[2] != p.aux[gx + 3] || mo[6] != static_cast<int32_t>(kRsqrt) || mo[8] != mo[1] ||
+          p.aux[gx + 1] != mo[7])
         continue;
-      const uint32_t gin[8] = {gr.a, gr.b, gr.p2, gr.p3, gr.p4, gr.p5, gr.p6, gr.p7};
-      bool same = true;
-      for (int k = 0; k < p.aux[gx]; ++k) same = same && gin[k] == rd.dst;
-      if (!same) continue;
       const int si = sole_writer(rd.a);
       if (si < 0) continue;
       const VmTask &sq = p.tasks[si];
@@ -1534,10 +1533,26 @@ static bool BuildDeviceTablesFor(const VmProgram &p, uint64_t arena_base, Device
       std::memset(du.p, 0, sizeof(du.p));
       du.p[0] = static_cast<uint32_t>(rows);
       du.p[1] = static_cast<uint32_t>(d);
-      du.p[2] = gr.p0;
+      du.p[2] = static_cast<uint32_t>(mo[4]);      // the affine's s and t
+      du.p[4] = static_cast<uint32_t>(mo[5]);
       du.adt = kBF16;
       for (DEntry &e : out->entries)
         if (e.task == M2 || e.task == M1 || e.task == C || e.task == G || e.task == R || e.task == S) e.task = kEntNop;
+      // the gain's own convert from bf16 goes too when the idiom alone reads its result and the bf16 source is a
+      // program argument nothing writes
+      const int gw = sole_writer(gid);
+      if (gw >= 0) {
+        const VmTask &gc = p.tasks[gw];
+        bool written = false;
+        for (const VmTask &o : p.tasks) written = written || o.dst == gc.a;
+        if (is_ew(gc, kConvert, kF32, kBF16) && gc.p2 == 0u && gc.p1 == static_cast<uint32_t>(d) && scratch_only(gid, {M2}) &&
+            in_ids.count(gc.a) && !written && c.Aligned16(gc.a)) {
+          du.ptr[2] = c.Ref(gc.a);
+          du.p[3] = 1u;
+          for (DEntry &e : out->entries)
+            if (e.task == static_cast<uint32_t>(gw)) e.task = kEntNop;
+        }
+      }
       // a task that forwarded into one of these in a chain stores its result again
       for (size_t k = 0; k < p.tasks.size(); ++k)
         if (succ[k] == ci || succ[k] == m1i || succ[k] == m2i || succ[k] == si) out->tasks[k].flags &= ~kDeadStore;

@@ -395,25 +395,22 @@ static __device__ __noinline__ void rows_tiles(const Lane &L, const DTask &t, ui
 }
 
 // kTopRmsRows: what the loader makes of the decomposed RMS norm over bf16 rows
-//   xf = f32(x); ss = rowsum(xf * xf); r = region(ss); y = bf16((xf * r) * g)
-// (convert, multiply, RED_SEG, a MAP_REGION on the row scalars, two multiplies through broadcast views, convert:
-// seven tile ops, five phases, four f32 intermediates of the tensor's size). One pass instead: a warp owns a row,
-// every lane keeps its 16-byte words of the row in registers, the row sum is a warp reduction, the region's
-// micro-program runs on the one scalar (every lane, redundantly), and the scaled row leaves as bf16. Same roundings
-// per element as the separate ops (f32 multiply, f32 multiply, round to bf16); the row sum's order differs.
-// p[0] rows, p[1] row length (a multiple of 256, at most 2048), p[2] the region's descriptor in the aux pool;
-// ptr[0] result, ptr[1] x, ptr[2] g (f32, one per column). Entries name elementwise tiles of the result.
-static __device__ __noinline__ void rms_rows_tiles(const Lane &L, const DTask &t, uint32_t tile_lo, uint32_t tile_hi) {
+//   xf = f32(x); ss = rowsum(xf * xf); r = 1 / sqrt(ss * s + t); y = bf16((xf * r) * g)
+// (convert, multiply, RED_SEG, a MAP_REGION {affine, rsqrt} on the row sums, two multiplies through broadcast views,
+// convert: seven tile ops, five phases, four f32 intermediates of the tensor's size). One pass instead: a warp owns a
+// row, every lane keeps its W 16-byte words of the row in registers, the row sum is a warp reduction and the scaled
+// row leaves as bf16. Same roundings per element as the separate ops (f32 multiply, f32 multiply, round to bf16;
+// affine with two roundings, correctly rounded square root and division); the row sum's order differs.
+// p[0] rows, p[1] row length (256 W, W = 1, 2, 4 or 8), p[2] / p[4] the affine's s / t (f32 bits), p[3] != 0: g is
+// bf16; ptr[0] result, ptr[1] x, ptr[2] g (f32 or bf16, one per column). Entries name elementwise tiles of the result.
+template <uint32_t W>
+__device__ __forceinline__ void rms_rows_w(const Lane &L, const DTask &t, uint32_t r_lo, uint32_t r_hi) {
   const KParams &P = *L.P;
-  const uint32_t rows = t.p[0], d = t.p[1];
-  const uint64_t e_lo = static_cast<uint64_t>(tile_lo) * kEwTs, e_hi = min(static_cast<uint64_t>(tile_hi) * kEwTs, static_cast<uint64_t>(rows) * d);
-  if (e_lo >= e_hi) return;
-  const uint32_t r_lo = static_cast<uint32_t>(e_lo / d), r_hi = static_cast<uint32_t>(e_hi / d);
   const uint4 *x = reinterpret_cast<const uint4 *>(resolve(P, t.ptr[1]));
   uint4 *y = reinterpret_cast<uint4 *>(resolve(P, t.ptr[0]));
-  const float4 *g = reinterpret_cast<const float4 *>(resolve(P, t.ptr[2]));
-  const int32_t *e = P.aux + t.p[2];
-  const uint32_t W = d >> 8;                       // 16-byte words of a row per lane
+  const uint8_t *g = resolve(P, t.ptr[2]);
+  const float as = __uint_as_float(t.p[2]), at = __uint_as_float(t.p[4]);
+  const bool g16 = t.p[3] != 0u;
   const uint32_t w = L.tid / kWarp, lane = L.tid % kWarp, nw = L.nthr / kWarp;
   auto unpack8 = [](const uint4 q, float (&f)[8]) {
     f[0] = __uint_as_float(q.x << 16); f[1] = __uint_as_float(q.x & 0xffff0000u);
@@ -422,44 +419,50 @@ static __device__ __noinline__ void rms_rows_tiles(const Lane &L, const DTask &t
     f[6] = __uint_as_float(q.w << 16); f[7] = __uint_as_float(q.w & 0xffff0000u);
   };
   for (uint32_t row = r_lo + w; row < r_hi; row += nw) {
-    const uint4 *xr = x + static_cast<size_t>(row) * (d >> 3);
-    uint4 v[8];
+    const uint4 *xr = x + static_cast<size_t>(row) * (W * kWarp);
+    uint4 v[W];
 #pragma unroll
-    for (uint32_t k = 0; k < 8; ++k)
-      if (k < W) v[k] = ldg_v4(xr + k * kWarp + lane);
+    for (uint32_t k = 0; k < W; ++k) v[k] = ldg_v4(xr + k * kWarp + lane);
     float ss = 0.0f;
 #pragma unroll
-    for (uint32_t k = 0; k < 8; ++k)
-      if (k < W) {
-        float f[8];
-        unpack8(v[k], f);
+    for (uint32_t k = 0; k < W; ++k) {
+      float f[8];
+      unpack8(v[k], f);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) ss = __fadd_rn(ss, __fmul_rn(f[i], f[i]));
-      }
+      for (int i = 0; i < 8; ++i) ss = __fadd_rn(ss, __fmul_rn(f[i], f[i]));
+    }
     ss = warp_reduce(ss, [](float a, float c) { return a + c; });
-    // the region's micro-program on the row scalar (python/pjrt_ocl/ops/region.py:19-23: n_in, out_slot, n_micro,
-    // in_slot[n_in], n_micro x {kind, dst, a, b, s, t}); every input is the row sum
-    float slot[8];
+    const float r = __fdiv_rn(1.0f, __fsqrt_rn(affine2(ss, as, at)));
+    uint4 *yr = y + static_cast<size_t>(row) * (W * kWarp);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) slot[i] = 0.0f;
-    const int32_t n_in = e[0], n_micro = e[2];
-    for (int32_t k = 0; k < n_in; ++k) slot[e[3 + k] & 7] = ss;
-    const int32_t *m = e + 3 + n_in;
-    for (int32_t i = 0; i < n_micro; ++i, m += 6)
-      slot[m[1] & 7] = micro_alu(static_cast<uint32_t>(m[0]), slot[m[2] & 7], slot[m[3] & 7], __int_as_float(m[4]), __int_as_float(m[5]));
-    const float r = slot[e[1] & 7];
-    uint4 *yr = y + static_cast<size_t>(row) * (d >> 3);
-#pragma unroll
-    for (uint32_t k = 0; k < 8; ++k)
-      if (k < W) {
-        float f[8];
-        unpack8(v[k], f);
-        const float4 ga = g[(k * kWarp + lane) * 2u], gb = g[(k * kWarp + lane) * 2u + 1u];
-        const float gg[8] = {ga.x, ga.y, ga.z, ga.w, gb.x, gb.y, gb.z, gb.w};
-#pragma unroll
-        for (int i = 0; i < 8; ++i) f[i] = __fmul_rn(__fmul_rn(f[i], r), gg[i]);
-        yr[k * kWarp + lane] = make_uint4(cvt_bf16x2(f[1], f[0]), cvt_bf16x2(f[3], f[2]), cvt_bf16x2(f[5], f[4]), cvt_bf16x2(f[7], f[6]));
+    for (uint32_t k = 0; k < W; ++k) {
+      float f[8], gg[8];
+      unpack8(v[k], f);
+      if (g16) {      // the gain still in bf16 (its convert to f32 was folded in too)
+        unpack8(reinterpret_cast<const uint4 *>(g)[k * kWarp + lane], gg);
+      } else {
+        const float4 *g4 = reinterpret_cast<const float4 *>(g);
+        const float4 ga = g4[(k * kWarp + lane) * 2u], gb = g4[(k * kWarp + lane) * 2u + 1u];
+        gg[0] = ga.x; gg[1] = ga.y; gg[2] = ga.z; gg[3] = ga.w; gg[4] = gb.x; gg[5] = gb.y; gg[6] = gb.z; gg[7] = gb.w;
       }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) f[i] = __fmul_rn(__fmul_rn(f[i], r), gg[i]);
+      yr[k * kWarp + lane] = make_uint4(cvt_bf16x2(f[1], f[0]), cvt_bf16x2(f[3], f[2]), cvt_bf16x2(f[5], f[4]), cvt_bf16x2(f[7], f[6]));
+    }
+  }
+}
+
+static __device__ __noinline__ void rms_rows_tiles(const Lane &L, const DTask &t, uint32_t tile_lo, uint32_t tile_hi) {
+  const uint32_t rows = t.p[0], d = t.p[1];
+  const uint64_t e_lo = static_cast<uint64_t>(tile_lo) * kEwTs, e_hi = min(static_cast<uint64_t>(tile_hi) * kEwTs, static_cast<uint64_t>(rows) * d);
+  if (e_lo >= e_hi) return;
+  const uint32_t r_lo = static_cast<uint32_t>(e_lo / d), r_hi = static_cast<uint32_t>(e_hi / d);
+  switch (d >> 8) {
+    case 1: rms_rows_w<1>(L, t, r_lo, r_hi); break;
+    case 2: rms_rows_w<2>(L, t, r_lo, r_hi); break;
+    case 4: rms_rows_w<4>(L, t, r_lo, r_hi); break;
+    case 8: rms_rows_w<8>(L, t, r_lo, r_hi); break;
+    default: break;      // the loader only makes the op for these row lengths
   }
 }
 
