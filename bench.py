@@ -87,7 +87,7 @@ WORKLOADS = {
     "c5_block": _wl("c5_block_bf16", "transformer-block tokens/s per B200", "tokens/s", _C5_TOK, 1.0, "tensor", "bf16",
                     "config 5: pre-norm decoder block forward, batch 8 x seq 2048, d_model 1024, 16 x 64 heads, "
                     "causal flash attention, GELU FFN 4096, bf16",
-                    roof_alg=_C5_MM_FLOPS + _C5_ATT_FLOPS, plan="c5_block", traffic=2008.8e6,
+                    roof_alg=_C5_MM_FLOPS + _C5_ATT_FLOPS, plan="c5_block", traffic=1139.5e6,
                     sample="c5_block_bf16_cpu_sample", sample_frac=512 / _C5_TOK,
                     sample_what="one sequence of 512 tokens through the same block (8 x 2048 in the workload)"),
     "c4_nbody": _wl("c4_nbody", "n-body pair interactions/s", "G interactions/s", 4096 * 4096 * 4 * 200, 1e9, "hbm",
@@ -111,7 +111,7 @@ WORKLOADS = {
                               "config 5 decode step, batch 32, KV cache 2048 + the new position: K/V written in place "
                               "(in/out buffers), K read through its view; bytes = weights + KV cache read once",
                               roof_alg=2 * (4 * 1024 * 1024 + 2 * 1024 * 4096) + 2 * 32 * 16 * 2049 * 64 * 2,
-                              plan="c5_decode_in_place", traffic=312.0e6),
+                              plan="c5_decode_in_place", traffic=310.5e6),
     "c5_decode": _wl("c5_decode_bf16", "transformer-block tokens/s per B200", "tokens/s", 32, 1.0, "hbm", "bf16",
                      "config 5 decode step: batch 32, KV cache 2048; bytes = weights + KV cache read once",
                      roof_alg=2 * (4 * 1024 * 1024 + 2 * 1024 * 4096) + 2 * 32 * 16 * 2048 * 64 * 2, plan="c5_decode"),
