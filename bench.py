@@ -335,6 +335,15 @@ def main():
             if lp2 is not None:
                 lp2.ExecuteDeviceAsync(ins2, outs2, stream.cuda_stream)
 
+        def every_rank(cond: bool) -> bool:
+            """The same answer on all ranks (true if any rank says so): loops whose steps hold collectives must run
+            the same number of times everywhere, so none of them may end on a rank's own clock."""
+            if world == 1:
+                return cond
+            flag = torch.tensor([1 if cond else 0], dtype=torch.int32, device="cuda")
+            dist.all_reduce(flag, op=dist.ReduceOp.MAX)
+            return bool(flag.item())
+
         sampler = ClockSampler(local_rank)
         sampler.start()
         for _ in range(warmup):
@@ -344,7 +353,7 @@ def main():
             # nvidia-smi needs most of a second before its first sample: keep the same load running until it
             # reports, so that the clock record covers the timed region that follows
             t_soak = time.perf_counter()
-            while not sampler.lines and time.perf_counter() - t_soak < 2.0:
+            while every_rank(not sampler.lines and time.perf_counter() - t_soak < 2.0):
                 for _ in range(8):
                     step()
                 torch.cuda.synchronize()
@@ -387,7 +396,7 @@ def main():
             # the timed region of a short run fits between two samples: the same steps continue (untimed)
             # until the sampler has seen at least 0.3 s of this load
             t_soak = time.perf_counter()
-            while time.perf_counter() - t_soak < max(0.0, 0.3 - ms * 1e-3):
+            while every_rank(time.perf_counter() - t_soak < max(0.0, 0.3 - ms * 1e-3)):
                 for _ in range(8):
                     step()
                 torch.cuda.synchronize()
