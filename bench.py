@@ -336,13 +336,8 @@ def main():
                 lp2.ExecuteDeviceAsync(ins2, outs2, stream.cuda_stream)
 
         def every_rank(cond: bool) -> bool:
-            """The same answer on all ranks (true if any rank says so): loops whose steps hold collectives must run
-            the same number of times everywhere, so none of them may end on a rank's own clock."""
-            if world == 1:
-                return cond
-            flag = torch.tensor([1 if cond else 0], dtype=torch.int32, device="cuda")
-            dist.all_reduce(flag, op=dist.ReduceOp.MAX)
-            return bool(flag.item())
+            # the same answer on all ranks: the loops below hold steps with collectives in them
+            return dp.ranks_agree(cond, "cuda")
 
         sampler = ClockSampler(local_rank)
         sampler.start()

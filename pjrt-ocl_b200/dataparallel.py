@@ -19,6 +19,19 @@ from typing import Callable, Optional, Sequence
 import numpy as np
 
 
+def ranks_agree(cond: bool, device=None) -> bool:
+    """`cond` or-ed over all ranks of the default process group (just `cond` without one). A loop whose body holds
+    collectives must run the same number of times on every rank, so it may not end on a rank's own clock or
+    sampler: every rank asks this instead, once per iteration."""
+    import torch
+    import torch.distributed as dist
+    if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size() == 1:
+        return bool(cond)
+    flag = torch.tensor([1 if cond else 0], dtype=torch.int32, device=device)
+    dist.all_reduce(flag, op=dist.ReduceOp.MAX)
+    return bool(flag.item())
+
+
 def shard_rows(arr: np.ndarray, rank: int, world: int) -> np.ndarray:
     """Rank `rank`'s rows of a batch-major array (the batch must divide evenly)."""
     n = arr.shape[0]

@@ -83,6 +83,49 @@ def test_c3_data_parallel_equals_single_program():
         assert err < 1e-4, f"rank {rank}: data-parallel step differs from the single-program step by {err}"
 
 
+def _agree_worker(rank, world, port, q):
+    import importlib
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        dp = importlib.import_module("pjrt-ocl_b200.dataparallel")
+        # each rank would stop on its own after a different number of trips; the body holds a collective
+        mine, trips, total = (3, 5)[rank], 0, 0.0
+        while dp.ranks_agree(trips < mine):
+            t = torch.ones(1)
+            dist.all_reduce(t)
+            total += float(t.item())
+            trips += 1
+        # the next collective still pairs up: nothing is left over from the loop
+        t = torch.tensor([float(rank + 1)])
+        dist.all_reduce(t)
+        q.put((rank, trips, total, float(t.item())))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_loops_with_collectives_end_on_all_ranks_together():
+    """The bench keeps its steps running while a per-rank sampler warms up; steps of replica and gradient plans
+    hold all-reduces, so the loop condition is agreed between the ranks (dataparallel.ranks_agree)."""
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_agree_worker, args=(r, world, port, q)) for r in range(world)]
+    for p_ in procs:
+        p_.start()
+    got = sorted(q.get(timeout=120) for _ in range(world))
+    for p_ in procs:
+        p_.join(60)
+        assert p_.exitcode == 0
+    assert [g[1] for g in got] == [5, 5]              # both ran until the slower-to-stop rank was done
+    assert [g[2] for g in got] == [10.0, 10.0]        # every all-reduce in the body met its partner
+    assert [g[3] for g in got] == [3.0, 3.0]
+    dp = __import__("importlib").import_module("pjrt-ocl_b200.dataparallel")
+    assert dp.ranks_agree(True) is True and dp.ranks_agree(False) is False      # no process group: the rank's own answer
+
+
 def test_shard_rows_and_plan_names():
     import importlib
     dp = importlib.import_module("pjrt-ocl_b200.dataparallel")
